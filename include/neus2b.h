@@ -1,0 +1,200 @@
+/*
+ * neus2b -- C ABI of the B200-native NeuS2 training-step kernels (libneus2b.so).
+ *
+ * Plain pointers and sizes only.  Every pointer named d_* is DEVICE memory owned by the caller; nothing in the
+ * kernel-level section allocates.  fp16 tensors are passed as `uint16_t*` bit patterns (device `__half`).
+ * All matrices are "AoS" (tiny-cuda-nn's column-major GPUMatrix): one sample's values are contiguous, [n][width].
+ * Return value: 0 on success, a positive cudaError_t, or a negative NEUS2B_E_* code.  Nothing throws across this ABI
+ * and nothing touches the default stream: every call enqueues on the `stream` it is given.
+ *
+ * Each entry point names the reference interface it stands in for (file:line inside 19reborn/NeuS2).  The bodies of
+ * the tiny-cuda-nn methods are not part of that tree (empty submodule dependencies/neus2_tcnn); the citation is the
+ * call site that fixes their contract.
+ */
+#ifndef NEUS2B_H
+#define NEUS2B_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* neus2b_stream_t;
+
+#define NEUS2B_OK 0
+#define NEUS2B_E_INVALID (-1)     /* bad argument (null pointer, unsupported width, misaligned pointer) */
+#define NEUS2B_E_UNSUPPORTED (-2) /* configuration outside what the kernels are built for */
+#define NEUS2B_E_NO_DEVICE (-3)
+#define NEUS2B_E_OVERFLOW (-4)    /* a device-side capacity was exceeded (flag read back by the caller) */
+#define NEUS2B_E_TOO_LARGE (-5)   /* request beyond a fixed compiled-in capacity */
+
+#define NEUS2B_MAX_LEVELS 16
+#define NEUS2B_GRIDSIZE 128u /* NERF_GRIDSIZE  include/neural-graphics-primitives/nerf.h:24 */
+#define NEUS2B_CASCADES 8u   /* NERF_CASCADES  src/testbed_nerf.cu:49 */
+#define NEUS2B_STEPS 1024u   /* NERF_STEPS     src/testbed_nerf.cu:48 */
+
+/* tcnn::EGradientMode (include/neural-graphics-primitives/nerf_network.h:229,402,534) */
+#define NEUS2B_GRAD_IGNORE 0
+#define NEUS2B_GRAD_OVERWRITE 1
+#define NEUS2B_GRAD_ACCUMULATE 2
+
+/* Hash-grid geometry: the "encoding" block of configs/nerf/base.json:29-39 (n_features_per_level is fixed at 2). */
+typedef struct {
+	uint32_t n_levels;          /* <= 16 */
+	uint32_t log2_hashmap_size;
+	uint32_t base_resolution;
+	float per_level_scale;
+	uint32_t n_active_levels;   /* progressive mask (Encoding::set_training_step, src/testbed.cu:2643-2647) */
+} neus2b_grid_desc;
+
+/* Parameter block order, fp16 scalars (NerfNetwork::set_params, nerf_network.h:728-772):
+ * SDF MLP 64x48,16x64 | colour MLP 64x48,64x64,16x64 | grid | variance (4). Weight matrices are row-major [out][in]. */
+#define NEUS2B_SDF_W1 0
+#define NEUS2B_SDF_W2 3072
+#define NEUS2B_RGB_W1 4096
+#define NEUS2B_RGB_W2 7168
+#define NEUS2B_RGB_W3 11264
+#define NEUS2B_MLP_N 12288
+#define NEUS2B_GRID_OFF 12288
+
+const char* neus2b_version(void);
+const char* neus2b_error_string(int code);
+
+/* GridEncoding::level_n_params / level_params_offset (src/testbed.cu:1861-1877).  offsets[17] in grid ENTRIES (2 fp16). */
+int neus2b_grid_level_table(const neus2b_grid_desc* desc, uint32_t* offsets, uint32_t* resolutions, float* scales,
+                            uint32_t* hashed);
+int neus2b_grid_n_params(const neus2b_grid_desc* desc, uint64_t* n_fp16);  /* Encoding::n_params() */
+int neus2b_model_n_params(const neus2b_grid_desc* desc, uint64_t* n_fp16); /* NerfNetwork::n_params(), nerf_network.h:902 */
+
+/* ---------------------------------------------------------------- component kernels (tcnn Encoding / Network) */
+
+/* GridEncoding::forward with prepare_input_gradients (nerf_network.h:184-190; inference :671-676).
+ * d_x [n][x_stride] fp32 (first 3 used), d_enc [n][2L] fp16, d_dy_dx [n][2L][3] fp32 or NULL. */
+int neus2b_grid_forward(const neus2b_grid_desc* desc, uint32_t n, const float* d_x, uint32_t x_stride, const uint16_t* d_grid,
+                        uint16_t* d_enc, float* d_dy_dx, neus2b_stream_t stream);
+/* GridEncoding::backward(..., &dL_dinput, EGradientMode::Ignore) (nerf_network.h:234). d_dL_dx [n][3] fp32. */
+int neus2b_grid_backward_input(const neus2b_grid_desc* desc, uint32_t n, const float* d_x, uint32_t x_stride,
+                               const uint16_t* d_grid, const uint16_t* d_dL_denc, float* d_dL_dx, neus2b_stream_t stream);
+/* GridEncoding::backward(..., param_gradients_mode) (nerf_network.h:419-429). d_grad [grid n_params] fp16. */
+int neus2b_grid_backward_params(const neus2b_grid_desc* desc, uint32_t n, const float* d_x, uint32_t x_stride,
+                                const uint16_t* d_dL_denc, uint16_t* d_grad, int grad_mode, neus2b_stream_t stream);
+/* GridEncoding::backward_backward_input (nerf_network.h:534-544): d_v = dL/d(dy/dx) [n][3] fp32, d_g_e = dL_doutput of the
+ * first-order pass [n][2L] fp16; writes d_dy_enc [n][2L] fp16 (dL/d(dL_doutput)) and adds the parameter gradient. */
+int neus2b_grid_backward_backward_input(const neus2b_grid_desc* desc, uint32_t n, const float* d_x, uint32_t x_stride,
+                                        const uint16_t* d_grid, const float* d_v, const uint16_t* d_g_e, uint16_t* d_dy_enc,
+                                        uint16_t* d_grad, int grad_mode, neus2b_stream_t stream);
+
+/* FullyFusedMLP::forward, 64 neurons, ReLU, no output activation, 16 outputs (nerf_network.h:212 SDF net: in_width 48,
+ * n_hidden 1; :271 colour net: in_width 48, n_hidden 2).  d_hidden [n][n_hidden][64] fp16 may be NULL. */
+int neus2b_mlp_forward(uint32_t n, uint32_t in_width, uint32_t n_hidden, const uint16_t* d_weights, const uint16_t* d_in,
+                       uint16_t* d_out, uint16_t* d_hidden, neus2b_stream_t stream);
+/* FullyFusedMLP::backward (nerf_network.h:229,340,402,509). d_dL_din [n][in_width] fp16 or NULL; d_wgrad fp32
+ * [n_params of the net] or NULL (EGradientMode::Ignore). */
+int neus2b_mlp_backward(uint32_t n, uint32_t in_width, uint32_t n_hidden, const uint16_t* d_weights, const uint16_t* d_in,
+                        const uint16_t* d_hidden, const uint16_t* d_dL_dout, uint16_t* d_dL_din, float* d_wgrad,
+                        int grad_mode, neus2b_stream_t stream);
+/* FullyFusedMLP::backward_backward_input, one hidden layer (nerf_network.h:560-571): d_u = dL/d(dL_dinput) [n][in_width],
+ * d_dy = dL_doutput of the differentiated pass [n][16]; adds into d_wgrad. */
+int neus2b_mlp_backward_backward_input(uint32_t n, uint32_t in_width, const uint16_t* d_weights, const uint16_t* d_hidden,
+                                       const uint16_t* d_u, const uint16_t* d_dy, float* d_wgrad, int grad_mode,
+                                       neus2b_stream_t stream);
+/* SphericalHarmonics degree 4 of 2*dir-1 (configs/nerf/base.json:48-62; nerf_network.h:251). */
+int neus2b_sh4_forward(uint32_t n, const float* d_dir01, uint32_t stride, uint16_t* d_out, neus2b_stream_t stream);
+
+/* ---------------------------------------------------------------- fused NeuS graph (NerfNetwork) */
+
+/* NerfNetwork::inference_mixed_precision == forward_impl (nerf_network.h:87-90,132-315), static scene.
+ * d_coords [n][7] fp32 (xyz, dt, dir in [0,1]); d_out [n][16] fp16 rows: 0-2 raw rgb, 3 sdf+bias, 4-6 normal,
+ * 7 variance, 8-10 dir.  If d_n is non-NULL the sample count is read from it on the device (clamped to n). */
+int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
+                        const uint32_t* d_n, const float* d_coords, uint16_t* d_out, neus2b_stream_t stream);
+/* NerfNetwork::forward + backward of one training batch in a single pass (nerf_network.h:132-315 + :317-641,
+ * called at src/testbed_nerf.cu:3931-3932).  Gradients are accumulated: d_grad_mlp fp32 [12288], d_grad_grid fp16
+ * [grid n_params], d_grad_variance fp32 [1]; zero them first for EGradientMode::Overwrite. */
+int neus2b_neus_train(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
+                      const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp, uint16_t* d_grad_grid,
+                      float* d_grad_variance, neus2b_stream_t stream);
+/* NerfNetwork::sdf (nerf_network.h:643-709): d_sdf [n] fp16 = y0 + bias. */
+int neus2b_neus_sdf(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
+                    uint32_t x_stride, uint16_t* d_sdf, neus2b_stream_t stream);
+
+/* ---------------------------------------------------------------- ray march, loss, occupancy (src/testbed_nerf.cu) */
+
+typedef struct {
+	uint64_t state, inc;
+} neus2b_pcg32; /* tcnn::default_rng_t */
+void neus2b_pcg32_seed(neus2b_pcg32* rng, uint64_t seed);
+void neus2b_pcg32_advance(neus2b_pcg32* rng, uint64_t delta);
+
+typedef struct {
+	uint32_t n_images, width, height;
+	const uint32_t* d_pixels; /* [n_images][height][width] RGBA8 (EImageDataType::Byte) */
+	const float* d_xforms;    /* [n_images][12] 3x4 camera-to-world, column major (TrainingXForm::start) */
+	const float* d_focal;     /* [n_images][2]  (TrainingImageMetadata::focal_length) */
+	const float* d_principal; /* [n_images][2]  (TrainingImageMetadata::principal_point) */
+} neus2b_dataset;
+
+typedef struct {
+	float aabb_min[3], aabb_max[3];
+	float cone_angle_constant;
+	uint32_t snap_to_pixel_centers;
+	uint32_t random_bg_color;
+	float background_color[3];
+	float loss_scale; /* LOSS_SCALE, include/neural-graphics-primitives/testbed.h:237 */
+	float mask_loss_weight, ek_loss_weight, cos_anneal_ratio;
+} neus2b_train_cfg;
+
+/* Scratch for one batch of rays; every array is caller-allocated device memory. */
+typedef struct {
+	uint32_t max_rays, max_samples;
+	uint32_t* d_ray_indices; /* [max_rays] */
+	float* d_rays;           /* [max_rays][6] origin, unnormalised direction */
+	uint32_t* d_numsteps;    /* [max_rays][2] {n, base} */
+	float* d_coords;         /* [max_samples][7] */
+	uint32_t* d_counters;    /* [8]: 0 kept rays, 1 samples, 2 compacted samples (unclipped), 3 overflow flag */
+	uint64_t* d_scan_tmp;    /* [max_rays + 1024] */
+	float* d_ray_tmp;        /* [max_rays][8] */
+} neus2b_ray_workspace;
+
+/* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is
+ * canonical (by ray index, prefix sum) instead of atomicAdd order.  If d_n_rays is non-NULL the ray count is read on
+ * the device (clamped to n_rays). */
+int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                            uint32_t n_rays_total, neus2b_pcg32 rng, const uint8_t* d_bitfield, neus2b_ray_workspace* ws,
+                            neus2b_stream_t stream);
+/* compute_loss_kernel_train_nerf_with_global_movement (src/testbed_nerf.cu:1465-1996) followed by fill_rollover /
+ * fill_rollover_and_rescale (:3908-3916).  d_mlp_out [samples][16] fp16 from neus2b_neus_forward on ws->d_coords.
+ * Writes d_coords_out [max_compacted][7], d_dloss_dout [max_compacted][16] fp16, per-ray d_loss / d_ek_loss [max_rays]. */
+int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                        uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, const uint16_t* d_mlp_out,
+                        neus2b_ray_workspace* ws, float* d_coords_out, uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss,
+                        int rollover, neus2b_stream_t stream);
+
+/* Occupancy grid (src/testbed_nerf.cu:630-785, 3287-3391). One call = update_density_grid_nerf's inner step for
+ * n_uniform + n_nonuniform samples followed by update_density_grid_mean_and_bitfield.
+ * d_grid float[128^3 * n_cascades], d_grid_tmp same size, d_bitfield uint8[128^3], d_mean float[1],
+ * scratch: d_pos float[n][3], d_idx uint32[n], d_sdf fp16[n], d_partial double[1024]. */
+int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n_cascades,
+                            uint32_t n_uniform, uint32_t n_nonuniform, neus2b_pcg32 rng_uniform, neus2b_pcg32 rng_nonuniform,
+                            uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp, uint8_t* d_bitfield,
+                            float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
+                            neus2b_stream_t stream);
+
+/* ---------------------------------------------------------------- optimizer (Trainer::optimizer_step, src/testbed_nerf.cu:3498) */
+typedef struct {
+	float learning_rate, beta1, beta2, epsilon, l2_reg, ema_decay, loss_scale;
+	uint32_t step;     /* 1-based */
+	uint32_t n_matrix; /* leading MLP-weight entries */
+} neus2b_adam_cfg;
+/* Ema o ExponentialDecay o Adam (configs/nerf/dtu.json:5-27) over the flat parameter block.  Gradients: d_grad_mlp fp32
+ * for [0, n_matrix), d_grad_grid fp16 for [n_matrix, n - 4), d_grad_variance fp32 for the last 4; all are zeroed after
+ * use.  Writes fp32 master, Adam moments, fp16 params, and (if d_params_ema) the EMA copies. */
+int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid, float* d_grad_variance,
+                     float* d_master, float* d_m, float* d_v, uint16_t* d_params, uint16_t* d_params_ema, float* d_ema_master,
+                     neus2b_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

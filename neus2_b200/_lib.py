@@ -1,0 +1,146 @@
+"""ctypes binding of libneus2b.so: one Python function per C entry point of include/neus2b.h.
+
+There is no fallback: if the shared library is missing or a call returns an error, an exception is raised."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "_build", "libneus2b.so")
+
+MLP_N = 12288
+GRID_OFF = 12288
+GRAD_IGNORE, GRAD_OVERWRITE, GRAD_ACCUMULATE = 0, 1, 2
+
+
+class GridDesc(C.Structure):
+    _fields_ = [("n_levels", C.c_uint32), ("log2_hashmap_size", C.c_uint32), ("base_resolution", C.c_uint32),
+                ("per_level_scale", C.c_float), ("n_active_levels", C.c_uint32)]
+
+
+class Pcg32(C.Structure):
+    _fields_ = [("state", C.c_uint64), ("inc", C.c_uint64)]
+
+
+class Dataset(C.Structure):
+    _fields_ = [("n_images", C.c_uint32), ("width", C.c_uint32), ("height", C.c_uint32), ("d_pixels", C.c_void_p),
+                ("d_xforms", C.c_void_p), ("d_focal", C.c_void_p), ("d_principal", C.c_void_p)]
+
+
+class TrainCfg(C.Structure):
+    _fields_ = [("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
+                ("snap_to_pixel_centers", C.c_uint32), ("random_bg_color", C.c_uint32), ("background_color", C.c_float * 3),
+                ("loss_scale", C.c_float), ("mask_loss_weight", C.c_float), ("ek_loss_weight", C.c_float),
+                ("cos_anneal_ratio", C.c_float)]
+
+
+class RayWorkspace(C.Structure):
+    _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_indices", C.c_void_p), ("d_rays", C.c_void_p),
+                ("d_numsteps", C.c_void_p), ("d_coords", C.c_void_p), ("d_counters", C.c_void_p), ("d_scan_tmp", C.c_void_p),
+                ("d_ray_tmp", C.c_void_p)]
+
+
+class AdamCfg(C.Structure):
+    _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
+                ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("loss_scale", C.c_float), ("step", C.c_uint32),
+                ("n_matrix", C.c_uint32)]
+
+
+class Neus2bError(RuntimeError):
+    pass
+
+
+_lib = None
+
+# every symbol include/neus2b.h declares
+EXPORTS = [
+    "neus2b_version", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
+    "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
+    "neus2b_mlp_forward", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
+    "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
+    "neus2b_generate_samples", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_adam_step",
+]
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Neus2bError(f"{LIB_PATH} is missing: run `python -m neus2_b200.build` (there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.neus2b_version.restype = C.c_char_p
+        _lib.neus2b_error_string.restype = C.c_char_p
+        _lib.neus2b_pcg32_seed.restype = None
+        _lib.neus2b_pcg32_advance.restype = None
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise Neus2bError(f"neus2b error {rc}: {lib().neus2b_error_string(C.c_int(rc)).decode()}")
+
+
+def ptr(t):
+    """Device pointer of a torch tensor (or None)."""
+    if t is None:
+        return C.c_void_p(0)
+    assert t.is_cuda and t.is_contiguous(), "neus2b takes contiguous CUDA tensors"
+    return C.c_void_p(t.data_ptr())
+
+
+def cur_stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def grid_desc(n_levels=16, log2_hashmap_size=19, base_resolution=16, per_level_scale=1.447, n_active_levels=None):
+    return GridDesc(n_levels, log2_hashmap_size, base_resolution, per_level_scale,
+                    n_levels if n_active_levels is None else n_active_levels)
+
+
+def grid_n_params(d):
+    n = C.c_uint64(0)
+    check(lib().neus2b_grid_n_params(C.byref(d), C.byref(n)))
+    return int(n.value)
+
+
+def model_n_params(d):
+    n = C.c_uint64(0)
+    check(lib().neus2b_model_n_params(C.byref(d), C.byref(n)))
+    return int(n.value)
+
+
+def grid_level_table(d):
+    off = (C.c_uint32 * 17)()
+    res = (C.c_uint32 * 16)()
+    scale = (C.c_float * 16)()
+    hashed = (C.c_uint32 * 16)()
+    check(lib().neus2b_grid_level_table(C.byref(d), off, res, scale, hashed))
+    return list(off), list(res), list(scale), list(hashed)
+
+
+def pcg32(seed):
+    r = Pcg32()
+    lib().neus2b_pcg32_seed(C.byref(r), C.c_uint64(seed))
+    return r
+
+
+def pcg32_advance(r, delta):
+    r2 = Pcg32(r.state, r.inc)
+    lib().neus2b_pcg32_advance(C.byref(r2), C.c_uint64(delta))
+    return r2
+
+
+def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, snap_to_pixel_centers=False,
+              cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0)):
+    c = TrainCfg()
+    c.aabb_min[:] = [0.0, 0.0, 0.0]
+    c.aabb_max[:] = [1.0, 1.0, 1.0]
+    c.cone_angle_constant = 0.0
+    c.snap_to_pixel_centers = int(snap_to_pixel_centers)
+    c.random_bg_color = int(random_bg_color)
+    c.background_color[:] = list(background_color)
+    c.loss_scale = loss_scale
+    c.mask_loss_weight = mask_loss_weight
+    c.ek_loss_weight = ek_loss_weight
+    c.cos_anneal_ratio = cos_anneal_ratio
+    return c

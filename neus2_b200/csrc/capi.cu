@@ -1,0 +1,18 @@
+// Library-level entry points of libneus2b.so.
+#include "common.cuh"
+
+extern "C" const char* neus2b_version(void) { return "neus2b 0.1 (sm_100a)"; }
+
+extern "C" const char* neus2b_error_string(int code) {
+	switch (code) {
+		case NEUS2B_OK: return "ok";
+		case NEUS2B_E_INVALID: return "invalid argument";
+		case NEUS2B_E_UNSUPPORTED: return "unsupported configuration";
+		case NEUS2B_E_NO_DEVICE: return "no CUDA device";
+		case NEUS2B_E_OVERFLOW: return "device-side capacity exceeded";
+		case NEUS2B_E_TOO_LARGE: return "request exceeds a compiled-in capacity";
+		default: break;
+	}
+	if (code > 0) return cudaGetErrorString((cudaError_t)code);
+	return "unknown error";
+}

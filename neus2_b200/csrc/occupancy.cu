@@ -1,0 +1,243 @@
+// Occupancy grid maintenance and the fused optimizer step.
+//  * occupancy: src/testbed_nerf.cu:630-785 (kernels) and :3287-3391 (update_density_grid_nerf,
+//    update_density_grid_mean_and_bitfield) of the reference; the SDF evaluation in the middle is the fused
+//    encoding + SDF-MLP kernel (neus2b_neus_sdf).
+//  * optimizer: Ema o ExponentialDecay o Adam of configs/nerf/dtu.json:5-27, one streaming pass that also casts to
+//    fp16, maintains the EMA copy and clears the gradients for the next step.
+#include "common.cuh"
+
+namespace n2b {
+
+__device__ __forceinline__ uint32_t expand_bits_o(uint32_t v) {
+	v = (v * 0x00010001u) & 0xFF0000FFu;
+	v = (v * 0x00000101u) & 0x0F00F00Fu;
+	v = (v * 0x00000011u) & 0xC30C30C3u;
+	v = (v * 0x00000005u) & 0x49249249u;
+	return v;
+}
+__device__ __forceinline__ uint32_t morton3d_o(uint32_t x, uint32_t y, uint32_t z) {
+	return expand_bits_o(x) | (expand_bits_o(y) << 1) | (expand_bits_o(z) << 2);
+}
+__device__ __forceinline__ uint32_t morton3d_invert(uint32_t x) {
+	x = x & 0x49249249u;
+	x = (x | (x >> 2)) & 0xc30c30c3u;
+	x = (x | (x >> 4)) & 0x0f00f00fu;
+	x = (x | (x >> 8)) & 0xff0000ffu;
+	x = (x | (x >> 16)) & 0x0000ffffu;
+	return x;
+}
+
+constexpr uint32_t kCells = NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE;
+
+// generate_grid_samples_nerf_nonuniform, src/testbed_nerf.cu:630-659 (unit-cube aabb: warp_position is the identity)
+__global__ void occ_samples_kernel(uint32_t n, Pcg32 rng, uint32_t step, const float* __restrict__ grid_in, uint32_t n_cascades,
+                                   float thresh, float* __restrict__ pos, uint32_t* __restrict__ indices) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n) return;
+	rng.advance((uint64_t)i * 4u);
+	const uint32_t level = (uint32_t)(rng.next_float() * (float)n_cascades) % n_cascades;
+	uint32_t idx = 0;
+	for (uint32_t j = 0; j < 10; ++j) {
+		idx = ((i + step * n) * 56924617u + j * 19349663u + 96925573u) % kCells;
+		idx += level * kCells;
+		if (grid_in[idx] > thresh) break;
+	}
+	const uint32_t pi = idx % kCells;
+	const float c[3] = {(float)morton3d_invert(pi >> 0), (float)morton3d_invert(pi >> 1), (float)morton3d_invert(pi >> 2)};
+	float r[3];
+#pragma unroll
+	for (int e = 0; e < 3; ++e) r[e] = rng.next_float();
+#pragma unroll
+	for (int e = 0; e < 3; ++e)
+		pos[(size_t)i * 3 + e] = __fadd_rn(__fmul_rn(__fsub_rn(__fdiv_rn(__fadd_rn(c[e], r[e]), (float)NEUS2B_GRIDSIZE), 0.5f),
+		                                             scalbnf(1.0f, (int)level)), 0.5f);
+	indices[i] = idx;
+}
+
+// ema_grid_samples_nerf, :700-730
+__global__ void occ_ema_kernel(uint32_t n, float decay, float* __restrict__ grid, const float* __restrict__ grid_tmp) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n) return;
+	const float prev = grid[i];
+	grid[i] = prev < 0.f ? prev : fmaxf(__fmul_rn(prev, decay), grid_tmp[i]);
+}
+
+// mean of max(density, 0) over cascade 0 (:3383): fixed-shape double-precision tree, reproducible run to run
+__global__ void __launch_bounds__(256) occ_mean_partial_kernel(const float* __restrict__ grid, double* __restrict__ partial) {
+	__shared__ double sh[256];
+	double acc = 0.0;
+	const uint32_t per_block = kCells / 1024u;
+	for (uint32_t k = threadIdx.x; k < per_block; k += 256) acc += (double)__fdiv_rn(fmaxf(grid[blockIdx.x * per_block + k], 0.f), (float)kCells);
+	sh[threadIdx.x] = acc;
+	__syncthreads();
+	for (int o = 128; o > 0; o >>= 1) {
+		if ((int)threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+		__syncthreads();
+	}
+	if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+__global__ void occ_mean_final_kernel(const double* __restrict__ partial, float* __restrict__ mean) {
+	if (threadIdx.x == 0 && blockIdx.x == 0) {
+		double acc = 0.0;
+		for (int k = 0; k < 1024; ++k) acc += partial[k];
+		*mean = (float)acc;
+	}
+}
+
+// grid_to_bitfield, :738-762
+__global__ void occ_bitfield_kernel(uint32_t n_bytes, uint32_t n_nonzero, const float* __restrict__ grid, uint8_t* __restrict__ bitfield,
+                                    const float* __restrict__ mean) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n_bytes) return;
+	if (i >= n_nonzero) {
+		bitfield[i] = 0;
+		return;
+	}
+	const float thresh = fminf(0.1f, *mean);
+	uint8_t bits = 0;
+#pragma unroll
+	for (uint32_t j = 0; j < 8; ++j) bits |= grid[(size_t)i * 8 + j] > thresh ? (uint8_t)(1u << j) : 0;
+	bitfield[i] = bits;
+}
+
+// bitfield_max_pool, :764-785
+__global__ void occ_maxpool_kernel(uint32_t n, const uint8_t* __restrict__ prev, uint8_t* __restrict__ next) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n) return;
+	uint8_t bits = 0;
+#pragma unroll
+	for (uint32_t j = 0; j < 8; ++j) bits |= prev[(size_t)i * 8 + j] > 0 ? (uint8_t)(1u << j) : 0;
+	const uint32_t x = morton3d_invert(i >> 0) + NEUS2B_GRIDSIZE / 8;
+	const uint32_t y = morton3d_invert(i >> 1) + NEUS2B_GRIDSIZE / 8;
+	const uint32_t z = morton3d_invert(i >> 2) + NEUS2B_GRIDSIZE / 8;
+	next[morton3d_o(x, y, z)] |= bits;
+}
+
+// ------------------------------------------------------------------------------------------------ Adam
+__global__ void __launch_bounds__(256) adam_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
+                                                   float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
+                                                   float* __restrict__ grad_var, float* __restrict__ master, float* __restrict__ m,
+                                                   float* __restrict__ v, __half* __restrict__ params, __half* __restrict__ params_ema,
+                                                   float* __restrict__ ema_master) {
+	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+	const uint64_t n_grid_end = n - 4u;
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+		float g;
+		if (i < c.n_matrix) {
+			g = grad_mlp[i];
+			grad_mlp[i] = 0.f;
+		} else if (i < n_grid_end) {
+			g = __half2float(grad_grid[i - c.n_matrix]);
+			grad_grid[i - c.n_matrix] = __float2half_rn(0.f);
+		} else {
+			g = grad_var[i - n_grid_end];
+			grad_var[i - n_grid_end] = 0.f;
+		}
+		float w = master[i];
+		g = g / c.loss_scale;
+		bool upd = true;
+		if (i < c.n_matrix) g += c.l2_reg * w;
+		else if (g == 0.0f) upd = false;
+		if (upd) {
+			const float mi = c.beta1 * m[i] + (1.0f - c.beta1) * g;
+			const float vi = c.beta2 * v[i] + (1.0f - c.beta2) * g * g;
+			m[i] = mi;
+			v[i] = vi;
+			w -= lr_t * mi / (sqrtf(vi) + c.epsilon);
+			master[i] = w;
+		}
+		params[i] = __float2half_rn(w);
+		if (params_ema) {
+			const float e = ((1.0f - c.ema_decay) * w + c.ema_decay * ema_master[i] * ema_old) * ema_new_inv;
+			ema_master[i] = e;
+			params_ema[i] = __float2half_rn(e);
+		}
+	}
+}
+
+}  // namespace n2b
+
+using namespace n2b;
+
+extern "C" int neus2b_neus_sdf(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
+                               uint32_t x_stride, uint16_t* d_sdf, neus2b_stream_t stream);
+
+namespace {
+// sdf_to_density_variance_buffer (common_operation.cuh:310-328, every operation in fp16) followed by
+// splat_grid_samples_nerf_max_nearest_neighbor (src/testbed_nerf.cu:661-680)
+__global__ void occ_splat_entry(uint32_t n, const uint32_t* __restrict__ indices, const __half* __restrict__ sdf,
+                                const __half* __restrict__ variance_ptr, float* __restrict__ grid_tmp) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n) return;
+	const __half variance = *variance_ptr;
+	const __half s = __float2half_rn(expf(__half2float(__hmul(variance, __float2half_rn(10.0f)))));
+	const __half x = __hmul(sdf[i], s);
+	const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(x))));
+	const __half dens = __hmul(__hmul(s, sg), __hsub(__float2half_rn(1.0f), sg));
+	atomicMax(reinterpret_cast<uint32_t*>(grid_tmp) + indices[i], __float_as_uint(__half2float(dens)));
+}
+}  // namespace
+
+extern "C" int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n_cascades,
+                                       uint32_t n_uniform, uint32_t n_nonuniform, neus2b_pcg32 rng_uniform, neus2b_pcg32 rng_nonuniform,
+                                       uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp, uint8_t* d_bitfield,
+                                       float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
+                                       neus2b_stream_t stream) {
+	if (!desc || !d_params || !d_grid || !d_grid_tmp || !d_bitfield || !d_mean || !d_pos || !d_idx || !d_sdf || !d_partial)
+		return NEUS2B_E_INVALID;
+	if (n_cascades == 0 || n_cascades > NEUS2B_CASCADES) return NEUS2B_E_INVALID;
+	GridLevels lv;
+	int rc = make_levels(desc, &lv);
+	if (rc) return rc;
+	const uint32_t n_elements = kCells * n_cascades;
+	const uint32_t n = n_uniform + n_nonuniform;
+	N2B_CHECK_CUDA(cudaMemsetAsync(d_grid_tmp, 0, sizeof(float) * (size_t)n_elements, stream));
+	if (n_uniform) {
+		occ_samples_kernel<<<div_up(n_uniform, 256), 256, 0, stream>>>(n_uniform, Pcg32{rng_uniform.state, rng_uniform.inc}, ema_step,
+		                                                               d_grid, n_cascades, -0.01f, d_pos, d_idx);
+		N2B_CHECK_LAUNCH();
+	}
+	if (n_nonuniform) {
+		occ_samples_kernel<<<div_up(n_nonuniform, 256), 256, 0, stream>>>(n_nonuniform, Pcg32{rng_nonuniform.state, rng_nonuniform.inc},
+		                                                                  ema_step, d_grid, n_cascades, 0.1f, d_pos + (size_t)n_uniform * 3,
+		                                                                  d_idx + n_uniform);
+		N2B_CHECK_LAUNCH();
+	}
+	if (n) {
+		rc = neus2b_neus_sdf(desc, d_params, sdf_bias, n, d_pos, 3, d_sdf, stream);
+		if (rc) return rc;
+		const __half* var_ptr = (const __half*)d_params + NEUS2B_GRID_OFF + (size_t)lv.offset[NEUS2B_MAX_LEVELS] * 2;
+		occ_splat_entry<<<div_up(n, 256), 256, 0, stream>>>(n, d_idx, (const __half*)d_sdf, var_ptr, d_grid_tmp);
+		N2B_CHECK_LAUNCH();
+	}
+	occ_ema_kernel<<<div_up(n_elements, 256), 256, 0, stream>>>(n_elements, decay, d_grid, d_grid_tmp);
+	N2B_CHECK_LAUNCH();
+	occ_mean_partial_kernel<<<1024, 256, 0, stream>>>(d_grid, d_partial);
+	N2B_CHECK_LAUNCH();
+	occ_mean_final_kernel<<<1, 32, 0, stream>>>(d_partial, d_mean);
+	N2B_CHECK_LAUNCH();
+	const uint32_t n_bytes = kCells / 8 * NEUS2B_CASCADES, n_nonzero = kCells / 8 * n_cascades;
+	occ_bitfield_kernel<<<div_up(n_bytes, 256), 256, 0, stream>>>(n_bytes, n_nonzero, d_grid, d_bitfield, d_mean);
+	N2B_CHECK_LAUNCH();
+	for (uint32_t level = 1; level < NEUS2B_CASCADES; ++level) {
+		occ_maxpool_kernel<<<div_up(kCells / 64, 256), 256, 0, stream>>>(kCells / 64, d_bitfield + (size_t)(kCells / 8) * (level - 1),
+		                                                                 d_bitfield + (size_t)(kCells / 8) * level);
+		N2B_CHECK_LAUNCH();
+	}
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid, float* d_grad_variance,
+                                float* d_master, float* d_m, float* d_v, uint16_t* d_params, uint16_t* d_params_ema, float* d_ema_master,
+                                neus2b_stream_t stream) {
+	if (!cfg || !d_grad_mlp || !d_grad_grid || !d_grad_variance || !d_master || !d_m || !d_v || !d_params) return NEUS2B_E_INVALID;
+	if (d_params_ema && !d_ema_master) return NEUS2B_E_INVALID;
+	if (n < cfg->n_matrix + 4u || cfg->step == 0) return NEUS2B_E_INVALID;
+	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
+	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
+	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
+	adam_kernel<<<kSMs * 8, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
+	                                          d_master, d_m, d_v, (__half*)d_params, (__half*)d_params_ema, d_ema_master);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}

@@ -1,0 +1,635 @@
+// Ray-march side of the NeuS training step: occupancy-grid DDA sample generation, NeuS compositing + loss + loss
+// gradient, compaction and roll-over (src/testbed_nerf.cu:1253-1996, 3908-3916 of the reference).
+//
+// The reference reserves output ranges with atomicAdd, so its sample order changes from run to run.  Here every
+// range comes from an exclusive prefix sum over the ray index: the set of samples, each ray's step count and the
+// compaction result are reproducible and identical to the canonical-order CPU restatement.
+//
+// This file is compiled with -fmad=false: the DDA decides integer step counts from fp32 arithmetic, so every
+// operation is a single IEEE operation in a fixed order (fused multiply-adds only where written explicitly).
+#include "common.cuh"
+
+namespace n2b {
+
+__device__ __forceinline__ float clampf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
+__device__ __forceinline__ float min_cone_stepsize() { return 1.73205080757f / (float)NEUS2B_STEPS; }
+__device__ __forceinline__ float max_cone_stepsize() {
+	return min_cone_stepsize() * (float)(1u << (NEUS2B_CASCADES - 1)) * (float)NEUS2B_STEPS / (float)NEUS2B_GRIDSIZE;
+}
+// calc_dt, src/testbed_nerf.cu:152
+__device__ __forceinline__ float calc_dt(float t, float cone_angle) { return clampf(t * cone_angle, min_cone_stepsize(), max_cone_stepsize()); }
+// warp_dt / unwarp_dt, src/testbed_nerf.cu:474-482
+__device__ __forceinline__ float warp_dt(float dt) {
+	const float mx = min_cone_stepsize() * (float)(1u << (NEUS2B_CASCADES - 1));
+	return (dt - min_cone_stepsize()) / (mx - min_cone_stepsize());
+}
+__device__ __forceinline__ float unwarp_dt(float dt) {
+	const float mx = min_cone_stepsize() * (float)(1u << (NEUS2B_CASCADES - 1));
+	return dt * (mx - min_cone_stepsize()) + min_cone_stepsize();
+}
+__device__ __forceinline__ uint32_t expand_bits(uint32_t v) {
+	v = (v * 0x00010001u) & 0xFF0000FFu;
+	v = (v * 0x00000101u) & 0x0F00F00Fu;
+	v = (v * 0x00000011u) & 0xC30C30C3u;
+	v = (v * 0x00000005u) & 0x49249249u;
+	return v;
+}
+__device__ __forceinline__ uint32_t morton3d(uint32_t x, uint32_t y, uint32_t z) {
+	return expand_bits(x) | (expand_bits(y) << 1) | (expand_bits(z) << 2);
+}
+// mip_from_pos / mip_from_dt, src/testbed_nerf.cu:614-628
+__device__ __forceinline__ int mip_from_pos(const float* p) {
+	int exponent;
+	const float m = fmaxf(fmaxf(fabsf(p[0] - 0.5f), fabsf(p[1] - 0.5f)), fabsf(p[2] - 0.5f));
+	frexpf(m, &exponent);
+	return min((int)NEUS2B_CASCADES - 1, max(0, exponent + 1));
+}
+__device__ __forceinline__ int mip_from_dt(float dt, const float* p) {
+	const int mip = mip_from_pos(p);
+	dt *= 2.f * (float)NEUS2B_GRIDSIZE;
+	if (dt < 1.f) return mip;
+	int exponent;
+	frexpf(dt, &exponent);
+	return min((int)NEUS2B_CASCADES - 1, max(exponent, mip));
+}
+// cascaded_grid_idx_at / density_grid_occupied_at, src/testbed_nerf.cu:484-510
+__device__ __forceinline__ bool occupied_at(const float* pos, const uint8_t* __restrict__ bitfield, uint32_t mip) {
+	const float mip_scale = scalbnf(1.0f, -(int)mip);
+	int c[3];
+#pragma unroll
+	for (int d = 0; d < 3; ++d) {
+		const float p = (pos[d] - 0.5f) * mip_scale + 0.5f;
+		const int v = (int)(p * (float)NEUS2B_GRIDSIZE);
+		c[d] = v < 0 ? 0 : (v > (int)NEUS2B_GRIDSIZE - 1 ? (int)NEUS2B_GRIDSIZE - 1 : v);
+	}
+	const uint32_t idx = morton3d((uint32_t)c[0], (uint32_t)c[1], (uint32_t)c[2]);
+	const uint32_t cells = NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE;
+	return (__ldg(bitfield + idx / 8 + (cells * mip) / 8) & (1u << (idx % 8))) != 0;
+}
+// distance_to_next_voxel / advance_to_next_voxel, src/testbed_nerf.cu:346-368
+__device__ __forceinline__ float advance_to_next_voxel(float t, float cone_angle, const float* pos, const float* dir, const float* idir,
+                                                       uint32_t res) {
+	float tt[3];
+#pragma unroll
+	for (int d = 0; d < 3; ++d) {
+		const float p = (float)res * pos[d];
+		tt[d] = (floorf(p + 0.5f + 0.5f * copysignf(1.0f, dir[d])) - p) * idir[d];
+	}
+	const float tmin = fminf(fminf(tt[0], tt[1]), tt[2]);
+	const float t_target = t + fmaxf(tmin / (float)res, 0.0f);
+	do {
+		t += calc_dt(t, cone_angle);
+	} while (t < t_target);
+	return t;
+}
+// BoundingBox::ray_intersect, include/neural-graphics-primitives/bounding_box.cuh:163-210
+__device__ __forceinline__ void aabb_ray_intersect(const float* mn, const float* mx, const float* o, const float* d, float& tmin_out,
+                                                   float& tmax_out) {
+	const float big = 3.402823466e+38f;
+	float tmin = (mn[0] - o[0]) / d[0], tmax = (mx[0] - o[0]) / d[0];
+	if (tmin > tmax) { float t = tmin; tmin = tmax; tmax = t; }
+	float tymin = (mn[1] - o[1]) / d[1], tymax = (mx[1] - o[1]) / d[1];
+	if (tymin > tymax) { float t = tymin; tymin = tymax; tymax = t; }
+	if (tmin > tymax || tymin > tmax) { tmin_out = tmax_out = big; return; }
+	if (tymin > tmin) tmin = tymin;
+	if (tymax < tmax) tmax = tymax;
+	float tzmin = (mn[2] - o[2]) / d[2], tzmax = (mx[2] - o[2]) / d[2];
+	if (tzmin > tzmax) { float t = tzmin; tzmin = tzmax; tzmax = t; }
+	if (tmin > tzmax || tzmin > tmax) { tmin_out = tmax_out = big; return; }
+	if (tzmin > tmin) tmin = tzmin;
+	if (tzmax < tmax) tmax = tzmax;
+	tmin_out = tmin;
+	tmax_out = tmax;
+}
+__device__ __forceinline__ bool aabb_contains(const float* mn, const float* mx, const float* p) {
+	return p[0] >= mn[0] && p[0] <= mx[0] && p[1] >= mn[1] && p[1] <= mx[1] && p[2] >= mn[2] && p[2] <= mx[2];
+}
+// include/neural-graphics-primitives/common_device.cuh:31-77
+__device__ __forceinline__ float srgb_to_linear(float s) { return s <= 0.04045f ? s / 12.92f : powf((s + 0.055f) / 1.055f, 2.4f); }
+__device__ __forceinline__ float linear_to_srgb(float l) { return l < 0.0031308f ? 12.92f * l : 1.055f * powf(l, 0.41666f) - 0.055f; }
+// image_pos / read_rgba for EImageDataType::Byte, common_device.cuh:591-642
+__device__ __forceinline__ void read_rgba(const neus2b_dataset& ds, uint32_t img, const float* xy, float* rgba) {
+	int px = (int)(xy[0] * (float)ds.width), py = (int)(xy[1] * (float)ds.height);
+	px = min(px, (int)ds.width - 1);
+	py = min(py, (int)ds.height - 1);
+	px = max(px, 0);
+	py = max(py, 0);
+	const uint32_t v = __ldg(ds.d_pixels + (size_t)img * ds.width * ds.height + (size_t)py * ds.width + px);
+	if (v == 0x00FF00FFu) {
+		rgba[0] = rgba[1] = rgba[2] = rgba[3] = -1.0f;
+		return;
+	}
+	const float a = (float)(v >> 24) * (1.0f / 255.0f);
+	rgba[0] = srgb_to_linear((float)(v & 0xFF) * (1.0f / 255.0f)) * a;
+	rgba[1] = srgb_to_linear((float)((v >> 8) & 0xFF) * (1.0f / 255.0f)) * a;
+	rgba[2] = srgb_to_linear((float)((v >> 16) & 0xFF) * (1.0f / 255.0f)) * a;
+	rgba[3] = a;
+}
+// image_idx without the error-map CDF, src/testbed_nerf.cu:1231-1251 (32-bit wrap-around like the reference)
+__device__ __forceinline__ uint32_t image_idx(uint32_t base_idx, uint32_t n_rays, uint32_t n_rays_total, uint32_t n_images) {
+	return (((base_idx + n_rays_total) * n_images) / n_rays) % n_images;
+}
+// nerf_random_image_pos_training without CDF, src/testbed_nerf.cu:1216-1229
+__device__ __forceinline__ void random_image_pos(Pcg32& rng, const neus2b_dataset& ds, bool snap, float* xy) {
+	xy[0] = rng.next_float();
+	xy[1] = rng.next_float();
+	if (snap) {
+		int px = (int)(xy[0] * (float)ds.width), py = (int)(xy[1] * (float)ds.height);
+		px = max(0, min(px, (int)ds.width - 1));
+		py = max(0, min(py, (int)ds.height - 1));
+		xy[0] = ((float)px + 0.5f) / (float)ds.width;
+		xy[1] = ((float)py + 0.5f) / (float)ds.height;
+	}
+}
+
+struct RayTmp {  // 8 floats per ray
+	float o[3], d[3], startt;
+	uint32_t numsteps;
+};
+
+// First half of generate_training_samples_nerf_with_global_movement (:1287-1409): build the ray and count its steps.
+__global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
+                                                          const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total, Pcg32 rng,
+                                                          const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
+                                                          uint64_t* __restrict__ scan_in) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
+	if (i >= n_rays_max) return;
+	if (i >= n_rays) {
+		scan_in[i] = 0;
+		return;
+	}
+	RayTmp r;
+	r.numsteps = 0;
+	r.startt = 0.f;
+	const uint32_t img = image_idx(i, n_rays, n_rays_total, ds.n_images);
+	rng.advance((uint64_t)i * 8u);
+	float xy[2], rgba[4];
+	random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
+	read_rgba(ds, img, xy, rgba);
+	bool keep = !(rgba[0] <= 0.0f && rng.next_float() >= 0.9f);
+	if (keep) {
+		(void)rng.next_float();  // motion-blur time (:1307)
+		const float* X = ds.d_xforms + (size_t)img * 12;
+		const float fx = ds.d_focal[img * 2], fy = ds.d_focal[img * 2 + 1];
+		const float ppx = ds.d_principal[img * 2], ppy = ds.d_principal[img * 2 + 1];
+		const float dl[3] = {(xy[0] - ppx) * (float)ds.width / fx, (xy[1] - ppy) * (float)ds.height / fy, 1.0f};
+		float dirn[3];
+#pragma unroll
+		for (int e = 0; e < 3; ++e) {
+			r.o[e] = X[9 + e];
+			r.d[e] = X[0 + e] * dl[0] + X[3 + e] * dl[1] + X[6 + e] * dl[2];
+		}
+		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+#pragma unroll
+		for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+		float tmin, tmax;
+		aabb_ray_intersect(cfg.aabb_min, cfg.aabb_max, r.o, dirn, tmin, tmax);
+		const float cone_angle = cfg.cone_angle_constant;
+		tmin = fmaxf(tmin, 0.0f);
+		float startt = tmin;
+		startt += calc_dt(startt, cone_angle) * rng.next_float();
+		const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
+		uint32_t j = 0;
+		float t = startt, pos[3];
+		for (;;) {
+#pragma unroll
+			for (int e = 0; e < 3; ++e) pos[e] = r.o[e] + t * dirn[e];
+			if (!(aabb_contains(cfg.aabb_min, cfg.aabb_max, pos) && j < NEUS2B_STEPS)) break;
+			const float dt = calc_dt(t, cone_angle);
+			const uint32_t mip = (uint32_t)mip_from_dt(dt, pos);
+			if (occupied_at(pos, bitfield, mip)) {
+				++j;
+				t += dt;
+			} else {
+				t = advance_to_next_voxel(t, cone_angle, pos, dirn, idir, NEUS2B_GRIDSIZE >> mip);
+			}
+		}
+		r.startt = startt;
+		r.numsteps = j;
+	}
+	tmp[i] = r;
+	scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
+}
+
+// Exclusive prefix sum of n 64-bit keys with one CTA (n <= 2^18 rays per batch); total goes to scan[n_max].
+// TODO(perf): decoupled look-back over all SMs.
+__global__ void __launch_bounds__(1024) scan_kernel(uint32_t n, uint64_t* __restrict__ data) {
+	__shared__ uint64_t warp_sums[32];
+	__shared__ uint64_t carry;
+	const uint32_t tid = threadIdx.x;
+	const uint32_t per = (n + 1023u) / 1024u;
+	const uint32_t lo = min(n, tid * per), hi = min(n, lo + per);
+	uint64_t sum = 0;
+	for (uint32_t k = lo; k < hi; ++k) sum += data[k];
+	// block-wide exclusive scan of the per-thread sums
+	uint64_t incl = sum;
+#pragma unroll
+	for (int o = 1; o < 32; o <<= 1) {
+		const uint64_t v = __shfl_up_sync(0xffffffffu, incl, o);
+		if ((tid & 31) >= (uint32_t)o) incl += v;
+	}
+	if ((tid & 31) == 31) warp_sums[tid >> 5] = incl;
+	__syncthreads();
+	if (tid < 32) {
+		uint64_t w = warp_sums[tid], wi = w;
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1) {
+			const uint64_t v = __shfl_up_sync(0xffffffffu, wi, o);
+			if (tid >= (uint32_t)o) wi += v;
+		}
+		warp_sums[tid] = wi - w;
+		if (tid == 31) carry = wi;
+	}
+	__syncthreads();
+	uint64_t run = warp_sums[tid >> 5] + incl - sum;
+	for (uint32_t k = lo; k < hi; ++k) {
+		const uint64_t v = data[k];
+		data[k] = run;
+		run += v;
+	}
+	if (tid == 0) data[n] = carry;
+}
+
+// Second half of the sample generator (:1410-1445): canonical ranges, then march again and write the coordinates.
+__global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, uint32_t max_samples,
+                                                           const uint8_t* __restrict__ bitfield, const RayTmp* __restrict__ tmp,
+                                                           const uint64_t* __restrict__ scan, uint32_t* __restrict__ ray_indices,
+                                                           float* __restrict__ rays, uint32_t* __restrict__ numsteps,
+                                                           float* __restrict__ coords, uint32_t* __restrict__ counters) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps found, dropped rays included
+	if (i >= n_rays_max) return;
+	const RayTmp r = tmp[i];
+	if (r.numsteps == 0) return;
+	const uint64_t key = scan[i];
+	const uint32_t base = (uint32_t)(key & 0xFFFFFFFFull), kidx = (uint32_t)(key >> 32);
+	if (base + r.numsteps > max_samples) {  // sample buffer exhausted: drop the ray (:1412-1414)
+		atomicOr(&counters[3], 1u);
+		return;
+	}
+	atomicMax(&counters[0], kidx + 1u);
+	atomicMax(&counters[4], base + r.numsteps);
+	ray_indices[kidx] = i;
+#pragma unroll
+	for (int e = 0; e < 3; ++e) {
+		rays[(size_t)kidx * 6 + e] = r.o[e];
+		rays[(size_t)kidx * 6 + 3 + e] = r.d[e];
+	}
+	numsteps[kidx * 2 + 0] = r.numsteps;
+	numsteps[kidx * 2 + 1] = base;
+	const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+	const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
+	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
+	const float wd[3] = {(dirn[0] + 1.f) * 0.5f, (dirn[1] + 1.f) * 0.5f, (dirn[2] + 1.f) * 0.5f};
+	const float cone_angle = cfg.cone_angle_constant;
+	float* co = coords + (size_t)base * 7;
+	float t = r.startt, pos[3];
+	uint32_t j = 0;
+	for (;;) {
+#pragma unroll
+		for (int e = 0; e < 3; ++e) pos[e] = r.o[e] + t * dirn[e];
+		if (!(aabb_contains(cfg.aabb_min, cfg.aabb_max, pos) && j < r.numsteps)) break;
+		const float dt = calc_dt(t, cone_angle);
+		const uint32_t mip = (uint32_t)mip_from_dt(dt, pos);
+		if (occupied_at(pos, bitfield, mip)) {
+			float* c = co + (size_t)j * 7;
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				c[e] = (pos[e] - cfg.aabb_min[e]) / (cfg.aabb_max[e] - cfg.aabb_min[e]);  // warp_position
+				c[4 + e] = wd[e];
+			}
+			c[3] = warp_dt(dt);
+			++j;
+			t += dt;
+		} else {
+			t = advance_to_next_voxel(t, cone_angle, pos, dirn, idir, NEUS2B_GRIDSIZE >> mip);
+		}
+	}
+}
+
+// ------------------------------------------------------------------------------------------------ loss
+struct NeusSample {
+	float alpha, p_div_c, inv_s, iter_cos, true_cos, dt, next_sdf;
+	float rgb[3], nrm[3];
+};
+__device__ __forceinline__ float logisticf(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// NeuS alpha of one sample (src/testbed_nerf.cu:1568-1606 == :1779-1805)
+__device__ __forceinline__ void neus_sample(const __half* o, float dt_warped, const float* dir, float anneal, NeusSample& s) {
+#pragma unroll
+	for (int e = 0; e < 3; ++e) s.rgb[e] = logisticf(__half2float(o[e]));
+	s.dt = unwarp_dt(dt_warped);
+	s.inv_s = __expf(__half2float(__hmul(__float2half_rn(10.0f), o[7])));
+	const float sdf = __half2float(o[3]);
+#pragma unroll
+	for (int e = 0; e < 3; ++e) s.nrm[e] = __half2float(o[4 + e]);
+	s.true_cos = dir[0] * s.nrm[0] + dir[1] * s.nrm[1] + dir[2] * s.nrm[2];
+	const float r1 = -s.true_cos * 0.5f + 0.5f, r2 = -s.true_cos;
+	s.iter_cos = -(fmaxf(r1, 0.f) * (1.0f - anneal) + fmaxf(r2, 0.f) * anneal);
+	s.next_sdf = sdf + s.iter_cos * s.dt * 0.5f;
+	const float prev_sdf = sdf - s.iter_cos * s.dt * 0.5f;
+	const float next_cdf = logisticf(s.next_sdf * s.inv_s), prev_cdf = logisticf(prev_sdf * s.inv_s);
+	s.p_div_c = (prev_cdf - next_cdf + 1e-5f) / (prev_cdf + 1e-5f);
+	s.alpha = clampf(s.p_div_c, 0.0f, 1.0f);
+}
+
+__device__ __forceinline__ void load_out16(const __half* src, __half* dst) {
+	const uint4* p = reinterpret_cast<const uint4*>(src);
+	reinterpret_cast<uint4*>(dst)[0] = __ldg(p);
+	reinterpret_cast<uint4*>(dst)[1] = __ldg(p + 1);
+}
+
+struct CompTmp {  // 8 floats per kept ray
+	float rgb[3], T, weight_sum;
+	uint32_t n, full, pad;
+};
+
+// Pass A (:1563-1617): composite along the ray until transmittance drops below 1e-4; count the surviving samples.
+__global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, const uint32_t* __restrict__ counters,
+                                                        const __half* __restrict__ mlp_out, const float* __restrict__ rays,
+                                                        const uint32_t* __restrict__ numsteps, const float* __restrict__ coords,
+                                                        CompTmp* __restrict__ tmp, uint64_t* __restrict__ scan_in) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n_rays_max) return;
+	if (i >= counters[0]) {
+		scan_in[i] = 0;
+		return;
+	}
+	const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
+	float dir[3];
+	CompTmp c;
+	c.rgb[0] = c.rgb[1] = c.rgb[2] = 0.f;
+	c.T = 1.f;
+	c.weight_sum = 0.f;
+	c.n = 0;
+	c.pad = 0;
+	for (; c.n < ns; ++c.n) {
+		if (c.T < 1e-4f) break;
+		__align__(16) __half o[16];
+		load_out16(mlp_out + (size_t)(base + c.n) * 16, o);
+		if (c.n == 0) {  // BENT_DIR (:1574-1579): the direction the network saw replaces the ray direction
+			const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
+			const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+#pragma unroll
+			for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+		}
+		NeusSample s;
+		neus_sample(o, coords[(size_t)(base + c.n) * 7 + 3], dir, cfg.cos_anneal_ratio, s);
+		const float w = s.alpha * c.T;
+#pragma unroll
+		for (int e = 0; e < 3; ++e) c.rgb[e] += w * s.rgb[e];
+		c.weight_sum += w;
+		c.T *= (1.f - s.alpha);
+	}
+	c.full = c.n == ns;
+	tmp[i] = c;
+	scan_in[i] = (uint64_t)c.n;
+}
+
+// Target pixel, Huber loss, pass B (:1619-1952): loss gradient w.r.t. the 16 network outputs of every kept sample.
+__global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
+                                                   const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total, Pcg32 rng0,
+                                                   uint32_t max_compacted, uint32_t* __restrict__ counters,
+                                                   const __half* __restrict__ mlp_out, const uint32_t* __restrict__ ray_indices,
+                                                   uint32_t* __restrict__ numsteps, const float* __restrict__ coords,
+                                                   const CompTmp* __restrict__ tmp, const uint64_t* __restrict__ scan,
+                                                   float* __restrict__ coords_out, __half* __restrict__ dloss_dout,
+                                                   float* __restrict__ loss_out, float* __restrict__ ek_loss_out) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i == 0) counters[2] = (uint32_t)scan[n_rays_max];
+	if (i >= n_rays_max) return;
+	if (i >= counters[0]) {
+		if (loss_out) loss_out[i] = 0.f;
+		if (ek_loss_out) ek_loss_out[i] = 0.f;
+		return;
+	}
+	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
+	const uint32_t base = numsteps[i * 2 + 1];
+	const CompTmp c = tmp[i];
+	const uint32_t compacted_base = (uint32_t)scan[i];
+	const uint32_t cn = min(max_compacted - min(max_compacted, compacted_base), c.n);
+	numsteps[i * 2 + 0] = cn;
+	numsteps[i * 2 + 1] = compacted_base;
+	if (loss_out) loss_out[i] = 0.f;
+	if (ek_loss_out) ek_loss_out[i] = 0.f;
+	if (cn == 0) return;
+	// target colour (:1619-1667)
+	const uint32_t ray_idx = ray_indices[i];
+	Pcg32 rng = rng0;
+	rng.advance((uint64_t)ray_idx * 8u);
+	const uint32_t img = image_idx(ray_idx, n_rays, n_rays_total, ds.n_images);
+	float xy[2], bg[3], tex[4], target[3];
+	random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
+	if (cfg.random_bg_color) {
+#pragma unroll
+		for (int e = 0; e < 3; ++e) bg[e] = rng.next_float();
+	} else {
+#pragma unroll
+		for (int e = 0; e < 3; ++e) bg[e] = cfg.background_color[e];
+	}
+#pragma unroll
+	for (int e = 0; e < 3; ++e) bg[e] = srgb_to_linear(bg[e]);
+	read_rgba(ds, img, xy, tex);
+#pragma unroll
+	for (int e = 0; e < 3; ++e) {
+		target[e] = linear_to_srgb(tex[e] + (1.0f - tex[3]) * bg[e]);
+		bg[e] = linear_to_srgb(bg[e]);
+	}
+	float rgb_ray[3] = {c.rgb[0], c.rgb[1], c.rgb[2]};
+	if (c.full) {
+#pragma unroll
+		for (int e = 0; e < 3; ++e) rgb_ray[e] += c.T * bg[e];
+	}
+	// Huber(0.1) / 5 (:301-317, :1459)
+	float lgl[3], lgg[3];
+#pragma unroll
+	for (int e = 0; e < 3; ++e) {
+		const float diff = rgb_ray[e] - target[e], ad = fabsf(diff), al = 0.1f;
+		lgl[e] = (ad > al ? (ad - 0.5f * al) : 0.5f / al * diff * diff) / 5.0f;
+		lgg[e] = (ad > al ? (diff > 0 ? 1.0f : -1.0f) : diff / al) / 5.0f;
+	}
+	const float mask_gt = tex[3] > 0.9999f ? 1.f : 0.f;
+	float gws, ws = c.weight_sum;
+	if (ws >= 1.0f - 1e-4f) {
+		ws = 1.0f - 1e-4f;
+		gws = 0.f;
+	} else if (ws <= 1e-4f) {
+		ws = 1e-4f;
+		gws = 0.f;
+	} else {
+		const float sg = 1.0f / (1.0f + expf(-ws));
+		gws = (mask_gt - sg) * ws * cfg.mask_loss_weight;
+	}
+	if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / (float)n_rays;
+	const float loss_scale = cfg.loss_scale / (float)n_rays;
+	float dir[3];
+	float rgb2[3] = {0.f, 0.f, 0.f}, T = 1.f, ek = 0.f;
+	for (uint32_t j = 0; j < cn; ++j) {
+		__align__(16) __half o[16];
+		load_out16(mlp_out + (size_t)(base + j) * 16, o);
+		if (j == 0) {
+			const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
+			const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+#pragma unroll
+			for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+		}
+		const float* cin = coords + (size_t)(base + j) * 7;
+		float* cout = coords_out + (size_t)(compacted_base + j) * 7;
+		float cdt = 0.f;
+#pragma unroll
+		for (int e = 0; e < 7; ++e) {
+			const float vv = cin[e];
+			cout[e] = vv;
+			if (e == 3) cdt = vv;
+		}
+		NeusSample s;
+		neus_sample(o, cdt, dir, cfg.cos_anneal_ratio, s);
+		const float w = s.alpha * T;
+#pragma unroll
+		for (int e = 0; e < 3; ++e) rgb2[e] += w * s.rgb[e];
+		T *= (1.f - s.alpha);
+		float g[16];
+#pragma unroll
+		for (int k = 0; k < 16; ++k) g[k] = 0.f;
+		float dla = gws * (1.0f - ws);
+#pragma unroll
+		for (int e = 0; e < 3; ++e) {
+			const float suffix = rgb_ray[e] - rgb2[e];
+			g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
+			dla += lgg[e] * (T * s.rgb[e] - suffix);
+		}
+		dla /= (1.0f - s.alpha + 1e-5f);
+		float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
+		if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {
+			const float P = __expf(s.inv_s * s.iter_cos * s.dt);
+			const float E = __expf(-s.next_sdf * s.inv_s);
+			dE_dsdf = -s.inv_s * E;
+			dE_ds = -s.next_sdf * E;
+			const float a = 1 + E, b = 1 + P * E, cc = 1e-5f + 1 / (1 + P * E);
+			const float delta = a * (b * b) * (cc * cc);
+			da_dE = -(P / delta - 1 / (a * a * cc));
+			da_dP = -E / delta;
+			dP_ds = P * s.iter_cos * s.dt;
+			dP_dic = P * s.inv_s * s.dt;
+			dE_dic = -s.inv_s * E * s.dt * 0.5f;
+		}
+		const float dl_dinvs = dla * (da_dE * dE_ds + da_dP * dP_ds);
+		const float dl_dvar = dl_dinvs * s.inv_s * 10;
+		const float dic_dcos = s.true_cos >= 0 ? 0.0f : 1.0f;
+		const float gn = sqrtf(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2] + 1e-6f);
+		const float gni = 1 - 1 / gn;
+		const float dl_dnn = dla * (da_dE * dE_dic + dP_dic * da_dP) * dic_dcos;
+		g[3] = loss_scale * (dla * da_dE * dE_dsdf);
+		ek += (gn - 1.0f) * (gn - 1.0f);
+#pragma unroll
+		for (int e = 0; e < 3; ++e) {
+			g[4 + e] = cfg.ek_loss_weight * 2 * cfg.loss_scale * gni * s.nrm[e];
+			g[8 + e] = loss_scale * dl_dnn * dir[e];
+		}
+		g[7] = loss_scale * dl_dvar;
+		__align__(16) __half gh[16];
+#pragma unroll
+		for (int k = 0; k < 16; ++k) gh[k] = __float2half_rn(g[k]);
+		uint4* dst = reinterpret_cast<uint4*>(dloss_dout + (size_t)(compacted_base + j) * 16);
+		dst[0] = reinterpret_cast<const uint4*>(gh)[0];
+		dst[1] = reinterpret_cast<const uint4*>(gh)[1];
+	}
+	if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * (float)n_rays);
+}
+
+// fill_rollover / fill_rollover_and_rescale (call sites :3908-3916): pad [n_valid, n_target) with wrap-around copies
+// of [0, n_valid); the gradient is also rescaled by n_valid / n_target so the copies do not over-weight the batch.
+__global__ void rollover_tail_kernel(uint32_t n_target, const uint32_t* __restrict__ counters, float* __restrict__ coords,
+                                     __half* __restrict__ dloss) {
+	const uint32_t nv = min(counters[2], n_target);
+	if (nv == 0 || nv >= n_target) return;
+	const float scale = (float)nv / (float)n_target;
+	const size_t n_tail = (size_t)(n_target - nv);
+	for (size_t r = blockIdx.x * (size_t)blockDim.x + threadIdx.x; r < n_tail * 16; r += (size_t)gridDim.x * blockDim.x) {
+		const size_t row = nv + r / 16, k = r % 16;
+		const size_t src = row % nv;
+		dloss[row * 16 + k] = __float2half_rn(__half2float(dloss[src * 16 + k]) * scale);
+		if (k < 7) coords[row * 7 + k] = coords[src * 7 + k];
+	}
+}
+__global__ void rollover_head_kernel(uint32_t n_target, const uint32_t* __restrict__ counters, __half* __restrict__ dloss) {
+	const uint32_t nv = min(counters[2], n_target);
+	if (nv == 0 || nv >= n_target) return;
+	const float scale = (float)nv / (float)n_target;
+	for (size_t r = blockIdx.x * (size_t)blockDim.x + threadIdx.x; r < (size_t)nv * 16; r += (size_t)gridDim.x * blockDim.x)
+		dloss[r] = __float2half_rn(__half2float(dloss[r]) * scale);
+}
+
+}  // namespace n2b
+
+using namespace n2b;
+
+extern "C" void neus2b_pcg32_seed(neus2b_pcg32* rng, uint64_t seed) {
+	Pcg32 r;
+	r.state = 0u;
+	r.inc = (0xda3e39cb94b95bdbULL << 1u) | 1u;
+	r.next_uint();
+	r.state += seed;
+	r.next_uint();
+	rng->state = r.state;
+	rng->inc = r.inc;
+}
+extern "C" void neus2b_pcg32_advance(neus2b_pcg32* rng, uint64_t delta) {
+	Pcg32 r{rng->state, rng->inc};
+	r.advance(delta);
+	rng->state = r.state;
+}
+
+static int check_ws(const neus2b_ray_workspace* ws) {
+	if (!ws || !ws->d_ray_indices || !ws->d_rays || !ws->d_numsteps || !ws->d_coords || !ws->d_counters || !ws->d_scan_tmp ||
+	    !ws->d_ray_tmp || ws->max_rays == 0 || ws->max_samples == 0)
+		return NEUS2B_E_INVALID;
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                                       uint32_t n_rays_total, neus2b_pcg32 rng, const uint8_t* d_bitfield, neus2b_ray_workspace* ws,
+                                       neus2b_stream_t stream) {
+	if (!ds || !cfg || !d_bitfield || check_ws(ws)) return NEUS2B_E_INVALID;
+	if (n_rays == 0 || n_rays > ws->max_rays || ds->n_images == 0) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
+	Pcg32 r{rng.state, rng.inc};
+	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, r, d_bitfield,
+	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
+	N2B_CHECK_LAUNCH();
+	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
+	N2B_CHECK_LAUNCH();
+	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
+	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
+	                                                             ws->d_coords, ws->d_counters);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                                   uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, const uint16_t* d_mlp_out,
+                                   neus2b_ray_workspace* ws, float* d_coords_out, uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss,
+                                   int rollover, neus2b_stream_t stream) {
+	if (!ds || !cfg || !d_mlp_out || !d_coords_out || !d_dloss_dout || check_ws(ws)) return NEUS2B_E_INVALID;
+	if (n_rays == 0 || n_rays > ws->max_rays || max_compacted == 0) return NEUS2B_E_INVALID;
+	if (((uintptr_t)d_mlp_out | (uintptr_t)d_dloss_dout) & 15u) return NEUS2B_E_INVALID;
+	Pcg32 r{rng.state, rng.inc};
+	composite_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, ws->d_counters, (const __half*)d_mlp_out, ws->d_rays,
+	                                                          ws->d_numsteps, ws->d_coords, (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
+	N2B_CHECK_LAUNCH();
+	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
+	N2B_CHECK_LAUNCH();
+	loss_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, r, max_compacted, ws->d_counters,
+	                                                     (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
+	                                                     (const CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, d_coords_out,
+	                                                     (__half*)d_dloss_dout, d_loss, d_ek_loss);
+	N2B_CHECK_LAUNCH();
+	if (rollover) {
+		rollover_tail_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, d_coords_out, (__half*)d_dloss_dout);
+		N2B_CHECK_LAUNCH();
+		rollover_head_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, (__half*)d_dloss_dout);
+		N2B_CHECK_LAUNCH();
+	}
+	return NEUS2B_OK;
+}

@@ -1,0 +1,162 @@
+"""Tensor-level wrappers over the C ABI (torch is only the owner of device memory and streams)."""
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+u32 = C.c_uint32
+_H = torch.float16
+
+
+def _half(shape, dev):
+    return torch.empty(shape, dtype=_H, device=dev)
+
+
+def grid_forward(d, x, grid, want_dydx=False):
+    n, W = x.shape[0], 2 * d.n_levels
+    enc = _half((n, W), x.device)
+    dydx = torch.empty((n, W, 3), dtype=torch.float32, device=x.device) if want_dydx else None
+    L.check(L.lib().neus2b_grid_forward(C.byref(d), u32(n), L.ptr(x), u32(x.shape[1]), L.ptr(grid), L.ptr(enc), L.ptr(dydx),
+                                        L.cur_stream()))
+    return (enc, dydx) if want_dydx else enc
+
+
+def grid_backward_input(d, x, grid, dL_denc):
+    out = torch.empty((x.shape[0], 3), dtype=torch.float32, device=x.device)
+    L.check(L.lib().neus2b_grid_backward_input(C.byref(d), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]), L.ptr(grid),
+                                               L.ptr(dL_denc), L.ptr(out), L.cur_stream()))
+    return out
+
+
+def grid_backward_params(d, x, dL_denc, grad, mode=L.GRAD_ACCUMULATE):
+    L.check(L.lib().neus2b_grid_backward_params(C.byref(d), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]), L.ptr(dL_denc),
+                                                L.ptr(grad), C.c_int(mode), L.cur_stream()))
+    return grad
+
+
+def grid_backward_backward_input(d, x, grid, v, g_e, grad, mode=L.GRAD_ACCUMULATE):
+    dy = _half((x.shape[0], 2 * d.n_levels), x.device)
+    L.check(L.lib().neus2b_grid_backward_backward_input(C.byref(d), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]), L.ptr(grid),
+                                                        L.ptr(v), L.ptr(g_e), L.ptr(dy), L.ptr(grad), C.c_int(mode),
+                                                        L.cur_stream()))
+    return dy
+
+
+def mlp_forward(in_w, n_hidden, w, inp):
+    n = inp.shape[0]
+    out = _half((n, 16), inp.device)
+    hidden = _half((n, n_hidden, 64), inp.device)
+    L.check(L.lib().neus2b_mlp_forward(u32(n), u32(in_w), u32(n_hidden), L.ptr(w), L.ptr(inp), L.ptr(out), L.ptr(hidden),
+                                       L.cur_stream()))
+    return out, hidden
+
+
+def mlp_backward(in_w, n_hidden, w, inp, hidden, dL_dout, wgrad=None, mode=L.GRAD_OVERWRITE, want_din=True):
+    n = inp.shape[0]
+    din = _half((n, in_w), inp.device) if want_din else None
+    if wgrad is None and mode != L.GRAD_IGNORE:
+        wgrad = torch.zeros(64 * in_w + (n_hidden - 1) * 4096 + 1024, dtype=torch.float32, device=inp.device)
+    L.check(L.lib().neus2b_mlp_backward(u32(n), u32(in_w), u32(n_hidden), L.ptr(w), L.ptr(inp), L.ptr(hidden), L.ptr(dL_dout),
+                                        L.ptr(din), L.ptr(wgrad), C.c_int(mode), L.cur_stream()))
+    return din, wgrad
+
+
+def mlp_backward_backward_input(in_w, w, hidden, u, dy, wgrad=None, mode=L.GRAD_OVERWRITE):
+    if wgrad is None:
+        wgrad = torch.zeros(64 * in_w + 1024, dtype=torch.float32, device=u.device)
+    L.check(L.lib().neus2b_mlp_backward_backward_input(u32(u.shape[0]), u32(in_w), L.ptr(w), L.ptr(hidden), L.ptr(u), L.ptr(dy),
+                                                       L.ptr(wgrad), C.c_int(mode), L.cur_stream()))
+    return wgrad
+
+
+def sh4(dir01):
+    out = _half((dir01.shape[0], 16), dir01.device)
+    L.check(L.lib().neus2b_sh4_forward(u32(dir01.shape[0]), L.ptr(dir01), u32(dir01.shape[1]), L.ptr(out), L.cur_stream()))
+    return out
+
+
+def neus_forward(d, params, coords, sdf_bias=-0.1, n_dev=None, out=None):
+    n = coords.shape[0]
+    if out is None:
+        out = _half((n, 16), coords.device)
+    L.check(L.lib().neus2b_neus_forward(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(n), L.ptr(n_dev), L.ptr(coords),
+                                        L.ptr(out), L.cur_stream()))
+    return out
+
+
+def neus_train(d, params, coords, dL_dout, indeed_batch_size, grad_mlp, grad_grid, grad_var):
+    L.check(L.lib().neus2b_neus_train(C.byref(d), L.ptr(params), u32(coords.shape[0]), L.ptr(coords), L.ptr(dL_dout),
+                                      u32(indeed_batch_size), L.ptr(grad_mlp), L.ptr(grad_grid), L.ptr(grad_var), L.cur_stream()))
+
+
+def neus_sdf(d, params, x, sdf_bias=-0.1):
+    out = _half((x.shape[0],), x.device)
+    L.check(L.lib().neus2b_neus_sdf(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]),
+                                    L.ptr(out), L.cur_stream()))
+    return out
+
+
+class RayBatch:
+    """Device scratch of one ray batch (neus2b_ray_workspace) plus the dataset handle."""
+
+    def __init__(self, max_rays, max_samples, device="cuda"):
+        self.max_rays, self.max_samples = max_rays, max_samples
+        i32, f32 = torch.int32, torch.float32
+        self.ray_indices = torch.zeros(max_rays, dtype=i32, device=device)
+        self.rays = torch.zeros((max_rays, 6), dtype=f32, device=device)
+        self.numsteps = torch.zeros((max_rays, 2), dtype=i32, device=device)
+        self.coords = torch.zeros((max_samples, 7), dtype=f32, device=device)
+        self.counters = torch.zeros(8, dtype=i32, device=device)
+        self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
+        self.ray_tmp = torch.zeros((max_rays, 8), dtype=f32, device=device)
+        self.ws = L.RayWorkspace(max_rays, max_samples, L.ptr(self.ray_indices), L.ptr(self.rays), L.ptr(self.numsteps),
+                                 L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp))
+
+
+def make_dataset(pixels, xforms, focal, principal):
+    """pixels int32/uint8x4 [n][H][W] (RGBA8 packed), xforms [n][12], focal/principal [n][2], all CUDA tensors."""
+    ds = L.Dataset(pixels.shape[0], pixels.shape[2], pixels.shape[1], L.ptr(pixels), L.ptr(xforms), L.ptr(focal), L.ptr(principal))
+    ds._keep = (pixels, xforms, focal, principal)
+    return ds
+
+
+def generate_samples(ds, cfg, n_rays, n_rays_total, rng, bitfield, batch, n_rays_dev=None):
+    L.check(L.lib().neus2b_generate_samples(C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total), rng,
+                                            L.ptr(bitfield), C.byref(batch.ws), L.cur_stream()))
+
+
+def compute_loss(ds, cfg, n_rays, n_rays_total, rng, max_compacted, mlp_out, batch, coords_out, dloss, loss=None, ek_loss=None,
+                 rollover=True, n_rays_dev=None):
+    L.check(L.lib().neus2b_compute_loss(C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total), rng,
+                                        u32(max_compacted), L.ptr(mlp_out), C.byref(batch.ws), L.ptr(coords_out), L.ptr(dloss),
+                                        L.ptr(loss), L.ptr(ek_loss), C.c_int(int(rollover)), L.cur_stream()))
+
+
+class OccupancyGrid:
+    def __init__(self, n_cascades=1, max_samples=128 ** 3, device="cuda"):
+        cells = 128 ** 3
+        self.n_cascades = n_cascades
+        self.grid = torch.zeros(cells * n_cascades, dtype=torch.float32, device=device)
+        self.grid_tmp = torch.zeros_like(self.grid)
+        self.bitfield = torch.zeros(cells, dtype=torch.uint8, device=device)
+        self.mean = torch.zeros(1, dtype=torch.float32, device=device)
+        self.pos = torch.zeros((max_samples, 3), dtype=torch.float32, device=device)
+        self.idx = torch.zeros(max_samples, dtype=torch.int32, device=device)
+        self.sdf = torch.zeros(max_samples, dtype=_H, device=device)
+        self.partial = torch.zeros(1024, dtype=torch.float64, device=device)
+        self.ema_step = 0
+
+    def update(self, d, params, n_uniform, n_nonuniform, rng_u, rng_nu, decay=0.95, sdf_bias=-0.1):
+        L.check(L.lib().neus2b_occupancy_update(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(self.n_cascades),
+                                                u32(n_uniform), u32(n_nonuniform), rng_u, rng_nu, u32(self.ema_step),
+                                                C.c_float(decay), L.ptr(self.grid), L.ptr(self.grid_tmp), L.ptr(self.bitfield),
+                                                L.ptr(self.mean), L.ptr(self.pos), L.ptr(self.idx), L.ptr(self.sdf),
+                                                L.ptr(self.partial), L.cur_stream()))
+        self.ema_step += 1
+
+
+def adam_step(cfg, grad_mlp, grad_grid, grad_var, master, m, v, params, params_ema=None, ema_master=None):
+    L.check(L.lib().neus2b_adam_step(C.byref(cfg), C.c_uint64(master.numel()), L.ptr(grad_mlp), L.ptr(grad_grid), L.ptr(grad_var),
+                                     L.ptr(master), L.ptr(m), L.ptr(v), L.ptr(params), L.ptr(params_ema), L.ptr(ema_master),
+                                     L.cur_stream()))

@@ -1,0 +1,127 @@
+"""Seeded synthetic scenes in the reference's data convention (RGBA8 images with the mask in alpha, 3x4 camera-to-world
+matrices already in the unit-cube frame the testbed trains in, pinhole intrinsics in pixels).
+
+They stand in for the DTU-style captures the reference is run on: an analytic sphere (radius 0.3, centred in the unit
+cube) with a 3-octave value-noise albedo, Lambert + ambient shading, cameras on a Fibonacci sphere looking at the
+centre.  Everything is generated with torch so it can be made directly on the GPU for benchmarks or on the CPU for the
+oracle tests; it is input preparation, not part of the timed path."""
+import math
+
+import numpy as np
+import torch
+
+
+def fibonacci_cameras(n_views, radius=2.5, center=(0.5, 0.5, 0.5)):
+    """[n][12] column-major 3x4 camera-to-world matrices: columns right, down, forward, origin."""
+    out = np.zeros((n_views, 12), np.float32)
+    golden = math.pi * (3.0 - math.sqrt(5.0))
+    c = np.asarray(center, np.float64)
+    for i in range(n_views):
+        z = 1.0 - 2.0 * (i + 0.5) / n_views
+        r = math.sqrt(max(0.0, 1.0 - z * z))
+        th = golden * i
+        n = np.array([r * math.cos(th), r * math.sin(th), z])
+        origin = c + radius * n
+        fwd = -n
+        up = np.array([0.0, 0.0, 1.0]) if abs(n[2]) < 0.99 else np.array([0.0, 1.0, 0.0])
+        right = np.cross(fwd, up)
+        right /= np.linalg.norm(right)
+        down = np.cross(fwd, right)
+        out[i, 0:3], out[i, 3:6], out[i, 6:9], out[i, 9:12] = right, down, fwd, origin
+    return out
+
+
+def _value_noise(p, seed, octaves=3, base_freq=4.0):
+    """3-channel value noise in [0,1]: trilinear interpolation of a seeded random lattice, summed over octaves."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    out = torch.zeros(p.shape[0], 3, device=p.device)
+    amp_sum = 0.0
+    for o in range(octaves):
+        freq, amp = base_freq * (2 ** o), 0.5 ** o
+        res = int(freq) + 2
+        table = torch.rand((res, res, res, 3), generator=g).to(p.device)
+        q = p * freq
+        q0 = torch.floor(q)
+        f = q - q0
+        i0 = q0.long().clamp(0, res - 2)
+        acc = 0
+        for k in range(8):
+            b = [(k >> e) & 1 for e in range(3)]
+            w = 1.0
+            for e in range(3):
+                w = w * (f[:, e] if b[e] else 1.0 - f[:, e])
+            acc = acc + w[:, None] * table[i0[:, 0] + b[0], i0[:, 1] + b[1], i0[:, 2] + b[2]]
+        out += amp * acc
+        amp_sum += amp
+    return out / amp_sum
+
+
+def _linear_to_srgb(x):
+    return torch.where(x < 0.0031308, 12.92 * x, 1.055 * x.clamp_min(1e-8) ** (1 / 2.4) - 0.055)
+
+
+def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=0.3, seed=0, device="cpu", cam_radius=2.5):
+    """Returns dict(pixels int32 [n][H][W] (RGBA8, R low byte), xforms [n][12], focal [n][2], principal [n][2])."""
+    xforms = torch.from_numpy(fibonacci_cameras(n_views, cam_radius)).to(device)
+    focal_px = 0.5 * width / math.tan(0.5 * math.radians(fov_deg))
+    focal = torch.full((n_views, 2), focal_px, dtype=torch.float32, device=device)
+    principal = torch.full((n_views, 2), 0.5, dtype=torch.float32, device=device)
+    ys, xs = torch.meshgrid(torch.arange(height, device=device), torch.arange(width, device=device), indexing="ij")
+    u = ((xs.float() + 0.5) / width).reshape(-1)
+    v = ((ys.float() + 0.5) / height).reshape(-1)
+    dl = torch.stack([(u - 0.5) * width / focal_px, (v - 0.5) * height / focal_px, torch.ones_like(u)], 1)
+    center = torch.tensor([0.5, 0.5, 0.5], device=device)
+    light = torch.tensor([0.4, -0.5, 0.77], device=device)
+    light = light / light.norm()
+    pixels = torch.zeros((n_views, height, width), dtype=torch.int32, device=device)
+    for i in range(n_views):
+        X = xforms[i]
+        R = torch.stack([X[0:3], X[3:6], X[6:9]], 1)  # columns
+        o = X[9:12]
+        d = dl @ R.T
+        d = d / d.norm(dim=1, keepdim=True)
+        oc = o - center
+        b = (d * oc).sum(1)
+        disc = b * b - (oc @ oc - radius * radius)
+        hit = disc > 0
+        t = -b - torch.sqrt(disc.clamp_min(0))
+        p = o + t[:, None] * d
+        nrm = (p - center) / radius
+        albedo = 0.15 + 0.8 * _value_noise(p.clamp(0, 1), seed)
+        shade = 0.3 + 0.7 * (nrm @ light).clamp_min(0)
+        col = _linear_to_srgb((albedo * shade[:, None]).clamp(0, 1))
+        rgb8 = (col * 255.0 + 0.5).clamp(0, 255).to(torch.int64)
+        rgb8 = torch.where(hit[:, None], rgb8, torch.zeros_like(rgb8))
+        a8 = torch.where(hit, 255, 0).to(torch.int64)
+        packed = rgb8[:, 0] | (rgb8[:, 1] << 8) | (rgb8[:, 2] << 16) | (a8 << 24)
+        packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed)  # keep the bit pattern in int32
+        pixels[i] = packed.to(torch.int32).reshape(height, width)
+    return dict(pixels=pixels, xforms=xforms, focal=focal, principal=principal, width=width, height=height)
+
+
+def geometric_init_sdf_weights(seed=7, in_width=48, bias_radius=None):
+    """Sphere-like initialisation of the one-hidden-layer SDF net (the role utils/mlp_weights.txt plays in the
+    reference, nerf_network.h:774-823): first layer ~ N(0, sqrt(2)/sqrt(64)) on the xyz columns only, last layer
+    rows = sqrt(pi)/sqrt(64).  Returns float32 [64*in_width + 16*64], row-major [out][in]."""
+    rng = np.random.default_rng(seed)
+    W1 = np.zeros((64, in_width), np.float32)
+    W1[:, :3] = rng.normal(0.0, math.sqrt(2.0) / math.sqrt(64.0), (64, 3))
+    W2 = np.full((16, 64), math.sqrt(math.pi) / math.sqrt(64.0), np.float32)
+    return np.concatenate([W1.ravel(), W2.ravel()])
+
+
+def init_params(grid_n_params, seed=1337, variance=0.3):
+    """fp32 master parameters of the whole block: SDF net geometric init, colour net Xavier-uniform, grid U(-1e-4,1e-4)
+    (takikawa_encoding.cuh:454 shows the convention), variance 0.3 (nerf_network.h:872)."""
+    rng = np.random.default_rng(seed)
+    p = np.zeros(12288 + grid_n_params + 4, np.float32)
+    p[:4096] = geometric_init_sdf_weights(seed)
+    off = 4096
+    for (o, i) in ((64, 48), (64, 64), (16, 64)):
+        lim = math.sqrt(6.0 / (o + i))
+        p[off:off + o * i] = rng.uniform(-lim, lim, o * i)
+        off += o * i
+    p[12288:12288 + grid_n_params] = rng.uniform(-1e-4, 1e-4, grid_n_params)
+    p[12288 + grid_n_params:] = variance
+    return p
