@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""NeuS2 training-step benchmark on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): BASELINE config 1 -- static NeuS training on the seeded analytic sphere scene (64 RGBA views 512x512,
+Fibonacci-sphere cameras, fov 40 deg), hash grid 16 levels x 2 features, T=2^19, SDF MLP 48->64->16, colour MLP
+48->64->64->16, target batch 2^18 samples/step, 128^3 occupancy grid, eikonal weight 0.1, Adam lr 1e-2.  A step is one
+call of the reference's Testbed::train(batch): occupancy update when due, ray sampling, fused forward, loss + compaction,
+fused forward+backward, Adam(+EMA), batch re-tune.  Synthetic data, random-init (geometric-init) weights; the scene is
+pre-trained for `--pretrain` untimed steps so the occupancy grid and the rays-per-batch tuner are in steady state.
+
+`value` = training samples per second with everything resident in HBM (CUDA events on the library's stream, max over
+ranks).  `e2e` = the same through the host-facing call with host buffers every step (camera block H2D from pinned memory,
+counters + losses D2H, host sync).  `--impl reference` times the CPU oracle (OpenMP port of the same step) instead.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "neus_train_samples_per_s"
+UNIT = "samples/s"
+BATCH = 1 << 18
+
+
+def workload_config(n_gpus):
+    return {"workload": "BASELINE config 1: sphere scene 64x512x512 RGBA, hash grid L16 F2 T2^19, batch 2^18 samples/step, "
+                        "eikonal 0.1, Adam lr 1e-2", "global_batch": BATCH * n_gpus, "n_views": 64, "resolution": 512,
+            "parallelism": "dp%d (rays sharded, one gradient all-reduce per step)" % n_gpus if n_gpus > 1 else "single GPU",
+            "l2": "per-step working set (~0.6 GB: 25 MB grid + 25 MB gradients + 200 MB Adam state + sample buffers) exceeds the "
+                  "126 MB L2, no explicit flush"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.lines, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for nme, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nme)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def occupancy_updates_between(step0, n_steps):
+    """How many of the steps [step0, step0+n) run training_prep_nerf (src/testbed.cu:2659)."""
+    c = 0
+    for s in range(step0, step0 + n_steps):
+        skip = min(max(s // 16, 1), 16)
+        c += (s % skip == 0)
+    return c
+
+
+def make_scene(device):
+    from neus2_b200 import synthetic as S
+    return S.render_sphere_views(64, 512, 512, fov_deg=40.0, radius=0.3, seed=0, device=device)
+
+
+def cuda_view(ptr, nbytes):
+    """uint8 torch tensor over a raw device pointer (memory owned by libneus2b.so)."""
+    import torch
+
+    class _V:
+        pass
+    v = _V()
+    v.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+    return torch.as_tensor(v, device="cuda")
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from neus2_b200 import _lib as L
+    from neus2_b200 import ops
+    from neus2_b200 import synthetic as S
+    from neus2_b200.testbed import Testbed
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L.lib()
+
+    scene = make_scene("cuda")
+    tb = Testbed(batch_size=BATCH, world_size=world, rank=rank)
+    px = scene["pixels"].cpu().numpy()
+    cams = [scene[k].cpu().numpy() for k in ("xforms", "focal", "principal")]
+    tb.load_training_data(px, *cams)
+    ng = L.grid_n_params(tb.config.grid)
+    tb.set_params(S.init_params(ng, seed=1337))
+    ptrs = tb.device_ptrs()
+    stream = torch.cuda.ExternalStream(ptrs["stream"])
+    grads = None
+    if world > 1:
+        grads = [cuda_view(ptrs["grad_grid"], ng * 2).view(torch.float16), cuda_view(ptrs["grad_mlp"], 12288 * 4).view(torch.float32),
+                 cuda_view(ptrs["grad_variance"], 16).view(torch.float32)]
+
+    def step(read_stats=False):
+        if world == 1:
+            return tb.train(1, read_stats=read_stats)
+        tb.train_backward()
+        with torch.cuda.stream(stream):
+            for g in grads:
+                dist.all_reduce(g)
+        return tb.optimizer_step(read_stats=read_stats)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.pretrain):
+        step()
+    st = step(read_stats=True)
+    for _ in range(max(args.warmup - 1, 0)):
+        step()
+    # ---- device-resident timing
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_step = args.pretrain + max(args.warmup, 1)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    # ---- end to end through the host-facing call: camera block H2D + stats D2H + host sync every step
+    t_e2e0, t_e2e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_e2e0.record(stream)
+    for _ in range(args.steps):
+        tb.update_cameras(*cams)
+        st = step(read_stats=True)
+    t_e2e1.record(stream)
+    barrier()
+    ms_e2e = t_e2e0.elapsed_time(t_e2e1)
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+    ms_step = ms / args.steps
+    value = BATCH * world * args.steps / (ms * 1e-3)
+    e2e_value = BATCH * world * args.steps / (ms_e2e * 1e-3)
+    n_occ = occupancy_updates_between(first_step, args.steps)
+    launches = args.steps * 12 + n_occ * 16
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(sum(c.nbytes for c in cams)), "d2h_bytes_per_step": 32},
+            "gpu_launches": launches, "clocks": clocks,
+            "train_state": {"training_step": int(st.training_step), "rays_per_batch": int(st.rays_per_batch),
+                            "samples_before_compaction": int(st.measured_batch_size_before_compaction),
+                            "samples_after_compaction": int(st.measured_batch_size), "loss": float(st.loss),
+                            "ek_loss": float(st.ek_loss), "overflow": int(st.overflow)}}
+
+    if rank == 0:
+        # ---- roofline of the dominant kernel (fused forward+backward over the 2^18 compacted samples), timed alone
+        line["roofline"] = roofline_train_kernel(tb, ptrs, st, ng)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(tb, sample=args.cpu_sample)
+        print(json.dumps(line), flush=True)
+    barrier()
+    tb.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def roofline_train_kernel(tb, ptrs, st, ng):
+    """CUDA-event time of neus2b_neus_train on a 2^18-sample batch drawn around the trained surface, with the testbed's
+    current parameters.  Algorithmic bytes per sample: 28 (coordinate) + 32 (output gradient) + 512 (one gather pass
+    over 16 levels x 8 corners x 4 B) + 512 (one merged scatter pass) = 1084 B."""
+    import torch
+    from neus2_b200 import ops
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak, src = 6650.0, "fallback"
+    if os.path.exists(peaks_path):
+        try:
+            peak, src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+        except (KeyError, ValueError, OSError):
+            pass
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    n = BATCH
+    # samples in a shell around the r=0.3 sphere, ordered along rays like a real batch (consecutive samples 1.7e-3 apart)
+    rays = n // 64
+    o = torch.randn(rays, 3, device="cuda", generator=g)
+    o = 0.5 + 0.3 * o / o.norm(dim=1, keepdim=True)
+    d = torch.randn(rays, 3, device="cuda", generator=g)
+    d = d / d.norm(dim=1, keepdim=True)
+    t = (torch.arange(64, device="cuda") - 32) * (math.sqrt(3) / 1024)
+    pos = (o[:, None, :] + t[None, :, None] * d[:, None, :]).reshape(-1, 3).clamp(0.0, 1.0)
+    coords = torch.zeros(n, 7, device="cuda")
+    coords[:, :3] = pos
+    coords[:, 4:] = ((d + 1) * 0.5)[:, None, :].expand(rays, 64, 3).reshape(-1, 3)
+    dl = (torch.randn(n, 16, device="cuda", generator=g) * 1e-2).half()
+    params = cuda_view(ptrs["params"], (12288 + ng + 4) * 2).view(torch.float16)
+    gm = torch.zeros(12288, device="cuda")
+    gg = torch.zeros(ng, dtype=torch.float16, device="cuda")
+    gv = torch.zeros(4, device="cuda")
+    desc = tb.config.grid
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for it in range(8):
+        flush.zero_()  # write a buffer larger than L2 between timed launches
+        torch.cuda.synchronize()
+        e0.record()
+        ops.neus_train(desc, params, coords, dl, n, gm, gg, gv)
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+    ms = sum(times) / len(times)
+    bytes_per_sample = 28 + 32 + 512 + 512
+    achieved = bytes_per_sample * n / (ms * 1e-3) / 1e9
+    return {"kernel": "neus_kernel<MODE_TRAIN> (fused forward+backward, 2^18 samples)", "bound": "hbm", "achieved": achieved,
+            "peak": peak, "peak_source": src + " (MEASURED_PEAKS.json hbm_gbs)" if src == "measured" else "fallback 6.65 TB/s",
+            "unit": "GB/s", "frac": achieved / peak, "traffic": None, "ms_per_launch": ms,
+            "algorithmic_bytes_per_sample": bytes_per_sample, "flop_per_sample": 96256,
+            "achieved_tflops": 96256 * n / (ms * 1e-3) / 1e12}
+
+
+def run_kernel_only(args):
+    """Small stand-alone case of one fused kernel for profiler captures:
+    `ncu ... python bench.py --kernel train --kernel-n 131072 --kernel-iters 3`."""
+    import numpy as np
+    import torch
+    from neus2_b200 import _lib as L
+    from neus2_b200 import ops
+    from neus2_b200 import synthetic as S
+    torch.cuda.set_device(0)
+    desc = L.grid_desc()
+    ng = L.grid_n_params(desc)
+    p = S.init_params(ng, seed=1337)
+    rng = np.random.default_rng(9)
+    p[12288:12288 + ng] = rng.uniform(-1e-2, 1e-2, ng)
+    p[:3072].reshape(64, 48)[:, 3:35] = rng.normal(0, 0.05, (64, 32))
+    params = torch.from_numpy(p).cuda().half()
+    n = args.kernel_n
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    rays = max(n // 64, 1)
+    o = torch.randn(rays, 3, device="cuda", generator=g)
+    o = 0.5 + 0.3 * o / o.norm(dim=1, keepdim=True)
+    d = torch.randn(rays, 3, device="cuda", generator=g)
+    d = d / d.norm(dim=1, keepdim=True)
+    t = (torch.arange(64, device="cuda") - 32) * (math.sqrt(3) / 1024)
+    pos = (o[:, None, :] + t[None, :, None] * d[:, None, :]).reshape(-1, 3).clamp(0.0, 1.0)[:n]
+    n = pos.shape[0]
+    coords = torch.zeros(n, 7, device="cuda")
+    coords[:, :3] = pos
+    coords[:, 4:] = ((d + 1) * 0.5)[:, None, :].expand(rays, 64, 3).reshape(-1, 3)[:n]
+    dl = (torch.randn(n, 16, device="cuda", generator=g) * 1e-2).half()
+    gm = torch.zeros(12288, device="cuda")
+    gg = torch.zeros(ng, dtype=torch.float16, device="cuda")
+    gv = torch.zeros(4, device="cuda")
+    out = torch.zeros(n, 16, dtype=torch.float16, device="cuda")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for it in range(args.kernel_iters):
+        torch.cuda.synchronize()
+        e0.record()
+        if args.kernel == "train":
+            ops.neus_train(desc, params, coords, dl, n, gm, gg, gv)
+        else:
+            ops.neus_forward(desc, params, coords, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    print(json.dumps({"kernel": args.kernel, "n": n, "ms": times}))
+
+
+def cpu_baseline(tb, sample=1 << 16):
+    """The CPU oracle (OpenMP port of the same step) on a bounded sample of the workload: fused forward on 2x sample
+    pre-compaction samples, forward+backward on `sample` compacted samples, Adam over all parameters; scaled to
+    samples/s.  Reported beside the GPU number, not a target."""
+    import numpy as np
+    from oracle import oracle as O
+    cores = os.cpu_count() or 1
+    d = O.grid_desc()
+    p32 = tb.get_params()
+    params = O.f16_bits(p32)
+    rng = np.random.default_rng(3)
+    n = sample
+    dirs = rng.normal(size=(n, 3))
+    dirs /= np.linalg.norm(dirs, axis=1, keepdims=True)
+    coords = np.zeros((n, 7), np.float32)
+    coords[:, :3] = np.clip(0.5 + dirs * (0.3 + rng.normal(0, 0.02, (n, 1))), 0, 1)
+    coords[:, 4:] = rng.random((n, 3))
+    g = O.f16_bits(rng.normal(0, 1e-2, (n, 16)))
+    t0 = time.time()
+    O.neus_forward(d, params, np.concatenate([coords, coords]))       # pre-compaction pass (N_pre ~ 2 N)
+    grad = O.neus_backward(d, params, coords, g, indeed_batch_size=n)  # forward + backward on the compacted batch
+    m, v = np.zeros_like(p32), np.zeros_like(p32)
+    pe, em = np.zeros(p32.size, np.uint16), p32.copy()
+    cfg = O.AdamCfg(1e-2, 0.9, 0.99, 1e-15, 1e-6, 0.95, 128.0, 1, 12288)
+    O.adam_step(cfg, grad.astype(np.float32), p32, m, v, params, pe, em)
+    dt = time.time() - t0
+    return {"value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "%d compacted samples (+2x pre-compaction forward, Adam over all 12.6 M parameters), %.2f s" % (n, dt)}
+
+
+def run_reference(args):
+    """Reference arm: the reference has no CPU path and its CUDA build needs the un-vendored tiny-cuda-nn fork, so the
+    timed thing is the CPU oracle (OpenMP port of the same step) on all host cores, on a bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    from neus2_b200 import synthetic as S
+    cores = os.cpu_count() or 1
+    d = O.grid_desc()
+    ng = O.grid_n_params(d)
+    p32 = S.init_params(ng, seed=1337)
+    params = O.f16_bits(p32)
+    rng = np.random.default_rng(3)
+
+    def make_batch(n):
+        dirs = rng.normal(size=(n, 3))
+        dirs /= np.linalg.norm(dirs, axis=1, keepdims=True)
+        c = np.zeros((n, 7), np.float32)
+        c[:, :3] = np.clip(0.5 + dirs * (0.3 + rng.normal(0, 0.02, (n, 1))), 0, 1)
+        c[:, 4:] = rng.random((n, 3))
+        return c, O.f16_bits(rng.normal(0, 1e-2, (n, 16)))
+
+    m, v = np.zeros_like(p32), np.zeros_like(p32)
+    pe, em = np.zeros(p32.size, np.uint16), p32.copy()
+    # size the per-step sample so that the K + W steps end within ~2.5 minutes
+    coords, g = make_batch(2048)
+    t0 = time.time()
+    O.neus_forward(d, params, np.concatenate([coords, coords]))
+    O.neus_backward(d, params, coords, g, indeed_batch_size=2048)
+    rate = 2048 / max(time.time() - t0, 1e-3)
+    n = int(min(max(rate * 150.0 / (args.steps + args.warmup), 512), min(args.cpu_sample * 4, BATCH))) // 128 * 128
+    coords, g = make_batch(n)
+
+    def step(k):
+        O.neus_forward(d, params, np.concatenate([coords, coords]))
+        grad = O.neus_backward(d, params, coords, g, indeed_batch_size=n)
+        cfg = O.AdamCfg(1e-2, 0.9, 0.99, 1e-15, 1e-6, 0.95, 128.0, k + 1, 12288)
+        O.adam_step(cfg, grad.astype(np.float32), p32, m, v, params, pe, em)
+
+    for k in range(args.warmup):
+        step(k)
+    t0 = time.time()
+    for k in range(args.steps):
+        step(args.warmup + k)
+    dt = time.time() - t0
+    value = n * args.steps / dt
+    sample = "%d compacted samples per step (+2x pre-compaction forward, Adam over all parameters) of the 2^18-sample step" % n
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 * (BATCH / n), "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "fp16 storage, fp32 math (CPU)", "data": "synthetic",
+                      "config": workload_config(world),
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "note": "the reference's own CUDA build needs the un-vendored tiny-cuda-nn fork (empty submodule) and it has "
+                              "no CPU path: this arm times the CPU oracle port"}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--pretrain", type=int, default=500)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample", type=int, default=1 << 16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel-n", type=int, default=1 << 17)
+    ap.add_argument("--kernel-iters", type=int, default=3)
+    args = ap.parse_args()
+    if args.kernel:
+        run_kernel_only(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

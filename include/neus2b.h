@@ -143,6 +143,9 @@ typedef struct {
 	float background_color[3];
 	float loss_scale; /* LOSS_SCALE, include/neural-graphics-primitives/testbed.h:237 */
 	float mask_loss_weight, ek_loss_weight, cos_anneal_ratio;
+	/* data-parallel ray sharding: this process draws rays [ray_index_offset, ray_index_offset + n_rays) of a logical
+	 * batch that is ray_count_scale times larger (loss normalisation uses n_rays * ray_count_scale); 0 / 1 = single GPU */
+	uint32_t ray_index_offset, ray_count_scale;
 } neus2b_train_cfg;
 
 /* Scratch for one batch of rays; every array is caller-allocated device memory. */
@@ -155,6 +158,7 @@ typedef struct {
 	uint32_t* d_counters;    /* [8]: 0 kept rays, 1 samples, 2 compacted samples (unclipped), 3 overflow flag */
 	uint64_t* d_scan_tmp;    /* [max_rays + 1024] */
 	float* d_ray_tmp;        /* [max_rays][8] */
+	const uint32_t* d_n_rays_total; /* optional: overrides the n_rays_total argument with a device value */
 } neus2b_ray_workspace;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is
@@ -193,6 +197,72 @@ typedef struct {
 int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid, float* d_grad_variance,
                      float* d_master, float* d_m, float* d_v, uint16_t* d_params, uint16_t* d_params_ema, float* d_ema_master,
                      neus2b_stream_t stream);
+
+/* ---------------------------------------------------------------- training loop (Testbed, src/testbed.cu / src/testbed_nerf.cu) */
+
+/* The subset of configs/nerf/base.json + Testbed members that the NeuS training step reads. */
+typedef struct {
+	neus2b_grid_desc grid;         /* "encoding" */
+	float sdf_bias;                /* "network.sdf_bias" (nerf_network.h:74) */
+	uint32_t batch_size;           /* hyperparams.batch_size, default 1<<18 (src/testbed.cu:2110) */
+	uint32_t n_cascades;           /* max_cascade + 1; 1 when aabb_scale == 1 (src/testbed_nerf.cu:3084) */
+	uint32_t seed;                 /* Testbed::m_seed = 1337 (testbed.h:515) */
+	float learning_rate, beta1, beta2, epsilon, l2_reg; /* "optimizer" Adam (configs/nerf/dtu.json:14-19) */
+	float ema_decay;               /* Ema decay 0.95 */
+	uint32_t lr_decay_start, lr_decay_interval; /* ExponentialDecay 20000 / 10000 */
+	float lr_decay_base;           /* 0.33 */
+	float ek_loss_weight, mask_loss_weight; /* hyperparams (src/testbed.cu:2125-2126) */
+	uint32_t anneal_end;           /* hyperparams.anneal_end (nerf_network.h:1109-1118) */
+	float density_grid_decay;      /* 0.95 (testbed.h:635) */
+	uint32_t random_bg_color, snap_to_pixel_centers;
+	/* progressive level mask: n_active = min(L, start + per_increment * (step / steps_per_increment)); 0 steps = off */
+	uint32_t progressive_start_levels, progressive_levels_per_increment, progressive_steps_per_increment;
+	uint32_t world_size, rank;     /* ray sharding for data-parallel training (one process per GPU) */
+} neus2b_testbed_config;
+
+typedef struct {
+	uint32_t training_step;
+	uint32_t rays_per_batch;                       /* Counters::rays_per_batch after the step's re-tune */
+	uint32_t n_rays_kept;
+	uint32_t measured_batch_size_before_compaction;
+	uint32_t measured_batch_size;
+	uint32_t overflow;
+	float loss, ek_loss;                           /* Testbed.loss / ek_loss (python_api.cu:447-449) */
+} neus2b_train_stats;
+
+typedef struct neus2b_testbed neus2b_testbed;
+
+void neus2b_testbed_default_config(neus2b_testbed_config* cfg);
+/* Testbed(ETestbedMode::Nerf) + reset_network (src/testbed.cu:2074-2339): allocates parameters, optimizer state,
+ * occupancy grid and batch scratch on the current device; all later calls run on an internal stream. */
+int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_testbed** out);
+void neus2b_testbed_destroy(neus2b_testbed* tb);
+/* Testbed::load_training_data (src/testbed.cu:83): HOST arrays, copied to the device. */
+int neus2b_testbed_load_training_data(neus2b_testbed* tb, uint32_t n_images, uint32_t width, uint32_t height,
+                                      const uint32_t* h_pixels, const float* h_xforms, const float* h_focal,
+                                      const float* h_principal);
+/* Re-upload the camera block only (NerfDataset::update_transforms). */
+int neus2b_testbed_update_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal);
+/* Trainer::set_params_full_precision (src/testbed.cu:2335) / params_full_precision(): HOST fp32 arrays. */
+int neus2b_testbed_set_params(neus2b_testbed* tb, const float* h_params, uint64_t n);
+int neus2b_testbed_get_params(neus2b_testbed* tb, float* h_params, uint64_t n, int ema);
+int neus2b_testbed_n_params(const neus2b_testbed* tb, uint64_t* n);
+/* Testbed::train(batch_size) x n_steps (src/testbed.cu:2630-2726): occupancy update when due, sample generation, fused
+ * forward, loss + compaction, fused forward+backward, optimizer step, batch re-tune -- enqueued without any host
+ * synchronisation.  If h_stats is non-NULL the stream is synchronised once at the end and the last step's counters
+ * and losses are copied back. */
+int neus2b_testbed_train(neus2b_testbed* tb, uint32_t n_steps, neus2b_train_stats* h_stats);
+/* Device views for tests and for the caller's own streams/collectives (valid until destroy). */
+int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_params, uint16_t** d_params_ema, float** d_master,
+                               float** d_grad_mlp, uint16_t** d_grad_grid, float** d_grad_variance, uint8_t** d_bitfield,
+                               float** d_density_grid, neus2b_stream_t* stream);
+/* Split one step for data-parallel training: backward leaves the local gradients in place, the caller all-reduces them
+ * (NCCL) on the returned stream, then optimizer_step applies Adam.  neus2b_testbed_train == both halves back to back. */
+int neus2b_testbed_train_backward(neus2b_testbed* tb);
+int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats);
+/* get_density_on_grid (src/testbed_nerf.cu:4082-4133): SDF on a res[0] x res[1] x res[2] lattice x/res (no half-voxel
+ * offset), z range [z0, z1), EMA parameters when use_ema.  d_out float[(z1-z0) * res[1] * res[0]] on the device. */
+int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3], uint32_t z0, uint32_t z1, int use_ema, float* d_out);
 
 #ifdef __cplusplus
 }

@@ -30,19 +30,36 @@ class TrainCfg(C.Structure):
     _fields_ = [("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
                 ("snap_to_pixel_centers", C.c_uint32), ("random_bg_color", C.c_uint32), ("background_color", C.c_float * 3),
                 ("loss_scale", C.c_float), ("mask_loss_weight", C.c_float), ("ek_loss_weight", C.c_float),
-                ("cos_anneal_ratio", C.c_float)]
+                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32)]
 
 
 class RayWorkspace(C.Structure):
     _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_indices", C.c_void_p), ("d_rays", C.c_void_p),
                 ("d_numsteps", C.c_void_p), ("d_coords", C.c_void_p), ("d_counters", C.c_void_p), ("d_scan_tmp", C.c_void_p),
-                ("d_ray_tmp", C.c_void_p)]
+                ("d_ray_tmp", C.c_void_p), ("d_n_rays_total", C.c_void_p)]
 
 
 class AdamCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
                 ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("loss_scale", C.c_float), ("step", C.c_uint32),
                 ("n_matrix", C.c_uint32)]
+
+
+class TestbedConfig(C.Structure):
+    _fields_ = [("grid", GridDesc), ("sdf_bias", C.c_float), ("batch_size", C.c_uint32), ("n_cascades", C.c_uint32),
+                ("seed", C.c_uint32), ("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+                ("epsilon", C.c_float), ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("lr_decay_start", C.c_uint32),
+                ("lr_decay_interval", C.c_uint32), ("lr_decay_base", C.c_float), ("ek_loss_weight", C.c_float),
+                ("mask_loss_weight", C.c_float), ("anneal_end", C.c_uint32), ("density_grid_decay", C.c_float),
+                ("random_bg_color", C.c_uint32), ("snap_to_pixel_centers", C.c_uint32),
+                ("progressive_start_levels", C.c_uint32), ("progressive_levels_per_increment", C.c_uint32),
+                ("progressive_steps_per_increment", C.c_uint32), ("world_size", C.c_uint32), ("rank", C.c_uint32)]
+
+
+class TrainStats(C.Structure):
+    _fields_ = [("training_step", C.c_uint32), ("rays_per_batch", C.c_uint32), ("n_rays_kept", C.c_uint32),
+                ("measured_batch_size_before_compaction", C.c_uint32), ("measured_batch_size", C.c_uint32),
+                ("overflow", C.c_uint32), ("loss", C.c_float), ("ek_loss", C.c_float)]
 
 
 class Neus2bError(RuntimeError):
@@ -58,6 +75,10 @@ EXPORTS = [
     "neus2b_mlp_forward", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
     "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_adam_step",
+    "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
+    "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
+    "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
+    "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid",
 ]
 
 
@@ -71,6 +92,9 @@ def lib():
         _lib.neus2b_error_string.restype = C.c_char_p
         _lib.neus2b_pcg32_seed.restype = None
         _lib.neus2b_pcg32_advance.restype = None
+        _lib.neus2b_testbed_default_config.restype = None
+        _lib.neus2b_testbed_destroy.restype = None
+        _lib.neus2b_testbed_destroy.argtypes = [C.c_void_p]
     return _lib
 
 
@@ -131,7 +155,8 @@ def pcg32_advance(r, delta):
 
 
 def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, snap_to_pixel_centers=False,
-              cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0)):
+              cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0), ray_index_offset=0,
+              ray_count_scale=1):
     c = TrainCfg()
     c.aabb_min[:] = [0.0, 0.0, 0.0]
     c.aabb_max[:] = [1.0, 1.0, 1.0]
@@ -143,4 +168,6 @@ def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, sn
     c.mask_loss_weight = mask_loss_weight
     c.ek_loss_weight = ek_loss_weight
     c.cos_anneal_ratio = cos_anneal_ratio
+    c.ray_index_offset = ray_index_offset
+    c.ray_count_scale = ray_count_scale
     return c

@@ -149,21 +149,25 @@ struct RayTmp {  // 8 floats per ray
 
 // First half of generate_training_samples_nerf_with_global_movement (:1287-1409): build the ray and count its steps.
 __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
-                                                          const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total, Pcg32 rng,
+                                                          const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
+                                                          const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng,
                                                           const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
                                                           uint64_t* __restrict__ scan_in) {
 	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	if (i >= n_rays_max) return;
 	if (i >= n_rays) {
 		scan_in[i] = 0;
+		tmp[i].numsteps = 0;
 		return;
 	}
 	RayTmp r;
 	r.numsteps = 0;
 	r.startt = 0.f;
-	const uint32_t img = image_idx(i, n_rays, n_rays_total, ds.n_images);
-	rng.advance((uint64_t)i * 8u);
+	const uint32_t ig = i + cfg.ray_index_offset;
+	const uint32_t img = image_idx(ig, n_rays, n_rays_total, ds.n_images);
+	rng.advance((uint64_t)ig * 8u);
 	float xy[2], rgba[4];
 	random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
 	read_rgba(ds, img, xy, rgba);
@@ -389,7 +393,8 @@ __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, ui
 
 // Target pixel, Huber loss, pass B (:1619-1952): loss gradient w.r.t. the 16 network outputs of every kept sample.
 __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
-                                                   const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total, Pcg32 rng0,
+                                                   const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
+                                                   const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
                                                    uint32_t max_compacted, uint32_t* __restrict__ counters,
                                                    const __half* __restrict__ mlp_out, const uint32_t* __restrict__ ray_indices,
                                                    uint32_t* __restrict__ numsteps, const float* __restrict__ coords,
@@ -397,6 +402,7 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
                                                    float* __restrict__ coords_out, __half* __restrict__ dloss_dout,
                                                    float* __restrict__ loss_out, float* __restrict__ ek_loss_out) {
 	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	if (i == 0) counters[2] = (uint32_t)scan[n_rays_max];
 	if (i >= n_rays_max) return;
 	if (i >= counters[0]) {
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 	if (ek_loss_out) ek_loss_out[i] = 0.f;
 	if (cn == 0) return;
 	// target colour (:1619-1667)
-	const uint32_t ray_idx = ray_indices[i];
+	const uint32_t ray_idx = ray_indices[i] + cfg.ray_index_offset;
 	Pcg32 rng = rng0;
 	rng.advance((uint64_t)ray_idx * 8u);
 	const uint32_t img = image_idx(ray_idx, n_rays, n_rays_total, ds.n_images);
@@ -461,8 +467,9 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 		const float sg = 1.0f / (1.0f + expf(-ws));
 		gws = (mask_gt - sg) * ws * cfg.mask_loss_weight;
 	}
-	if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / (float)n_rays;
-	const float loss_scale = cfg.loss_scale / (float)n_rays;
+	const float n_rays_f = (float)n_rays * (float)(cfg.ray_count_scale ? cfg.ray_count_scale : 1u);
+	if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
+	const float loss_scale = cfg.loss_scale / n_rays_f;
 	float dir[3];
 	float rgb2[3] = {0.f, 0.f, 0.f}, T = 1.f, ek = 0.f;
 	for (uint32_t j = 0; j < cn; ++j) {
@@ -535,7 +542,7 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 		dst[0] = reinterpret_cast<const uint4*>(gh)[0];
 		dst[1] = reinterpret_cast<const uint4*>(gh)[1];
 	}
-	if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * (float)n_rays);
+	if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * n_rays_f);
 }
 
 // fill_rollover / fill_rollover_and_rescale (call sites :3908-3916): pad [n_valid, n_target) with wrap-around copies
@@ -595,7 +602,7 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	if (n_rays == 0 || n_rays > ws->max_rays || ds->n_images == 0) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
-	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, r, d_bitfield,
+	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
 	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
@@ -620,7 +627,7 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	loss_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, r, max_compacted, ws->d_counters,
+	loss_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted, ws->d_counters,
 	                                                     (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
 	                                                     (const CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, d_coords_out,
 	                                                     (__half*)d_dloss_dout, d_loss, d_ek_loss);

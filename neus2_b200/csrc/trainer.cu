@@ -1,0 +1,492 @@
+// Host-side training loop: the part of the reference's Testbed that drives one NeuS training step
+// (Testbed::train src/testbed.cu:2630-2726, training_prep_nerf / train_nerf / train_nerf_step
+// src/testbed_nerf.cu:3434-3990), re-designed so that a step is a fixed sequence of asynchronous launches on one
+// stream with no host synchronisation: ray count, sample counts and the batch re-tune live in device memory.
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace n2b {
+
+struct TrainState {  // device resident, one per testbed
+	uint32_t rays_per_batch;
+	uint32_t n_rays_total;
+	uint32_t measured_pre, measured, n_kept, overflow;
+	float loss, ek_loss;
+};
+
+// Counters::update_after_training (src/testbed_nerf.cu:3406-3432) on the device.
+__global__ void tune_kernel(TrainState* st, const uint32_t* __restrict__ counters, uint32_t target, uint32_t max_rays) {
+	if (threadIdx.x != 0 || blockIdx.x != 0) return;
+	const uint32_t rays = st->rays_per_batch;
+	st->n_rays_total += rays;
+	st->measured_pre = counters[1];
+	st->measured = counters[2];
+	st->n_kept = counters[0];
+	st->overflow |= counters[3];
+	if (counters[1] == 0 || counters[2] == 0) return;  // the reference stops training here; keep the batch as it is
+	uint32_t next = (uint32_t)((float)rays * (float)target / (float)counters[2]);
+	next = (next + 127u) / 128u * 128u;
+	st->rays_per_batch = max(128u, min(next, max_rays));
+}
+
+// loss / ek_loss scalars: sum over the batch's rays, scaled by measured/target (:3423-3425); fixed-shape tree.
+__global__ void __launch_bounds__(1024) loss_reduce_kernel(TrainState* st, const float* __restrict__ loss, const float* __restrict__ ek,
+                                                           uint32_t target) {
+	__shared__ float sl[1024], se[1024];
+	const uint32_t n = st->n_kept;
+	float a = 0.f, b = 0.f;
+	for (uint32_t k = threadIdx.x; k < n; k += 1024) {
+		a += loss[k];
+		b += ek[k];
+	}
+	sl[threadIdx.x] = a;
+	se[threadIdx.x] = b;
+	__syncthreads();
+	for (int o = 512; o > 0; o >>= 1) {
+		if ((int)threadIdx.x < o) {
+			sl[threadIdx.x] += sl[threadIdx.x + o];
+			se[threadIdx.x] += se[threadIdx.x + o];
+		}
+		__syncthreads();
+	}
+	if (threadIdx.x == 0) {
+		const float s = (float)st->measured / (float)target;
+		st->loss = sl[0] * s;
+		st->ek_loss = se[0] * s;
+	}
+}
+
+__global__ void master_to_half_kernel(uint64_t n, const float* __restrict__ master, __half* __restrict__ p, __half* __restrict__ pe,
+                                      float* __restrict__ ema) {
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+		const float w = master[i];
+		p[i] = __float2half_rn(w);
+		pe[i] = __float2half_rn(w);
+		ema[i] = w;
+	}
+}
+
+// generate_grid_samples_nerf_uniform (src/testbed_nerf.cu:586-599): lattice positions x / res, unit aabb
+__global__ void sdf_grid_positions_kernel(uint32_t rx, uint32_t ry, uint64_t first, uint32_t n, float ix, float iy, float iz,
+                                          float* __restrict__ pos) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= n) return;
+	const uint64_t g = first + i;
+	const uint32_t x = (uint32_t)(g % rx), y = (uint32_t)((g / rx) % ry), z = (uint32_t)(g / ((uint64_t)rx * ry));
+	pos[(size_t)i * 3 + 0] = (float)x * ix;
+	pos[(size_t)i * 3 + 1] = (float)y * iy;
+	pos[(size_t)i * 3 + 2] = (float)z * iz;
+}
+// grid_samples_half_to_float (:682-698)
+__global__ void half_to_float_kernel(uint32_t n, const __half* __restrict__ src, float* __restrict__ dst) {
+	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i < n) dst[i] = __half2float(src[i]);
+}
+
+}  // namespace n2b
+
+using namespace n2b;
+
+struct neus2b_testbed {
+	neus2b_testbed_config cfg;
+	int device = 0;
+	cudaStream_t stream = nullptr;
+	uint64_t n_params = 0, n_grid = 0;
+	uint32_t max_rays = 1u << 18, max_samples = 0, target = 0;
+	uint32_t training_step = 0, ema_step = 0;
+	Pcg32 rng, density_rng;
+	// parameters / optimizer
+	__half *params = nullptr, *params_ema = nullptr, *grad_grid = nullptr;
+	float *master = nullptr, *ema_master = nullptr, *adam_m = nullptr, *adam_v = nullptr, *grad_mlp = nullptr, *grad_var = nullptr;
+	// occupancy
+	float *density_grid = nullptr, *density_tmp = nullptr, *density_mean = nullptr, *occ_pos = nullptr;
+	uint8_t* bitfield = nullptr;
+	uint32_t* occ_idx = nullptr;
+	__half* occ_sdf = nullptr;
+	double* occ_partial = nullptr;
+	// batch
+	neus2b_ray_workspace ws{};
+	__half *mlp_out = nullptr, *dloss = nullptr;
+	float *coords_compacted = nullptr, *loss = nullptr, *ek_loss = nullptr;
+	TrainState* state = nullptr;
+	TrainState* h_state = nullptr;  // pinned
+	// dataset
+	neus2b_dataset ds{};
+	float* h_cam = nullptr;  // pinned staging for the camera block
+	std::vector<void*> allocs;
+};
+
+template <typename T>
+static int dev_alloc(neus2b_testbed* tb, T** p, size_t n) {
+	void* q = nullptr;
+	cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+	if (e != cudaSuccess) return (int)e;
+	e = cudaMemsetAsync(q, 0, n * sizeof(T), tb->stream);
+	if (e != cudaSuccess) return (int)e;
+	tb->allocs.push_back(q);
+	*p = (T*)q;
+	return NEUS2B_OK;
+}
+#define TB_ALLOC(ptr, n)                        \
+	do {                                        \
+		int _rc = dev_alloc(tb, &(ptr), (n));   \
+		if (_rc) {                              \
+			neus2b_testbed_destroy(tb);         \
+			return _rc;                         \
+		}                                       \
+	} while (0)
+
+extern "C" void neus2b_testbed_default_config(neus2b_testbed_config* c) {
+	if (!c) return;
+	*c = neus2b_testbed_config{};
+	c->grid = neus2b_grid_desc{16, 19, 16, 1.447f, 16};
+	c->sdf_bias = -0.1f;
+	c->batch_size = 1u << 18;
+	c->n_cascades = 1;
+	c->seed = 1337;
+	c->learning_rate = 1e-2f;
+	c->beta1 = 0.9f;
+	c->beta2 = 0.99f;
+	c->epsilon = 1e-15f;
+	c->l2_reg = 1e-6f;
+	c->ema_decay = 0.95f;
+	c->lr_decay_start = 20000;
+	c->lr_decay_interval = 10000;
+	c->lr_decay_base = 0.33f;
+	c->ek_loss_weight = 0.1f;
+	c->mask_loss_weight = 0.f;
+	c->anneal_end = 0;
+	c->density_grid_decay = 0.95f;
+	c->random_bg_color = 1;
+	c->snap_to_pixel_centers = 0;
+	c->world_size = 1;
+	c->rank = 0;
+}
+
+extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
+	if (!tb) return;
+	if (tb->stream) cudaStreamSynchronize(tb->stream);
+	for (void* p : tb->allocs) cudaFree(p);
+	if (tb->h_state) cudaFreeHost(tb->h_state);
+	if (tb->h_cam) cudaFreeHost(tb->h_cam);
+	if (tb->stream) cudaStreamDestroy(tb->stream);
+	delete tb;
+}
+
+extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_testbed** out) {
+	if (!cfg || !out) return NEUS2B_E_INVALID;
+	GridLevels lv;
+	int rc = make_levels(&cfg->grid, &lv);
+	if (rc) return rc;
+	if (cfg->batch_size == 0 || cfg->batch_size % 128u || cfg->n_cascades == 0 || cfg->n_cascades > NEUS2B_CASCADES ||
+	    cfg->world_size == 0 || cfg->rank >= cfg->world_size)
+		return NEUS2B_E_INVALID;
+	int ndev = 0;
+	if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return NEUS2B_E_NO_DEVICE;
+	neus2b_testbed* tb = new (std::nothrow) neus2b_testbed();
+	if (!tb) return NEUS2B_E_INVALID;
+	tb->cfg = *cfg;
+	N2B_CHECK_CUDA(cudaGetDevice(&tb->device));
+	cudaError_t e = cudaStreamCreateWithFlags(&tb->stream, cudaStreamNonBlocking);
+	if (e != cudaSuccess) {
+		delete tb;
+		return (int)e;
+	}
+	tb->n_grid = (uint64_t)lv.offset[NEUS2B_MAX_LEVELS] * 2u;
+	tb->n_params = NEUS2B_MLP_N + tb->n_grid + 4u;
+	tb->target = cfg->batch_size;
+	tb->max_samples = cfg->batch_size * 16u;  // "somewhat of a worst case" (src/testbed_nerf.cu:3719)
+	// rng streams as in reset_network (src/testbed.cu:2077-2091)
+	neus2b_pcg32 r;
+	neus2b_pcg32_seed(&r, cfg->seed);
+	tb->rng = Pcg32{r.state, r.inc};
+	neus2b_pcg32 dr;
+	neus2b_pcg32_seed(&dr, tb->rng.next_uint());
+	tb->density_rng = Pcg32{dr.state, dr.inc};
+	(void)tb->rng.next_uint();  // tv_loss_rng
+
+	TB_ALLOC(tb->params, tb->n_params);
+	TB_ALLOC(tb->params_ema, tb->n_params);
+	TB_ALLOC(tb->grad_grid, tb->n_grid);
+	TB_ALLOC(tb->master, tb->n_params);
+	TB_ALLOC(tb->ema_master, tb->n_params);
+	TB_ALLOC(tb->adam_m, tb->n_params);
+	TB_ALLOC(tb->adam_v, tb->n_params);
+	TB_ALLOC(tb->grad_mlp, (size_t)NEUS2B_MLP_N);
+	TB_ALLOC(tb->grad_var, (size_t)4);
+	const size_t cells = (size_t)NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE;
+	const size_t n_occ = cells * cfg->n_cascades;
+	TB_ALLOC(tb->density_grid, n_occ);
+	TB_ALLOC(tb->density_tmp, n_occ);
+	TB_ALLOC(tb->density_mean, (size_t)1);
+	TB_ALLOC(tb->bitfield, cells / 8 * NEUS2B_CASCADES);
+	TB_ALLOC(tb->occ_pos, n_occ * 3);
+	TB_ALLOC(tb->occ_idx, n_occ);
+	TB_ALLOC(tb->occ_sdf, n_occ);
+	TB_ALLOC(tb->occ_partial, (size_t)1024);
+	tb->ws.max_rays = tb->max_rays;
+	tb->ws.max_samples = tb->max_samples;
+	TB_ALLOC(tb->ws.d_ray_indices, (size_t)tb->max_rays);
+	TB_ALLOC(tb->ws.d_rays, (size_t)tb->max_rays * 6);
+	TB_ALLOC(tb->ws.d_numsteps, (size_t)tb->max_rays * 2);
+	TB_ALLOC(tb->ws.d_coords, (size_t)tb->max_samples * 7);
+	TB_ALLOC(tb->ws.d_counters, (size_t)8);
+	TB_ALLOC(tb->ws.d_scan_tmp, (size_t)tb->max_rays + 1024);
+	TB_ALLOC(tb->ws.d_ray_tmp, (size_t)tb->max_rays * 8);
+	TB_ALLOC(tb->mlp_out, (size_t)tb->max_samples * 16);
+	TB_ALLOC(tb->dloss, (size_t)tb->target * 16);
+	TB_ALLOC(tb->coords_compacted, (size_t)tb->target * 7);
+	TB_ALLOC(tb->loss, (size_t)tb->max_rays);
+	TB_ALLOC(tb->ek_loss, (size_t)tb->max_rays);
+	TB_ALLOC(tb->state, (size_t)1);
+	tb->ws.d_n_rays_total = &tb->state->n_rays_total;
+	e = cudaMallocHost((void**)&tb->h_state, sizeof(TrainState));
+	if (e != cudaSuccess) {
+		neus2b_testbed_destroy(tb);
+		return (int)e;
+	}
+	TrainState init{};
+	init.rays_per_batch = 1u << 12;  // Counters::rays_per_batch (testbed.h)
+	*tb->h_state = init;
+	e = cudaMemcpyAsync(tb->state, tb->h_state, sizeof(TrainState), cudaMemcpyHostToDevice, tb->stream);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(tb->stream);
+	if (e != cudaSuccess) {
+		neus2b_testbed_destroy(tb);
+		return (int)e;
+	}
+	*out = tb;
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_n_params(const neus2b_testbed* tb, uint64_t* n) {
+	if (!tb || !n) return NEUS2B_E_INVALID;
+	*n = tb->n_params;
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_update_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal) {
+	if (!tb || !tb->ds.n_images || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
+	const uint32_t n = tb->ds.n_images;
+	memcpy(tb->h_cam, h_xforms, sizeof(float) * 12 * n);
+	memcpy(tb->h_cam + 12 * n, h_focal, sizeof(float) * 2 * n);
+	memcpy(tb->h_cam + 14 * n, h_principal, sizeof(float) * 2 * n);
+	// the three arrays are one allocation, in this order
+	N2B_CHECK_CUDA(cudaMemcpyAsync((void*)tb->ds.d_xforms, tb->h_cam, sizeof(float) * 16 * n, cudaMemcpyHostToDevice, tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_load_training_data(neus2b_testbed* tb, uint32_t n_images, uint32_t width, uint32_t height,
+                                                 const uint32_t* h_pixels, const float* h_xforms, const float* h_focal,
+                                                 const float* h_principal) {
+	if (!tb || !n_images || !width || !height || !h_pixels || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
+	if (tb->ds.n_images) return NEUS2B_E_UNSUPPORTED;  // one dataset per testbed
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	uint32_t* px = nullptr;
+	float* cam = nullptr;
+	const size_t npx = (size_t)n_images * width * height;
+	int rc = dev_alloc(tb, &px, npx);
+	if (rc) return rc;
+	rc = dev_alloc(tb, &cam, (size_t)16 * n_images);
+	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaMallocHost((void**)&tb->h_cam, sizeof(float) * 16 * n_images));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(px, h_pixels, npx * 4, cudaMemcpyHostToDevice, tb->stream));
+	tb->ds.n_images = n_images;
+	tb->ds.width = width;
+	tb->ds.height = height;
+	tb->ds.d_pixels = px;
+	tb->ds.d_xforms = cam;
+	tb->ds.d_focal = cam + (size_t)12 * n_images;
+	tb->ds.d_principal = cam + (size_t)14 * n_images;
+	rc = neus2b_testbed_update_cameras(tb, h_xforms, h_focal, h_principal);
+	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_set_params(neus2b_testbed* tb, const float* h_params, uint64_t n) {
+	if (!tb || !h_params || n != tb->n_params) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->master, h_params, n * sizeof(float), cudaMemcpyHostToDevice, tb->stream));
+	master_to_half_kernel<<<kSMs * 4, 256, 0, tb->stream>>>(n, tb->master, tb->params, tb->params_ema, tb->ema_master);
+	N2B_CHECK_LAUNCH();
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_get_params(neus2b_testbed* tb, float* h_params, uint64_t n, int ema) {
+	if (!tb || !h_params || n != tb->n_params) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaMemcpyAsync(h_params, ema ? tb->ema_master : tb->master, n * sizeof(float), cudaMemcpyDeviceToHost, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_params, uint16_t** d_params_ema, float** d_master,
+                                          float** d_grad_mlp, uint16_t** d_grad_grid, float** d_grad_variance, uint8_t** d_bitfield,
+                                          float** d_density_grid, neus2b_stream_t* stream) {
+	if (!tb) return NEUS2B_E_INVALID;
+	if (d_params) *d_params = (uint16_t*)tb->params;
+	if (d_params_ema) *d_params_ema = (uint16_t*)tb->params_ema;
+	if (d_master) *d_master = tb->master;
+	if (d_grad_mlp) *d_grad_mlp = tb->grad_mlp;
+	if (d_grad_grid) *d_grad_grid = (uint16_t*)tb->grad_grid;
+	if (d_grad_variance) *d_grad_variance = tb->grad_var;
+	if (d_bitfield) *d_bitfield = tb->bitfield;
+	if (d_density_grid) *d_density_grid = tb->density_grid;
+	if (stream) *stream = tb->stream;
+	return NEUS2B_OK;
+}
+
+static neus2b_grid_desc active_desc(const neus2b_testbed* tb) {
+	neus2b_grid_desc d = tb->cfg.grid;
+	const neus2b_testbed_config& c = tb->cfg;
+	if (c.progressive_steps_per_increment) {
+		uint32_t n = c.progressive_start_levels + c.progressive_levels_per_increment * (tb->training_step / c.progressive_steps_per_increment);
+		d.n_active_levels = n < d.n_levels ? n : d.n_levels;
+	}
+	return d;
+}
+
+// training_prep_nerf (src/testbed_nerf.cu:3989-4003), called every clamp(step/16, 1, 16) steps (src/testbed.cu:2659)
+static int training_prep(neus2b_testbed* tb) {
+	const uint32_t cells = NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE, nc = tb->cfg.n_cascades;
+	uint32_t n_uniform, n_nonuniform;
+	if (tb->training_step < 256) {
+		n_uniform = cells * nc;
+		n_nonuniform = 0;
+	} else {
+		n_uniform = cells / 4 * nc;
+		n_nonuniform = cells / 4 * nc;
+	}
+	const neus2b_pcg32 ru{tb->density_rng.state, tb->density_rng.inc};
+	tb->density_rng.advance(1ull << 32);
+	const neus2b_pcg32 rn{tb->density_rng.state, tb->density_rng.inc};
+	tb->density_rng.advance(1ull << 32);
+	const neus2b_grid_desc d = active_desc(tb);
+	int rc = neus2b_occupancy_update(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, nc, n_uniform, n_nonuniform, ru, rn, tb->ema_step,
+	                                 tb->cfg.density_grid_decay, tb->density_grid, tb->density_tmp, tb->bitfield, tb->density_mean,
+	                                 tb->occ_pos, tb->occ_idx, (uint16_t*)tb->occ_sdf, tb->occ_partial, tb->stream);
+	++tb->ema_step;
+	return rc;
+}
+
+static neus2b_train_cfg make_train_cfg(const neus2b_testbed* tb) {
+	neus2b_train_cfg c{};
+	for (int e = 0; e < 3; ++e) {
+		c.aabb_min[e] = 0.f;
+		c.aabb_max[e] = 1.f;
+	}
+	c.cone_angle_constant = 0.f;  // aabb_scale <= 1 (src/testbed_nerf.cu:3084)
+	c.snap_to_pixel_centers = tb->cfg.snap_to_pixel_centers;
+	c.random_bg_color = tb->cfg.random_bg_color;
+	c.loss_scale = 128.f;
+	c.mask_loss_weight = tb->cfg.mask_loss_weight;
+	c.ek_loss_weight = tb->cfg.ek_loss_weight;
+	// NerfNetwork::cos_anneal_ratio (nerf_network.h:1109-1118)
+	c.ray_index_offset = tb->cfg.rank * tb->max_rays;
+	c.ray_count_scale = tb->cfg.world_size;
+	c.cos_anneal_ratio = tb->cfg.anneal_end == 0 ? 1.0f : fminf(1.0f, (float)tb->training_step / (float)tb->cfg.anneal_end);
+	return c;
+}
+
+extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
+	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	int rc;
+	const uint32_t skip = tb->training_step / 16u < 1u ? 1u : (tb->training_step / 16u > 16u ? 16u : tb->training_step / 16u);
+	if (tb->training_step % skip == 0) {
+		rc = training_prep(tb);
+		if (rc) return rc;
+	}
+	const neus2b_grid_desc d = active_desc(tb);
+	const neus2b_train_cfg tc = make_train_cfg(tb);
+	const neus2b_pcg32 rng{tb->rng.state, tb->rng.inc};
+	const uint32_t* d_n_rays = &tb->state->rays_per_batch;
+	rc = neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->bitfield, &tb->ws, tb->stream);
+	if (rc) return rc;
+	rc = neus2b_neus_forward(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, tb->max_samples, tb->ws.d_counters + 4, tb->ws.d_coords,
+	                         (uint16_t*)tb->mlp_out, tb->stream);
+	if (rc) return rc;
+	rc = neus2b_compute_loss(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->target, (const uint16_t*)tb->mlp_out, &tb->ws,
+	                         tb->coords_compacted, (uint16_t*)tb->dloss, tb->loss, tb->ek_loss, 1, tb->stream);
+	if (rc) return rc;
+	rc = neus2b_neus_train(&d, (const uint16_t*)tb->params, tb->target, tb->coords_compacted, (const uint16_t*)tb->dloss,
+	                       tb->target * tb->cfg.world_size, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->stream);
+	if (rc) return rc;
+	tb->rng.advance(1ull << 32);  // m_rng.advance() (src/testbed_nerf.cu:3981)
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats) {
+	if (!tb) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	const neus2b_testbed_config& c = tb->cfg;
+	neus2b_adam_cfg ac{};
+	ac.learning_rate = c.learning_rate;
+	const uint32_t step = tb->training_step + 1;
+	if (c.lr_decay_interval && step >= c.lr_decay_start)  // ExponentialDecay (configs/nerf/dtu.json:8-12)
+		ac.learning_rate *= powf(c.lr_decay_base, (float)((step - c.lr_decay_start) / c.lr_decay_interval + 1));
+	ac.beta1 = c.beta1;
+	ac.beta2 = c.beta2;
+	ac.epsilon = c.epsilon;
+	ac.l2_reg = c.l2_reg;
+	ac.ema_decay = c.ema_decay;
+	ac.loss_scale = 128.f;  // LOSS_SCALE (testbed.h:237)
+	ac.step = step;
+	ac.n_matrix = NEUS2B_MLP_N;
+	int rc = neus2b_adam_step(&ac, tb->n_params, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->master, tb->adam_m, tb->adam_v,
+	                          (uint16_t*)tb->params, (uint16_t*)tb->params_ema, tb->ema_master, tb->stream);
+	if (rc) return rc;
+	tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
+	N2B_CHECK_LAUNCH();
+	++tb->training_step;
+	if (h_stats) {
+		loss_reduce_kernel<<<1, 1024, 0, tb->stream>>>(tb->state, tb->loss, tb->ek_loss, tb->target);
+		N2B_CHECK_LAUNCH();
+		N2B_CHECK_CUDA(cudaMemcpyAsync(tb->h_state, tb->state, sizeof(TrainState), cudaMemcpyDeviceToHost, tb->stream));
+		N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+		h_stats->training_step = tb->training_step;
+		h_stats->rays_per_batch = tb->h_state->rays_per_batch;
+		h_stats->n_rays_kept = tb->h_state->n_kept;
+		h_stats->measured_batch_size_before_compaction = tb->h_state->measured_pre;
+		h_stats->measured_batch_size = tb->h_state->measured;
+		h_stats->overflow = tb->h_state->overflow;
+		h_stats->loss = tb->h_state->loss;
+		h_stats->ek_loss = tb->h_state->ek_loss;
+	}
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_train(neus2b_testbed* tb, uint32_t n_steps, neus2b_train_stats* h_stats) {
+	if (!tb || n_steps == 0) return NEUS2B_E_INVALID;
+	for (uint32_t s = 0; s < n_steps; ++s) {
+		int rc = neus2b_testbed_train_backward(tb);
+		if (rc) return rc;
+		rc = neus2b_testbed_train_optimizer_step(tb, s + 1 == n_steps ? h_stats : nullptr);
+		if (rc) return rc;
+	}
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3], uint32_t z0, uint32_t z1, int use_ema, float* d_out) {
+	if (!tb || !res || !d_out || z1 <= z0 || z1 > res[2] || !res[0] || !res[1]) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	const uint64_t first = (uint64_t)z0 * res[0] * res[1], total = (uint64_t)(z1 - z0) * res[0] * res[1];
+	const uint32_t chunk = NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * tb->cfg.n_cascades;  // reuse the occupancy scratch (>= 2^21)
+	neus2b_grid_desc d = tb->cfg.grid;  // every level: inference does not mask
+	const float ix = 1.f / (float)res[0], iy = 1.f / (float)res[1], iz = 1.f / (float)res[2];
+	for (uint64_t off = 0; off < total; off += chunk) {
+		const uint32_t n = (uint32_t)((total - off) < chunk ? (total - off) : chunk);
+		sdf_grid_positions_kernel<<<div_up(n, 256), 256, 0, tb->stream>>>(res[0], res[1], first + off, n, ix, iy, iz, tb->occ_pos);
+		N2B_CHECK_LAUNCH();
+		int rc = neus2b_neus_sdf(&d, (const uint16_t*)(use_ema ? tb->params_ema : tb->params), tb->cfg.sdf_bias, n, tb->occ_pos, 3,
+		                         (uint16_t*)tb->occ_sdf, tb->stream);
+		if (rc) return rc;
+		half_to_float_kernel<<<div_up(n, 256), 256, 0, tb->stream>>>(n, tb->occ_sdf, d_out + off);
+		N2B_CHECK_LAUNCH();
+	}
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}

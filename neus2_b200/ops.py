@@ -111,7 +111,7 @@ class RayBatch:
         self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
         self.ray_tmp = torch.zeros((max_rays, 8), dtype=f32, device=device)
         self.ws = L.RayWorkspace(max_rays, max_samples, L.ptr(self.ray_indices), L.ptr(self.rays), L.ptr(self.numsteps),
-                                 L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp))
+                                 L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp), None)
 
 
 def make_dataset(pixels, xforms, focal, principal):

@@ -1,0 +1,119 @@
+"""Host-side mirror of the training subset of the reference's ``pyngp.Testbed`` (src/python_api.cu:317-471) over the
+C ABI: ``load_training_data`` / ``train`` / ``frame`` / ``training_step`` / ``loss`` / ``ek_loss`` keep their names and
+meaning.  All work happens in libneus2b.so; this class owns nothing but the handle."""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+
+
+class Testbed:
+    def __init__(self, config=None, **overrides):
+        cfg = L.TestbedConfig()
+        L.lib().neus2b_testbed_default_config(C.byref(cfg))
+        if config is not None:
+            cfg = config
+        for k, v in overrides.items():
+            if k in ("n_levels", "log2_hashmap_size", "base_resolution", "per_level_scale", "n_active_levels"):
+                setattr(cfg.grid, k, v)
+            else:
+                if not hasattr(cfg, k):
+                    raise AttributeError(k)
+                setattr(cfg, k, v)
+        if "n_levels" in overrides and "n_active_levels" not in overrides:
+            cfg.grid.n_active_levels = cfg.grid.n_levels
+        self.config = cfg
+        self._h = C.c_void_p()
+        L.check(L.lib().neus2b_testbed_create(C.byref(cfg), C.byref(self._h)))
+        self.stats = L.TrainStats()
+        self.shall_train = True
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            L.lib().neus2b_testbed_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # --- data / parameters (HOST arrays in, as the reference's loader hands them over)
+    def load_training_data(self, pixels, xforms, focal, principal):
+        pixels = np.ascontiguousarray(pixels).view(np.uint32)
+        self._cams = [np.ascontiguousarray(a, dtype=np.float32) for a in (xforms, focal, principal)]
+        n, h, w = pixels.shape
+        L.check(L.lib().neus2b_testbed_load_training_data(self._h, C.c_uint32(n), C.c_uint32(w), C.c_uint32(h),
+                                                          pixels.ctypes.data_as(C.c_void_p),
+                                                          *[a.ctypes.data_as(C.c_void_p) for a in self._cams]))
+
+    def update_cameras(self, xforms=None, focal=None, principal=None):
+        cams = [np.ascontiguousarray(a, dtype=np.float32) if a is not None else b
+                for a, b in zip((xforms, focal, principal), self._cams)]
+        L.check(L.lib().neus2b_testbed_update_cameras(self._h, *[a.ctypes.data_as(C.c_void_p) for a in cams]))
+
+    @property
+    def n_params(self):
+        n = C.c_uint64(0)
+        L.check(L.lib().neus2b_testbed_n_params(self._h, C.byref(n)))
+        return int(n.value)
+
+    def set_params(self, params_fp32):
+        p = np.ascontiguousarray(params_fp32, dtype=np.float32)
+        L.check(L.lib().neus2b_testbed_set_params(self._h, p.ctypes.data_as(C.c_void_p), C.c_uint64(p.size)))
+
+    def get_params(self, ema=False):
+        p = np.empty(self.n_params, np.float32)
+        L.check(L.lib().neus2b_testbed_get_params(self._h, p.ctypes.data_as(C.c_void_p), C.c_uint64(p.size), C.c_int(int(ema))))
+        return p
+
+    # --- training
+    def train(self, n_steps=1, read_stats=True):
+        L.check(L.lib().neus2b_testbed_train(self._h, C.c_uint32(n_steps), C.byref(self.stats) if read_stats else None))
+        return self.stats
+
+    def frame(self):
+        """One training step, like ``Testbed::frame`` with ``shall_train`` set (src/testbed.cu:1712)."""
+        if self.shall_train:
+            self.train(1)
+        return True
+
+    def train_backward(self):
+        L.check(L.lib().neus2b_testbed_train_backward(self._h))
+
+    def optimizer_step(self, read_stats=True):
+        L.check(L.lib().neus2b_testbed_train_optimizer_step(self._h, C.byref(self.stats) if read_stats else None))
+        return self.stats
+
+    @property
+    def training_step(self):
+        return int(self.stats.training_step)
+
+    @property
+    def loss(self):
+        return float(self.stats.loss)
+
+    @property
+    def ek_loss(self):
+        return float(self.stats.ek_loss)
+
+    # --- device views (torch tensors over the library's buffers; for tests and for NCCL)
+    def device_ptrs(self):
+        names = ("params", "params_ema", "master", "grad_mlp", "grad_grid", "grad_variance", "bitfield", "density_grid")
+        ptrs = [C.c_void_p() for _ in names]
+        stream = C.c_void_p()
+        L.check(L.lib().neus2b_testbed_device_ptrs(self._h, *[C.byref(p) for p in ptrs], C.byref(stream)))
+        out = {k: p.value for k, p in zip(names, ptrs)}
+        out["stream"] = stream.value
+        return out
+
+    def sdf_grid(self, res, z0=0, z1=None, use_ema=True):
+        import torch
+        res = [int(r) for r in (res if hasattr(res, "__len__") else (res, res, res))]
+        z1 = res[2] if z1 is None else z1
+        out = torch.empty((z1 - z0, res[1], res[0]), dtype=torch.float32, device="cuda")
+        L.check(L.lib().neus2b_testbed_sdf_grid(self._h, (C.c_uint32 * 3)(*res), C.c_uint32(z0), C.c_uint32(z1), C.c_int(int(use_ema)),
+                                                C.c_void_p(out.data_ptr())))
+        return out

@@ -793,8 +793,9 @@ static void ray_setup(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint32_t 
                       n2o_pcg32 rng, const uint8_t* bitfield, ray_tmp* r) {
 	r->keep = 0;
 	r->numsteps = 0;
-	uint32_t img = image_idx(i, n_rays, n_rays_total, ds->n_images);
-	n2o_pcg32_advance(&rng, (uint64_t)i * 8u);
+	const uint32_t ig = i + cfg->ray_index_offset;
+	uint32_t img = image_idx(ig, n_rays, n_rays_total, ds->n_images);
+	n2o_pcg32_advance(&rng, (uint64_t)ig * 8u);
 	float xy[2], rgba[4];
 	random_image_pos(&rng, ds, (int)cfg->snap_to_pixel_centers, xy);
 	read_rgba(ds, img, xy, rgba);
@@ -975,7 +976,7 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 		if (ek_loss_out) ek_loss_out[i] = 0.f;
 		if (cn == 0) continue;
 		/* target colour (:1619-1667) */
-		uint32_t ray_idx = ray_indices[i];
+		uint32_t ray_idx = ray_indices[i] + cfg->ray_index_offset;
 		n2o_pcg32 rng = rng0;
 		n2o_pcg32_advance(&rng, (uint64_t)ray_idx * 8u);
 		uint32_t img = image_idx(ray_idx, n_rays, n_rays_total, ds->n_images);
@@ -1006,8 +1007,9 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 		if (ws >= 1.0f - 1e-4f) { ws = 1.0f - 1e-4f; gws = 0.f; }
 		else if (ws <= 1e-4f) { ws = 1e-4f; gws = 0.f; }
 		else { float sg = 1.0f / (1.0f + expf(-ws)); gws = (mask_gt - sg) * ws * cfg->mask_loss_weight; }
-		if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / (float)n_rays;
-		const float loss_scale = cfg->loss_scale / (float)n_rays;
+		const float n_rays_f = (float)n_rays * (float)(cfg->ray_count_scale ? cfg->ray_count_scale : 1u);
+		if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
+		const float loss_scale = cfg->loss_scale / n_rays_f;
 		/* pass B (:1761-1952) */
 		const float* rd = rays + (size_t)i * 6 + 3;
 		float inv = 1.0f / sqrtf(rd[0] * rd[0] + rd[1] * rd[1] + rd[2] * rd[2]);
@@ -1067,7 +1069,7 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 			uint16_t* go = dloss_dout + (size_t)(compacted_base + j) * 16;
 			for (int k = 0; k < 16; ++k) go[k] = f2h(g[k]);
 		}
-		if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * (float)n_rays);
+		if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * n_rays_f);
 	}
 	free(cp);
 	free(cbase);

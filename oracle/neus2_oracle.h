@@ -113,6 +113,7 @@ typedef struct {
 	float background_color[3];
 	float loss_scale;        /* LOSS_SCALE = 128, include/neural-graphics-primitives/testbed.h:237 */
 	float mask_loss_weight, ek_loss_weight, cos_anneal_ratio;
+	uint32_t ray_index_offset, ray_count_scale; /* data-parallel ray sharding; 0 / 1 = single process */
 } n2o_train_cfg;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene, canonical

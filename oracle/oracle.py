@@ -47,7 +47,7 @@ class TrainCfg(C.Structure):
     _fields_ = [("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
                 ("snap_to_pixel_centers", C.c_uint32), ("random_bg_color", C.c_uint32), ("background_color", C.c_float * 3),
                 ("loss_scale", C.c_float), ("mask_loss_weight", C.c_float), ("ek_loss_weight", C.c_float),
-                ("cos_anneal_ratio", C.c_float)]
+                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32)]
 
 
 class AdamCfg(C.Structure):
@@ -223,6 +223,11 @@ def pcg32_advance(r, delta):
     return r2
 
 
+def pcg32_next_uint(r):
+    """Advances r in place and returns the next 32-bit output."""
+    return int(lib().n2o_pcg32_next_uint(C.byref(r)))
+
+
 def pcg32_floats(r, n):
     r2 = Pcg32(r.state, r.inc)
     return np.array([lib().n2o_pcg32_next_float(C.byref(r2)) for _ in range(n)], np.float32)
@@ -240,7 +245,8 @@ def make_dataset(pixels, xforms, focal, principal):
 
 
 def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, snap_to_pixel_centers=False,
-              cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0)):
+              cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0), ray_index_offset=0,
+              ray_count_scale=1):
     c = TrainCfg()
     c.aabb_min[:] = [0.0, 0.0, 0.0]
     c.aabb_max[:] = [1.0, 1.0, 1.0]
@@ -252,6 +258,8 @@ def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, sn
     c.mask_loss_weight = mask_loss_weight
     c.ek_loss_weight = ek_loss_weight
     c.cos_anneal_ratio = cos_anneal_ratio
+    c.ray_index_offset = ray_index_offset
+    c.ray_count_scale = ray_count_scale
     return c
 
 

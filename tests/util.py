@@ -10,11 +10,17 @@ _METRICS = {}
 
 def record(name, **kw):
     """Keeps the measured errors of the GPU parity tests next to the run (gpurun_out/parity_metrics.json)."""
-    _METRICS[name] = {k: (float(v) if np.isscalar(v) else v) for k, v in kw.items()}
     out = os.path.join(ROOT, "gpurun_out")
+    path = os.path.join(out, "parity_metrics.json")
+    if not _METRICS and os.path.exists(path):
+        try:
+            _METRICS.update(json.load(open(path)))
+        except (OSError, ValueError):
+            pass
+    _METRICS[name] = {k: (float(v) if np.isscalar(v) else v) for k, v in kw.items()}
     try:
         os.makedirs(out, exist_ok=True)
-        with open(os.path.join(out, "parity_metrics.json"), "w") as f:
+        with open(path, "w") as f:
             json.dump(_METRICS, f, indent=1, sort_keys=True)
     except OSError:
         pass
