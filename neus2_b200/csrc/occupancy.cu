@@ -114,43 +114,106 @@ __global__ void occ_maxpool_kernel(uint32_t n, const uint8_t* __restrict__ prev,
 }
 
 // ------------------------------------------------------------------------------------------------ Adam
+// One element of the Ema o Adam update.  Returns the new weight; m/v are updated in place.
+__device__ __forceinline__ float adam_element(const neus2b_adam_cfg& c, float lr_t, bool matrix, float g, float w, float& m, float& v) {
+	g = g / c.loss_scale;
+	bool upd = true;
+	if (matrix) g += c.l2_reg * w;
+	else if (g == 0.0f) upd = false;  // grid entries no sample touched keep their weight and moments
+	if (upd) {
+		m = c.beta1 * m + (1.0f - c.beta1) * g;
+		v = c.beta2 * v + (1.0f - c.beta2) * g * g;
+		w -= lr_t * m / (sqrtf(v) + c.epsilon);
+	}
+	return w;
+}
+
+// Streaming pass over the parameter block, 8 parameters (16..32-byte accesses) per thread and iteration.  The block is
+// [n_matrix MLP weights | grid | 4 variance slots]; n_matrix and the grid size are multiples of 8.
 __global__ void __launch_bounds__(256) adam_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
                                                    float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
                                                    float* __restrict__ grad_var, float* __restrict__ master, float* __restrict__ m,
                                                    float* __restrict__ v, __half* __restrict__ params, __half* __restrict__ params_ema,
                                                    float* __restrict__ ema_master) {
-	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 8u;
 	const uint64_t n_grid_end = n - 4u;
-	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-		float g;
-		if (i < c.n_matrix) {
-			g = grad_mlp[i];
-			grad_mlp[i] = 0.f;
-		} else if (i < n_grid_end) {
-			g = __half2float(grad_grid[i - c.n_matrix]);
-			grad_grid[i - c.n_matrix] = __float2half_rn(0.f);
+	for (uint64_t i0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8u; i0 < n; i0 += stride) {
+		float g[8], w[8], mm[8], vv[8], em[8];
+		const bool full = i0 + 8u <= n_grid_end;  // tail: the 4 variance slots
+		const bool matrix = i0 < c.n_matrix;
+		if (full) {
+			if (matrix) {
+				const float4 a = *reinterpret_cast<const float4*>(grad_mlp + i0), b = *reinterpret_cast<const float4*>(grad_mlp + i0 + 4);
+				g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+				*reinterpret_cast<float4*>(grad_mlp + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
+				*reinterpret_cast<float4*>(grad_mlp + i0 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+			} else {
+				uint4 raw = *reinterpret_cast<const uint4*>(grad_grid + (i0 - c.n_matrix));
+				const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+				for (int e = 0; e < 4; ++e) {
+					const float2 f = __half22float2(h[e]);
+					g[2 * e] = f.x;
+					g[2 * e + 1] = f.y;
+				}
+				*reinterpret_cast<uint4*>(grad_grid + (i0 - c.n_matrix)) = make_uint4(0u, 0u, 0u, 0u);
+			}
+#pragma unroll
+			for (int q = 0; q < 2; ++q) {
+				const float4 a = *reinterpret_cast<const float4*>(master + i0 + 4 * q);
+				const float4 b = *reinterpret_cast<const float4*>(m + i0 + 4 * q);
+				const float4 d = *reinterpret_cast<const float4*>(v + i0 + 4 * q);
+				w[4 * q] = a.x; w[4 * q + 1] = a.y; w[4 * q + 2] = a.z; w[4 * q + 3] = a.w;
+				mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
+				vv[4 * q] = d.x; vv[4 * q + 1] = d.y; vv[4 * q + 2] = d.z; vv[4 * q + 3] = d.w;
+				if (params_ema) {
+					const float4 e4 = *reinterpret_cast<const float4*>(ema_master + i0 + 4 * q);
+					em[4 * q] = e4.x; em[4 * q + 1] = e4.y; em[4 * q + 2] = e4.z; em[4 * q + 3] = e4.w;
+				}
+			}
+#pragma unroll
+			for (int e = 0; e < 8; ++e) w[e] = adam_element(c, lr_t, matrix, g[e], w[e], mm[e], vv[e]);
+			__align__(16) __half ph[8], peh[8];
+#pragma unroll
+			for (int e = 0; e < 8; ++e) {
+				ph[e] = __float2half_rn(w[e]);
+				if (params_ema) {
+					em[e] = ((1.0f - c.ema_decay) * w[e] + c.ema_decay * em[e] * ema_old) * ema_new_inv;
+					peh[e] = __float2half_rn(em[e]);
+				}
+			}
+#pragma unroll
+			for (int q = 0; q < 2; ++q) {
+				*reinterpret_cast<float4*>(master + i0 + 4 * q) = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+				*reinterpret_cast<float4*>(m + i0 + 4 * q) = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
+				*reinterpret_cast<float4*>(v + i0 + 4 * q) = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
+				if (params_ema)
+					*reinterpret_cast<float4*>(ema_master + i0 + 4 * q) = make_float4(em[4 * q], em[4 * q + 1], em[4 * q + 2], em[4 * q + 3]);
+			}
+			*reinterpret_cast<uint4*>(params + i0) = *reinterpret_cast<const uint4*>(ph);
+			if (params_ema) *reinterpret_cast<uint4*>(params_ema + i0) = *reinterpret_cast<const uint4*>(peh);
 		} else {
-			g = grad_var[i - n_grid_end];
-			grad_var[i - n_grid_end] = 0.f;
-		}
-		float w = master[i];
-		g = g / c.loss_scale;
-		bool upd = true;
-		if (i < c.n_matrix) g += c.l2_reg * w;
-		else if (g == 0.0f) upd = false;
-		if (upd) {
-			const float mi = c.beta1 * m[i] + (1.0f - c.beta1) * g;
-			const float vi = c.beta2 * v[i] + (1.0f - c.beta2) * g * g;
-			m[i] = mi;
-			v[i] = vi;
-			w -= lr_t * mi / (sqrtf(vi) + c.epsilon);
-			master[i] = w;
-		}
-		params[i] = __float2half_rn(w);
-		if (params_ema) {
-			const float e = ((1.0f - c.ema_decay) * w + c.ema_decay * ema_master[i] * ema_old) * ema_new_inv;
-			ema_master[i] = e;
-			params_ema[i] = __float2half_rn(e);
+			for (uint64_t i = i0; i < n && i < i0 + 8u; ++i) {
+				float gi;
+				if (i < n_grid_end) {
+					gi = __half2float(grad_grid[i - c.n_matrix]);
+					grad_grid[i - c.n_matrix] = __float2half_rn(0.f);
+				} else {
+					gi = grad_var[i - n_grid_end];
+					grad_var[i - n_grid_end] = 0.f;
+				}
+				float mi = m[i], vi = v[i];
+				const float wi = adam_element(c, lr_t, false, gi, master[i], mi, vi);
+				master[i] = wi;
+				m[i] = mi;
+				v[i] = vi;
+				params[i] = __float2half_rn(wi);
+				if (params_ema) {
+					const float e = ((1.0f - c.ema_decay) * wi + c.ema_decay * ema_master[i] * ema_old) * ema_new_inv;
+					ema_master[i] = e;
+					params_ema[i] = __float2half_rn(e);
+				}
+			}
 		}
 	}
 }
@@ -232,7 +295,10 @@ extern "C" int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d
                                 neus2b_stream_t stream) {
 	if (!cfg || !d_grad_mlp || !d_grad_grid || !d_grad_variance || !d_master || !d_m || !d_v || !d_params) return NEUS2B_E_INVALID;
 	if (d_params_ema && !d_ema_master) return NEUS2B_E_INVALID;
-	if (n < cfg->n_matrix + 4u || cfg->step == 0) return NEUS2B_E_INVALID;
+	if (n < cfg->n_matrix + 4u || cfg->step == 0 || (cfg->n_matrix & 7u)) return NEUS2B_E_INVALID;
+	if (((uintptr_t)d_grad_mlp | (uintptr_t)d_grad_grid | (uintptr_t)d_master | (uintptr_t)d_m | (uintptr_t)d_v | (uintptr_t)d_params |
+	     (uintptr_t)d_params_ema | (uintptr_t)d_ema_master) & 15u)
+		return NEUS2B_E_INVALID;
 	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
 	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
 	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));

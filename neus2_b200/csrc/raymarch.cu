@@ -157,11 +157,7 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	if (i >= n_rays_max) return;
-	if (i >= n_rays) {
-		scan_in[i] = 0;
-		tmp[i].numsteps = 0;
-		return;
-	}
+	if (i >= n_rays) return;
 	RayTmp r;
 	r.numsteps = 0;
 	r.startt = 0.f;
@@ -216,54 +212,63 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 	scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
 }
 
-// Exclusive prefix sum of n 64-bit keys with one CTA (n <= 2^18 rays per batch); total goes to scan[n_max].
-// TODO(perf): decoupled look-back over all SMs.
-__global__ void __launch_bounds__(1024) scan_kernel(uint32_t n, uint64_t* __restrict__ data) {
+// Exclusive prefix sum of n 64-bit keys, n read on the device (the live ray count is a few thousand once the batch
+// tuner has converged, 2^18 at most).  One CTA walks tiles of 4096 keys with coalesced 32-byte accesses; the total goes
+// to data[n_max].
+__global__ void __launch_bounds__(1024) scan_kernel(uint32_t n_max, const uint32_t* __restrict__ d_n, uint64_t* __restrict__ data) {
 	__shared__ uint64_t warp_sums[32];
-	__shared__ uint64_t carry;
+	__shared__ uint64_t tile_total;
 	const uint32_t tid = threadIdx.x;
-	const uint32_t per = (n + 1023u) / 1024u;
-	const uint32_t lo = min(n, tid * per), hi = min(n, lo + per);
-	uint64_t sum = 0;
-	for (uint32_t k = lo; k < hi; ++k) sum += data[k];
-	// block-wide exclusive scan of the per-thread sums
-	uint64_t incl = sum;
+	const uint32_t n = d_n ? min(*d_n, n_max) : n_max;
+	uint64_t carry = 0;
+	for (uint32_t t0 = 0; t0 < n; t0 += 4096u) {
+		const uint32_t k0 = t0 + tid * 4u;
+		uint64_t v[4];
 #pragma unroll
-	for (int o = 1; o < 32; o <<= 1) {
-		const uint64_t v = __shfl_up_sync(0xffffffffu, incl, o);
-		if ((tid & 31) >= (uint32_t)o) incl += v;
-	}
-	if ((tid & 31) == 31) warp_sums[tid >> 5] = incl;
-	__syncthreads();
-	if (tid < 32) {
-		uint64_t w = warp_sums[tid], wi = w;
+		for (int e = 0; e < 4; ++e) v[e] = (k0 + e < n) ? data[k0 + e] : 0ull;
+		const uint64_t sum = v[0] + v[1] + v[2] + v[3];
+		uint64_t incl = sum;
 #pragma unroll
 		for (int o = 1; o < 32; o <<= 1) {
-			const uint64_t v = __shfl_up_sync(0xffffffffu, wi, o);
-			if (tid >= (uint32_t)o) wi += v;
+			const uint64_t u = __shfl_up_sync(0xffffffffu, incl, o);
+			if ((tid & 31) >= (uint32_t)o) incl += u;
 		}
-		warp_sums[tid] = wi - w;
-		if (tid == 31) carry = wi;
+		if ((tid & 31) == 31) warp_sums[tid >> 5] = incl;
+		__syncthreads();
+		if (tid < 32) {
+			const uint64_t w = warp_sums[tid];
+			uint64_t wi = w;
+#pragma unroll
+			for (int o = 1; o < 32; o <<= 1) {
+				const uint64_t u = __shfl_up_sync(0xffffffffu, wi, o);
+				if (tid >= (uint32_t)o) wi += u;
+			}
+			warp_sums[tid] = wi - w;
+			if (tid == 31) tile_total = wi;
+		}
+		__syncthreads();
+		uint64_t run = carry + warp_sums[tid >> 5] + incl - sum;
+#pragma unroll
+		for (int e = 0; e < 4; ++e) {
+			if (k0 + e < n) data[k0 + e] = run;
+			run += v[e];
+		}
+		carry += tile_total;
+		__syncthreads();
 	}
-	__syncthreads();
-	uint64_t run = warp_sums[tid >> 5] + incl - sum;
-	for (uint32_t k = lo; k < hi; ++k) {
-		const uint64_t v = data[k];
-		data[k] = run;
-		run += v;
-	}
-	if (tid == 0) data[n] = carry;
+	if (tid == 0) data[n_max] = carry;
 }
 
 // Second half of the sample generator (:1410-1445): canonical ranges, then march again and write the coordinates.
-__global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, uint32_t max_samples,
-                                                           const uint8_t* __restrict__ bitfield, const RayTmp* __restrict__ tmp,
+__global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, const uint32_t* __restrict__ d_n_rays,
+                                                           uint32_t max_samples, const uint8_t* __restrict__ bitfield,
+                                                           const RayTmp* __restrict__ tmp,
                                                            const uint64_t* __restrict__ scan, uint32_t* __restrict__ ray_indices,
                                                            float* __restrict__ rays, uint32_t* __restrict__ numsteps,
                                                            float* __restrict__ coords, uint32_t* __restrict__ counters) {
 	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
 	if (i == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps found, dropped rays included
-	if (i >= n_rays_max) return;
+	if (i >= (d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max)) return;
 	const RayTmp r = tmp[i];
 	if (r.numsteps == 0) return;
 	const uint64_t key = scan[i];
@@ -349,49 +354,100 @@ struct CompTmp {  // 8 floats per kept ray
 	uint32_t n, full, pad;
 };
 
+constexpr uint32_t kFull = 0xffffffffu;
+
+// Transmittance in front of each lane's sample, multiplied in ray order exactly like the reference's serial loop
+// (T *= 1 - alpha), so the early-termination decision T < 1e-4 does not depend on how the work is parallelised.
+__device__ __forceinline__ float serial_transmittance(float T_carry, float one_minus_alpha, int lane) {
+	float run = T_carry, mine = 0.f;
+#pragma unroll
+	for (int k = 0; k < 32; ++k) {
+		const float om = __shfl_sync(kFull, one_minus_alpha, k);
+		if (lane == k) mine = run;
+		run *= om;
+	}
+	return mine;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+	return v;
+}
+__device__ __forceinline__ float warp_incl_scan(float v, int lane) {
+#pragma unroll
+	for (int o = 1; o < 32; o <<= 1) {
+		const float u = __shfl_up_sync(kFull, v, o);
+		if (lane >= o) v += u;
+	}
+	return v;
+}
+
+// BENT_DIR (:1574-1579): the direction the network saw at the ray's first sample replaces the ray direction
+__device__ __forceinline__ void bent_dir(const __half* __restrict__ mlp_out, uint32_t base, float* dir) {
+	const __half* o = mlp_out + (size_t)base * 16;
+	const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
+	const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+#pragma unroll
+	for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+}
+
 // Pass A (:1563-1617): composite along the ray until transmittance drops below 1e-4; count the surviving samples.
-__global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, const uint32_t* __restrict__ counters,
-                                                        const __half* __restrict__ mlp_out, const float* __restrict__ rays,
-                                                        const uint32_t* __restrict__ numsteps, const float* __restrict__ coords,
-                                                        CompTmp* __restrict__ tmp, uint64_t* __restrict__ scan_in) {
-	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-	if (i >= n_rays_max) return;
-	if (i >= counters[0]) {
-		scan_in[i] = 0;
-		return;
-	}
-	const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
-	float dir[3];
-	CompTmp c;
-	c.rgb[0] = c.rgb[1] = c.rgb[2] = 0.f;
-	c.T = 1.f;
-	c.weight_sum = 0.f;
-	c.n = 0;
-	c.pad = 0;
-	for (; c.n < ns; ++c.n) {
-		if (c.T < 1e-4f) break;
-		__align__(16) __half o[16];
-		load_out16(mlp_out + (size_t)(base + c.n) * 16, o);
-		if (c.n == 0) {  // BENT_DIR (:1574-1579): the direction the network saw replaces the ray direction
-			const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
-			const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+// One warp per kept ray, 32 samples per iteration.
+__global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, const uint32_t* __restrict__ counters,
+                                                        const __half* __restrict__ mlp_out, const uint32_t* __restrict__ numsteps,
+                                                        const float* __restrict__ coords, CompTmp* __restrict__ tmp,
+                                                        uint64_t* __restrict__ scan_in) {
+	const int lane = threadIdx.x & 31;
+	const uint32_t n_kept = counters[0];
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_kept; i += warps) {
+		const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
+		float dir[3];
+		bent_dir(mlp_out, base, dir);
+		float T = 1.f, rgb[3] = {0.f, 0.f, 0.f}, ws = 0.f;
+		uint32_t n = 0;
+		bool done = false;
+		for (uint32_t j0 = 0; j0 < ns && !done; j0 += 32) {
+			const uint32_t j = j0 + lane;
+			const bool valid = j < ns;
+			NeusSample s;
+			s.alpha = 0.f;
+			s.rgb[0] = s.rgb[1] = s.rgb[2] = 0.f;
+			if (valid) {
+				__align__(16) __half o[16];
+				load_out16(mlp_out + (size_t)(base + j) * 16, o);
+				neus_sample(o, coords[(size_t)(base + j) * 7 + 3], dir, cfg.cos_anneal_ratio, s);
+			}
+			const float om = 1.f - s.alpha;
+			const float Tb = serial_transmittance(T, om, lane);
+			const bool active = valid && !(Tb < 1e-4f);
+			const uint32_t cnt = __popc(__ballot_sync(kFull, active));
+			const float w = active ? s.alpha * Tb : 0.f;
 #pragma unroll
-			for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+			for (int e = 0; e < 3; ++e) rgb[e] += warp_sum(w * s.rgb[e]);
+			ws += warp_sum(w);
+			if (cnt) T = __shfl_sync(kFull, Tb * om, cnt - 1);
+			n += cnt;
+			done = cnt < 32;
 		}
-		NeusSample s;
-		neus_sample(o, coords[(size_t)(base + c.n) * 7 + 3], dir, cfg.cos_anneal_ratio, s);
-		const float w = s.alpha * c.T;
-#pragma unroll
-		for (int e = 0; e < 3; ++e) c.rgb[e] += w * s.rgb[e];
-		c.weight_sum += w;
-		c.T *= (1.f - s.alpha);
+		if (lane == 0) {
+			CompTmp c;
+			c.rgb[0] = rgb[0];
+			c.rgb[1] = rgb[1];
+			c.rgb[2] = rgb[2];
+			c.T = T;
+			c.weight_sum = ws;
+			c.n = n;
+			c.full = n == ns;
+			c.pad = 0;
+			tmp[i] = c;
+			scan_in[i] = (uint64_t)n;
+		}
 	}
-	c.full = c.n == ns;
-	tmp[i] = c;
-	scan_in[i] = (uint64_t)c.n;
 }
 
 // Target pixel, Huber loss, pass B (:1619-1952): loss gradient w.r.t. the 16 network outputs of every kept sample.
+// One warp per kept ray; a lane owns one sample of the current 32-sample chunk.
 __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
                                                    const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
                                                    const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
@@ -401,148 +457,160 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
                                                    const CompTmp* __restrict__ tmp, const uint64_t* __restrict__ scan,
                                                    float* __restrict__ coords_out, __half* __restrict__ dloss_dout,
                                                    float* __restrict__ loss_out, float* __restrict__ ek_loss_out) {
-	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	const int lane = threadIdx.x & 31;
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
-	if (i == 0) counters[2] = (uint32_t)scan[n_rays_max];
-	if (i >= n_rays_max) return;
-	if (i >= counters[0]) {
-		if (loss_out) loss_out[i] = 0.f;
-		if (ek_loss_out) ek_loss_out[i] = 0.f;
-		return;
-	}
+	if (blockIdx.x == 0 && threadIdx.x == 0) counters[2] = (uint32_t)scan[n_rays_max];
+	const uint32_t n_kept = counters[0];
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
-	const uint32_t base = numsteps[i * 2 + 1];
-	const CompTmp c = tmp[i];
-	const uint32_t compacted_base = (uint32_t)scan[i];
-	const uint32_t cn = min(max_compacted - min(max_compacted, compacted_base), c.n);
-	numsteps[i * 2 + 0] = cn;
-	numsteps[i * 2 + 1] = compacted_base;
-	if (loss_out) loss_out[i] = 0.f;
-	if (ek_loss_out) ek_loss_out[i] = 0.f;
-	if (cn == 0) return;
-	// target colour (:1619-1667)
-	const uint32_t ray_idx = ray_indices[i] + cfg.ray_index_offset;
-	Pcg32 rng = rng0;
-	rng.advance((uint64_t)ray_idx * 8u);
-	const uint32_t img = image_idx(ray_idx, n_rays, n_rays_total, ds.n_images);
-	float xy[2], bg[3], tex[4], target[3];
-	random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
-	if (cfg.random_bg_color) {
-#pragma unroll
-		for (int e = 0; e < 3; ++e) bg[e] = rng.next_float();
-	} else {
-#pragma unroll
-		for (int e = 0; e < 3; ++e) bg[e] = cfg.background_color[e];
-	}
-#pragma unroll
-	for (int e = 0; e < 3; ++e) bg[e] = srgb_to_linear(bg[e]);
-	read_rgba(ds, img, xy, tex);
-#pragma unroll
-	for (int e = 0; e < 3; ++e) {
-		target[e] = linear_to_srgb(tex[e] + (1.0f - tex[3]) * bg[e]);
-		bg[e] = linear_to_srgb(bg[e]);
-	}
-	float rgb_ray[3] = {c.rgb[0], c.rgb[1], c.rgb[2]};
-	if (c.full) {
-#pragma unroll
-		for (int e = 0; e < 3; ++e) rgb_ray[e] += c.T * bg[e];
-	}
-	// Huber(0.1) / 5 (:301-317, :1459)
-	float lgl[3], lgg[3];
-#pragma unroll
-	for (int e = 0; e < 3; ++e) {
-		const float diff = rgb_ray[e] - target[e], ad = fabsf(diff), al = 0.1f;
-		lgl[e] = (ad > al ? (ad - 0.5f * al) : 0.5f / al * diff * diff) / 5.0f;
-		lgg[e] = (ad > al ? (diff > 0 ? 1.0f : -1.0f) : diff / al) / 5.0f;
-	}
-	const float mask_gt = tex[3] > 0.9999f ? 1.f : 0.f;
-	float gws, ws = c.weight_sum;
-	if (ws >= 1.0f - 1e-4f) {
-		ws = 1.0f - 1e-4f;
-		gws = 0.f;
-	} else if (ws <= 1e-4f) {
-		ws = 1e-4f;
-		gws = 0.f;
-	} else {
-		const float sg = 1.0f / (1.0f + expf(-ws));
-		gws = (mask_gt - sg) * ws * cfg.mask_loss_weight;
-	}
-	const float n_rays_f = (float)n_rays * (float)(cfg.ray_count_scale ? cfg.ray_count_scale : 1u);
-	if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
-	const float loss_scale = cfg.loss_scale / n_rays_f;
-	float dir[3];
-	float rgb2[3] = {0.f, 0.f, 0.f}, T = 1.f, ek = 0.f;
-	for (uint32_t j = 0; j < cn; ++j) {
-		__align__(16) __half o[16];
-		load_out16(mlp_out + (size_t)(base + j) * 16, o);
-		if (j == 0) {
-			const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
-			const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
-#pragma unroll
-			for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_kept; i += warps) {
+		const uint32_t base = numsteps[i * 2 + 1];
+		const CompTmp c = tmp[i];
+		const uint32_t compacted_base = (uint32_t)scan[i];
+		const uint32_t cn = min(max_compacted - min(max_compacted, compacted_base), c.n);
+		__syncwarp();
+		if (lane == 0) {
+			numsteps[i * 2 + 0] = cn;
+			numsteps[i * 2 + 1] = compacted_base;
+			if (loss_out) loss_out[i] = 0.f;
+			if (ek_loss_out) ek_loss_out[i] = 0.f;
 		}
-		const float* cin = coords + (size_t)(base + j) * 7;
-		float* cout = coords_out + (size_t)(compacted_base + j) * 7;
-		float cdt = 0.f;
+		if (cn == 0) continue;
+		// target colour (:1619-1667), computed by every lane
+		const uint32_t ray_idx = ray_indices[i] + cfg.ray_index_offset;
+		Pcg32 rng = rng0;
+		rng.advance((uint64_t)ray_idx * 8u);
+		const uint32_t img = image_idx(ray_idx, n_rays, n_rays_total, ds.n_images);
+		float xy[2], bg[3], tex[4], target[3];
+		random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
+		if (cfg.random_bg_color) {
 #pragma unroll
-		for (int e = 0; e < 7; ++e) {
-			const float vv = cin[e];
-			cout[e] = vv;
-			if (e == 3) cdt = vv;
+			for (int e = 0; e < 3; ++e) bg[e] = rng.next_float();
+		} else {
+#pragma unroll
+			for (int e = 0; e < 3; ++e) bg[e] = cfg.background_color[e];
 		}
-		NeusSample s;
-		neus_sample(o, cdt, dir, cfg.cos_anneal_ratio, s);
-		const float w = s.alpha * T;
 #pragma unroll
-		for (int e = 0; e < 3; ++e) rgb2[e] += w * s.rgb[e];
-		T *= (1.f - s.alpha);
-		float g[16];
-#pragma unroll
-		for (int k = 0; k < 16; ++k) g[k] = 0.f;
-		float dla = gws * (1.0f - ws);
+		for (int e = 0; e < 3; ++e) bg[e] = srgb_to_linear(bg[e]);
+		read_rgba(ds, img, xy, tex);
 #pragma unroll
 		for (int e = 0; e < 3; ++e) {
-			const float suffix = rgb_ray[e] - rgb2[e];
-			g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
-			dla += lgg[e] * (T * s.rgb[e] - suffix);
+			target[e] = linear_to_srgb(tex[e] + (1.0f - tex[3]) * bg[e]);
+			bg[e] = linear_to_srgb(bg[e]);
 		}
-		dla /= (1.0f - s.alpha + 1e-5f);
-		float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
-		if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {
-			const float P = __expf(s.inv_s * s.iter_cos * s.dt);
-			const float E = __expf(-s.next_sdf * s.inv_s);
-			dE_dsdf = -s.inv_s * E;
-			dE_ds = -s.next_sdf * E;
-			const float a = 1 + E, b = 1 + P * E, cc = 1e-5f + 1 / (1 + P * E);
-			const float delta = a * (b * b) * (cc * cc);
-			da_dE = -(P / delta - 1 / (a * a * cc));
-			da_dP = -E / delta;
-			dP_ds = P * s.iter_cos * s.dt;
-			dP_dic = P * s.inv_s * s.dt;
-			dE_dic = -s.inv_s * E * s.dt * 0.5f;
+		float rgb_ray[3] = {c.rgb[0], c.rgb[1], c.rgb[2]};
+		if (c.full) {
+#pragma unroll
+			for (int e = 0; e < 3; ++e) rgb_ray[e] += c.T * bg[e];
 		}
-		const float dl_dinvs = dla * (da_dE * dE_ds + da_dP * dP_ds);
-		const float dl_dvar = dl_dinvs * s.inv_s * 10;
-		const float dic_dcos = s.true_cos >= 0 ? 0.0f : 1.0f;
-		const float gn = sqrtf(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2] + 1e-6f);
-		const float gni = 1 - 1 / gn;
-		const float dl_dnn = dla * (da_dE * dE_dic + dP_dic * da_dP) * dic_dcos;
-		g[3] = loss_scale * (dla * da_dE * dE_dsdf);
-		ek += (gn - 1.0f) * (gn - 1.0f);
+		// Huber(0.1) / 5 (:301-317, :1459)
+		float lgl[3], lgg[3];
 #pragma unroll
 		for (int e = 0; e < 3; ++e) {
-			g[4 + e] = cfg.ek_loss_weight * 2 * cfg.loss_scale * gni * s.nrm[e];
-			g[8 + e] = loss_scale * dl_dnn * dir[e];
+			const float diff = rgb_ray[e] - target[e], ad = fabsf(diff), al = 0.1f;
+			lgl[e] = (ad > al ? (ad - 0.5f * al) : 0.5f / al * diff * diff) / 5.0f;
+			lgg[e] = (ad > al ? (diff > 0 ? 1.0f : -1.0f) : diff / al) / 5.0f;
 		}
-		g[7] = loss_scale * dl_dvar;
-		__align__(16) __half gh[16];
+		const float mask_gt = tex[3] > 0.9999f ? 1.f : 0.f;
+		float gws, ws = c.weight_sum;
+		if (ws >= 1.0f - 1e-4f) {
+			ws = 1.0f - 1e-4f;
+			gws = 0.f;
+		} else if (ws <= 1e-4f) {
+			ws = 1e-4f;
+			gws = 0.f;
+		} else {
+			const float sg = 1.0f / (1.0f + expf(-ws));
+			gws = (mask_gt - sg) * ws * cfg.mask_loss_weight;
+		}
+		const float n_rays_f = (float)n_rays * (float)(cfg.ray_count_scale ? cfg.ray_count_scale : 1u);
+		if (lane == 0 && loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
+		const float loss_scale = cfg.loss_scale / n_rays_f;
+		float dir[3];
+		bent_dir(mlp_out, base, dir);
+		float rgb2c[3] = {0.f, 0.f, 0.f}, T = 1.f, ek = 0.f;
+		for (uint32_t j0 = 0; j0 < cn; j0 += 32) {
+			const uint32_t j = j0 + lane;
+			const bool valid = j < cn;
+			NeusSample s;
+			s.alpha = 0.f;
+			s.rgb[0] = s.rgb[1] = s.rgb[2] = 0.f;
+			if (valid) {
+				__align__(16) __half o[16];
+				load_out16(mlp_out + (size_t)(base + j) * 16, o);
+				const float* cin = coords + (size_t)(base + j) * 7;
+				float* cout = coords_out + (size_t)(compacted_base + j) * 7;
+				float cdt = 0.f;
 #pragma unroll
-		for (int k = 0; k < 16; ++k) gh[k] = __float2half_rn(g[k]);
-		uint4* dst = reinterpret_cast<uint4*>(dloss_dout + (size_t)(compacted_base + j) * 16);
-		dst[0] = reinterpret_cast<const uint4*>(gh)[0];
-		dst[1] = reinterpret_cast<const uint4*>(gh)[1];
+				for (int e = 0; e < 7; ++e) {
+					const float vv = cin[e];
+					cout[e] = vv;
+					if (e == 3) cdt = vv;
+				}
+				neus_sample(o, cdt, dir, cfg.cos_anneal_ratio, s);
+			}
+			const float om = 1.f - s.alpha;
+			const float Tb = serial_transmittance(T, om, lane);
+			const float w = valid ? s.alpha * Tb : 0.f;
+			const float Ta = Tb * om;  // transmittance after this sample
+			float rgb2[3];
+#pragma unroll
+			for (int e = 0; e < 3; ++e) rgb2[e] = rgb2c[e] + warp_incl_scan(w * s.rgb[e], lane);
+			if (valid) {
+				float g[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k) g[k] = 0.f;
+				float dla = gws * (1.0f - ws);
+#pragma unroll
+				for (int e = 0; e < 3; ++e) {
+					const float suffix = rgb_ray[e] - rgb2[e];
+					g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
+					dla += lgg[e] * (Ta * s.rgb[e] - suffix);
+				}
+				dla /= (1.0f - s.alpha + 1e-5f);
+				float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
+				if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {
+					const float P = __expf(s.inv_s * s.iter_cos * s.dt);
+					const float E = __expf(-s.next_sdf * s.inv_s);
+					dE_dsdf = -s.inv_s * E;
+					dE_ds = -s.next_sdf * E;
+					const float a = 1 + E, b = 1 + P * E, cc = 1e-5f + 1 / (1 + P * E);
+					const float delta = a * (b * b) * (cc * cc);
+					da_dE = -(P / delta - 1 / (a * a * cc));
+					da_dP = -E / delta;
+					dP_ds = P * s.iter_cos * s.dt;
+					dP_dic = P * s.inv_s * s.dt;
+					dE_dic = -s.inv_s * E * s.dt * 0.5f;
+				}
+				const float dl_dinvs = dla * (da_dE * dE_ds + da_dP * dP_ds);
+				const float dl_dvar = dl_dinvs * s.inv_s * 10;
+				const float dic_dcos = s.true_cos >= 0 ? 0.0f : 1.0f;
+				const float gn = sqrtf(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2] + 1e-6f);
+				const float gni = 1 - 1 / gn;
+				const float dl_dnn = dla * (da_dE * dE_dic + dP_dic * da_dP) * dic_dcos;
+				g[3] = loss_scale * (dla * da_dE * dE_dsdf);
+				ek += (gn - 1.0f) * (gn - 1.0f);
+#pragma unroll
+				for (int e = 0; e < 3; ++e) {
+					g[4 + e] = cfg.ek_loss_weight * 2 * cfg.loss_scale * gni * s.nrm[e];
+					g[8 + e] = loss_scale * dl_dnn * dir[e];
+				}
+				g[7] = loss_scale * dl_dvar;
+				__align__(16) __half gh[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k) gh[k] = __float2half_rn(g[k]);
+				uint4* dst = reinterpret_cast<uint4*>(dloss_dout + (size_t)(compacted_base + j) * 16);
+				dst[0] = reinterpret_cast<const uint4*>(gh)[0];
+				dst[1] = reinterpret_cast<const uint4*>(gh)[1];
+			}
+			// carry to the next chunk
+#pragma unroll
+			for (int e = 0; e < 3; ++e) rgb2c[e] = __shfl_sync(kFull, rgb2[e], 31);
+			T = __shfl_sync(kFull, Ta, 31);
+		}
+		ek = warp_sum(ek);
+		if (lane == 0 && ek_loss_out) ek_loss_out[i] = ek / ((float)cn * n_rays_f);
 	}
-	if (ek_loss_out) ek_loss_out[i] = ek / ((float)cn * n_rays_f);
 }
 
 // fill_rollover / fill_rollover_and_rescale (call sites :3908-3916): pad [n_valid, n_target) with wrap-around copies
@@ -605,9 +673,9 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
 	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
+	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
+	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
 	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
 	                                                             ws->d_coords, ws->d_counters);
 	N2B_CHECK_LAUNCH();
@@ -622,15 +690,16 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 	if (n_rays == 0 || n_rays > ws->max_rays || max_compacted == 0) return NEUS2B_E_INVALID;
 	if (((uintptr_t)d_mlp_out | (uintptr_t)d_dloss_dout) & 15u) return NEUS2B_E_INVALID;
 	Pcg32 r{rng.state, rng.inc};
-	composite_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, ws->d_counters, (const __half*)d_mlp_out, ws->d_rays,
-	                                                          ws->d_numsteps, ws->d_coords, (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
+	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);  // 4 warps per CTA, one warp per ray, grid-stride
+	composite_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, ws->d_counters, (const __half*)d_mlp_out, ws->d_numsteps, ws->d_coords,
+	                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_scan_tmp);
+	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_counters, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	loss_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted, ws->d_counters,
-	                                                     (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
-	                                                     (const CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, d_coords_out,
-	                                                     (__half*)d_dloss_dout, d_loss, d_ek_loss);
+	loss_kernel<<<ray_ctas, 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted,
+	                                          ws->d_counters, (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
+	                                          (const CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, d_coords_out, (__half*)d_dloss_dout, d_loss,
+	                                          d_ek_loss);
 	N2B_CHECK_LAUNCH();
 	if (rollover) {
 		rollover_tail_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, d_coords_out, (__half*)d_dloss_dout);
