@@ -167,6 +167,21 @@ typedef struct {
 int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
                             uint32_t n_rays_total, neus2b_pcg32 rng, const uint8_t* d_bitfield, neus2b_ray_workspace* ws,
                             neus2b_stream_t stream);
+/* No counterpart in the reference.  Same result as neus2b_generate_samples, for hosts that cannot give the library any
+ * scratch memory: callers that have handed the whole device to their own allocator, or that may not call cudaMalloc
+ * after start-up because it synchronises the device and can fail late.  The generator's scratch (per-ray staging
+ * records and prefix-sum keys, about 2.5 MiB) sits in static device arrays inside the library, so this call allocates
+ * nothing -- no cudaMalloc, no cudaFree, no allocating library routine -- and takes at most NEUS2B_STATIC_MAX_RAYS rays
+ * (more returns NEUS2B_E_TOO_LARGE).  The first call on a device looks the arrays' addresses up
+ * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls on a device share the arrays:
+ * calls that overlap on the GPU race, so issue them one after another on one stream.
+ * Outputs (caller-allocated): d_ray_indices [n_rays], d_rays [n_rays][6], d_numsteps [n_rays][2],
+ * d_coords [max_samples][7], d_counters [8] (layout as in neus2b_ray_workspace). */
+#define NEUS2B_STATIC_MAX_RAYS 65536u
+int neus2b_generate_samples_static(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays,
+                                   const uint32_t* d_n_rays, uint32_t n_rays_total, neus2b_pcg32 rng, const uint8_t* d_bitfield,
+                                   uint32_t max_samples, uint32_t* d_ray_indices, float* d_rays, uint32_t* d_numsteps,
+                                   float* d_coords, uint32_t* d_counters, neus2b_stream_t stream);
 /* compute_loss_kernel_train_nerf_with_global_movement (src/testbed_nerf.cu:1465-1996) followed by fill_rollover /
  * fill_rollover_and_rescale (:3908-3916).  d_mlp_out [samples][16] fp16 from neus2b_neus_forward on ws->d_coords.
  * Writes d_coords_out [max_compacted][7], d_dloss_dout [max_compacted][16] fp16, per-ray d_loss / d_ek_loss [max_rays]. */

@@ -7,6 +7,8 @@
 //
 // This file is compiled with -fmad=false: the DDA decides integer step counts from fp32 arithmetic, so every
 // operation is a single IEEE operation in a fixed order (fused multiply-adds only where written explicitly).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace n2b {
@@ -707,5 +709,73 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 		rollover_head_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, (__half*)d_dloss_dout);
 		N2B_CHECK_LAUNCH();
 	}
+	return NEUS2B_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Sample generation for callers that cannot allocate.
+//
+// Some hosts of this library own every byte of device memory themselves: a renderer or trainer that carved the whole
+// GPU into its own arena at start-up, or a process that is not allowed to call cudaMalloc once it is running because
+// the call synchronises the device and can fail late.  Such a caller can hand over buffers for inputs and outputs,
+// but it has no pool to take the generator's scratch from (the per-ray staging records and the prefix-sum keys).  For
+// them the scratch lives in the two file-scope device arrays below.  Every GPU that loads the library holds them
+// (about 2.5 MiB) until the process exits, and the ray count per call is limited to NEUS2B_STATIC_MAX_RAYS.
+//
+// The arrays are shared by every call on a device: two calls whose kernels overlap on the GPU (different streams,
+// different threads) race on them, so issue calls to this entry point one after the other on one stream.  Nothing in
+// the scratch has to start at zero: each element a kernel reads was written earlier in the same call, so whatever the
+// previous call left behind is harmless.
+namespace {
+constexpr uint32_t kStaticMaxRays = 65536;  // == NEUS2B_STATIC_MAX_RAYS
+static __device__ __align__(256) uint64_t g_static_scan[kStaticMaxRays + 1024];
+static __device__ __align__(256) float g_static_ray_tmp[(size_t)kStaticMaxRays * 8];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+uint64_t* g_static_scan_ptr[kMaxDevices] = {};
+float* g_static_ray_tmp_ptr[kMaxDevices] = {};
+
+// In host code the array names above are host-side stand-ins, not device addresses; the addresses the kernels need
+// come from cudaGetSymbolAddress, looked up once per device with that device current.
+int static_scratch(uint64_t** scan, float** ray_tmp) {
+	int dev = -1;
+	N2B_CHECK_CUDA(cudaGetDevice(&dev));
+	if (dev < 0 || dev >= kMaxDevices) return NEUS2B_E_UNSUPPORTED;
+	std::lock_guard<std::mutex> lock(g_static_mutex);
+	if (!g_static_scan_ptr[dev]) {
+		void *a = nullptr, *b = nullptr;
+		N2B_CHECK_CUDA(cudaGetSymbolAddress(&a, g_static_scan));
+		N2B_CHECK_CUDA(cudaGetSymbolAddress(&b, g_static_ray_tmp));
+		g_static_scan_ptr[dev] = (uint64_t*)a;
+		g_static_ray_tmp_ptr[dev] = (float*)b;
+	}
+	*scan = g_static_scan_ptr[dev];
+	*ray_tmp = g_static_ray_tmp_ptr[dev];
+	return NEUS2B_OK;
+}
+}  // namespace
+
+extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays,
+                                              const uint32_t* d_n_rays, uint32_t n_rays_total, neus2b_pcg32 rng, const uint8_t* d_bitfield,
+                                              uint32_t max_samples, uint32_t* d_ray_indices, float* d_rays, uint32_t* d_numsteps,
+                                              float* d_coords, uint32_t* d_counters, neus2b_stream_t stream) {
+	if (!ds || !cfg || !d_bitfield || !d_ray_indices || !d_rays || !d_numsteps || !d_coords || !d_counters) return NEUS2B_E_INVALID;
+	if (n_rays == 0 || max_samples == 0 || ds->n_images == 0) return NEUS2B_E_INVALID;
+	if (n_rays > kStaticMaxRays) return NEUS2B_E_TOO_LARGE;  // the built-in scratch holds NEUS2B_STATIC_MAX_RAYS rays
+	uint64_t* scan = nullptr;
+	float* ray_tmp = nullptr;
+	int rc = static_scratch(&scan, &ray_tmp);
+	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaMemsetAsync(d_counters, 0, 8 * sizeof(uint32_t), stream));
+	Pcg32 r{rng.state, rng.inc};
+	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
+	                                                            (RayTmp*)ray_tmp, scan);
+	N2B_CHECK_LAUNCH();
+	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
+	N2B_CHECK_LAUNCH();
+	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
+	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters);
+	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }

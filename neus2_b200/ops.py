@@ -126,6 +126,15 @@ def generate_samples(ds, cfg, n_rays, n_rays_total, rng, bitfield, batch, n_rays
                                             L.ptr(bitfield), C.byref(batch.ws), L.cur_stream()))
 
 
+def generate_samples_static(ds, cfg, n_rays, n_rays_total, rng, bitfield, max_samples, ray_indices, rays, numsteps, coords,
+                            counters, n_rays_dev=None):
+    """neus2b_generate_samples_static: same outputs, scratch inside the library (no allocation; at most
+    NEUS2B_STATIC_MAX_RAYS rays)."""
+    L.check(L.lib().neus2b_generate_samples_static(C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total),
+                                                   rng, L.ptr(bitfield), u32(max_samples), L.ptr(ray_indices), L.ptr(rays),
+                                                   L.ptr(numsteps), L.ptr(coords), L.ptr(counters), L.cur_stream()))
+
+
 def compute_loss(ds, cfg, n_rays, n_rays_total, rng, max_compacted, mlp_out, batch, coords_out, dloss, loss=None, ek_loss=None,
                  rollover=True, n_rays_dev=None):
     L.check(L.lib().neus2b_compute_loss(C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total), rng,
