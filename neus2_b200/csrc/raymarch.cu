@@ -149,69 +149,146 @@ struct RayTmp {  // 8 floats per ray
 	uint32_t numsteps;
 };
 
+// One warp marches one ray.  The reference's loop visits a sequence of ray parameters t defined by the serial recurrence
+// t <- t + calc_dt(t); at a visited t it either takes a sample (occupied cell) or jumps: it keeps adding steps until t
+// reaches the far side of the empty cell (advance_to_next_voxel).  Here the 32 lanes evaluate 32 consecutive t of that
+// same recurrence at once (position, containment, occupancy bit, jump target: the expensive, independent part), then
+// every lane replays the visit / jump decisions over the chunk in ray order, which is cheap and keeps the result
+// identical to the serial loop: same visited set, same samples, same count.
+template <bool EMIT>
+__device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
+                                              const uint8_t* __restrict__ bitfield, uint32_t limit, float* __restrict__ coords_out,
+                                              int lane) {
+	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
+	const float cone_angle = cfg.cone_angle_constant;
+	float t_chunk = startt, skip_until = -3.402823466e+38f;
+	uint32_t j = 0;
+	bool stop = false;
+	// every chunk moves t forward by at least 32 minimum steps, so the ray leaves the box after a bounded number of
+	// chunks; the cap only guards against non-finite inputs
+	for (uint32_t chunk = 0; chunk < 8192u && !stop; ++chunk) {
+		// this lane's candidate: t after `lane` steps of the recurrence from the chunk start
+		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
+#pragma unroll
+		for (int k = 0; k < 32; ++k) {
+			const float dt = calc_dt(t, cone_angle);
+			if (lane == k) {
+				my_t = t;
+				my_dt = dt;
+			}
+			t += dt;
+		}
+		float pos[3];
+#pragma unroll
+		for (int e = 0; e < 3; ++e) pos[e] = o[e] + my_t * dirn[e];
+		const bool inside = aabb_contains(cfg.aabb_min, cfg.aabb_max, pos);
+		bool occ = false;
+		float target = 0.f;
+		if (inside) {
+			const uint32_t mip = (uint32_t)mip_from_dt(my_dt, pos);
+			occ = occupied_at(pos, bitfield, mip);
+			if (!occ) {  // far side of the empty cell: distance_to_next_voxel (:346-354)
+				const uint32_t res = NEUS2B_GRIDSIZE >> mip;
+				float tt[3];
+#pragma unroll
+				for (int d = 0; d < 3; ++d) {
+					const float p = (float)res * pos[d];
+					tt[d] = (floorf(p + 0.5f + 0.5f * copysignf(1.0f, dirn[d])) - p) * idir[d];
+				}
+				const float tmin = fminf(fminf(tt[0], tt[1]), tt[2]);
+				target = my_t + fmaxf(tmin / (float)res, 0.0f);
+			}
+		}
+		const uint32_t in_mask = __ballot_sync(0xffffffffu, inside), occ_mask = __ballot_sync(0xffffffffu, occ);
+		// replay the chunk in ray order (identical in every lane)
+		bool emit = false;
+		uint32_t slot = 0;
+		t = t_chunk;
+#pragma unroll 4
+		for (int k = 0; k < 32; ++k) {
+			const float tk = t;
+			t += calc_dt(t, cone_angle);
+			if (stop || tk < skip_until) continue;  // not visited: the reference was still jumping here
+			if (!((in_mask >> k) & 1u) || j >= limit) {
+				stop = true;
+				continue;
+			}
+			if ((occ_mask >> k) & 1u) {
+				if (lane == k) {
+					emit = true;
+					slot = j;
+				}
+				++j;
+			} else {
+				skip_until = __shfl_sync(0xffffffffu, target, k);
+			}
+		}
+		t_chunk = t;
+		if (EMIT && emit) {
+			float* c = coords_out + (size_t)slot * 7;
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				c[e] = (pos[e] - cfg.aabb_min[e]) / (cfg.aabb_max[e] - cfg.aabb_min[e]);  // warp_position
+				c[4 + e] = (dirn[e] + 1.f) * 0.5f;                                          // warp_direction
+			}
+			c[3] = warp_dt(my_dt);
+		}
+	}
+	return j;
+}
+
 // First half of generate_training_samples_nerf_with_global_movement (:1287-1409): build the ray and count its steps.
 __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
                                                           const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
-                                                          const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng,
+                                                          const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
                                                           const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
                                                           uint64_t* __restrict__ scan_in) {
-	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+	const int lane = threadIdx.x & 31;
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
-	if (i >= n_rays_max) return;
-	if (i >= n_rays) return;
-	RayTmp r;
-	r.numsteps = 0;
-	r.startt = 0.f;
-	const uint32_t ig = i + cfg.ray_index_offset;
-	const uint32_t img = image_idx(ig, n_rays, n_rays_total, ds.n_images);
-	rng.advance((uint64_t)ig * 8u);
-	float xy[2], rgba[4];
-	random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
-	read_rgba(ds, img, xy, rgba);
-	bool keep = !(rgba[0] <= 0.0f && rng.next_float() >= 0.9f);
-	if (keep) {
-		(void)rng.next_float();  // motion-blur time (:1307)
-		const float* X = ds.d_xforms + (size_t)img * 12;
-		const float fx = ds.d_focal[img * 2], fy = ds.d_focal[img * 2 + 1];
-		const float ppx = ds.d_principal[img * 2], ppy = ds.d_principal[img * 2 + 1];
-		const float dl[3] = {(xy[0] - ppx) * (float)ds.width / fx, (xy[1] - ppy) * (float)ds.height / fy, 1.0f};
-		float dirn[3];
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
+		RayTmp r;
+		r.numsteps = 0;
+		r.startt = 0.f;
 #pragma unroll
-		for (int e = 0; e < 3; ++e) {
-			r.o[e] = X[9 + e];
-			r.d[e] = X[0 + e] * dl[0] + X[3 + e] * dl[1] + X[6 + e] * dl[2];
-		}
-		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+		for (int e = 0; e < 3; ++e) r.o[e] = r.d[e] = 0.f;
+		const uint32_t ig = i + cfg.ray_index_offset;
+		const uint32_t img = image_idx(ig, n_rays, n_rays_total, ds.n_images);
+		Pcg32 rng = rng0;
+		rng.advance((uint64_t)ig * 8u);
+		float xy[2], rgba[4];
+		random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
+		read_rgba(ds, img, xy, rgba);
+		const bool keep = !(rgba[0] <= 0.0f && rng.next_float() >= 0.9f);
+		if (keep) {  // uniform across the warp: every lane computes the same ray
+			(void)rng.next_float();  // motion-blur time (:1307)
+			const float* X = ds.d_xforms + (size_t)img * 12;
+			const float fx = ds.d_focal[img * 2], fy = ds.d_focal[img * 2 + 1];
+			const float ppx = ds.d_principal[img * 2], ppy = ds.d_principal[img * 2 + 1];
+			const float dl[3] = {(xy[0] - ppx) * (float)ds.width / fx, (xy[1] - ppy) * (float)ds.height / fy, 1.0f};
+			float dirn[3];
 #pragma unroll
-		for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
-		float tmin, tmax;
-		aabb_ray_intersect(cfg.aabb_min, cfg.aabb_max, r.o, dirn, tmin, tmax);
-		const float cone_angle = cfg.cone_angle_constant;
-		tmin = fmaxf(tmin, 0.0f);
-		float startt = tmin;
-		startt += calc_dt(startt, cone_angle) * rng.next_float();
-		const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
-		uint32_t j = 0;
-		float t = startt, pos[3];
-		for (;;) {
-#pragma unroll
-			for (int e = 0; e < 3; ++e) pos[e] = r.o[e] + t * dirn[e];
-			if (!(aabb_contains(cfg.aabb_min, cfg.aabb_max, pos) && j < NEUS2B_STEPS)) break;
-			const float dt = calc_dt(t, cone_angle);
-			const uint32_t mip = (uint32_t)mip_from_dt(dt, pos);
-			if (occupied_at(pos, bitfield, mip)) {
-				++j;
-				t += dt;
-			} else {
-				t = advance_to_next_voxel(t, cone_angle, pos, dirn, idir, NEUS2B_GRIDSIZE >> mip);
+			for (int e = 0; e < 3; ++e) {
+				r.o[e] = X[9 + e];
+				r.d[e] = X[0 + e] * dl[0] + X[3 + e] * dl[1] + X[6 + e] * dl[2];
 			}
+			const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+#pragma unroll
+			for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+			float tmin, tmax;
+			aabb_ray_intersect(cfg.aabb_min, cfg.aabb_max, r.o, dirn, tmin, tmax);
+			tmin = fmaxf(tmin, 0.0f);
+			float startt = tmin;
+			startt += calc_dt(startt, cfg.cone_angle_constant) * rng.next_float();
+			r.startt = startt;
+			r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane);
 		}
-		r.startt = startt;
-		r.numsteps = j;
+		if (lane == 0) {
+			tmp[i] = r;
+			scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
+		}
 	}
-	tmp[i] = r;
-	scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
 }
 
 // Exclusive prefix sum of n 64-bit keys, n read on the device (the live ray count is a few thousand once the batch
@@ -268,54 +345,34 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
                                                            const uint64_t* __restrict__ scan, uint32_t* __restrict__ ray_indices,
                                                            float* __restrict__ rays, uint32_t* __restrict__ numsteps,
                                                            float* __restrict__ coords, uint32_t* __restrict__ counters) {
-	const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-	if (i == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps found, dropped rays included
-	if (i >= (d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max)) return;
-	const RayTmp r = tmp[i];
-	if (r.numsteps == 0) return;
-	const uint64_t key = scan[i];
-	const uint32_t base = (uint32_t)(key & 0xFFFFFFFFull), kidx = (uint32_t)(key >> 32);
-	if (base + r.numsteps > max_samples) {  // sample buffer exhausted: drop the ray (:1412-1414)
-		atomicOr(&counters[3], 1u);
-		return;
-	}
-	atomicMax(&counters[0], kidx + 1u);
-	atomicMax(&counters[4], base + r.numsteps);
-	ray_indices[kidx] = i;
-#pragma unroll
-	for (int e = 0; e < 3; ++e) {
-		rays[(size_t)kidx * 6 + e] = r.o[e];
-		rays[(size_t)kidx * 6 + 3 + e] = r.d[e];
-	}
-	numsteps[kidx * 2 + 0] = r.numsteps;
-	numsteps[kidx * 2 + 1] = base;
-	const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
-	const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
-	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
-	const float wd[3] = {(dirn[0] + 1.f) * 0.5f, (dirn[1] + 1.f) * 0.5f, (dirn[2] + 1.f) * 0.5f};
-	const float cone_angle = cfg.cone_angle_constant;
-	float* co = coords + (size_t)base * 7;
-	float t = r.startt, pos[3];
-	uint32_t j = 0;
-	for (;;) {
-#pragma unroll
-		for (int e = 0; e < 3; ++e) pos[e] = r.o[e] + t * dirn[e];
-		if (!(aabb_contains(cfg.aabb_min, cfg.aabb_max, pos) && j < r.numsteps)) break;
-		const float dt = calc_dt(t, cone_angle);
-		const uint32_t mip = (uint32_t)mip_from_dt(dt, pos);
-		if (occupied_at(pos, bitfield, mip)) {
-			float* c = co + (size_t)j * 7;
+	const int lane = threadIdx.x & 31;
+	if (blockIdx.x == 0 && threadIdx.x == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps, dropped rays included
+	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
+		const RayTmp r = tmp[i];
+		if (r.numsteps == 0) continue;
+		const uint64_t key = scan[i];
+		const uint32_t base = (uint32_t)(key & 0xFFFFFFFFull), kidx = (uint32_t)(key >> 32);
+		if (base + r.numsteps > max_samples) {  // sample buffer exhausted: drop the ray (:1412-1414)
+			if (lane == 0) atomicOr(&counters[3], 1u);
+			continue;
+		}
+		if (lane == 0) {
+			atomicMax(&counters[0], kidx + 1u);
+			atomicMax(&counters[4], base + r.numsteps);
+			ray_indices[kidx] = i;
 #pragma unroll
 			for (int e = 0; e < 3; ++e) {
-				c[e] = (pos[e] - cfg.aabb_min[e]) / (cfg.aabb_max[e] - cfg.aabb_min[e]);  // warp_position
-				c[4 + e] = wd[e];
+				rays[(size_t)kidx * 6 + e] = r.o[e];
+				rays[(size_t)kidx * 6 + 3 + e] = r.d[e];
 			}
-			c[3] = warp_dt(dt);
-			++j;
-			t += dt;
-		} else {
-			t = advance_to_next_voxel(t, cone_angle, pos, dirn, idir, NEUS2B_GRIDSIZE >> mip);
+			numsteps[kidx * 2 + 0] = r.numsteps;
+			numsteps[kidx * 2 + 1] = base;
 		}
+		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+		const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
+		march_ray<true>(cfg, r.o, dirn, r.startt, bitfield, r.numsteps, coords + (size_t)base * 7, lane);
 	}
 }
 
@@ -672,12 +729,12 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	if (n_rays == 0 || n_rays > ws->max_rays || ds->n_images == 0) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
-	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
+	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
 	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
+	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
 	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
 	                                                             ws->d_coords, ws->d_counters);
 	N2B_CHECK_LAUNCH();
@@ -769,12 +826,12 @@ extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const ne
 	if (rc) return rc;
 	N2B_CHECK_CUDA(cudaMemsetAsync(d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
-	count_steps_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
+	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
 	                                                            (RayTmp*)ray_tmp, scan);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
 	N2B_CHECK_LAUNCH();
-	emit_samples_kernel<<<div_up(n_rays, 128), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
+	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
 	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
