@@ -89,6 +89,11 @@ int neus2b_grid_backward_backward_input(const neus2b_grid_desc* desc, uint32_t n
  * n_hidden 1; :271 colour net: in_width 48, n_hidden 2).  d_hidden [n][n_hidden][64] fp16 may be NULL. */
 int neus2b_mlp_forward(uint32_t n, uint32_t in_width, uint32_t n_hidden, const uint16_t* d_weights, const uint16_t* d_in,
                        uint16_t* d_out, uint16_t* d_hidden, neus2b_stream_t stream);
+/* Same contract as neus2b_mlp_forward, computed with tcgen05.mma on 128-sample tiles with the accumulators in tensor memory
+ * (in_width 48 with 1 or 2 hidden layers, or 64 with 2).  d_status (optional, device uint32) gets bit 0 set if a bounded
+ * completion wait inside the kernel ran out. */
+int neus2b_mlp_forward_tcgen05(uint32_t n, uint32_t in_width, uint32_t n_hidden, const uint16_t* d_weights, const uint16_t* d_in,
+                               uint16_t* d_out, uint16_t* d_hidden, uint32_t* d_status, neus2b_stream_t stream);
 /* FullyFusedMLP::backward (nerf_network.h:229,340,402,509). d_dL_din [n][in_width] fp16 or NULL; d_wgrad fp32
  * [n_params of the net] or NULL (EGradientMode::Ignore). */
 int neus2b_mlp_backward(uint32_t n, uint32_t in_width, uint32_t n_hidden, const uint16_t* d_weights, const uint16_t* d_in,

@@ -5,7 +5,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "_build", "libneus2b.so")
+LIB_PATH = os.environ.get("NEUS2B_LIB", os.path.join(HERE, "_build", "libneus2b.so"))
 
 MLP_N = 12288
 GRID_OFF = 12288
@@ -72,7 +72,7 @@ _lib = None
 EXPORTS = [
     "neus2b_version", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
     "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
-    "neus2b_mlp_forward", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
+    "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
     "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_adam_step",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",

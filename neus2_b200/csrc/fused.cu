@@ -145,24 +145,98 @@ __device__ void stage_weights(WeightsSmem& w, const __half* params, int tid, int
 	}
 }
 
-// Encoding of the warp's 16 samples into columns [0, 32) of Zs.
-__device__ __forceinline__ void encode_tile(const GridLevels& lv, const __half* grid, const float* x, int s, int hl, __half* Zs) {
-#pragma unroll 2
+// Per (sample, level) geometry, factored so that a corner costs a handful of integer / fp32 operations:
+// index = combine(hx[bx], hy[by], hz[bz]), weight = ax[bx] * ay[by] * az[bz].
+struct LevelGeom {
+	uint32_t hx[2], hy[2], hz[2];
+	float ax[2], ay[2], az[2];
+	uint32_t mask_or_size, offset;
+	bool hashed;
+};
+
+__device__ __forceinline__ LevelGeom level_geom(const GridLevels& lv, uint32_t l, const float* x) {
+	LevelGeom g;
+	const Cell c = level_cell(lv, l, x);
+	g.ax[0] = 1.0f - c.f[0];
+	g.ax[1] = c.f[0];
+	g.ay[0] = 1.0f - c.f[1];
+	g.ay[1] = c.f[1];
+	g.az[0] = 1.0f - c.f[2];
+	g.az[1] = c.f[2];
+	g.hashed = lv.hashed[l] != 0;
+	g.offset = lv.offset[l];
+	if (g.hashed) {
+		g.hx[0] = c.c0[0];
+		g.hx[1] = c.c0[0] + 1u;
+		g.hy[0] = c.c0[1] * 2654435761u;
+		g.hy[1] = (c.c0[1] + 1u) * 2654435761u;
+		g.hz[0] = c.c0[2] * 805459861u;
+		g.hz[1] = (c.c0[2] + 1u) * 805459861u;
+		g.mask_or_size = lv.size[l] - 1u;
+	} else {
+		const uint32_t res = lv.res[l];
+		g.hx[0] = c.c0[0];
+		g.hx[1] = c.c0[0] + 1u;
+		g.hy[0] = c.c0[1] * res;
+		g.hy[1] = g.hy[0] + res;
+		g.hz[0] = c.c0[2] * res * res;
+		g.hz[1] = g.hz[0] + res * res;
+		g.mask_or_size = lv.size[l];
+	}
+	return g;
+}
+
+__device__ __forceinline__ uint32_t geom_index(const LevelGeom& g, uint32_t k) {
+	const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+	uint32_t idx;
+	if (g.hashed) {
+		idx = (g.hx[bx] ^ g.hy[by] ^ g.hz[bz]) & g.mask_or_size;
+	} else {
+		idx = g.hx[bx] + g.hy[by] + g.hz[bz];  // < 2 * size: a corner on the far cube face wraps once (== idx % size)
+		if (idx >= g.mask_or_size) idx -= g.mask_or_size;
+	}
+	return g.offset + idx;
+}
+
+// Encoding of the warp's 16 samples into columns [0, 32) of Zs.  With JAC the lane also keeps, per level it owns,
+// J[d][f] = d enc_f / d x_d (6 floats): the normal (d sdf/dx), and in the backward pass the second-order term
+// dL/d(d sdf/d enc) = J v, come from it without touching the grid again.
+template <bool JAC>
+__device__ __forceinline__ void encode_tile(const GridLevels& lv, const __half* grid, const float* x, int s, int hl, __half* Zs,
+                                            float (&J)[8][6]) {
+#pragma unroll
 	for (int j = 0; j < 8; ++j) {
 		const uint32_t l = 2 * j + hl;
 		__half2 feat = __floats2half2_rn(0.f, 0.f);
+		if (JAC) {
+#pragma unroll
+			for (int e = 0; e < 6; ++e) J[j][e] = 0.f;
+		}
 		if (l < lv.n_active) {
-			const Cell c = level_cell(lv, l, x);
+			const LevelGeom g = level_geom(lv, l, x);
 			__half2 th[8];
 #pragma unroll
-			for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, corner_index(lv, l, c, k));
+			for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, geom_index(g, k));
+			const float scale = lv.scale[l];
 			float a0 = 0.f, a1 = 0.f;
 #pragma unroll
 			for (uint32_t k = 0; k < 8; ++k) {
+				const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
 				const float2 t = __half22float2(th[k]);
-				const float w = corner_weight(c, k);
+				const float w = g.ax[bx] * g.ay[by] * g.az[bz];
 				a0 = __fmaf_rn(w, t.x, a0);
 				a1 = __fmaf_rn(w, t.y, a1);
+				if (JAC) {
+					const float dwx = (bx ? scale : -scale) * g.ay[by] * g.az[bz];
+					const float dwy = (by ? scale : -scale) * g.ax[bx] * g.az[bz];
+					const float dwz = (bz ? scale : -scale) * g.ax[bx] * g.ay[by];
+					J[j][0] = __fmaf_rn(dwx, t.x, J[j][0]);
+					J[j][1] = __fmaf_rn(dwx, t.y, J[j][1]);
+					J[j][2] = __fmaf_rn(dwy, t.x, J[j][2]);
+					J[j][3] = __fmaf_rn(dwy, t.y, J[j][3]);
+					J[j][4] = __fmaf_rn(dwz, t.x, J[j][4]);
+					J[j][5] = __fmaf_rn(dwz, t.y, J[j][5]);
+				}
 			}
 			feat = __floats2half2_rn(a0, a1);
 		}
@@ -224,7 +298,8 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == MODE_TRAIN ? 1 : 2) neus_
 			}
 		}
 		// ---- F1: encoding -> Zs[:, 0:32], xyz - 0.5 -> Zs[:, 32:35]
-		encode_tile(a.lv, grid, x, s, hl, T.Zs());
+		float J[8][6];
+		encode_tile<MODE != MODE_SDF>(a.lv, grid, x, s, hl, T.Zs(), J);
 		if (hl == 0) {
 #pragma unroll
 			for (int e = 0; e < 3; ++e)
@@ -272,25 +347,12 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == MODE_TRAIN ? 1 : 2) neus_
 			__syncwarp();
 			// ---- F6: normal = Gz[xyz] + (d enc / d x)^T Gz[enc]
 			float nrm[3] = {0.f, 0.f, 0.f};
-#pragma unroll 2
+#pragma unroll
 			for (int j = 0; j < 8; ++j) {
 				const uint32_t l = 2 * j + hl;
-				if (l < a.lv.n_active) {
-					const Cell c = level_cell(a.lv, l, x);
-					const float2 ge = __half22float2(*reinterpret_cast<const __half2*>(T.Gz() + s * LD48 + 2 * l));
-					__half2 th[8];
+				const float2 ge = __half22float2(*reinterpret_cast<const __half2*>(T.Gz() + s * LD48 + 2 * l));
 #pragma unroll
-					for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, corner_index(a.lv, l, c, k));
-#pragma unroll
-					for (uint32_t k = 0; k < 8; ++k) {
-						const float2 t = __half22float2(th[k]);
-						float dw[3];
-						corner_dweight(c, a.lv.scale[l], k, dw);
-						const float tg = t.x * ge.x + t.y * ge.y;
-#pragma unroll
-						for (int e = 0; e < 3; ++e) nrm[e] = __fmaf_rn(dw[e], tg, nrm[e]);
-					}
-				}
+				for (int e = 0; e < 3; ++e) nrm[e] = __fmaf_rn(J[j][2 * e], ge.x, __fmaf_rn(J[j][2 * e + 1], ge.y, nrm[e]));
 			}
 #pragma unroll
 			for (int e = 0; e < 3; ++e) {
@@ -445,35 +507,43 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == MODE_TRAIN ? 1 : 2) neus_
 				store_acc_half<48, false>(acc, T.dZs(), LD48, lane);
 			}
 			__syncwarp();
-			// ---- B6: grid gradient, first order (w_k * dZs) and second order ((grad w_k . v) * Gz) merged; U = dL/dGz
-#pragma unroll 2
+			// ---- B6: grid gradient, first order (w_k * dZs) and second order ((grad w_k . v) * Gz) merged into one
+			//      reduction per corner; U = dL/dGz = J v comes from the Jacobian kept since F1 (no second gather)
+#pragma unroll
 			for (int j = 0; j < 8; ++j) {
 				const uint32_t l = 2 * j + hl;
 				__half2 dy = __floats2half2_rn(0.f, 0.f);
 				if (l < a.lv.n_active) {
-					const Cell c = level_cell(a.lv, l, x);
-					const float2 ge = __half22float2(*reinterpret_cast<const __half2*>(T.Gz() + s * LD48 + 2 * l));
-					const float2 dz = __half22float2(*reinterpret_cast<const __half2*>(T.dZs() + s * LD48 + 2 * l));
-					uint32_t idx[8];
-					__half2 th[8];
+					dy = __floats2half2_rn(J[j][0] * v[0] + J[j][2] * v[1] + J[j][4] * v[2], J[j][1] * v[0] + J[j][3] * v[1] + J[j][5] * v[2]);
+					if (valid) {
+						const LevelGeom g = level_geom(a.lv, l, x);
+						const float2 ge = __half22float2(*reinterpret_cast<const __half2*>(T.Gz() + s * LD48 + 2 * l));
+						const float2 dz = __half22float2(*reinterpret_cast<const __half2*>(T.dZs() + s * LD48 + 2 * l));
+						const float scale = a.lv.scale[l];
+						// coef_k = grad w_k . v = q[bx][by] * az[bz] + p[bx][by] * bzv[bz],  w_k = p[bx][by] * az[bz]
+						const float bxv[2] = {-scale * v[0], scale * v[0]}, byv[2] = {-scale * v[1], scale * v[1]};
+						const float bzv[2] = {-scale * v[2], scale * v[2]};
 #pragma unroll
-					for (uint32_t k = 0; k < 8; ++k) {
-						idx[k] = corner_index(a.lv, l, c, k);
-						th[k] = ldg_h2(grid, idx[k]);
+						for (uint32_t k = 0; k < 8; ++k) {
+							const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+							const float p = g.ax[bx] * g.ay[by];
+							const float q = bxv[bx] * g.ay[by] + g.ax[bx] * byv[by];
+							const float w = p * g.az[bz];
+							const float coef = q * g.az[bz] + p * bzv[bz];
+#if defined(N2B_EXP_NO_COARSE)
+							if (l >= 8)
+#elif defined(N2B_EXP_NO_FINE)
+							if (l < 8)
+#elif defined(N2B_EXP_ONLY_L0_3)
+							if (l < 4)
+#endif
+#ifndef N2B_EXP_NO_SCATTER
+							red_add_h2(a.grad_grid, geom_index(g, k), __fmaf_rn(w, dz.x, coef * ge.x), __fmaf_rn(w, dz.y, coef * ge.y));
+#else
+							if (w == 123.f) a.grad_grid[geom_index(g, k)] = __float2half_rn(coef * ge.x + dz.x);
+#endif
+						}
 					}
-					float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-					for (uint32_t k = 0; k < 8; ++k) {
-						const float2 t = __half22float2(th[k]);
-						float dw[3];
-						corner_dweight(c, a.lv.scale[l], k, dw);
-						const float coef = dw[0] * v[0] + dw[1] * v[1] + dw[2] * v[2];
-						const float w = corner_weight(c, k);
-						a0 = __fmaf_rn(coef, t.x, a0);
-						a1 = __fmaf_rn(coef, t.y, a1);
-						if (valid) red_add_h2(a.grad_grid, idx[k], __fmaf_rn(w, dz.x, coef * ge.x), __fmaf_rn(w, dz.y, coef * ge.y));
-					}
-					dy = __floats2half2_rn(a0, a1);
 				}
 				*reinterpret_cast<__half2*>(T.U() + s * LD48 + 2 * l) = dy;
 			}

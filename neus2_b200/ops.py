@@ -52,6 +52,16 @@ def mlp_forward(in_w, n_hidden, w, inp):
     return out, hidden
 
 
+def mlp_forward_tcgen05(in_w, n_hidden, w, inp):
+    n = inp.shape[0]
+    out = _half((n, 16), inp.device)
+    hidden = _half((n, n_hidden, 64), inp.device)
+    status = torch.zeros(1, dtype=torch.int32, device=inp.device)
+    L.check(L.lib().neus2b_mlp_forward_tcgen05(u32(n), u32(in_w), u32(n_hidden), L.ptr(w), L.ptr(inp), L.ptr(out), L.ptr(hidden),
+                                               L.ptr(status), L.cur_stream()))
+    return out, hidden, status
+
+
 def mlp_backward(in_w, n_hidden, w, inp, hidden, dL_dout, wgrad=None, mode=L.GRAD_OVERWRITE, want_din=True):
     n = inp.shape[0]
     din = _half((n, in_w), inp.device) if want_din else None

@@ -131,6 +131,25 @@ def test_mlp_forward_backward(gpu, oracle, in_w, nh, n):
         check_grad("mlp_bwd_bwd_%d_%d" % (in_w, n), wg2.cpu().numpy(), wg2_ref, min_cos=0.9999, max_rel=5e-3)
 
 
+@pytest.mark.parametrize("in_w,nh,n", [(48, 1, 65536), (48, 2, 4113), (64, 2, 129), (48, 1, 1)])
+def test_mlp_forward_tcgen05(gpu, oracle, in_w, nh, n):
+    """The tcgen05 / TMEM forward against the oracle and against the mma.sync kernel."""
+    L, ops = gpu
+    O = oracle
+    rng = np.random.default_rng(in_w * 11 + nh)
+    npar = 64 * in_w + (nh - 1) * 4096 + 1024
+    w = O.f16_bits(rng.uniform(-0.3, 0.3, npar))
+    inp = O.f16_bits(rng.normal(0, 1, (n, in_w)))
+    out_ref, hid_ref = O.mlp_forward(in_w, nh, w, inp)
+    out, hid, status = ops.mlp_forward_tcgen05(in_w, nh, half(w), half(inp))
+    torch.cuda.synchronize()
+    assert status.item() == 0, "a bounded wait inside the tcgen05 kernel ran out"
+    check_fp16("mlp_tc_fwd_%d_%d_%d" % (in_w, nh, n), f32(out), O.bits_f32(out_ref))
+    check_fp16("mlp_tc_hid_%d_%d_%d" % (in_w, nh, n), f32(hid), O.bits_f32(hid_ref))
+    out2, hid2 = ops.mlp_forward(in_w, nh, half(w), half(inp))
+    check_fp16("mlp_tc_vs_mma_%d_%d_%d" % (in_w, nh, n), f32(out), f32(out2))
+
+
 def test_sh4(gpu, oracle):
     L, ops = gpu
     rng = np.random.default_rng(5)
