@@ -109,6 +109,15 @@ int neus2b_sh4_forward(uint32_t n, const float* d_dir01, uint32_t stride, uint16
 
 /* ---------------------------------------------------------------- fused NeuS graph (NerfNetwork) */
 
+/* Two implementations of the fused graph kernels exist: tcgen05.mma on 128-sample CTA tiles with accumulators in tensor
+ * memory (default) and mma.sync on 16-sample warp tiles.  Process-wide switch, for A/B measurements and tests. */
+#define NEUS2B_MMA_SYNC 0
+#define NEUS2B_MMA_TCGEN05 1
+int neus2b_set_mma_path(int path);
+int neus2b_get_mma_path(void);
+/* Sticky device-side error bits (bit 0: a bounded completion wait inside a tcgen05 kernel ran out). Synchronises. */
+int neus2b_device_error_flags(uint32_t* h_flags);
+
 /* NerfNetwork::inference_mixed_precision == forward_impl (nerf_network.h:87-90,132-315), static scene.
  * d_coords [n][7] fp32 (xyz, dt, dir in [0,1]); d_out [n][16] fp16 rows: 0-2 raw rgb, 3 sdf+bias, 4-6 normal,
  * 7 variance, 8-10 dir.  If d_n is non-NULL the sample count is read from it on the device (clamped to n). */

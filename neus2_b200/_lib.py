@@ -73,7 +73,7 @@ EXPORTS = [
     "neus2b_version", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
     "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
     "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
-    "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
+    "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_adam_step",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
@@ -96,6 +96,19 @@ def lib():
         _lib.neus2b_testbed_destroy.restype = None
         _lib.neus2b_testbed_destroy.argtypes = [C.c_void_p]
     return _lib
+
+
+MMA_SYNC, MMA_TCGEN05 = 0, 1
+
+
+def set_mma_path(path):
+    check(lib().neus2b_set_mma_path(C.c_int(path)))
+
+
+def device_error_flags():
+    v = C.c_uint32(0)
+    check(lib().neus2b_device_error_flags(C.byref(v)))
+    return int(v.value)
 
 
 def check(rc):

@@ -14,6 +14,7 @@
 // Internal column order of the SDF-net input is [encoding 0..31 | xyz-0.5 32..34 | zero 35..47] (the weight columns are
 // permuted to match while they are staged), so the per-level feature pair is 4-byte aligned.
 #include "common.cuh"
+#include "fused_common.cuh"
 #include "mma_tile.cuh"
 
 namespace n2b {
@@ -28,27 +29,6 @@ constexpr int C24 = 16 * LD16;
 // fp32 weight-gradient accumulators: row strides = 4 (mod 8) for conflict-free accumulation
 constexpr int GLD48 = 52;
 constexpr int GLD64 = 68;
-
-enum { MODE_FWD = 0, MODE_TRAIN = 1, MODE_SDF = 2 };
-
-struct NeusArgs {
-	GridLevels lv;
-	const __half* params;
-	uint32_t grid_entries;  // total grid entries (2 fp16 each)
-	float sdf_bias;
-	uint32_t n;
-	const uint32_t* d_n;
-	const float* coords;
-	uint32_t coord_stride;  // floats per sample (7 for NerfCoordinate, >=3 for positions only)
-	uint32_t dir_offset;
-	__half* out;
-	const __half* dL_dout;
-	float batch_size;
-	float* grad_mlp;
-	__half* grad_grid;
-	float* grad_var;
-	__half* sdf_out;
-};
 
 struct WeightsSmem {
 	__half W1s[64 * LD48];
@@ -125,9 +105,6 @@ struct SmemLayout<MODE_TRAIN> {
 	WarpTiles<MODE_TRAIN> t[kWarps];
 };
 
-// original column of the SDF-net input for internal column k
-__device__ __forceinline__ int sdf_orig_col(int k) { return k < 32 ? 3 + k : (k < 35 ? k - 32 : k); }
-
 __device__ void stage_weights(WeightsSmem& w, const __half* params, int tid, int nthreads) {
 	for (int e = tid; e < 64 * 48; e += nthreads) {
 		const int r = e / 48, k = e % 48;
@@ -143,59 +120,6 @@ __device__ void stage_weights(WeightsSmem& w, const __half* params, int tid, int
 		const int r = e / 64, k = e % 64;
 		w.W2c[r * LD64 + k] = params[NEUS2B_RGB_W2 + e];
 	}
-}
-
-// Per (sample, level) geometry, factored so that a corner costs a handful of integer / fp32 operations:
-// index = combine(hx[bx], hy[by], hz[bz]), weight = ax[bx] * ay[by] * az[bz].
-struct LevelGeom {
-	uint32_t hx[2], hy[2], hz[2];
-	float ax[2], ay[2], az[2];
-	uint32_t mask_or_size, offset;
-	bool hashed;
-};
-
-__device__ __forceinline__ LevelGeom level_geom(const GridLevels& lv, uint32_t l, const float* x) {
-	LevelGeom g;
-	const Cell c = level_cell(lv, l, x);
-	g.ax[0] = 1.0f - c.f[0];
-	g.ax[1] = c.f[0];
-	g.ay[0] = 1.0f - c.f[1];
-	g.ay[1] = c.f[1];
-	g.az[0] = 1.0f - c.f[2];
-	g.az[1] = c.f[2];
-	g.hashed = lv.hashed[l] != 0;
-	g.offset = lv.offset[l];
-	if (g.hashed) {
-		g.hx[0] = c.c0[0];
-		g.hx[1] = c.c0[0] + 1u;
-		g.hy[0] = c.c0[1] * 2654435761u;
-		g.hy[1] = (c.c0[1] + 1u) * 2654435761u;
-		g.hz[0] = c.c0[2] * 805459861u;
-		g.hz[1] = (c.c0[2] + 1u) * 805459861u;
-		g.mask_or_size = lv.size[l] - 1u;
-	} else {
-		const uint32_t res = lv.res[l];
-		g.hx[0] = c.c0[0];
-		g.hx[1] = c.c0[0] + 1u;
-		g.hy[0] = c.c0[1] * res;
-		g.hy[1] = g.hy[0] + res;
-		g.hz[0] = c.c0[2] * res * res;
-		g.hz[1] = g.hz[0] + res * res;
-		g.mask_or_size = lv.size[l];
-	}
-	return g;
-}
-
-__device__ __forceinline__ uint32_t geom_index(const LevelGeom& g, uint32_t k) {
-	const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
-	uint32_t idx;
-	if (g.hashed) {
-		idx = (g.hx[bx] ^ g.hy[by] ^ g.hz[bz]) & g.mask_or_size;
-	} else {
-		idx = g.hx[bx] + g.hy[by] + g.hz[bz];  // < 2 * size: a corner on the far cube face wraps once (== idx % size)
-		if (idx >= g.mask_or_size) idx -= g.mask_or_size;
-	}
-	return g.offset + idx;
 }
 
 // Encoding of the warp's 16 samples into columns [0, 32) of Zs.  With JAC the lane also keeps, per level it owns,
@@ -640,9 +564,26 @@ static int fill_common(NeusArgs& a, const neus2b_grid_desc* desc, const uint16_t
 	return NEUS2B_OK;
 }
 
+// tcgen05 / TMEM implementation of the same two kernels (fused_tc.cu)
+int launch_neus_tc_forward(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream);
+int launch_neus_tc_train(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream);
+int read_tc_error(uint32_t* h_flags);
+static int g_mma_path = NEUS2B_MMA_TCGEN05;
+
 }  // namespace n2b
 
 using namespace n2b;
+
+extern "C" int neus2b_set_mma_path(int path) {
+	if (path != NEUS2B_MMA_SYNC && path != NEUS2B_MMA_TCGEN05) return NEUS2B_E_INVALID;
+	g_mma_path = path;
+	return NEUS2B_OK;
+}
+extern "C" int neus2b_get_mma_path(void) { return g_mma_path; }
+extern "C" int neus2b_device_error_flags(uint32_t* h_flags) {
+	if (!h_flags) return NEUS2B_E_INVALID;
+	return read_tc_error(h_flags);
+}
 
 extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
                                    const uint32_t* d_n, const float* d_coords, uint16_t* d_out, neus2b_stream_t stream) {
@@ -657,6 +598,7 @@ extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t*
 	a.coord_stride = 7;
 	a.dir_offset = 4;
 	a.out = (__half*)d_out;
+	if (g_mma_path == NEUS2B_MMA_TCGEN05) return launch_neus_tc_forward(a, n, stream);
 	return launch_neus<MODE_FWD>(a, n, stream);
 }
 
@@ -678,6 +620,7 @@ extern "C" int neus2b_neus_train(const neus2b_grid_desc* desc, const uint16_t* d
 	a.grad_mlp = d_grad_mlp;
 	a.grad_grid = (__half*)d_grad_grid;
 	a.grad_var = d_grad_variance;
+	if (g_mma_path == NEUS2B_MMA_TCGEN05) return launch_neus_tc_train(a, n, stream);
 	return launch_neus<MODE_TRAIN>(a, n, stream);
 }
 

@@ -1,0 +1,511 @@
+// Fused NeuS graph kernels on tcgen05 / TMEM (NerfNetwork::forward_impl / backward_impl of the reference,
+// include/neural-graphics-primitives/nerf_network.h:132-641), sm_100a.
+//
+// A CTA of 256 threads owns a tile of 128 samples.  Thread t works for sample (t & 127): the two threads of a sample
+// split the 16 grid levels (gather, Jacobian, scatter) and the accumulator columns (epilogues).  Every dense
+// contraction of the graph is a tcgen05.mma chain issued by one thread with M = 128 (the samples), operands read from
+// shared memory in the core-matrix layout (tc05.cuh), fp32 accumulators in tensor memory:
+//   forward:  Hs = relu(Zs W1s^T), Ys = Hs W2s^T, Gz = S W1s (d y0 / d z), H1, H2 (, out) of the colour net;
+//   backward: input gradients dH2, dH1, dZc, dHs, dZs, the second-order T = D .* (U W1s^T);
+//   weight gradients: dW = D^T Z contracts over the 128 samples -- the activation tiles are read a second time as
+//             MN-major operands, and the five dW accumulators stay resident in tensor memory for the whole kernel
+//             (no shared-memory or register accumulators, no atomics until the final flush).
+// Weight matrices are staged once per CTA; as MN-major B operands they also serve the input-gradient GEMMs, so no
+// transposed copies exist.  Only rows 0..63 of a weight-gradient accumulator are meaningful (M is 128, the matrices
+// have 64 rows): the upper rows are computed from whatever follows the tile in shared memory and are never read.
+#include "common.cuh"
+#include "fused_common.cuh"
+#include "tc05.cuh"
+
+namespace n2b {
+namespace tcf {
+
+constexpr int kThreads = 256;
+constexpr int T48 = 128 * 48 * 2, T64 = 128 * 64 * 2, T16 = 128 * 16 * 2;
+
+static __device__ uint32_t g_tc_error;  // bit 0: a bounded completion wait ran out
+
+template <int MODE>
+struct Smem {
+	alignas(128) unsigned char W1s[64 * 48 * 2];
+	unsigned char W2s[16 * 64 * 2];
+	unsigned char W1c[64 * 48 * 2];
+	unsigned char W2c[64 * 64 * 2];
+	unsigned char W3c[16 * 64 * 2];
+	unsigned char Zs[T48];  // SDF-net input; training: later U
+	unsigned char Zc[T48];  // colour-net input
+	unsigned char Hs[T64];  // SDF hidden; inference: later H2
+	unsigned char X1[T64];  // S -> H1 -> (training) S again
+	unsigned char X2[MODE == MODE_TRAIN ? T64 : 16];  // H2 -> dH1
+	unsigned char X3[MODE == MODE_TRAIN ? T64 : 16];  // dH2 -> dHs -> T
+	unsigned char dY[MODE == MODE_TRAIN ? T16 : 16];  // dY3 -> dYs -> e0
+	float nrm[2][128][3];
+	float vbuf[128][4];
+	float red[8];
+	uint64_t mbar;
+	uint32_t tmem_base;
+	uint32_t pad;
+};
+
+__device__ __forceinline__ uint32_t sptr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+struct Opnd {
+	uint32_t addr, lbo, sbo, kstep, mn;
+};
+// [rows][C] tile as K-major operand (rows = M or N, columns = K) / as MN-major operand (columns = M or N, rows = K)
+__device__ __forceinline__ Opnd kmaj(const void* t, int C) { return Opnd{sptr(t), 128u, (uint32_t)C * 16u, 256u, 0u}; }
+__device__ __forceinline__ Opnd mnmaj(const void* t, int C) { return Opnd{sptr(t), (uint32_t)C * 16u, 128u, (uint32_t)C * 32u, 1u}; }
+
+template <int N>
+__device__ __forceinline__ void gemm(uint32_t d, const Opnd a, const Opnd b, int ksteps, bool accumulate) {
+	const uint32_t id = tc::idesc_f16(128, N, (int)a.mn, (int)b.mn);
+	for (int kk = 0; kk < ksteps; ++kk)
+		tc::mma_f16(d, tc::smem_desc(a.addr + kk * a.kstep, a.lbo, a.sbo), tc::smem_desc(b.addr + kk * b.kstep, b.lbo, b.sbo), id,
+		            (accumulate || kk > 0) ? 1u : 0u);
+}
+
+__device__ __forceinline__ void st16(unsigned char* tile, int row, int col, int C, const __half* h8) {
+	*reinterpret_cast<uint4*>(tile + tc::blk_off(row, col, C)) = *reinterpret_cast<const uint4*>(h8);
+}
+
+// Accumulator columns [c0, c0+32) of this thread's row -> fp16 tile row.  ACT: 0 = plain, 1 = ReLU (returns the mask of
+// positive outputs), 2 = multiply by the given mask bits (ReLU backward).
+template <int ACT>
+__device__ __forceinline__ uint32_t epilogue32(uint32_t taddr, int row, int c0, unsigned char* tile, uint32_t mask_in) {
+	uint32_t mask_out = 0;
+#pragma unroll
+	for (int q = 0; q < 2; ++q) {
+		float v[16];
+		tc::tmem_ld16(taddr + c0 + 16 * q, v);
+		tc::tmem_ld_wait();
+		__align__(16) __half h[16];
+#pragma unroll
+		for (int e = 0; e < 16; ++e) {
+			float x = v[e];
+			if (ACT == 1) x = fmaxf(x, 0.f);
+			__half hx = __float2half_rn(x);
+			if (ACT == 1 && __half2float(hx) > 0.f) mask_out |= 1u << (16 * q + e);
+			if (ACT == 2 && !((mask_in >> (16 * q + e)) & 1u)) hx = __float2half_rn(0.f);
+			h[e] = hx;
+		}
+		st16(tile, row, c0 + 16 * q, 64, h);
+		st16(tile, row, c0 + 16 * q + 8, 64, h + 8);
+	}
+	return mask_out;
+}
+
+// S[row][c0 .. c0+32) = mask ? W2s[0][c] : 0   (W2s row 0 read from the staged, blocked weight tile)
+__device__ __forceinline__ void write_S(const unsigned char* W2s, unsigned char* tile, int row, int c0, uint32_t mask) {
+#pragma unroll
+	for (int q = 0; q < 4; ++q) {
+		const int c = c0 + 8 * q;
+		__align__(16) __half w[8];
+		*reinterpret_cast<uint4*>(w) = *reinterpret_cast<const uint4*>(W2s + tc::blk_off(0, c, 64));
+#pragma unroll
+		for (int e = 0; e < 8; ++e)
+			if (!((mask >> (8 * q + e)) & 1u)) w[e] = __float2half_rn(0.f);
+		st16(tile, row, c, 64, w);
+	}
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) {
+	extern __shared__ __align__(128) unsigned char smem_raw[];
+	Smem<MODE>& sm = *reinterpret_cast<Smem<MODE>*>(smem_raw);
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int s = tid & 127, hl = tid >> 7;
+	const __half* grid = a.params + NEUS2B_GRID_OFF;
+	constexpr uint32_t kTmemCols = MODE == MODE_TRAIN ? 512u : 128u;
+
+	// ---- one-time set-up: zero the tiles (padding columns stay zero), stage the weights, allocate tensor memory
+	for (int e = tid; e < (int)(sizeof(Smem<MODE>) / 16); e += kThreads) reinterpret_cast<uint4*>(smem_raw)[e] = make_uint4(0, 0, 0, 0);
+	__syncthreads();
+	for (int e = tid; e < 64 * 48; e += kThreads) {
+		const int r = e / 48, k = e % 48;
+		*reinterpret_cast<__half*>(sm.W1s + tc::blk_off(r, k, 48)) = a.params[NEUS2B_SDF_W1 + r * 48 + sdf_orig_col(k)];
+		*reinterpret_cast<__half*>(sm.W1c + tc::blk_off(r, k, 48)) = a.params[NEUS2B_RGB_W1 + e];
+	}
+	for (int e = tid; e < 16 * 64; e += kThreads) {
+		*reinterpret_cast<__half*>(sm.W2s + tc::blk_off(e / 64, e % 64, 64)) = a.params[NEUS2B_SDF_W2 + e];
+		*reinterpret_cast<__half*>(sm.W3c + tc::blk_off(e / 64, e % 64, 64)) = a.params[NEUS2B_RGB_W3 + e];
+	}
+	for (int e = tid; e < 64 * 64; e += kThreads)
+		*reinterpret_cast<__half*>(sm.W2c + tc::blk_off(e / 64, e % 64, 64)) = a.params[NEUS2B_RGB_W2 + e];
+	const uint32_t mbar = sptr(&sm.mbar);
+	if (tid == 0) tc::mbar_init(mbar, 1);
+	if (warp == 0) tc::tmem_alloc(sptr(&sm.tmem_base), kTmemCols);
+	tc::fence_before_sync();
+	__syncthreads();
+	tc::fence_after_sync();
+	const uint32_t tm = sm.tmem_base;
+	const uint32_t lrow = (uint32_t)((warp & 3) * 32) << 16;  // this warp's tensor-memory lanes: rows (warp & 3) * 32 + lane == s
+	const uint32_t R0 = tm + lrow, R1 = tm + 64 + lrow;
+	const uint32_t WG_W2c = tm + 128, WG_W1c = tm + 192, WG_W1s = tm + 240, WG_W3cT = tm + 288, WG_W2sT = tm + 304;
+	(void)lane;
+
+	const uint32_t n = a.d_n ? min(*a.d_n, a.n) : a.n;
+	const uint32_t n_tiles = (n + 127u) / 128u;
+	const __half variance = a.params[NEUS2B_GRID_OFF + (size_t)a.grid_entries * 2];
+	const float bias = __half2float(__float2half_rn(a.sdf_bias));
+	float var_grad = 0.f;
+	uint32_t phase = 0;
+	bool ok = true, first = true;
+
+#define N2B_ISSUE(BODY)                                  \
+	tc::fence_async_smem();                              \
+	tc::fence_before_sync();                             \
+	__syncthreads();                                     \
+	if (tid == 0) {                                      \
+		tc::fence_after_sync();                          \
+		BODY;                                            \
+		tc::commit(mbar);                                \
+	}                                                    \
+	ok = tc::mbar_wait(mbar, phase);                     \
+	phase ^= 1u;                                         \
+	if (!ok) break;                                      \
+	tc::fence_after_sync();
+
+	for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+		const uint32_t i = tile * 128u + (uint32_t)s;
+		const bool valid = i < n;
+		float x[3] = {0.5f, 0.5f, 0.5f}, dir[3] = {0.5f, 0.5f, 0.5f};
+		if (valid) {
+			const float* c = a.coords + (size_t)i * a.coord_stride;
+			x[0] = c[0];
+			x[1] = c[1];
+			x[2] = c[2];
+			dir[0] = c[a.dir_offset];
+			dir[1] = c[a.dir_offset + 1];
+			dir[2] = c[a.dir_offset + 2];
+		}
+		// ---- gather: features of this thread's 8 levels -> Zs, Jacobian d enc / d x kept in registers
+		float J[8][6];
+#pragma unroll
+		for (int j = 0; j < 8; ++j) {
+			const uint32_t l = 2 * j + hl;
+			__half2 feat = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+			for (int e = 0; e < 6; ++e) J[j][e] = 0.f;
+			if (l < a.lv.n_active) {
+				const LevelGeom g = level_geom(a.lv, l, x);
+				__half2 th[8];
+#pragma unroll
+				for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, geom_index(g, k));
+				const float scale = a.lv.scale[l];
+				float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+				for (uint32_t k = 0; k < 8; ++k) {
+					const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+					const float2 t = __half22float2(th[k]);
+					const float w = g.ax[bx] * g.ay[by] * g.az[bz];
+					a0 = __fmaf_rn(w, t.x, a0);
+					a1 = __fmaf_rn(w, t.y, a1);
+					const float dwx = (bx ? scale : -scale) * g.ay[by] * g.az[bz];
+					const float dwy = (by ? scale : -scale) * g.ax[bx] * g.az[bz];
+					const float dwz = (bz ? scale : -scale) * g.ax[bx] * g.ay[by];
+					J[j][0] = __fmaf_rn(dwx, t.x, J[j][0]);
+					J[j][1] = __fmaf_rn(dwx, t.y, J[j][1]);
+					J[j][2] = __fmaf_rn(dwy, t.x, J[j][2]);
+					J[j][3] = __fmaf_rn(dwy, t.y, J[j][3]);
+					J[j][4] = __fmaf_rn(dwz, t.x, J[j][4]);
+					J[j][5] = __fmaf_rn(dwz, t.y, J[j][5]);
+				}
+				feat = __floats2half2_rn(a0, a1);
+			}
+			*reinterpret_cast<__half2*>(sm.Zs + tc::blk_off(s, 2 * l, 48)) = feat;
+		}
+		if (hl == 0) {
+#pragma unroll
+			for (int e = 0; e < 3; ++e)
+				*reinterpret_cast<__half*>(sm.Zs + tc::blk_off(s, 32 + e, 48)) = __float2half_rn(__half2float(__float2half_rn(x[e])) - 0.5f);
+		}
+		// ---- Hs = relu(Zs W1s^T)
+		N2B_ISSUE(gemm<64>(tm, kmaj(sm.Zs, 48), kmaj(sm.W1s, 48), 3, false));
+		const uint32_t m_hs = epilogue32<1>(R0, s, hl * 32, sm.Hs, 0u);
+		write_S(sm.W2s, sm.X1, s, hl * 32, m_hs);
+		// ---- Ys = Hs W2s^T (R1[0:16]) ; Gz = S W1s (R0[0:48])
+		N2B_ISSUE(gemm<16>(tm + 64, kmaj(sm.Hs, 64), kmaj(sm.W2s, 64), 4, false);
+		          gemm<48>(tm, kmaj(sm.X1, 64), mnmaj(sm.W1s, 48), 4, false));
+		__half2 ge[8];
+		float nrm[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+		for (int q = 0; q < 3; ++q) {
+			float v[16];
+			tc::tmem_ld16(R0 + 16 * q, v);
+			tc::tmem_ld_wait();
+			if (q < 2) {
+#pragma unroll
+				for (int jj = 0; jj < 4; ++jj) {
+					const int j = 4 * q + jj;
+					const float g0 = __half2float(__float2half_rn(hl ? v[4 * jj + 2] : v[4 * jj]));
+					const float g1 = __half2float(__float2half_rn(hl ? v[4 * jj + 3] : v[4 * jj + 1]));
+					ge[j] = __floats2half2_rn(g0, g1);
+#pragma unroll
+					for (int e = 0; e < 3; ++e) nrm[e] = __fmaf_rn(J[j][2 * e], g0, __fmaf_rn(J[j][2 * e + 1], g1, nrm[e]));
+				}
+			} else if (hl == 0) {
+#pragma unroll
+				for (int e = 0; e < 3; ++e) nrm[e] += __half2float(__float2half_rn(v[e]));
+			}
+		}
+#pragma unroll
+		for (int e = 0; e < 3; ++e) sm.nrm[hl][s][e] = nrm[e];
+		if (hl == 1) {
+			float v[16];
+			tc::tmem_ld16(R1, v);
+			tc::tmem_ld_wait();
+			__align__(16) __half h[16];
+#pragma unroll
+			for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(v[e]);
+			st16(sm.Zc, s, 0, 48, h);
+			st16(sm.Zc, s, 8, 48, h + 8);
+			float sh[16];
+			sh4_eval(dir, sh);
+#pragma unroll
+			for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(sh[e]);
+			st16(sm.Zc, s, 16, 48, h);
+			st16(sm.Zc, s, 24, 48, h + 8);
+		}
+		tc::fence_before_sync();
+		__syncthreads();
+		if (hl == 0) {
+			__align__(16) __half h[8];
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				nrm[e] = sm.nrm[0][s][e] + sm.nrm[1][s][e];
+				h[e] = __float2half_rn(x[e]);
+				h[3 + e] = __float2half_rn(nrm[e]);
+			}
+			h[6] = h[7] = __float2half_rn(0.f);
+			st16(sm.Zc, s, 32, 48, h);
+		}
+		// ---- colour net
+		N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.Zc, 48), kmaj(sm.W1c, 48), 3, false));
+		const uint32_t m_h1 = epilogue32<1>(R1, s, hl * 32, sm.X1, 0u);
+		N2B_ISSUE(gemm<64>(tm, kmaj(sm.X1, 64), kmaj(sm.W2c, 64), 4, false));
+		unsigned char* H2 = MODE == MODE_TRAIN ? sm.X2 : sm.Hs;
+		const uint32_t m_h2 = epilogue32<1>(R0, s, hl * 32, H2, 0u);
+		(void)m_h1;
+		(void)m_h2;
+		if constexpr (MODE == MODE_FWD) {
+			N2B_ISSUE(gemm<16>(tm + 64, kmaj(H2, 64), kmaj(sm.W3c, 64), 4, false));
+			if (hl == 0) {
+				float v[16];
+				tc::tmem_ld16(R1, v);
+				tc::tmem_ld_wait();
+				if (valid) {
+					__align__(16) __half o[16];
+#pragma unroll
+					for (int k = 0; k < 16; ++k) o[k] = __float2half_rn(v[k]);
+					o[3] = __float2half_rn(__half2float(*reinterpret_cast<const __half*>(sm.Zc + tc::blk_off(s, 0, 48))) + bias);
+#pragma unroll
+					for (int e = 0; e < 3; ++e) {
+						o[4 + e] = __float2half_rn(nrm[e]);
+						o[8 + e] = __float2half_rn(dir[e]);
+					}
+					o[7] = variance;
+					uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)i * 16);
+					dst[0] = reinterpret_cast<const uint4*>(o)[0];
+					dst[1] = reinterpret_cast<const uint4*>(o)[1];
+				}
+			}
+		} else {
+			// ---- B1: dY3 = rows 0-2 of dL_dout (nerf_network.h:331-340)
+			__align__(16) __half g[16];
+#pragma unroll
+			for (int k = 0; k < 16; ++k) g[k] = __float2half_rn(0.f);
+			if (hl == 0) {
+				if (valid) {
+					const uint4* src = reinterpret_cast<const uint4*>(a.dL_dout + (size_t)i * 16);
+					reinterpret_cast<uint4*>(g)[0] = __ldg(src);
+					reinterpret_cast<uint4*>(g)[1] = __ldg(src + 1);
+				}
+				__align__(16) __half d3[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k) d3[k] = k < 3 ? g[k] : __float2half_rn(0.f);
+				st16(sm.dY, s, 0, 16, d3);
+				st16(sm.dY, s, 8, 16, d3 + 8);
+			}
+			N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.dY, 16), mnmaj(sm.W3c, 64), 1, false);
+			          gemm<16>(WG_W3cT, mnmaj(sm.X2, 64), mnmaj(sm.dY, 16), 8, !first));
+			epilogue32<2>(R1, s, hl * 32, sm.X3, m_h2);  // dH2
+			// ---- B2
+			N2B_ISSUE(gemm<64>(tm, kmaj(sm.X3, 64), mnmaj(sm.W2c, 64), 4, false);
+			          gemm<64>(WG_W2c, mnmaj(sm.X3, 64), mnmaj(sm.X1, 64), 8, !first));
+			epilogue32<2>(R0, s, hl * 32, sm.X2, m_h1);  // dH1 (over H2)
+			// ---- B3
+			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X2, 64), mnmaj(sm.W1c, 48), 4, false);
+			          gemm<48>(WG_W1c, mnmaj(sm.X2, 64), mnmaj(sm.Zc, 48), 8, !first));
+			// ---- B4: SDF-net output gradient = colour-net input gradient rows 0-15 (+ dL/dsdf), v = dL/dnormal (:388-395, :465-491)
+			if (hl == 0) {
+				float v[16];
+				tc::tmem_ld16(R1, v);
+				tc::tmem_ld_wait();
+				__align__(16) __half h[16];
+#pragma unroll
+				for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(v[e]);
+				h[0] = __hadd(h[0], g[3]);
+				st16(sm.dY, s, 0, 16, h);
+				st16(sm.dY, s, 8, 16, h + 8);
+				tc::tmem_ld16(R1 + 32, v);
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int e = 0; e < 3; ++e)
+					sm.vbuf[s][e] = __half2float(__float2half_rn(v[3 + e])) + __half2float(g[4 + e]) / a.batch_size + __half2float(g[8 + e]);
+				var_grad += __half2float(g[7]);
+			}
+			N2B_ISSUE(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false);
+			          gemm<16>(WG_W2sT, mnmaj(sm.Hs, 64), mnmaj(sm.dY, 16), 8, !first));
+			epilogue32<2>(R0, s, hl * 32, sm.X3, m_hs);  // dHs
+			// ---- B5
+			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X3, 64), mnmaj(sm.W1s, 48), 4, false);
+			          gemm<48>(WG_W1s, mnmaj(sm.X3, 64), mnmaj(sm.Zs, 48), 8, !first));
+			// ---- B6: grid gradient (first + second order merged, one reduction per corner); U = [J v | v | 0] over Zs
+			const float v3[3] = {sm.vbuf[s][0], sm.vbuf[s][1], sm.vbuf[s][2]};
+#pragma unroll
+			for (int q = 0; q < 2; ++q) {
+				float dzv[16];
+				tc::tmem_ld16(R1 + 16 * q, dzv);
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int jj = 0; jj < 4; ++jj) {
+					const int j = 4 * q + jj;
+					const uint32_t l = 2 * j + hl;
+					__half2 dy = __floats2half2_rn(0.f, 0.f);
+					if (l < a.lv.n_active) {
+						dy = __floats2half2_rn(J[j][0] * v3[0] + J[j][2] * v3[1] + J[j][4] * v3[2],
+						                       J[j][1] * v3[0] + J[j][3] * v3[1] + J[j][5] * v3[2]);
+						if (valid) {
+							const float dz0 = __half2float(__float2half_rn(hl ? dzv[4 * jj + 2] : dzv[4 * jj]));
+							const float dz1 = __half2float(__float2half_rn(hl ? dzv[4 * jj + 3] : dzv[4 * jj + 1]));
+							const float2 gef = __half22float2(ge[j]);
+							const LevelGeom g2 = level_geom(a.lv, l, x);
+							const float scale = a.lv.scale[l];
+							const float bxv[2] = {-scale * v3[0], scale * v3[0]}, byv[2] = {-scale * v3[1], scale * v3[1]};
+							const float bzv[2] = {-scale * v3[2], scale * v3[2]};
+#pragma unroll
+							for (uint32_t k = 0; k < 8; ++k) {
+								const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+								const float p = g2.ax[bx] * g2.ay[by];
+								const float qq = bxv[bx] * g2.ay[by] + g2.ax[bx] * byv[by];
+								const float w = p * g2.az[bz];
+								const float coef = qq * g2.az[bz] + p * bzv[bz];
+								red_add_h2(a.grad_grid, geom_index(g2, k), __fmaf_rn(w, dz0, coef * gef.x), __fmaf_rn(w, dz1, coef * gef.y));
+							}
+						}
+					}
+					*reinterpret_cast<__half2*>(sm.Zs + tc::blk_off(s, 2 * l, 48)) = dy;
+				}
+			}
+			if (hl == 0) {
+#pragma unroll
+				for (int e = 0; e < 3; ++e) *reinterpret_cast<__half*>(sm.Zs + tc::blk_off(s, 32 + e, 48)) = __float2half_rn(v3[e]);
+			} else {
+				// second-order seed dy = e0 for every live sample (:497-503)
+				__align__(16) __half e0[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k) e0[k] = __float2half_rn((k == 0 && valid) ? 1.f : 0.f);
+				st16(sm.dY, s, 0, 16, e0);
+				st16(sm.dY, s, 8, 16, e0 + 8);
+			}
+			write_S(sm.W2s, sm.X1, s, hl * 32, m_hs);
+			// ---- B7: T = D .* (U W1s^T);  dW2s[0,:] += sum_b T;  dW1s += S^T U  (:560-571)
+			N2B_ISSUE(gemm<64>(tm, kmaj(sm.Zs, 48), kmaj(sm.W1s, 48), 3, false));
+			epilogue32<2>(R0, s, hl * 32, sm.X3, m_hs);  // T
+			N2B_ISSUE(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.dY, 16), 8, true);
+			          gemm<48>(WG_W1s, mnmaj(sm.X1, 64), mnmaj(sm.Zs, 48), 8, true));
+			first = false;
+		}
+		tc::fence_before_sync();
+		__syncthreads();  // tiles and accumulators are free for the next round
+	}
+#undef N2B_ISSUE
+	if (!ok) atomicOr(&g_tc_error, 1u);
+	tc::fence_before_sync();
+	__syncthreads();
+	tc::fence_after_sync();
+
+	if constexpr (MODE == MODE_TRAIN) {
+		// ---- flush the weight gradients held in tensor memory (rows 0..63 of each accumulator)
+		if (ok && !first && s < 64) {
+			if (hl == 0) {
+#pragma unroll
+				for (int q = 0; q < 4; ++q) {
+					float v[16];
+					tc::tmem_ld16(WG_W2c + lrow + 16 * q, v);
+					tc::tmem_ld_wait();
+#pragma unroll
+					for (int e = 0; e < 16; ++e)
+						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W2 + s * 64 + 16 * q + e, v[e]);
+				}
+				float v[16];
+				tc::tmem_ld16(WG_W3cT + lrow, v);  // [in = s][out]
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int e = 0; e < 16; ++e)
+					if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W3 + e * 64 + s, v[e]);
+			} else {
+#pragma unroll
+				for (int q = 0; q < 3; ++q) {
+					float v[16];
+					tc::tmem_ld16(WG_W1c + lrow + 16 * q, v);
+					tc::tmem_ld_wait();
+#pragma unroll
+					for (int e = 0; e < 16; ++e)
+						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W1 + s * 48 + 16 * q + e, v[e]);
+					tc::tmem_ld16(WG_W1s + lrow + 16 * q, v);
+					tc::tmem_ld_wait();
+#pragma unroll
+					for (int e = 0; e < 16; ++e)
+						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_SDF_W1 + s * 48 + sdf_orig_col(16 * q + e), v[e]);
+				}
+				float v[16];
+				tc::tmem_ld16(WG_W2sT + lrow, v);
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int e = 0; e < 16; ++e)
+					if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_SDF_W2 + e * 64 + s, v[e]);
+			}
+		}
+		// variance gradient = sum of row 7 over the batch (:452-460)
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) var_grad += __shfl_xor_sync(0xffffffffu, var_grad, o);
+		if ((tid & 31) == 0) sm.red[warp] = var_grad;
+		__syncthreads();
+		if (tid == 0) {
+			float t = 0.f;
+			for (int w = 0; w < 8; ++w) t += sm.red[w];
+			if (t != 0.f) atomicAdd(a.grad_var, t);
+		}
+	}
+	tc::fence_before_sync();
+	__syncthreads();
+	if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
+}
+
+template <int MODE>
+static int launch(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) {
+	const size_t smem = sizeof(Smem<MODE>) + 128;
+	N2B_CHECK_CUDA(cudaFuncSetAttribute(neus_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	uint32_t ctas = (n_upper + 127u) / 128u;
+	const uint32_t per_sm = MODE == MODE_TRAIN ? 1u : 2u;
+	if (ctas > kSMs * per_sm) ctas = kSMs * per_sm;
+	if (ctas == 0) return NEUS2B_OK;
+	neus_tc_kernel<MODE><<<ctas, kThreads, smem, stream>>>(a);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}
+
+}  // namespace tcf
+
+int launch_neus_tc_forward(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) { return tcf::launch<MODE_FWD>(a, n_upper, stream); }
+int launch_neus_tc_train(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) { return tcf::launch<MODE_TRAIN>(a, n_upper, stream); }
+int read_tc_error(uint32_t* h_flags) {
+	uint32_t v = 0;
+	cudaError_t e = cudaMemcpyFromSymbol(&v, tcf::g_tc_error, sizeof(v));
+	if (e != cudaSuccess) return (int)e;
+	*h_flags = v;
+	return NEUS2B_OK;
+}
+
+}  // namespace n2b

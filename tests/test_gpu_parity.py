@@ -168,14 +168,27 @@ FUSED_CASES = [
 ]
 
 
+PATHS = [pytest.param(0, id="mma_sync"), pytest.param(1, id="tcgen05")]
+
+
+@pytest.fixture(autouse=True)
+def _default_path():
+    yield
+    from neus2_b200 import _lib as L
+    L.set_mma_path(L.MMA_TCGEN05)
+
+
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("case", FUSED_CASES)
-def test_fused_forward(gpu, oracle, case):
+def test_fused_forward(gpu, oracle, case, path):
     L, ops = gpu
     O = oracle
+    L.set_mma_path(path)
     d, params, coords, rng = model(O, seed=3, grid_amp=0.05, **case)
     ref = O.bits_f32(O.neus_forward(d, params, coords, sdf_bias=-0.1))
     out = f32(ops.neus_forward(to_lib_desc(L, d), half(params), dev(coords), sdf_bias=-0.1))
-    tag = "fused_fwd_n%d_L%d_a%d" % (coords.shape[0], d.n_levels, d.n_active_levels)
+    assert L.device_error_flags() == 0
+    tag = "fused_fwd_p%d_n%d_L%d_a%d" % (path, coords.shape[0], d.n_levels, d.n_active_levels)
     check_fp16(tag + "_rgb", out[:, 0:3], ref[:, 0:3], min_frac=0.995, min_cos=0.999)
     check_fp16(tag + "_sdf", out[:, 3], ref[:, 3], min_frac=0.995, min_cos=0.9999)
     check_fp16(tag + "_normal", out[:, 4:7], ref[:, 4:7], min_frac=0.995, min_cos=0.999)
@@ -195,10 +208,12 @@ def test_fused_forward_device_count(gpu, oracle):
     assert out[333:].abs().max().item() == 0 and out[:333].abs().sum().item() > 0
 
 
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("case", FUSED_CASES)
-def test_fused_train_gradients(gpu, oracle, case):
+def test_fused_train_gradients(gpu, oracle, case, path):
     L, ops = gpu
     O = oracle
+    L.set_mma_path(path)
     d, params, coords, rng = model(O, seed=5, grid_amp=0.05, **case)
     n, ng = coords.shape[0], O.grid_n_params(d)
     g = np.zeros((n, 16), np.float32)
@@ -214,7 +229,8 @@ def test_fused_train_gradients(gpu, oracle, case):
     gv = torch.zeros(4, dtype=torch.float32, device="cuda")
     ops.neus_train(to_lib_desc(L, d), half(params), dev(coords), half(gb), max(n, 256), gm, gg, gv)
     torch.cuda.synchronize()
-    tag = "fused_train_n%d_L%d_a%d_" % (n, d.n_levels, d.n_active_levels)
+    assert L.device_error_flags() == 0
+    tag = "fused_train_p%d_n%d_L%d_a%d_" % (path, n, d.n_levels, d.n_active_levels)
     gm = gm.cpu().numpy()
     for name, a, b in [("sdf_w1", 0, 3072), ("sdf_w2", 3072, 4096), ("rgb_w1", 4096, 7168), ("rgb_w2", 7168, 11264),
                        ("rgb_w3", 11264, 12288)]:
