@@ -288,6 +288,30 @@ def run_kernel_only(args):
     torch.cuda.set_device(0)
     desc = L.grid_desc()
     ng = L.grid_n_params(desc)
+    if args.kernel == "adam":
+        n = 12288 + ng + 4
+        f32 = lambda: torch.randn(n, device="cuda") * 1e-3
+        master, m, v, ema = f32(), f32(), f32().abs(), f32()
+        P = torch.zeros(n, dtype=torch.float16, device="cuda")
+        Pe = torch.zeros(n, dtype=torch.float16, device="cuda")
+        gm, gv = torch.randn(12288, device="cuda"), torch.zeros(4, device="cuda")
+        gsrc = (torch.randn(ng, device="cuda") * (torch.rand(ng, device="cuda") < 0.3)).half()
+        gg = gsrc.clone()
+        cfg = L.AdamCfg(1e-2, 0.9, 0.99, 1e-15, 1e-6, 0.95, 128.0, 10, 12288)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for it in range(args.kernel_iters):
+            gg.copy_(gsrc)
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0.record()
+            ops.adam_step(cfg, gm, gg, gv, master, m, v, P, Pe, ema)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        print(json.dumps({"kernel": "adam", "n_params": n, "ms": times, "GBps": 40.0 * n / (min(times) * 1e-3) / 1e9}))
+        return
     p = S.init_params(ng, seed=1337)
     rng = np.random.default_rng(9)
     p[12288:12288 + ng] = rng.uniform(-1e-2, 1e-2, ng)
@@ -426,7 +450,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default=None, choices=["train", "forward"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam"], help="run one fused kernel alone (profiling)")
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
     args = ap.parse_args()

@@ -173,6 +173,7 @@ typedef struct {
 	uint64_t* d_scan_tmp;    /* [max_rays + 1024] */
 	float* d_ray_tmp;        /* [max_rays][8] */
 	const uint32_t* d_n_rays_total; /* optional: overrides the n_rays_total argument with a device value */
+	uint32_t* d_march_masks;        /* optional [max_rays][64]: lets the second march pass skip the occupancy lookups */
 } neus2b_ray_workspace;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is
@@ -226,6 +227,12 @@ typedef struct {
 int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid, float* d_grad_variance,
                      float* d_master, float* d_m, float* d_v, uint16_t* d_params, uint16_t* d_params_ema, float* d_ema_master,
                      neus2b_stream_t stream);
+
+/* The same step with the optimizer-private state interleaved per parameter: d_state [n][4] fp32 = {master weight, Adam m,
+ * Adam v, EMA master}.  One read-modify-write stream instead of eight: this is the layout the training loop uses. */
+int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid,
+                            float* d_grad_variance, float* d_state, uint16_t* d_params, uint16_t* d_params_ema,
+                            neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- training loop (Testbed, src/testbed.cu / src/testbed_nerf.cu) */
 

@@ -116,106 +116,138 @@ __global__ void occ_maxpool_kernel(uint32_t n, const uint8_t* __restrict__ prev,
 // ------------------------------------------------------------------------------------------------ Adam
 // One element of the Ema o Adam update.  Returns the new weight; m/v are updated in place.
 __device__ __forceinline__ float adam_element(const neus2b_adam_cfg& c, float lr_t, bool matrix, float g, float w, float& m, float& v) {
-	g = g / c.loss_scale;
+	g = __fdividef(g, c.loss_scale);
 	bool upd = true;
 	if (matrix) g += c.l2_reg * w;
 	else if (g == 0.0f) upd = false;  // grid entries no sample touched keep their weight and moments
 	if (upd) {
 		m = c.beta1 * m + (1.0f - c.beta1) * g;
 		v = c.beta2 * v + (1.0f - c.beta2) * g * g;
-		w -= lr_t * m / (sqrtf(v) + c.epsilon);
+		w -= __fdividef(lr_t * m, __fsqrt_rn(v) + c.epsilon);
 	}
 	return w;
 }
 
-// Streaming pass over the parameter block, 8 parameters (16..32-byte accesses) per thread and iteration.  The block is
-// [n_matrix MLP weights | grid | 4 variance slots]; n_matrix and the grid size are multiples of 8.
-__global__ void __launch_bounds__(256) adam_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
-                                                   float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
-                                                   float* __restrict__ grad_var, float* __restrict__ master, float* __restrict__ m,
-                                                   float* __restrict__ v, __half* __restrict__ params, __half* __restrict__ params_ema,
-                                                   float* __restrict__ ema_master) {
-	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 8u;
+// Streaming pass over the parameter block, 4 parameters (8..16-byte accesses) per thread and iteration, enough threads
+// resident (<= 32 registers would not buy more: the pass is bound by bytes in flight).  The block is
+// [n_matrix MLP weights | grid | 4 variance slots]; n_matrix and the grid size are multiples of 4.
+__global__ void __launch_bounds__(256, 8) adam_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
+                                                      float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
+                                                      float* __restrict__ grad_var, float* __restrict__ master, float* __restrict__ m,
+                                                      float* __restrict__ v, __half* __restrict__ params, __half* __restrict__ params_ema,
+                                                      float* __restrict__ ema_master) {
+	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 4u;
 	const uint64_t n_grid_end = n - 4u;
-	for (uint64_t i0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8u; i0 < n; i0 += stride) {
-		float g[8], w[8], mm[8], vv[8], em[8];
-		const bool full = i0 + 8u <= n_grid_end;  // tail: the 4 variance slots
+	for (uint64_t i0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4u; i0 < n; i0 += stride) {
 		const bool matrix = i0 < c.n_matrix;
-		if (full) {
-			if (matrix) {
-				const float4 a = *reinterpret_cast<const float4*>(grad_mlp + i0), b = *reinterpret_cast<const float4*>(grad_mlp + i0 + 4);
-				g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
-				*reinterpret_cast<float4*>(grad_mlp + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
-				*reinterpret_cast<float4*>(grad_mlp + i0 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-			} else {
-				uint4 raw = *reinterpret_cast<const uint4*>(grad_grid + (i0 - c.n_matrix));
-				const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-				for (int e = 0; e < 4; ++e) {
-					const float2 f = __half22float2(h[e]);
-					g[2 * e] = f.x;
-					g[2 * e + 1] = f.y;
-				}
-				*reinterpret_cast<uint4*>(grad_grid + (i0 - c.n_matrix)) = make_uint4(0u, 0u, 0u, 0u);
-			}
-#pragma unroll
-			for (int q = 0; q < 2; ++q) {
-				const float4 a = *reinterpret_cast<const float4*>(master + i0 + 4 * q);
-				const float4 b = *reinterpret_cast<const float4*>(m + i0 + 4 * q);
-				const float4 d = *reinterpret_cast<const float4*>(v + i0 + 4 * q);
-				w[4 * q] = a.x; w[4 * q + 1] = a.y; w[4 * q + 2] = a.z; w[4 * q + 3] = a.w;
-				mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
-				vv[4 * q] = d.x; vv[4 * q + 1] = d.y; vv[4 * q + 2] = d.z; vv[4 * q + 3] = d.w;
-				if (params_ema) {
-					const float4 e4 = *reinterpret_cast<const float4*>(ema_master + i0 + 4 * q);
-					em[4 * q] = e4.x; em[4 * q + 1] = e4.y; em[4 * q + 2] = e4.z; em[4 * q + 3] = e4.w;
-				}
-			}
-#pragma unroll
-			for (int e = 0; e < 8; ++e) w[e] = adam_element(c, lr_t, matrix, g[e], w[e], mm[e], vv[e]);
-			__align__(16) __half ph[8], peh[8];
-#pragma unroll
-			for (int e = 0; e < 8; ++e) {
-				ph[e] = __float2half_rn(w[e]);
-				if (params_ema) {
-					em[e] = ((1.0f - c.ema_decay) * w[e] + c.ema_decay * em[e] * ema_old) * ema_new_inv;
-					peh[e] = __float2half_rn(em[e]);
-				}
-			}
-#pragma unroll
-			for (int q = 0; q < 2; ++q) {
-				*reinterpret_cast<float4*>(master + i0 + 4 * q) = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-				*reinterpret_cast<float4*>(m + i0 + 4 * q) = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
-				*reinterpret_cast<float4*>(v + i0 + 4 * q) = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
-				if (params_ema)
-					*reinterpret_cast<float4*>(ema_master + i0 + 4 * q) = make_float4(em[4 * q], em[4 * q + 1], em[4 * q + 2], em[4 * q + 3]);
-			}
-			*reinterpret_cast<uint4*>(params + i0) = *reinterpret_cast<const uint4*>(ph);
-			if (params_ema) *reinterpret_cast<uint4*>(params_ema + i0) = *reinterpret_cast<const uint4*>(peh);
+		const bool var = i0 >= n_grid_end;
+		float g[4];
+		if (matrix) {
+			const float4 a = *reinterpret_cast<const float4*>(grad_mlp + i0);
+			g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+			*reinterpret_cast<float4*>(grad_mlp + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
+		} else if (!var) {
+			uint2 raw = *reinterpret_cast<const uint2*>(grad_grid + (i0 - c.n_matrix));
+			const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+			const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+			g[0] = f0.x; g[1] = f0.y; g[2] = f1.x; g[3] = f1.y;
+			*reinterpret_cast<uint2*>(grad_grid + (i0 - c.n_matrix)) = make_uint2(0u, 0u);
 		} else {
-			for (uint64_t i = i0; i < n && i < i0 + 8u; ++i) {
-				float gi;
-				if (i < n_grid_end) {
-					gi = __half2float(grad_grid[i - c.n_matrix]);
-					grad_grid[i - c.n_matrix] = __float2half_rn(0.f);
-				} else {
-					gi = grad_var[i - n_grid_end];
-					grad_var[i - n_grid_end] = 0.f;
-				}
-				float mi = m[i], vi = v[i];
-				const float wi = adam_element(c, lr_t, false, gi, master[i], mi, vi);
-				master[i] = wi;
-				m[i] = mi;
-				v[i] = vi;
-				params[i] = __float2half_rn(wi);
-				if (params_ema) {
-					const float e = ((1.0f - c.ema_decay) * wi + c.ema_decay * ema_master[i] * ema_old) * ema_new_inv;
-					ema_master[i] = e;
-					params_ema[i] = __float2half_rn(e);
-				}
-			}
+			const float4 a = *reinterpret_cast<const float4*>(grad_var);
+			g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+			*reinterpret_cast<float4*>(grad_var) = make_float4(0.f, 0.f, 0.f, 0.f);
+		}
+		const float4 w4 = *reinterpret_cast<const float4*>(master + i0);
+		const float4 m4 = *reinterpret_cast<const float4*>(m + i0);
+		const float4 v4 = *reinterpret_cast<const float4*>(v + i0);
+		float w[4] = {w4.x, w4.y, w4.z, w4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+		float em[4] = {0.f, 0.f, 0.f, 0.f};
+		if (params_ema) {
+			const float4 e4 = *reinterpret_cast<const float4*>(ema_master + i0);
+			em[0] = e4.x; em[1] = e4.y; em[2] = e4.z; em[3] = e4.w;
+		}
+#pragma unroll
+		for (int e = 0; e < 4; ++e) w[e] = adam_element(c, lr_t, matrix, g[e], w[e], mm[e], vv[e]);
+		*reinterpret_cast<float4*>(master + i0) = make_float4(w[0], w[1], w[2], w[3]);
+		*reinterpret_cast<float4*>(m + i0) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+		*reinterpret_cast<float4*>(v + i0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+		__half2 p01 = __floats2half2_rn(w[0], w[1]), p23 = __floats2half2_rn(w[2], w[3]);
+		*reinterpret_cast<uint2*>(params + i0) = make_uint2(*reinterpret_cast<uint32_t*>(&p01), *reinterpret_cast<uint32_t*>(&p23));
+		if (params_ema) {
+#pragma unroll
+			for (int e = 0; e < 4; ++e) em[e] = ((1.0f - c.ema_decay) * w[e] + c.ema_decay * em[e] * ema_old) * ema_new_inv;
+			*reinterpret_cast<float4*>(ema_master + i0) = make_float4(em[0], em[1], em[2], em[3]);
+			__half2 e01 = __floats2half2_rn(em[0], em[1]), e23 = __floats2half2_rn(em[2], em[3]);
+			*reinterpret_cast<uint2*>(params_ema + i0) = make_uint2(*reinterpret_cast<uint32_t*>(&e01), *reinterpret_cast<uint32_t*>(&e23));
 		}
 	}
+}
+
+// Same update with the optimizer-private state interleaved per parameter: state[i] = {master, m, v, ema master}.
+// Separate arrays make eleven concurrent address streams, and the pass then reaches about a third of the copy
+// bandwidth; packed, the state is one read-modify-write stream of 16 bytes per parameter.
+__global__ void __launch_bounds__(256, 8) adam_packed_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
+                                                             float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
+                                                             float* __restrict__ grad_var, float4* __restrict__ state,
+                                                             __half* __restrict__ params, __half* __restrict__ params_ema) {
+	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 2u;
+	const uint64_t n_grid_end = n - 4u;
+	for (uint64_t i0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2u; i0 < n; i0 += stride) {
+		const bool matrix = i0 < c.n_matrix;
+		float g[2];
+		if (matrix) {
+			const float2 a = *reinterpret_cast<const float2*>(grad_mlp + i0);
+			g[0] = a.x; g[1] = a.y;
+			*reinterpret_cast<float2*>(grad_mlp + i0) = make_float2(0.f, 0.f);
+		} else if (i0 < n_grid_end) {
+			const __half2 h = *reinterpret_cast<const __half2*>(grad_grid + (i0 - c.n_matrix));
+			const float2 f = __half22float2(h);
+			g[0] = f.x; g[1] = f.y;
+			*reinterpret_cast<__half2*>(grad_grid + (i0 - c.n_matrix)) = __floats2half2_rn(0.f, 0.f);
+		} else {
+			g[0] = grad_var[i0 - n_grid_end];
+			g[1] = grad_var[i0 - n_grid_end + 1];
+			grad_var[i0 - n_grid_end] = 0.f;
+			grad_var[i0 - n_grid_end + 1] = 0.f;
+		}
+		float4 s0 = state[i0], s1 = state[i0 + 1];
+		s0.x = adam_element(c, lr_t, matrix, g[0], s0.x, s0.y, s0.z);
+		s1.x = adam_element(c, lr_t, matrix, g[1], s1.x, s1.y, s1.z);
+		s0.w = ((1.0f - c.ema_decay) * s0.x + c.ema_decay * s0.w * ema_old) * ema_new_inv;
+		s1.w = ((1.0f - c.ema_decay) * s1.x + c.ema_decay * s1.w * ema_old) * ema_new_inv;
+		state[i0] = s0;
+		state[i0 + 1] = s1;
+		*reinterpret_cast<__half2*>(params + i0) = __floats2half2_rn(s0.x, s1.x);
+		if (params_ema) *reinterpret_cast<__half2*>(params_ema + i0) = __floats2half2_rn(s0.w, s1.w);
+	}
+}
+
+// state[i].{x|y|z|w} <-> contiguous array (set / get of the master or EMA parameters)
+__global__ void state_scatter_kernel(uint64_t n, const float* __restrict__ src, float4* __restrict__ state, __half* __restrict__ p,
+                                     __half* __restrict__ pe) {
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+		const float w = src[i];
+		state[i] = make_float4(w, 0.f, 0.f, w);
+		p[i] = __float2half_rn(w);
+		pe[i] = __float2half_rn(w);
+	}
+}
+__global__ void state_gather_kernel(uint64_t n, const float4* __restrict__ state, int field, float* __restrict__ dst) {
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+		const float4 sv = state[i];
+		dst[i] = field == 0 ? sv.x : (field == 1 ? sv.y : (field == 2 ? sv.z : sv.w));
+	}
+}
+
+int launch_state_scatter(uint64_t n, const float* src, float4* state, __half* p, __half* pe, cudaStream_t s) {
+	state_scatter_kernel<<<kSMs * 8, 256, 0, s>>>(n, src, state, p, pe);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}
+int launch_state_gather(uint64_t n, const float4* state, int field, float* dst, cudaStream_t s) {
+	state_gather_kernel<<<kSMs * 8, 256, 0, s>>>(n, state, field, dst);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
 }
 
 }  // namespace n2b
@@ -295,15 +327,32 @@ extern "C" int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d
                                 neus2b_stream_t stream) {
 	if (!cfg || !d_grad_mlp || !d_grad_grid || !d_grad_variance || !d_master || !d_m || !d_v || !d_params) return NEUS2B_E_INVALID;
 	if (d_params_ema && !d_ema_master) return NEUS2B_E_INVALID;
-	if (n < cfg->n_matrix + 4u || cfg->step == 0 || (cfg->n_matrix & 7u)) return NEUS2B_E_INVALID;
-	if (((uintptr_t)d_grad_mlp | (uintptr_t)d_grad_grid | (uintptr_t)d_master | (uintptr_t)d_m | (uintptr_t)d_v | (uintptr_t)d_params |
+	if (n < cfg->n_matrix + 4u || cfg->step == 0 || (cfg->n_matrix & 3u) || (n & 3u)) return NEUS2B_E_INVALID;
+	if (((uintptr_t)d_grad_variance | (uintptr_t)d_grad_mlp | (uintptr_t)d_grad_grid | (uintptr_t)d_master | (uintptr_t)d_m | (uintptr_t)d_v | (uintptr_t)d_params |
 	     (uintptr_t)d_params_ema | (uintptr_t)d_ema_master) & 15u)
 		return NEUS2B_E_INVALID;
 	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
 	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
 	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
-	adam_kernel<<<kSMs * 8, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
+	adam_kernel<<<kSMs * 16, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
 	                                          d_master, d_m, d_v, (__half*)d_params, (__half*)d_params_ema, d_ema_master);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid,
+                                       float* d_grad_variance, float* d_state, uint16_t* d_params, uint16_t* d_params_ema,
+                                       neus2b_stream_t stream) {
+	if (!cfg || !d_grad_mlp || !d_grad_grid || !d_grad_variance || !d_state || !d_params) return NEUS2B_E_INVALID;
+	if (n < cfg->n_matrix + 4u || cfg->step == 0 || (cfg->n_matrix & 3u) || (n & 3u)) return NEUS2B_E_INVALID;
+	if (((uintptr_t)d_grad_variance | (uintptr_t)d_grad_mlp | (uintptr_t)d_grad_grid | (uintptr_t)d_state | (uintptr_t)d_params |
+	     (uintptr_t)d_params_ema) & 15u)
+		return NEUS2B_E_INVALID;
+	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
+	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
+	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
+	adam_packed_kernel<<<kSMs * 16, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
+	                                                  (float4*)d_state, (__half*)d_params, (__half*)d_params_ema);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }

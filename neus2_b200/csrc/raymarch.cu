@@ -155,10 +155,13 @@ struct RayTmp {  // 8 floats per ray
 // same recurrence at once (position, containment, occupancy bit, jump target: the expensive, independent part), then
 // every lane replays the visit / jump decisions over the chunk in ray order, which is cheap and keeps the result
 // identical to the serial loop: same visited set, same samples, same count.
+constexpr uint32_t kMaskWords = 64;  // per-ray record of the count pass: one bit per ray parameter that became a sample
+
 template <bool EMIT>
 __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
                                               const uint8_t* __restrict__ bitfield, uint32_t limit, float* __restrict__ coords_out,
-                                              int lane) {
+                                              int lane, uint32_t* __restrict__ masks = nullptr,
+                                              uint32_t* n_chunks = nullptr) {
 	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
 	const float cone_angle = cfg.cone_angle_constant;
 	float t_chunk = startt, skip_until = -3.402823466e+38f;
@@ -166,7 +169,8 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 	bool stop = false;
 	// every chunk moves t forward by at least 32 minimum steps, so the ray leaves the box after a bounded number of
 	// chunks; the cap only guards against non-finite inputs
-	for (uint32_t chunk = 0; chunk < 8192u && !stop; ++chunk) {
+	uint32_t chunk = 0;
+	for (; chunk < 8192u && !stop; ++chunk) {
 		// this lane's candidate: t after `lane` steps of the recurrence from the chunk start
 		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
 #pragma unroll
@@ -224,6 +228,10 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 			}
 		}
 		t_chunk = t;
+		if (!EMIT && masks && chunk < kMaskWords) {
+			const uint32_t m = __ballot_sync(0xffffffffu, emit);
+			if (lane == 0) masks[chunk] = m;
+		}
 		if (EMIT && emit) {
 			float* c = coords_out + (size_t)slot * 7;
 #pragma unroll
@@ -234,7 +242,43 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 			c[3] = warp_dt(my_dt);
 		}
 	}
+	if (n_chunks) *n_chunks = chunk;
 	return j;
+}
+
+// Emit pass when the count pass recorded which ray parameters became samples: no occupancy lookups and no replay,
+// only the t recurrence and the coordinate writes.
+__device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
+                                                const uint32_t* __restrict__ masks, uint32_t numsteps, float* __restrict__ coords_out,
+                                                int lane) {
+	const float cone_angle = cfg.cone_angle_constant;
+	float t_chunk = startt;
+	uint32_t j = 0;
+	for (uint32_t chunk = 0; chunk < kMaskWords && j < numsteps; ++chunk) {
+		const uint32_t m = masks[chunk];
+		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
+#pragma unroll
+		for (int k = 0; k < 32; ++k) {
+			const float dt = calc_dt(t, cone_angle);
+			if (lane == k) {
+				my_t = t;
+				my_dt = dt;
+			}
+			t += dt;
+		}
+		t_chunk = t;
+		if ((m >> lane) & 1u) {
+			float* c = coords_out + (size_t)(j + __popc(m & ((1u << lane) - 1u))) * 7;
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				const float pos = o[e] + my_t * dirn[e];
+				c[e] = (pos - cfg.aabb_min[e]) / (cfg.aabb_max[e] - cfg.aabb_min[e]);
+				c[4 + e] = (dirn[e] + 1.f) * 0.5f;
+			}
+			c[3] = warp_dt(my_dt);
+		}
+		j += __popc(m);
+	}
 }
 
 // First half of generate_training_samples_nerf_with_global_movement (:1287-1409): build the ray and count its steps.
@@ -242,7 +286,7 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
                                                           const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
                                                           const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
                                                           const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
-                                                          uint64_t* __restrict__ scan_in) {
+                                                          uint64_t* __restrict__ scan_in, uint32_t* __restrict__ masks) {
 	const int lane = threadIdx.x & 31;
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
@@ -251,6 +295,7 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 		RayTmp r;
 		r.numsteps = 0;
 		r.startt = 0.f;
+		bool long_ray = false;
 #pragma unroll
 		for (int e = 0; e < 3; ++e) r.o[e] = r.d[e] = 0.f;
 		const uint32_t ig = i + cfg.ray_index_offset;
@@ -282,11 +327,15 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 			float startt = tmin;
 			startt += calc_dt(startt, cfg.cone_angle_constant) * rng.next_float();
 			r.startt = startt;
-			r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane);
+			uint32_t n_chunks = 0;
+			r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane,
+			                              masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks);
+			long_ray = n_chunks > kMaskWords;
 		}
 		if (lane == 0) {
-			tmp[i] = r;
 			scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
+			if (long_ray) r.numsteps |= 0x80000000u;  // the mask record does not cover this ray: the emit pass marches again
+			tmp[i] = r;
 		}
 	}
 }
@@ -344,13 +393,16 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
                                                            const RayTmp* __restrict__ tmp,
                                                            const uint64_t* __restrict__ scan, uint32_t* __restrict__ ray_indices,
                                                            float* __restrict__ rays, uint32_t* __restrict__ numsteps,
-                                                           float* __restrict__ coords, uint32_t* __restrict__ counters) {
+                                                           float* __restrict__ coords, uint32_t* __restrict__ counters,
+                                                           const uint32_t* __restrict__ masks) {
 	const int lane = threadIdx.x & 31;
 	if (blockIdx.x == 0 && threadIdx.x == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps, dropped rays included
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
-		const RayTmp r = tmp[i];
+		RayTmp r = tmp[i];
+		const bool long_ray = (r.numsteps & 0x80000000u) != 0;
+		r.numsteps &= 0x7fffffffu;
 		if (r.numsteps == 0) continue;
 		const uint64_t key = scan[i];
 		const uint32_t base = (uint32_t)(key & 0xFFFFFFFFull), kidx = (uint32_t)(key >> 32);
@@ -372,7 +424,11 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
 		}
 		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
 		const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
-		march_ray<true>(cfg, r.o, dirn, r.startt, bitfield, r.numsteps, coords + (size_t)base * 7, lane);
+		// the mask record covers the first kMaskWords * 32 ray parameters; longer rays march again
+		if (masks && !long_ray)
+			emit_from_masks(cfg, r.o, dirn, r.startt, masks + (size_t)i * kMaskWords, r.numsteps, coords + (size_t)base * 7, lane);
+		else
+			march_ray<true>(cfg, r.o, dirn, r.startt, bitfield, r.numsteps, coords + (size_t)base * 7, lane);
 	}
 }
 
@@ -730,13 +786,13 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
 	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
-	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
+	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_march_masks);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
 	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
-	                                                             ws->d_coords, ws->d_counters);
+	                                                             ws->d_coords, ws->d_counters, ws->d_march_masks);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }
@@ -827,12 +883,12 @@ extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const ne
 	N2B_CHECK_CUDA(cudaMemsetAsync(d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
 	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
-	                                                            (RayTmp*)ray_tmp, scan);
+	                                                            (RayTmp*)ray_tmp, scan, nullptr);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
 	N2B_CHECK_LAUNCH();
 	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
-	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters);
+	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters, nullptr);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }

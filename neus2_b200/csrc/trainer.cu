@@ -236,6 +236,7 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	TB_ALLOC(tb->ws.d_counters, (size_t)8);
 	TB_ALLOC(tb->ws.d_scan_tmp, (size_t)tb->max_rays + 1024);
 	TB_ALLOC(tb->ws.d_ray_tmp, (size_t)tb->max_rays * 8);
+	TB_ALLOC(tb->ws.d_march_masks, (size_t)tb->max_rays * 64);
 	TB_ALLOC(tb->mlp_out, (size_t)tb->max_samples * 16);
 	TB_ALLOC(tb->dloss, (size_t)tb->target * 16);
 	TB_ALLOC(tb->coords_compacted, (size_t)tb->target * 7);

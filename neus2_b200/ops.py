@@ -110,7 +110,7 @@ def neus_sdf(d, params, x, sdf_bias=-0.1):
 class RayBatch:
     """Device scratch of one ray batch (neus2b_ray_workspace) plus the dataset handle."""
 
-    def __init__(self, max_rays, max_samples, device="cuda"):
+    def __init__(self, max_rays, max_samples, device="cuda", march_masks=True):
         self.max_rays, self.max_samples = max_rays, max_samples
         i32, f32 = torch.int32, torch.float32
         self.ray_indices = torch.zeros(max_rays, dtype=i32, device=device)
@@ -120,8 +120,10 @@ class RayBatch:
         self.counters = torch.zeros(8, dtype=i32, device=device)
         self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
         self.ray_tmp = torch.zeros((max_rays, 8), dtype=f32, device=device)
+        self.march_masks = torch.zeros((max_rays, 64), dtype=i32, device=device) if march_masks else None
         self.ws = L.RayWorkspace(max_rays, max_samples, L.ptr(self.ray_indices), L.ptr(self.rays), L.ptr(self.numsteps),
-                                 L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp), None)
+                                 L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp), None,
+                                 L.ptr(self.march_masks))
 
 
 def make_dataset(pixels, xforms, focal, principal):
@@ -179,3 +181,9 @@ def adam_step(cfg, grad_mlp, grad_grid, grad_var, master, m, v, params, params_e
     L.check(L.lib().neus2b_adam_step(C.byref(cfg), C.c_uint64(master.numel()), L.ptr(grad_mlp), L.ptr(grad_grid), L.ptr(grad_var),
                                      L.ptr(master), L.ptr(m), L.ptr(v), L.ptr(params), L.ptr(params_ema), L.ptr(ema_master),
                                      L.cur_stream()))
+
+
+def adam_step_packed(cfg, grad_mlp, grad_grid, grad_var, state, params, params_ema=None):
+    """state: float32 [n][4] = {master, m, v, ema master}."""
+    L.check(L.lib().neus2b_adam_step_packed(C.byref(cfg), C.c_uint64(state.shape[0]), L.ptr(grad_mlp), L.ptr(grad_grid),
+                                            L.ptr(grad_var), L.ptr(state), L.ptr(params), L.ptr(params_ema), L.cur_stream()))

@@ -67,15 +67,16 @@ def sphere_model(O, variance=0.5):
     return d, O.f16_bits(p)
 
 
+@pytest.mark.parametrize("masks", [True, False])
 @pytest.mark.parametrize("n_rays,max_samples,snap", [(8192, 1 << 20, False), (4096, 20000, True), (128, 1 << 16, False)])
-def test_generate_samples_bit_exact(gpu, oracle, n_rays, max_samples, snap):
+def test_generate_samples_bit_exact(gpu, oracle, n_rays, max_samples, snap, masks):
     L, ops = gpu
     O = oracle
     ods, gds = scene(O, ops)
     _, bf, _ = ball_bitfield(O)
     ocfg, gcfg = O.train_cfg(snap_to_pixel_centers=snap), L.train_cfg(snap_to_pixel_centers=snap)
     ref = O.generate_samples(ods, ocfg, n_rays, 12345, max_samples, O.pcg32(1337), bf)
-    batch = ops.RayBatch(n_rays, max_samples)
+    batch = ops.RayBatch(n_rays, max_samples, march_masks=masks)
     ops.generate_samples(gds, gcfg, n_rays, 12345, L.pcg32(1337), torch.from_numpy(bf).cuda(), batch)
     torch.cuda.synchronize()
     cnt = batch.counters.cpu().numpy().view(np.uint32)
