@@ -140,19 +140,11 @@ def run_ours(args):
     tb.set_params(S.init_params(ng, seed=1337))
     ptrs = tb.device_ptrs()
     stream = torch.cuda.ExternalStream(ptrs["stream"])
-    grads = None
-    if world > 1:
-        grads = [cuda_view(ptrs["grad_grid"], ng * 2).view(torch.float16), cuda_view(ptrs["grad_mlp"], 12288 * 4).view(torch.float32),
-                 cuda_view(ptrs["grad_variance"], 16).view(torch.float32)]
+    from neus2_b200.parallel import DataParallelTrainer
+    dp = DataParallelTrainer(tb, ng)
 
     def step(read_stats=False):
-        if world == 1:
-            return tb.train(1, read_stats=read_stats)
-        tb.train_backward()
-        with torch.cuda.stream(stream):
-            for g in grads:
-                dist.all_reduce(g)
-        return tb.optimizer_step(read_stats=read_stats)
+        return dp.step(read_stats=read_stats)
 
     def barrier():
         torch.cuda.synchronize()

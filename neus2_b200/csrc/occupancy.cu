@@ -334,7 +334,7 @@ extern "C" int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d
 	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
 	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
 	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
-	adam_kernel<<<kSMs * 16, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
+	adam_kernel<<<div_up((n + 3) / 4, 256), 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
 	                                          d_master, d_m, d_v, (__half*)d_params, (__half*)d_params_ema, d_ema_master);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
