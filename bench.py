@@ -350,6 +350,7 @@ def cpu_baseline(tb, sample=1 << 16):
     import numpy as np
     from oracle import oracle as O
     cores = os.cpu_count() or 1
+    O.set_num_threads(cores)
     d = O.grid_desc()
     p32 = tb.get_params()
     params = O.f16_bits(p32)
@@ -384,6 +385,7 @@ def run_reference(args):
     from oracle import oracle as O
     from neus2_b200 import synthetic as S
     cores = os.cpu_count() or 1
+    O.set_num_threads(cores)  # torchrun pins OMP_NUM_THREADS=1: the reference arm uses every host core
     d = O.grid_desc()
     ng = O.grid_n_params(d)
     p32 = S.init_params(ng, seed=1337)

@@ -300,6 +300,20 @@ int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* 
  * offset), z range [z0, z1), EMA parameters when use_ema.  d_out float[(z1-z0) * res[1] * res[0]] on the device. */
 int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3], uint32_t z0, uint32_t z1, int use_ema, float* d_out);
 
+/* ---------------------------------------------------------------- mesh extraction (src/marching_cubes.cu) */
+
+/* marching_cubes_gpu (src/marching_cubes.cu:794-822; kernels gen_vertices :276-329, gen_faces :377-718).  Vertex and
+ * triangle numbering is canonical (cell-linear order, edges +x, +y, +z inside a cell) instead of atomicAdd order.
+ * d_sdf float[res[2]][res[1]][res[0]] (x fastest); d_tri_table int8[256][16] is the caller's case table (the reference keeps
+ * its own next to gen_faces); d_scratch from neus2b_marching_cubes_scratch_bytes.
+ * Call once with d_verts == NULL: counts -> d_counts[0] vertices, d_counts[1] indices (device).  Call again with the same
+ * d_scratch and buffers of at least those sizes: d_verts float[n][3] (scaled into the aabb like the reference,
+ * v * (max-min)/res + min), d_indices uint32[n]. */
+int neus2b_marching_cubes_scratch_bytes(const uint32_t res[3], uint64_t* bytes);
+int neus2b_marching_cubes(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], float thresh, const float* d_sdf,
+                          const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts, uint32_t* d_indices,
+                          uint32_t max_indices, uint32_t* d_counts, neus2b_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

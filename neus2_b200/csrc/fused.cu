@@ -454,18 +454,7 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == MODE_TRAIN ? 1 : 2) neus_
 							const float q = bxv[bx] * g.ay[by] + g.ax[bx] * byv[by];
 							const float w = p * g.az[bz];
 							const float coef = q * g.az[bz] + p * bzv[bz];
-#if defined(N2B_EXP_NO_COARSE)
-							if (l >= 8)
-#elif defined(N2B_EXP_NO_FINE)
-							if (l < 8)
-#elif defined(N2B_EXP_ONLY_L0_3)
-							if (l < 4)
-#endif
-#ifndef N2B_EXP_NO_SCATTER
 							red_add_h2(a.grad_grid, geom_index(g, k), __fmaf_rn(w, dz.x, coef * ge.x), __fmaf_rn(w, dz.y, coef * ge.y));
-#else
-							if (w == 123.f) a.grad_grid[geom_index(g, k)] = __float2half_rn(coef * ge.x + dz.x);
-#endif
 						}
 					}
 				}

@@ -140,9 +140,6 @@ __device__ __forceinline__ void smem_accumulate(const float (&acc)[N / 8][4], fl
 	float* r0 = dW + (m0 + g) * ldw + 2 * t;
 	float* r1 = dW + (m0 + g + 8) * ldw + 2 * t;
 	const int odd = g & 1;
-#ifdef N2B_EXP_NO_SMEM_ACC
-	if (acc[0][0] != 123.f) return;
-#endif
 #pragma unroll
 	for (int nt = 0; nt < N / 8; ++nt) {
 		atomicAdd(r0 + nt * 8 + odd, odd ? acc[nt][1] : acc[nt][0]);

@@ -187,3 +187,27 @@ def adam_step_packed(cfg, grad_mlp, grad_grid, grad_var, state, params, params_e
     """state: float32 [n][4] = {master, m, v, ema master}."""
     L.check(L.lib().neus2b_adam_step_packed(C.byref(cfg), C.c_uint64(state.shape[0]), L.ptr(grad_mlp), L.ptr(grad_grid),
                                             L.ptr(grad_var), L.ptr(state), L.ptr(params), L.ptr(params_ema), L.cur_stream()))
+
+
+def marching_cubes(sdf, tri_table=None, thresh=0.0, aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0)):
+    """sdf: float32 CUDA tensor [rz][ry][rx].  Returns (verts [n][3] float32, indices [m] int32) in canonical order.
+    tri_table: int8 [256][16] case table (defaults to the generated one of neus2_b200.mc_table)."""
+    if tri_table is None:
+        from .mc_table import make_table
+        tri_table = torch.from_numpy(make_table())
+    tt = tri_table.to(device=sdf.device, dtype=torch.int8).contiguous()
+    rz, ry, rx = sdf.shape
+    res = (C.c_uint32 * 3)(rx, ry, rz)
+    mn, mx = (C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max)
+    nb = C.c_uint64(0)
+    L.check(L.lib().neus2b_marching_cubes_scratch_bytes(res, C.byref(nb)))
+    scratch = torch.empty(nb.value // 8, dtype=torch.int64, device=sdf.device)
+    counts = torch.zeros(2, dtype=torch.int32, device=sdf.device)
+    L.check(L.lib().neus2b_marching_cubes(mn, mx, res, C.c_float(thresh), L.ptr(sdf), L.ptr(tt), L.ptr(scratch), None, u32(0), None,
+                                          u32(0), L.ptr(counts), L.cur_stream()))
+    nv, ni = [int(v) for v in counts.cpu()]
+    verts = torch.empty((max(nv, 1), 3), dtype=torch.float32, device=sdf.device)
+    idx = torch.empty(max(ni, 1), dtype=torch.int32, device=sdf.device)
+    L.check(L.lib().neus2b_marching_cubes(mn, mx, res, C.c_float(thresh), L.ptr(sdf), L.ptr(tt), L.ptr(scratch), L.ptr(verts), u32(nv),
+                                          L.ptr(idx), u32(ni), L.ptr(counts), L.cur_stream()))
+    return verts[:nv], idx[:ni]

@@ -117,3 +117,9 @@ class Testbed:
         L.check(L.lib().neus2b_testbed_sdf_grid(self._h, (C.c_uint32 * 3)(*res), C.c_uint32(z0), C.c_uint32(z1), C.c_int(int(use_ema)),
                                                 C.c_void_p(out.data_ptr())))
         return out
+
+    def compute_marching_cubes_mesh(self, resolution=256, thresh=0.0, tri_table=None, use_ema=True):
+        """Testbed::compute_and_save_marching_cubes_mesh without the file writer (src/testbed.cu:298): SDF on the lattice with the
+        EMA parameters, then marching cubes at `thresh`.  Returns (verts, indices) as CUDA tensors."""
+        from . import ops
+        return ops.marching_cubes(self.sdf_grid(resolution, use_ema=use_ema), tri_table=tri_table, thresh=thresh)

@@ -5,8 +5,11 @@
 #include "neus2_oracle.h"
 
 #include <math.h>
+#include <omp.h>
 #include <stdlib.h>
 #include <string.h>
+
+void n2o_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 /* ------------------------------------------------------------------ fp16 helpers */
 static inline float h2f(uint16_t h) {

@@ -53,6 +53,8 @@ typedef struct {
 #define N2O_MLP_N (N2O_RGB_W3 + 16 * 64)
 #define N2O_GRID_OFF N2O_MLP_N
 
+void n2o_set_num_threads(int n); /* OpenMP threads used by every entry point below */
+
 void n2o_grid_make_levels(const n2o_grid_desc* d, n2o_grid_levels* out);
 uint32_t n2o_grid_n_params(const n2o_grid_desc* d);  /* fp16 scalars */
 uint32_t n2o_model_n_params(const n2o_grid_desc* d); /* whole block incl. 4 variance slots */

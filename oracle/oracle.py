@@ -75,6 +75,10 @@ def lib():
     return _lib
 
 
+def set_num_threads(n):
+    lib().n2o_set_num_threads(C.c_int(int(n)))
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
