@@ -1,8 +1,11 @@
 // Fused NeuS graph kernels on tcgen05 / TMEM (NerfNetwork::forward_impl / backward_impl of the reference,
 // include/neural-graphics-primitives/nerf_network.h:132-641), sm_100a.
 //
-// A CTA of 256 threads owns a tile of 128 samples.  Thread t works for sample (t & 127): the two threads of a sample
-// split the 16 grid levels (gather, Jacobian, scatter) and the accumulator columns (epilogues).  Every dense
+// A CTA of 512 threads owns a tile of 128 samples.  Thread t works for sample (t & 127): the four threads of a sample
+// split the 16 grid levels (gather, Jacobian, scatter: levels 4 p .. 4 p + 3 for part p = t / 128) and the accumulator
+// columns (epilogues: 16 each).  The graph's per-sample arithmetic, not the tensor cores, bounds these kernels, and it
+// runs at the dependent-issue rate of the resident warps: 16 warps per SM instead of 8 is worth more than anything
+// else, while the shared memory stays small enough to leave about 100 KB of L1 for the hash-grid gather.  Every dense
 // contraction of the graph is a tcgen05.mma chain issued by one thread with M = 128 (the samples), operands read from
 // shared memory in the core-matrix layout (tc05.cuh), fp32 accumulators in tensor memory:
 //   forward:  Hs = relu(Zs W1s^T), Ys = Hs W2s^T, Gz = S W1s (d y0 / d z), H1, H2 (, out) of the colour net;
@@ -20,7 +23,7 @@
 namespace n2b {
 namespace tcf {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512, kParts = 4;
 constexpr int T48 = 128 * 48 * 2, T64 = 128 * 64 * 2, T16 = 128 * 16 * 2;
 
 static __device__ uint32_t g_tc_error;  // bit 0: a bounded completion wait ran out
@@ -39,9 +42,9 @@ struct Smem {
 	unsigned char X2[MODE == MODE_TRAIN ? T64 : 16];  // H2 -> dH1
 	unsigned char X3[MODE == MODE_TRAIN ? T64 : 16];  // dH2 -> dHs -> T
 	unsigned char dY[MODE == MODE_TRAIN ? T16 : 16];  // dY3 -> dYs -> e0
-	float nrm[2][128][3];
+	float nrm[kParts][128][3];
 	float vbuf[128][4];
-	float red[8];
+	float red[kThreads / 32];
 	uint64_t mbar;
 	uint32_t tmem_base;
 	uint32_t pad;
@@ -68,36 +71,33 @@ __device__ __forceinline__ void st16(unsigned char* tile, int row, int col, int 
 	*reinterpret_cast<uint4*>(tile + tc::blk_off(row, col, C)) = *reinterpret_cast<const uint4*>(h8);
 }
 
-// Accumulator columns [c0, c0+32) of this thread's row -> fp16 tile row.  ACT: 0 = plain, 1 = ReLU (returns the mask of
-// positive outputs), 2 = multiply by the given mask bits (ReLU backward).
+// Accumulator columns [c0, c0+16) of this thread's row -> fp16 tile row.  ACT: 1 = ReLU (returns the mask of positive
+// outputs), 2 = multiply by the given mask bits (ReLU backward).
 template <int ACT>
-__device__ __forceinline__ uint32_t epilogue32(uint32_t taddr, int row, int c0, unsigned char* tile, uint32_t mask_in) {
+__device__ __forceinline__ uint32_t epilogue16(uint32_t taddr, int row, int c0, unsigned char* tile, uint32_t mask_in) {
 	uint32_t mask_out = 0;
+	float v[16];
+	tc::tmem_ld16(taddr + c0, v);
+	tc::tmem_ld_wait();
+	__align__(16) __half h[16];
 #pragma unroll
-	for (int q = 0; q < 2; ++q) {
-		float v[16];
-		tc::tmem_ld16(taddr + c0 + 16 * q, v);
-		tc::tmem_ld_wait();
-		__align__(16) __half h[16];
-#pragma unroll
-		for (int e = 0; e < 16; ++e) {
-			float x = v[e];
-			if (ACT == 1) x = fmaxf(x, 0.f);
-			__half hx = __float2half_rn(x);
-			if (ACT == 1 && __half2float(hx) > 0.f) mask_out |= 1u << (16 * q + e);
-			if (ACT == 2 && !((mask_in >> (16 * q + e)) & 1u)) hx = __float2half_rn(0.f);
-			h[e] = hx;
-		}
-		st16(tile, row, c0 + 16 * q, 64, h);
-		st16(tile, row, c0 + 16 * q + 8, 64, h + 8);
+	for (int e = 0; e < 16; ++e) {
+		float x = v[e];
+		if (ACT == 1) x = fmaxf(x, 0.f);
+		__half hx = __float2half_rn(x);
+		if (ACT == 1 && __half2float(hx) > 0.f) mask_out |= 1u << e;
+		if (ACT == 2 && !((mask_in >> e) & 1u)) hx = __float2half_rn(0.f);
+		h[e] = hx;
 	}
+	st16(tile, row, c0, 64, h);
+	st16(tile, row, c0 + 8, 64, h + 8);
 	return mask_out;
 }
 
-// S[row][c0 .. c0+32) = mask ? W2s[0][c] : 0   (W2s row 0 read from the staged, blocked weight tile)
+// S[row][c0 .. c0+16) = mask ? W2s[0][c] : 0   (W2s row 0 read from the staged, blocked weight tile)
 __device__ __forceinline__ void write_S(const unsigned char* W2s, unsigned char* tile, int row, int c0, uint32_t mask) {
 #pragma unroll
-	for (int q = 0; q < 4; ++q) {
+	for (int q = 0; q < 2; ++q) {
 		const int c = c0 + 8 * q;
 		__align__(16) __half w[8];
 		*reinterpret_cast<uint4*>(w) = *reinterpret_cast<const uint4*>(W2s + tc::blk_off(0, c, 64));
@@ -108,12 +108,23 @@ __device__ __forceinline__ void write_S(const unsigned char* W2s, unsigned char*
 	}
 }
 
+// 8 consecutive fp32 columns of the thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+	uint32_t r[8];
+	asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+	             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+	             : "r"(taddr)
+	             : "memory");
+#pragma unroll
+	for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) {
 	extern __shared__ __align__(128) unsigned char smem_raw[];
 	Smem<MODE>& sm = *reinterpret_cast<Smem<MODE>*>(smem_raw);
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-	const int s = tid & 127, hl = tid >> 7;
+	const int s = tid & 127, part = tid >> 7;
 	const __half* grid = a.params + NEUS2B_GRID_OFF;
 	constexpr uint32_t kTmemCols = MODE == MODE_TRAIN ? 512u : 128u;
 
@@ -149,9 +160,11 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	const float bias = __half2float(__float2half_rn(a.sdf_bias));
 	float var_grad = 0.f;
 	uint32_t phase = 0;
-	bool ok = true, first = true;
+	bool ok = true, first = true, pending = false;
 
-#define N2B_ISSUE(BODY)                                  \
+	// A wait that ran out stays failed for the thread (later waits return at once); nobody leaves the tile loop early, so
+	// the barriers always match and the kernel ends by itself with the error flag raised.
+#define N2B_ISSUE_NOWAIT(BODY)                           \
 	tc::fence_async_smem();                              \
 	tc::fence_before_sync();                             \
 	__syncthreads();                                     \
@@ -159,11 +172,14 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		tc::fence_after_sync();                          \
 		BODY;                                            \
 		tc::commit(mbar);                                \
-	}                                                    \
-	ok = tc::mbar_wait(mbar, phase);                     \
+	}
+#define N2B_WAIT()                                       \
+	if (ok) ok = tc::mbar_wait(mbar, phase);             \
 	phase ^= 1u;                                         \
-	if (!ok) break;                                      \
 	tc::fence_after_sync();
+#define N2B_ISSUE(BODY)    \
+	N2B_ISSUE_NOWAIT(BODY) \
+	N2B_WAIT()
 
 	for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
 		const uint32_t i = tile * 128u + (uint32_t)s;
@@ -178,11 +194,12 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			dir[1] = c[a.dir_offset + 1];
 			dir[2] = c[a.dir_offset + 2];
 		}
-		// ---- gather: features of this thread's 8 levels -> Zs, Jacobian d enc / d x kept in registers
-		float J[8][6];
+		// ---- gather: features of this thread's 4 levels -> Zs, Jacobian d enc / d x kept in registers
+		float J[4][6];
+		__half2 feats[4];
 #pragma unroll
-		for (int j = 0; j < 8; ++j) {
-			const uint32_t l = 2 * j + hl;
+		for (int j = 0; j < 4; ++j) {
+			const uint32_t l = 4 * part + j;
 			__half2 feat = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
 			for (int e = 0; e < 6; ++e) J[j][e] = 0.f;
@@ -212,45 +229,59 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				}
 				feat = __floats2half2_rn(a0, a1);
 			}
-			*reinterpret_cast<__half2*>(sm.Zs + tc::blk_off(s, 2 * l, 48)) = feat;
+			feats[j] = feat;
 		}
-		if (hl == 0) {
+		// the previous tile's last GEMMs (weight gradients only) still read the tiles: wait for them here, behind the gather
+		if (pending) {
+			N2B_WAIT();
+			pending = false;
+		}
+		{
+			__align__(16) __half f8[8];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				f8[2 * j] = __low2half(feats[j]);
+				f8[2 * j + 1] = __high2half(feats[j]);
+			}
+			st16(sm.Zs, s, 8 * part, 48, f8);  // levels 4 p .. 4 p + 3 = columns 8 p .. 8 p + 7
+		}
+		if (part == 0) {
 #pragma unroll
 			for (int e = 0; e < 3; ++e)
 				*reinterpret_cast<__half*>(sm.Zs + tc::blk_off(s, 32 + e, 48)) = __float2half_rn(__half2float(__float2half_rn(x[e])) - 0.5f);
 		}
 		// ---- Hs = relu(Zs W1s^T)
 		N2B_ISSUE(gemm<64>(tm, kmaj(sm.Zs, 48), kmaj(sm.W1s, 48), 3, false));
-		const uint32_t m_hs = epilogue32<1>(R0, s, hl * 32, sm.Hs, 0u);
-		write_S(sm.W2s, sm.X1, s, hl * 32, m_hs);
+		const uint32_t m_hs = epilogue16<1>(R0, s, part * 16, sm.Hs, 0u);
+		write_S(sm.W2s, sm.X1, s, part * 16, m_hs);
 		// ---- Ys = Hs W2s^T (R1[0:16]) ; Gz = S W1s (R0[0:48])
 		N2B_ISSUE(gemm<16>(tm + 64, kmaj(sm.Hs, 64), kmaj(sm.W2s, 64), 4, false);
 		          gemm<48>(tm, kmaj(sm.X1, 64), mnmaj(sm.W1s, 48), 4, false));
-		__half2 ge[8];
+		__half2 ge[4];
 		float nrm[3] = {0.f, 0.f, 0.f};
-#pragma unroll
-		for (int q = 0; q < 3; ++q) {
-			float v[16];
-			tc::tmem_ld16(R0 + 16 * q, v);
+		{
+			float v[8];
+			tmem_ld8(R0 + 8 * part, v);  // d y0 / d (features of this thread's levels)
 			tc::tmem_ld_wait();
-			if (q < 2) {
 #pragma unroll
-				for (int jj = 0; jj < 4; ++jj) {
-					const int j = 4 * q + jj;
-					const float g0 = __half2float(__float2half_rn(hl ? v[4 * jj + 2] : v[4 * jj]));
-					const float g1 = __half2float(__float2half_rn(hl ? v[4 * jj + 3] : v[4 * jj + 1]));
-					ge[j] = __floats2half2_rn(g0, g1);
+			for (int j = 0; j < 4; ++j) {
+				const float g0 = __half2float(__float2half_rn(v[2 * j]));
+				const float g1 = __half2float(__float2half_rn(v[2 * j + 1]));
+				ge[j] = __floats2half2_rn(g0, g1);
 #pragma unroll
-					for (int e = 0; e < 3; ++e) nrm[e] = __fmaf_rn(J[j][2 * e], g0, __fmaf_rn(J[j][2 * e + 1], g1, nrm[e]));
-				}
-			} else if (hl == 0) {
-#pragma unroll
-				for (int e = 0; e < 3; ++e) nrm[e] += __half2float(__float2half_rn(v[e]));
+				for (int e = 0; e < 3; ++e) nrm[e] = __fmaf_rn(J[j][2 * e], g0, __fmaf_rn(J[j][2 * e + 1], g1, nrm[e]));
 			}
 		}
+		if (part == 0) {
+			float v[8];
+			tmem_ld8(R0 + 32, v);  // direct position columns of the SDF-net input
+			tc::tmem_ld_wait();
 #pragma unroll
-		for (int e = 0; e < 3; ++e) sm.nrm[hl][s][e] = nrm[e];
-		if (hl == 1) {
+			for (int e = 0; e < 3; ++e) nrm[e] += __half2float(__float2half_rn(v[e]));
+		}
+#pragma unroll
+		for (int e = 0; e < 3; ++e) sm.nrm[part][s][e] = nrm[e];
+		if (part == 1) {
 			float v[16];
 			tc::tmem_ld16(R1, v);
 			tc::tmem_ld_wait();
@@ -259,8 +290,10 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(v[e]);
 			st16(sm.Zc, s, 0, 48, h);
 			st16(sm.Zc, s, 8, 48, h + 8);
+		} else if (part == 2) {
 			float sh[16];
 			sh4_eval(dir, sh);
+			__align__(16) __half h[16];
 #pragma unroll
 			for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(sh[e]);
 			st16(sm.Zc, s, 16, 48, h);
@@ -268,11 +301,11 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		}
 		tc::fence_before_sync();
 		__syncthreads();
-		if (hl == 0) {
+		if (part == 0) {
 			__align__(16) __half h[8];
 #pragma unroll
 			for (int e = 0; e < 3; ++e) {
-				nrm[e] = sm.nrm[0][s][e] + sm.nrm[1][s][e];
+				nrm[e] = ((sm.nrm[0][s][e] + sm.nrm[1][s][e]) + sm.nrm[2][s][e]) + sm.nrm[3][s][e];
 				h[e] = __float2half_rn(x[e]);
 				h[3 + e] = __float2half_rn(nrm[e]);
 			}
@@ -281,15 +314,15 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		}
 		// ---- colour net
 		N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.Zc, 48), kmaj(sm.W1c, 48), 3, false));
-		const uint32_t m_h1 = epilogue32<1>(R1, s, hl * 32, sm.X1, 0u);
+		const uint32_t m_h1 = epilogue16<1>(R1, s, part * 16, sm.X1, 0u);
 		N2B_ISSUE(gemm<64>(tm, kmaj(sm.X1, 64), kmaj(sm.W2c, 64), 4, false));
 		unsigned char* H2 = MODE == MODE_TRAIN ? sm.X2 : sm.Hs;
-		const uint32_t m_h2 = epilogue32<1>(R0, s, hl * 32, H2, 0u);
+		const uint32_t m_h2 = epilogue16<1>(R0, s, part * 16, H2, 0u);
 		(void)m_h1;
 		(void)m_h2;
 		if constexpr (MODE == MODE_FWD) {
 			N2B_ISSUE(gemm<16>(tm + 64, kmaj(H2, 64), kmaj(sm.W3c, 64), 4, false));
-			if (hl == 0) {
+			if (part == 0) {
 				float v[16];
 				tc::tmem_ld16(R1, v);
 				tc::tmem_ld_wait();
@@ -314,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			__align__(16) __half g[16];
 #pragma unroll
 			for (int k = 0; k < 16; ++k) g[k] = __float2half_rn(0.f);
-			if (hl == 0) {
+			if (part == 0) {
 				if (valid) {
 					const uint4* src = reinterpret_cast<const uint4*>(a.dL_dout + (size_t)i * 16);
 					reinterpret_cast<uint4*>(g)[0] = __ldg(src);
@@ -328,16 +361,16 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			}
 			N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.dY, 16), mnmaj(sm.W3c, 64), 1, false);
 			          gemm<16>(WG_W3cT, mnmaj(sm.X2, 64), mnmaj(sm.dY, 16), 8, !first));
-			epilogue32<2>(R1, s, hl * 32, sm.X3, m_h2);  // dH2
+			epilogue16<2>(R1, s, part * 16, sm.X3, m_h2);  // dH2
 			// ---- B2
 			N2B_ISSUE(gemm<64>(tm, kmaj(sm.X3, 64), mnmaj(sm.W2c, 64), 4, false);
 			          gemm<64>(WG_W2c, mnmaj(sm.X3, 64), mnmaj(sm.X1, 64), 8, !first));
-			epilogue32<2>(R0, s, hl * 32, sm.X2, m_h1);  // dH1 (over H2)
+			epilogue16<2>(R0, s, part * 16, sm.X2, m_h1);  // dH1 (over H2)
 			// ---- B3
 			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X2, 64), mnmaj(sm.W1c, 48), 4, false);
 			          gemm<48>(WG_W1c, mnmaj(sm.X2, 64), mnmaj(sm.Zc, 48), 8, !first));
 			// ---- B4: SDF-net output gradient = colour-net input gradient rows 0-15 (+ dL/dsdf), v = dL/dnormal (:388-395, :465-491)
-			if (hl == 0) {
+			if (part == 0) {
 				float v[16];
 				tc::tmem_ld16(R1, v);
 				tc::tmem_ld_wait();
@@ -356,28 +389,27 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			}
 			N2B_ISSUE(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false);
 			          gemm<16>(WG_W2sT, mnmaj(sm.Hs, 64), mnmaj(sm.dY, 16), 8, !first));
-			epilogue32<2>(R0, s, hl * 32, sm.X3, m_hs);  // dHs
+			epilogue16<2>(R0, s, part * 16, sm.X3, m_hs);  // dHs
 			// ---- B5
 			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X3, 64), mnmaj(sm.W1s, 48), 4, false);
 			          gemm<48>(WG_W1s, mnmaj(sm.X3, 64), mnmaj(sm.Zs, 48), 8, !first));
 			// ---- B6: grid gradient (first + second order merged, one reduction per corner); U = [J v | v | 0] over Zs
 			const float v3[3] = {sm.vbuf[s][0], sm.vbuf[s][1], sm.vbuf[s][2]};
-#pragma unroll
-			for (int q = 0; q < 2; ++q) {
-				float dzv[16];
-				tc::tmem_ld16(R1 + 16 * q, dzv);
+			{
+				float dzv[8];
+				tmem_ld8(R1 + 8 * part, dzv);
 				tc::tmem_ld_wait();
+				__align__(16) __half u8[8];
 #pragma unroll
-				for (int jj = 0; jj < 4; ++jj) {
-					const int j = 4 * q + jj;
-					const uint32_t l = 2 * j + hl;
+				for (int j = 0; j < 4; ++j) {
+					const uint32_t l = 4 * part + j;
 					__half2 dy = __floats2half2_rn(0.f, 0.f);
 					if (l < a.lv.n_active) {
 						dy = __floats2half2_rn(J[j][0] * v3[0] + J[j][2] * v3[1] + J[j][4] * v3[2],
 						                       J[j][1] * v3[0] + J[j][3] * v3[1] + J[j][5] * v3[2]);
 						if (valid) {
-							const float dz0 = __half2float(__float2half_rn(hl ? dzv[4 * jj + 2] : dzv[4 * jj]));
-							const float dz1 = __half2float(__float2half_rn(hl ? dzv[4 * jj + 3] : dzv[4 * jj + 1]));
+							const float dz0 = __half2float(__float2half_rn(dzv[2 * j]));
+							const float dz1 = __half2float(__float2half_rn(dzv[2 * j + 1]));
 							const float2 gef = __half22float2(ge[j]);
 							const LevelGeom g2 = level_geom(a.lv, l, x);
 							const float scale = a.lv.scale[l];
@@ -394,13 +426,15 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 							}
 						}
 					}
-					*reinterpret_cast<__half2*>(sm.Zs + tc::blk_off(s, 2 * l, 48)) = dy;
+					u8[2 * j] = __low2half(dy);
+					u8[2 * j + 1] = __high2half(dy);
 				}
+				st16(sm.Zs, s, 8 * part, 48, u8);
 			}
-			if (hl == 0) {
+			if (part == 0) {
 #pragma unroll
 				for (int e = 0; e < 3; ++e) *reinterpret_cast<__half*>(sm.Zs + tc::blk_off(s, 32 + e, 48)) = __float2half_rn(v3[e]);
-			} else {
+			} else if (part == 1) {
 				// second-order seed dy = e0 for every live sample (:497-503)
 				__align__(16) __half e0[16];
 #pragma unroll
@@ -408,18 +442,26 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				st16(sm.dY, s, 0, 16, e0);
 				st16(sm.dY, s, 8, 16, e0 + 8);
 			}
-			write_S(sm.W2s, sm.X1, s, hl * 32, m_hs);
+			write_S(sm.W2s, sm.X1, s, part * 16, m_hs);
 			// ---- B7: T = D .* (U W1s^T);  dW2s[0,:] += sum_b T;  dW1s += S^T U  (:560-571)
 			N2B_ISSUE(gemm<64>(tm, kmaj(sm.Zs, 48), kmaj(sm.W1s, 48), 3, false));
-			epilogue32<2>(R0, s, hl * 32, sm.X3, m_hs);  // T
-			N2B_ISSUE(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.dY, 16), 8, true);
-			          gemm<48>(WG_W1s, mnmaj(sm.X1, 64), mnmaj(sm.Zs, 48), 8, true));
+			epilogue16<2>(R0, s, part * 16, sm.X3, m_hs);  // T
+			N2B_ISSUE_NOWAIT(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.dY, 16), 8, true);
+			                 gemm<48>(WG_W1s, mnmaj(sm.X1, 64), mnmaj(sm.Zs, 48), 8, true));
+			pending = true;
 			first = false;
 		}
-		tc::fence_before_sync();
-		__syncthreads();  // tiles and accumulators are free for the next round
+		if constexpr (MODE == MODE_FWD) {
+			tc::fence_before_sync();
+			__syncthreads();  // the output rows are out of tensor memory: tiles and accumulators are free for the next round
+		}
+	}
+	if (pending) {
+		N2B_WAIT();
 	}
 #undef N2B_ISSUE
+#undef N2B_ISSUE_NOWAIT
+#undef N2B_WAIT
 	if (!ok) atomicOr(&g_tc_error, 1u);
 	tc::fence_before_sync();
 	__syncthreads();
@@ -428,38 +470,40 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	if constexpr (MODE == MODE_TRAIN) {
 		// ---- flush the weight gradients held in tensor memory (rows 0..63 of each accumulator)
 		if (ok && !first && s < 64) {
-			if (hl == 0) {
+			float v[16];
+			if (part == 0) {
 #pragma unroll
 				for (int q = 0; q < 4; ++q) {
-					float v[16];
 					tc::tmem_ld16(WG_W2c + lrow + 16 * q, v);
 					tc::tmem_ld_wait();
 #pragma unroll
 					for (int e = 0; e < 16; ++e)
 						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W2 + s * 64 + 16 * q + e, v[e]);
 				}
-				float v[16];
-				tc::tmem_ld16(WG_W3cT + lrow, v);  // [in = s][out]
-				tc::tmem_ld_wait();
-#pragma unroll
-				for (int e = 0; e < 16; ++e)
-					if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W3 + e * 64 + s, v[e]);
-			} else {
+			} else if (part == 1) {
 #pragma unroll
 				for (int q = 0; q < 3; ++q) {
-					float v[16];
 					tc::tmem_ld16(WG_W1c + lrow + 16 * q, v);
 					tc::tmem_ld_wait();
 #pragma unroll
 					for (int e = 0; e < 16; ++e)
 						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W1 + s * 48 + 16 * q + e, v[e]);
+				}
+			} else if (part == 2) {
+#pragma unroll
+				for (int q = 0; q < 3; ++q) {
 					tc::tmem_ld16(WG_W1s + lrow + 16 * q, v);
 					tc::tmem_ld_wait();
 #pragma unroll
 					for (int e = 0; e < 16; ++e)
 						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_SDF_W1 + s * 48 + sdf_orig_col(16 * q + e), v[e]);
 				}
-				float v[16];
+			} else {
+				tc::tmem_ld16(WG_W3cT + lrow, v);  // [in = s][out]
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int e = 0; e < 16; ++e)
+					if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_RGB_W3 + e * 64 + s, v[e]);
 				tc::tmem_ld16(WG_W2sT + lrow, v);
 				tc::tmem_ld_wait();
 #pragma unroll
@@ -474,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		__syncthreads();
 		if (tid == 0) {
 			float t = 0.f;
-			for (int w = 0; w < 8; ++w) t += sm.red[w];
+			for (int w = 0; w < kThreads / 32; ++w) t += sm.red[w];
 			if (t != 0.f) atomicAdd(a.grad_var, t);
 		}
 	}
@@ -488,7 +532,7 @@ static int launch(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) {
 	const size_t smem = sizeof(Smem<MODE>) + 128;
 	N2B_CHECK_CUDA(cudaFuncSetAttribute(neus_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	uint32_t ctas = (n_upper + 127u) / 128u;
-	const uint32_t per_sm = MODE == MODE_TRAIN ? 1u : 2u;
+	const uint32_t per_sm = 1u;
 	if (ctas > kSMs * per_sm) ctas = kSMs * per_sm;
 	if (ctas == 0) return NEUS2B_OK;
 	neus_tc_kernel<MODE><<<ctas, kThreads, smem, stream>>>(a);
