@@ -145,17 +145,14 @@ __global__ void __launch_bounds__(256, 8) adam_kernel(neus2b_adam_cfg c, float l
 		if (matrix) {
 			const float4 a = *reinterpret_cast<const float4*>(grad_mlp + i0);
 			g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
-			*reinterpret_cast<float4*>(grad_mlp + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
 		} else if (!var) {
 			uint2 raw = *reinterpret_cast<const uint2*>(grad_grid + (i0 - c.n_matrix));
 			const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
 			const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
 			g[0] = f0.x; g[1] = f0.y; g[2] = f1.x; g[3] = f1.y;
-			*reinterpret_cast<uint2*>(grad_grid + (i0 - c.n_matrix)) = make_uint2(0u, 0u);
 		} else {
 			const float4 a = *reinterpret_cast<const float4*>(grad_var);
 			g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
-			*reinterpret_cast<float4*>(grad_var) = make_float4(0.f, 0.f, 0.f, 0.f);
 		}
 		const float4 w4 = *reinterpret_cast<const float4*>(master + i0);
 		const float4 m4 = *reinterpret_cast<const float4*>(m + i0);
@@ -180,12 +177,18 @@ __global__ void __launch_bounds__(256, 8) adam_kernel(neus2b_adam_cfg c, float l
 			__half2 e01 = __floats2half2_rn(em[0], em[1]), e23 = __floats2half2_rn(em[2], em[3]);
 			*reinterpret_cast<uint2*>(params_ema + i0) = make_uint2(*reinterpret_cast<uint32_t*>(&e01), *reinterpret_cast<uint32_t*>(&e23));
 		}
+		// Clear the gradient last, and only where it is set: a store to the address of a load still in flight holds up
+		// every later load of the thread until that load has returned (measured: 3.1 instead of 6.1 TB/s for the pass).
+		if (g[0] != 0.f || g[1] != 0.f || g[2] != 0.f || g[3] != 0.f) {
+			if (matrix) *reinterpret_cast<float4*>(grad_mlp + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
+			else if (!var) *reinterpret_cast<uint2*>(grad_grid + (i0 - c.n_matrix)) = make_uint2(0u, 0u);
+			else *reinterpret_cast<float4*>(grad_var) = make_float4(0.f, 0.f, 0.f, 0.f);
+		}
 	}
 }
 
-// Same update with the optimizer-private state interleaved per parameter: state[i] = {master, m, v, ema master}.
-// Separate arrays make eleven concurrent address streams, and the pass then reaches about a third of the copy
-// bandwidth; packed, the state is one read-modify-write stream of 16 bytes per parameter.
+// Same update with the optimizer-private state interleaved per parameter: state[i] = {master, m, v, ema master}, one
+// read-modify-write stream of 16 bytes per parameter instead of four arrays.
 __global__ void __launch_bounds__(256, 8) adam_packed_kernel(neus2b_adam_cfg c, float lr_t, float ema_old, float ema_new_inv, uint64_t n,
                                                              float* __restrict__ grad_mlp, __half* __restrict__ grad_grid,
                                                              float* __restrict__ grad_var, float4* __restrict__ state,
@@ -198,17 +201,13 @@ __global__ void __launch_bounds__(256, 8) adam_packed_kernel(neus2b_adam_cfg c, 
 		if (matrix) {
 			const float2 a = *reinterpret_cast<const float2*>(grad_mlp + i0);
 			g[0] = a.x; g[1] = a.y;
-			*reinterpret_cast<float2*>(grad_mlp + i0) = make_float2(0.f, 0.f);
 		} else if (i0 < n_grid_end) {
 			const __half2 h = *reinterpret_cast<const __half2*>(grad_grid + (i0 - c.n_matrix));
 			const float2 f = __half22float2(h);
 			g[0] = f.x; g[1] = f.y;
-			*reinterpret_cast<__half2*>(grad_grid + (i0 - c.n_matrix)) = __floats2half2_rn(0.f, 0.f);
 		} else {
 			g[0] = grad_var[i0 - n_grid_end];
 			g[1] = grad_var[i0 - n_grid_end + 1];
-			grad_var[i0 - n_grid_end] = 0.f;
-			grad_var[i0 - n_grid_end + 1] = 0.f;
 		}
 		float4 s0 = state[i0], s1 = state[i0 + 1];
 		s0.x = adam_element(c, lr_t, matrix, g[0], s0.x, s0.y, s0.z);
@@ -219,6 +218,11 @@ __global__ void __launch_bounds__(256, 8) adam_packed_kernel(neus2b_adam_cfg c, 
 		state[i0 + 1] = s1;
 		*reinterpret_cast<__half2*>(params + i0) = __floats2half2_rn(s0.x, s1.x);
 		if (params_ema) *reinterpret_cast<__half2*>(params_ema + i0) = __floats2half2_rn(s0.w, s1.w);
+		if (g[0] != 0.f || g[1] != 0.f) {  // cleared last and only where set, as in adam_kernel
+			if (matrix) *reinterpret_cast<float2*>(grad_mlp + i0) = make_float2(0.f, 0.f);
+			else if (i0 < n_grid_end) *reinterpret_cast<__half2*>(grad_grid + (i0 - c.n_matrix)) = __floats2half2_rn(0.f, 0.f);
+			else grad_var[i0 - n_grid_end] = grad_var[i0 - n_grid_end + 1] = 0.f;
+		}
 	}
 }
 
