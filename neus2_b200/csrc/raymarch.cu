@@ -152,9 +152,10 @@ struct RayTmp {  // 8 floats per ray
 // One warp marches one ray.  The reference's loop visits a sequence of ray parameters t defined by the serial recurrence
 // t <- t + calc_dt(t); at a visited t it either takes a sample (occupied cell) or jumps: it keeps adding steps until t
 // reaches the far side of the empty cell (advance_to_next_voxel).  Here the 32 lanes evaluate 32 consecutive t of that
-// same recurrence at once (position, containment, occupancy bit, jump target: the expensive, independent part), then
-// every lane replays the visit / jump decisions over the chunk in ray order, which is cheap and keeps the result
-// identical to the serial loop: same visited set, same samples, same count.
+// same recurrence at once (position, containment, occupancy bit, jump target: the expensive, independent part) and
+// where the serial loop would go next from there; then the warp follows that chain over the visited parameters of the
+// chunk in ray order (one shuffle per visited parameter), which keeps the result identical to the serial loop: same
+// visited set, same samples, same count.
 constexpr uint32_t kMaskWords = 64;  // per-ray record of the count pass: one bit per ray parameter that became a sample
 
 template <bool EMIT>
@@ -204,29 +205,44 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 			}
 		}
 		const uint32_t in_mask = __ballot_sync(0xffffffffu, inside), occ_mask = __ballot_sync(0xffffffffu, occ);
-		// replay the chunk in ray order (identical in every lane)
-		bool emit = false;
-		uint32_t slot = 0;
-		t = t_chunk;
-#pragma unroll 4
-		for (int k = 0; k < 32; ++k) {
-			const float tk = t;
-			t += calc_dt(t, cone_angle);
-			if (stop || tk < skip_until) continue;  // not visited: the reference was still jumping here
+		// Where the serial loop goes after visiting this lane's parameter: the next one if it becomes a sample, else the first
+		// later parameter with t >= target (t grows along the lanes: a binary search over the lanes' my_t).
+		uint32_t nxt;
+		{
+			uint32_t lo = (uint32_t)lane + 1u, hi = 32u;
+#pragma unroll
+			for (int it = 0; it < 5; ++it) {
+				const uint32_t mid = (lo + hi) >> 1;
+				const float tm = __shfl_sync(0xffffffffu, my_t, (int)(mid & 31u));
+				if (lo < hi) {
+					if (tm < target) lo = mid + 1u;
+					else hi = mid;
+				}
+			}
+			nxt = occ ? (uint32_t)lane + 1u : lo;
+		}
+		// Walk the visited parameters only, in ray order, identically in every lane: same visited set, same samples and
+		// the same count as the serial loop.
+		uint32_t emit_mask = 0u;
+		int last_empty = -1;
+		const uint32_t j0 = j;
+		uint32_t k = __ffs(__ballot_sync(0xffffffffu, my_t >= skip_until)) - 1u;  // first parameter not jumped over (0xffffffff: none)
+		while (k < 32u) {
 			if (!((in_mask >> k) & 1u) || j >= limit) {
 				stop = true;
-				continue;
+				break;
 			}
 			if ((occ_mask >> k) & 1u) {
-				if (lane == k) {
-					emit = true;
-					slot = j;
-				}
+				emit_mask |= 1u << k;
 				++j;
 			} else {
-				skip_until = __shfl_sync(0xffffffffu, target, k);
+				last_empty = (int)k;
 			}
+			k = __shfl_sync(0xffffffffu, nxt, (int)k);
 		}
+		if (last_empty >= 0) skip_until = __shfl_sync(0xffffffffu, target, last_empty);
+		const bool emit = (emit_mask >> lane) & 1u;
+		const uint32_t slot = j0 + __popc(emit_mask & ((1u << lane) - 1u));
 		t_chunk = t;
 		if (!EMIT && masks && chunk < kMaskWords) {
 			const uint32_t m = __ballot_sync(0xffffffffu, emit);
