@@ -2,7 +2,7 @@
 // include/neural-graphics-primitives/nerf_network.h:132-641), sm_100a.
 //
 // A CTA of 512 threads owns a tile of 128 samples.  Thread t works for sample (t & 127): the four threads of a sample
-// split the 16 grid levels (gather, Jacobian, scatter: levels 4 p .. 4 p + 3 for part p = t / 128) and the accumulator
+// split the 16 grid levels (gather, Jacobian, scatter: levels p, p + 4, p + 8, p + 12 for part p = t / 128) and the accumulator
 // columns (epilogues: 16 each).  The graph's per-sample arithmetic, not the tensor cores, bounds these kernels, and it
 // runs at the dependent-issue rate of the resident warps: 16 warps per SM instead of 8 is worth more than anything
 // else, while the shared memory stays small enough to leave about 100 KB of L1 for the hash-grid gather.  Every dense
@@ -24,6 +24,19 @@ namespace n2b {
 namespace tcf {
 
 constexpr int kThreads = 512, kParts = 4;
+#ifndef N2B_MERGED_J
+#define N2B_MERGED_J 2
+#endif
+constexpr int kMergedJ = N2B_MERGED_J;  // the levels 0 .. 4 * kMergedJ - 1 pre-reduce their grid gradients in the warp
+
+// Part p of a sample's four threads owns the levels p, p + 4, p + 8, p + 12 (a coarse, two middle and a fine one each, so
+// the parts carry equal work) and keeps their features in the internal columns 8 p .. 8 p + 7 of the SDF-net input;
+// the position follows in columns 32..34.  Original column (reference order: position, then the levels) of internal k:
+__device__ __forceinline__ int tc_orig_col(int k) {
+	if (k >= 32) return k < 35 ? k - 32 : k;
+	const int p = k >> 3, j = (k >> 1) & 3, f = k & 1;
+	return 3 + 2 * (p + 4 * j) + f;
+}
 constexpr int T48 = 128 * 48 * 2, T64 = 128 * 64 * 2, T16 = 128 * 16 * 2;
 
 static __device__ uint32_t g_tc_error;  // bit 0: a bounded completion wait ran out
@@ -133,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	__syncthreads();
 	for (int e = tid; e < 64 * 48; e += kThreads) {
 		const int r = e / 48, k = e % 48;
-		*reinterpret_cast<__half*>(sm.W1s + tc::blk_off(r, k, 48)) = a.params[NEUS2B_SDF_W1 + r * 48 + sdf_orig_col(k)];
+		*reinterpret_cast<__half*>(sm.W1s + tc::blk_off(r, k, 48)) = a.params[NEUS2B_SDF_W1 + r * 48 + tc_orig_col(k)];
 		*reinterpret_cast<__half*>(sm.W1c + tc::blk_off(r, k, 48)) = a.params[NEUS2B_RGB_W1 + e];
 	}
 	for (int e = tid; e < 16 * 64; e += kThreads) {
@@ -152,7 +165,6 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	const uint32_t lrow = (uint32_t)((warp & 3) * 32) << 16;  // this warp's tensor-memory lanes: rows (warp & 3) * 32 + lane == s
 	const uint32_t R0 = tm + lrow, R1 = tm + 64 + lrow;
 	const uint32_t WG_W2c = tm + 128, WG_W1c = tm + 192, WG_W1s = tm + 240, WG_W3cT = tm + 288, WG_W2sT = tm + 304;
-	(void)lane;
 
 	const uint32_t n = a.d_n ? min(*a.d_n, a.n) : a.n;
 	const uint32_t n_tiles = (n + 127u) / 128u;
@@ -199,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		__half2 feats[4];
 #pragma unroll
 		for (int j = 0; j < 4; ++j) {
-			const uint32_t l = 4 * part + j;
+			const uint32_t l = (uint32_t)(part + 4 * j);
 			__half2 feat = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
 			for (int e = 0; e < 6; ++e) J[j][e] = 0.f;
@@ -243,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				f8[2 * j] = __low2half(feats[j]);
 				f8[2 * j + 1] = __high2half(feats[j]);
 			}
-			st16(sm.Zs, s, 8 * part, 48, f8);  // levels 4 p .. 4 p + 3 = columns 8 p .. 8 p + 7
+			st16(sm.Zs, s, 8 * part, 48, f8);  // this part's levels = columns 8 p .. 8 p + 7
 		}
 		if (part == 0) {
 #pragma unroll
@@ -402,19 +414,46 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				__align__(16) __half u8[8];
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
-					const uint32_t l = 4 * part + j;
+					const uint32_t l = (uint32_t)(part + 4 * j);
 					__half2 dy = __floats2half2_rn(0.f, 0.f);
 					if (l < a.lv.n_active) {
 						dy = __floats2half2_rn(J[j][0] * v3[0] + J[j][2] * v3[1] + J[j][4] * v3[2],
 						                       J[j][1] * v3[0] + J[j][3] * v3[1] + J[j][5] * v3[2]);
-						if (valid) {
-							const float dz0 = __half2float(__float2half_rn(dzv[2 * j]));
-							const float dz1 = __half2float(__float2half_rn(dzv[2 * j + 1]));
-							const float2 gef = __half22float2(ge[j]);
-							const LevelGeom g2 = level_geom(a.lv, l, x);
-							const float scale = a.lv.scale[l];
-							const float bxv[2] = {-scale * v3[0], scale * v3[0]}, byv[2] = {-scale * v3[1], scale * v3[1]};
-							const float bzv[2] = {-scale * v3[2], scale * v3[2]};
+						const float dz0 = __half2float(__float2half_rn(dzv[2 * j]));
+						const float dz1 = __half2float(__float2half_rn(dzv[2 * j + 1]));
+						const float2 gef = __half22float2(ge[j]);
+						const LevelGeom g2 = level_geom(a.lv, l, x);
+						const float scale = a.lv.scale[l];
+						const float bxv[2] = {-scale * v3[0], scale * v3[0]}, byv[2] = {-scale * v3[1], scale * v3[1]};
+						const float bzv[2] = {-scale * v3[2], scale * v3[2]};
+						if (j < kMergedJ) {
+							// Coarse levels: consecutive samples of a ray sit in the same cell, and thousands of samples hit the same few
+							// hundred entries, where the L2 atomics serialise.  Lanes are consecutive samples: sum each run of lanes with
+							// the same cell inside the warp (segmented shuffle reduction) and let the run's first lane add the total.
+							const uint32_t px = __shfl_up_sync(0xffffffffu, g2.hx[0], 1), py = __shfl_up_sync(0xffffffffu, g2.hy[0], 1);
+							const uint32_t pz = __shfl_up_sync(0xffffffffu, g2.hz[0], 1);
+							const bool head = lane == 0 || px != g2.hx[0] || py != g2.hy[0] || pz != g2.hz[0];
+							const uint32_t after = (__ballot_sync(0xffffffffu, head) >> lane) >> 1;
+							const uint32_t rest = after ? (uint32_t)__ffs((int)after) - 1u : 31u - (uint32_t)lane;  // lanes behind this one in its run
+#pragma unroll
+							for (uint32_t k = 0; k < 8; ++k) {
+								const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+								const float p = g2.ax[bx] * g2.ay[by];
+								const float qq = bxv[bx] * g2.ay[by] + g2.ax[bx] * byv[by];
+								const float w = p * g2.az[bz];
+								const float coef = qq * g2.az[bz] + p * bzv[bz];
+								float v0 = valid ? __fmaf_rn(w, dz0, coef * gef.x) : 0.f, v1 = valid ? __fmaf_rn(w, dz1, coef * gef.y) : 0.f;
+#pragma unroll
+								for (uint32_t d = 1; d < 32; d <<= 1) {
+									const float o0 = __shfl_down_sync(0xffffffffu, v0, d), o1 = __shfl_down_sync(0xffffffffu, v1, d);
+									if (d <= rest) {
+										v0 += o0;
+										v1 += o1;
+									}
+								}
+								if (head && (v0 != 0.f || v1 != 0.f)) red_add_h2(a.grad_grid, geom_index(g2, k), v0, v1);
+							}
+						} else if (valid) {
 #pragma unroll
 							for (uint32_t k = 0; k < 8; ++k) {
 								const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
@@ -496,7 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 					tc::tmem_ld_wait();
 #pragma unroll
 					for (int e = 0; e < 16; ++e)
-						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_SDF_W1 + s * 48 + sdf_orig_col(16 * q + e), v[e]);
+						if (v[e] != 0.f) atomicAdd(a.grad_mlp + NEUS2B_SDF_W1 + s * 48 + tc_orig_col(16 * q + e), v[e]);
 				}
 			} else {
 				tc::tmem_ld16(WG_W3cT + lrow, v);  // [in = s][out]
