@@ -296,6 +296,11 @@ int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_params, uint16_t
  * (NCCL) on the returned stream, then optimizer_step applies Adam.  neus2b_testbed_train == both halves back to back. */
 int neus2b_testbed_train_backward(neus2b_testbed* tb);
 int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats);
+/* Times the fused forward+backward kernel inside the step (the reference keeps a moving average of the whole step only,
+ * m_training_ms, src/testbed.cu:2707-2721): arms CUDA-event pairs around that launch for the next max_steps steps on
+ * the training stream (0 = off).  When h_ms_sum and h_n are given, first returns the sum of the durations recorded
+ * since the previous call and their count (synchronises the stream). */
+int neus2b_testbed_profile(neus2b_testbed* tb, uint32_t max_steps, float* h_ms_sum, uint32_t* h_n);
 /* get_density_on_grid (src/testbed_nerf.cu:4082-4133): SDF on a res[0] x res[1] x res[2] lattice x/res (no half-voxel
  * offset), z range [z0, z1), EMA parameters when use_ema.  d_out float[(z1-z0) * res[1] * res[0]] on the device. */
 int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3], uint32_t z0, uint32_t z1, int use_ema, float* d_out);

@@ -117,6 +117,10 @@ struct neus2b_testbed {
 	neus2b_dataset ds{};
 	float* h_cam = nullptr;  // pinned staging for the camera block
 	std::vector<void*> allocs;
+	// optional timing of the fused forward+backward kernel inside the step (event pairs on the training stream)
+	std::vector<cudaEvent_t> prof_events;
+	uint32_t prof_used = 0;
+	bool prof_on = false;
 };
 
 template <typename T>
@@ -172,6 +176,7 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	for (void* p : tb->allocs) cudaFree(p);
 	if (tb->h_state) cudaFreeHost(tb->h_state);
 	if (tb->h_cam) cudaFreeHost(tb->h_cam);
+	for (cudaEvent_t e : tb->prof_events) cudaEventDestroy(e);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
 }
@@ -413,10 +418,40 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	rc = neus2b_compute_loss(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->target, (const uint16_t*)tb->mlp_out, &tb->ws,
 	                         tb->coords_compacted, (uint16_t*)tb->dloss, tb->loss, tb->ek_loss, 1, tb->stream);
 	if (rc) return rc;
+	const bool timed = tb->prof_on && tb->prof_used + 2 <= tb->prof_events.size();
+	if (timed) cudaEventRecord(tb->prof_events[tb->prof_used], tb->stream);
 	rc = neus2b_neus_train(&d, (const uint16_t*)tb->params, tb->target, tb->coords_compacted, (const uint16_t*)tb->dloss,
 	                       tb->target * tb->cfg.world_size, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->stream);
 	if (rc) return rc;
+	if (timed) {
+		cudaEventRecord(tb->prof_events[tb->prof_used + 1], tb->stream);
+		tb->prof_used += 2;
+	}
 	tb->rng.advance(1ull << 32);  // m_rng.advance() (src/testbed_nerf.cu:3981)
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_profile(neus2b_testbed* tb, uint32_t max_steps, float* h_ms_sum, uint32_t* h_n) {
+	if (!tb) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (h_ms_sum && h_n) {  // read back what has been recorded so far
+		N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+		float sum = 0.f;
+		for (uint32_t i = 0; i + 1 < tb->prof_used; i += 2) {
+			float ms = 0.f;
+			N2B_CHECK_CUDA(cudaEventElapsedTime(&ms, tb->prof_events[i], tb->prof_events[i + 1]));
+			sum += ms;
+		}
+		*h_ms_sum = sum;
+		*h_n = tb->prof_used / 2;
+	}
+	while (tb->prof_events.size() < 2u * (size_t)max_steps) {
+		cudaEvent_t e;
+		N2B_CHECK_CUDA(cudaEventCreate(&e));
+		tb->prof_events.push_back(e);
+	}
+	tb->prof_used = 0;
+	tb->prof_on = max_steps > 0;
 	return NEUS2B_OK;
 }
 

@@ -118,6 +118,13 @@ class Testbed:
                                                 C.c_void_p(out.data_ptr())))
         return out
 
+    def profile_train_kernel(self, max_steps=0):
+        """Arms timing of the fused forward+backward kernel for the next `max_steps` steps (0 = off) and returns
+        (sum of milliseconds, launches) recorded since the previous call."""
+        ms, n = C.c_float(0.0), C.c_uint32(0)
+        L.check(L.lib().neus2b_testbed_profile(self._h, C.c_uint32(max_steps), C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     def compute_marching_cubes_mesh(self, resolution=256, thresh=0.0, tri_table=None, use_ema=True):
         """Testbed::compute_and_save_marching_cubes_mesh without the file writer (src/testbed.cu:298): SDF on the lattice with the
         EMA parameters, then marching cubes at `thresh`.  Returns (verts, indices) as CUDA tensors."""
