@@ -317,6 +317,33 @@ def run_kernel_only(args):
             times.append(e0.elapsed_time(e1))
         print(json.dumps({"kernel": "adam", "n_params": n, "ms": times, "GBps": 40.0 * n / (min(times) * 1e-3) / 1e9}))
         return
+    if args.kernel == "mesh":
+        # BASELINE config 4's mesh half: SDF on a res^3 lattice through the fused SDF kernel, then marching cubes
+        import time
+        from neus2_b200.testbed import Testbed
+        res = args.mesh_res
+        tb = Testbed(batch_size=1 << 18)
+        tb.set_params(S.init_params(ng, seed=1337))  # geometric initialisation: a sphere-like SDF
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        stream = torch.cuda.ExternalStream(tb.device_ptrs()["stream"])
+        out = []
+        for it in range(args.kernel_iters):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            e[0].record(stream)
+            sdf = tb.sdf_grid(res, use_ema=False)
+            e[1].record(stream)
+            stream.synchronize()
+            e[2].record()
+            v, i = ops.marching_cubes(sdf)
+            e[3].record()
+            torch.cuda.synchronize()
+            out.append({"sdf_ms": e[0].elapsed_time(e[1]), "mc_ms": e[2].elapsed_time(e[3]), "wall_s": time.perf_counter() - t0,
+                        "verts": int(v.shape[0]), "triangles": int(i.shape[0]) // 3})
+            del sdf, v, i
+        print(json.dumps({"kernel": "mesh", "res": res, "runs": out}))
+        tb.close()
+        return
     p = S.init_params(ng, seed=1337)
     rng = np.random.default_rng(9)
     p[12288:12288 + ng] = rng.uniform(-1e-2, 1e-2, ng)
@@ -457,9 +484,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh"], help="run one fused kernel alone (profiling)")
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
+    ap.add_argument("--mesh-res", type=int, default=512)
     args = ap.parse_args()
     if args.kernel:
         run_kernel_only(args)
