@@ -229,7 +229,7 @@ int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, 
                      neus2b_stream_t stream);
 
 /* The same step with the optimizer-private state interleaved per parameter: d_state [n][4] fp32 = {master weight, Adam m,
- * Adam v, EMA master}.  One read-modify-write stream instead of eight: this is the layout the training loop uses. */
+ * Adam v, EMA master}: one read-modify-write stream instead of four arrays (the training loop keeps separate arrays). */
 int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid,
                             float* d_grad_variance, float* d_state, uint16_t* d_params, uint16_t* d_params_ema,
                             neus2b_stream_t stream);
