@@ -221,24 +221,36 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 #pragma unroll
 				for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, geom_index(g, k));
 				const float scale = a.lv.scale[l];
-				float a0 = 0.f, a1 = 0.f;
+				// Trilinear value and its gradient, factored: along an axis the derivative is the difference of the two faces
+				// weighted by the other two axes' products (fp32 throughout, one rounding of the value to fp16).
+				float2 t[8];
 #pragma unroll
-				for (uint32_t k = 0; k < 8; ++k) {
-					const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
-					const float2 t = __half22float2(th[k]);
-					const float w = g.ax[bx] * g.ay[by] * g.az[bz];
-					a0 = __fmaf_rn(w, t.x, a0);
-					a1 = __fmaf_rn(w, t.y, a1);
-					const float dwx = (bx ? scale : -scale) * g.ay[by] * g.az[bz];
-					const float dwy = (by ? scale : -scale) * g.ax[bx] * g.az[bz];
-					const float dwz = (bz ? scale : -scale) * g.ax[bx] * g.ay[by];
-					J[j][0] = __fmaf_rn(dwx, t.x, J[j][0]);
-					J[j][1] = __fmaf_rn(dwx, t.y, J[j][1]);
-					J[j][2] = __fmaf_rn(dwy, t.x, J[j][2]);
-					J[j][3] = __fmaf_rn(dwy, t.y, J[j][3]);
-					J[j][4] = __fmaf_rn(dwz, t.x, J[j][4]);
-					J[j][5] = __fmaf_rn(dwz, t.y, J[j][5]);
-				}
+				for (int k = 0; k < 8; ++k) t[k] = __half22float2(th[k]);
+				float a0 = 0.f, a1 = 0.f;
+				float jx0 = 0.f, jx1 = 0.f, jy0 = 0.f, jy1 = 0.f, jz0 = 0.f, jz1 = 0.f;
+#pragma unroll
+				for (int u = 0; u < 2; ++u)
+#pragma unroll
+					for (int v = 0; v < 2; ++v) {
+						const float pyz = g.ay[u] * g.az[v], pxz = g.ax[u] * g.az[v], pxy = g.ax[u] * g.ay[v];
+						const float2 x0 = t[2 * u + 4 * v], x1 = t[1 + 2 * u + 4 * v];  // bx = 0 | 1 at (by, bz) = (u, v)
+						a0 = __fmaf_rn(pyz, __fmaf_rn(g.ax[1], x1.x, g.ax[0] * x0.x), a0);
+						a1 = __fmaf_rn(pyz, __fmaf_rn(g.ax[1], x1.y, g.ax[0] * x0.y), a1);
+						jx0 = __fmaf_rn(pyz, x1.x - x0.x, jx0);
+						jx1 = __fmaf_rn(pyz, x1.y - x0.y, jx1);
+						const float2 y0 = t[u + 4 * v], y1 = t[u + 2 + 4 * v];  // by = 0 | 1 at (bx, bz) = (u, v)
+						jy0 = __fmaf_rn(pxz, y1.x - y0.x, jy0);
+						jy1 = __fmaf_rn(pxz, y1.y - y0.y, jy1);
+						const float2 z0 = t[u + 2 * v], z1 = t[u + 2 * v + 4];  // bz = 0 | 1 at (bx, by) = (u, v)
+						jz0 = __fmaf_rn(pxy, z1.x - z0.x, jz0);
+						jz1 = __fmaf_rn(pxy, z1.y - z0.y, jz1);
+					}
+				J[j][0] = scale * jx0;
+				J[j][1] = scale * jx1;
+				J[j][2] = scale * jy0;
+				J[j][3] = scale * jy1;
+				J[j][4] = scale * jz0;
+				J[j][5] = scale * jz1;
 				feat = __floats2half2_rn(a0, a1);
 			}
 			feats[j] = feat;
