@@ -158,55 +158,102 @@ struct RayTmp {  // 8 floats per ray
 // visited set, same samples, same count.
 constexpr uint32_t kMaskWords = 64;  // per-ray record of the count pass: one bit per ray parameter that became a sample
 
+// First half of a chunk: this lane's ray parameter (t after `lane` steps of the recurrence from the chunk start), its
+// position, and the occupancy byte on its way from memory.  Nothing here depends on the visit / jump decisions of earlier
+// chunks, so the next chunk's first half is issued before the current chunk is walked and the lookup latency hides there.
+struct ChunkHead {
+	float my_t, my_dt, t_end, pos[3];
+	uint32_t mip, byte, bit;
+	bool inside;
+};
+__device__ __forceinline__ ChunkHead chunk_head(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float t_chunk,
+                                                const uint8_t* __restrict__ bitfield, int lane) {
+	ChunkHead h;
+	const float cone_angle = cfg.cone_angle_constant;
+	float t = t_chunk;
+	h.my_t = t_chunk;
+	h.my_dt = 0.f;
+	if (cone_angle == 0.f) {
+		// calc_dt(t, 0) = clamp(t * 0, min, max) = the minimum step: same values, same sequence of roundings, a quarter of the
+		// dependent operations
+		const float dt = min_cone_stepsize();
+		h.my_dt = dt;
+#pragma unroll
+		for (int k = 0; k < 32; ++k) {
+			if (lane == k) h.my_t = t;
+			t += dt;
+		}
+	} else {
+#pragma unroll
+		for (int k = 0; k < 32; ++k) {
+			const float dt = calc_dt(t, cone_angle);
+			if (lane == k) {
+				h.my_t = t;
+				h.my_dt = dt;
+			}
+			t += dt;
+		}
+	}
+	h.t_end = t;
+#pragma unroll
+	for (int e = 0; e < 3; ++e) h.pos[e] = o[e] + h.my_t * dirn[e];
+	h.inside = aabb_contains(cfg.aabb_min, cfg.aabb_max, h.pos);
+	h.mip = 0u;
+	h.byte = 0u;
+	h.bit = 0u;
+	if (h.inside) {
+		// cascaded_grid_idx_at / density_grid_occupied_at (:484-510)
+		h.mip = (uint32_t)mip_from_dt(h.my_dt, h.pos);
+		const float mip_scale = scalbnf(1.0f, -(int)h.mip);
+		int c[3];
+#pragma unroll
+		for (int d = 0; d < 3; ++d) {
+			const float p = (h.pos[d] - 0.5f) * mip_scale + 0.5f;
+			const int v = (int)(p * (float)NEUS2B_GRIDSIZE);
+			c[d] = v < 0 ? 0 : (v > (int)NEUS2B_GRIDSIZE - 1 ? (int)NEUS2B_GRIDSIZE - 1 : v);
+		}
+		const uint32_t idx = morton3d((uint32_t)c[0], (uint32_t)c[1], (uint32_t)c[2]);
+		const uint32_t cells = NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE;
+		h.byte = __ldg(bitfield + idx / 8 + (cells * h.mip) / 8);
+		h.bit = 1u << (idx % 8);
+	}
+	return h;
+}
+
 template <bool EMIT>
 __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
                                               const uint8_t* __restrict__ bitfield, uint32_t limit, float* __restrict__ coords_out,
                                               int lane, uint32_t* __restrict__ masks = nullptr,
                                               uint32_t* n_chunks = nullptr) {
 	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
-	const float cone_angle = cfg.cone_angle_constant;
-	float t_chunk = startt, skip_until = -3.402823466e+38f;
+	float skip_until = -3.402823466e+38f;
 	uint32_t j = 0;
 	bool stop = false;
 	// every chunk moves t forward by at least 32 minimum steps, so the ray leaves the box after a bounded number of
 	// chunks; the cap only guards against non-finite inputs
 	uint32_t chunk = 0;
+	ChunkHead cur = chunk_head(cfg, o, dirn, startt, bitfield, lane);
 	for (; chunk < 8192u && !stop; ++chunk) {
-		// this lane's candidate: t after `lane` steps of the recurrence from the chunk start
-		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
-#pragma unroll
-		for (int k = 0; k < 32; ++k) {
-			const float dt = calc_dt(t, cone_angle);
-			if (lane == k) {
-				my_t = t;
-				my_dt = dt;
-			}
-			t += dt;
-		}
-		float pos[3];
-#pragma unroll
-		for (int e = 0; e < 3; ++e) pos[e] = o[e] + my_t * dirn[e];
-		const bool inside = aabb_contains(cfg.aabb_min, cfg.aabb_max, pos);
-		bool occ = false;
+		const ChunkHead next = chunk_head(cfg, o, dirn, cur.t_end, bitfield, lane);
+		const float my_t = cur.my_t, my_dt = cur.my_dt;
+		const float* pos = cur.pos;
+		const bool inside = cur.inside;
+		const bool occ = inside && (cur.byte & cur.bit) != 0;
 		float target = 0.f;
-		if (inside) {
-			const uint32_t mip = (uint32_t)mip_from_dt(my_dt, pos);
-			occ = occupied_at(pos, bitfield, mip);
-			if (!occ) {  // far side of the empty cell: distance_to_next_voxel (:346-354)
-				const uint32_t res = NEUS2B_GRIDSIZE >> mip;
-				float tt[3];
+		if (inside && !occ) {  // far side of the empty cell: distance_to_next_voxel (:346-354)
+			const uint32_t res = NEUS2B_GRIDSIZE >> cur.mip;
+			float tt[3];
 #pragma unroll
-				for (int d = 0; d < 3; ++d) {
-					const float p = (float)res * pos[d];
-					tt[d] = (floorf(p + 0.5f + 0.5f * copysignf(1.0f, dirn[d])) - p) * idir[d];
-				}
-				const float tmin = fminf(fminf(tt[0], tt[1]), tt[2]);
-				target = my_t + fmaxf(tmin / (float)res, 0.0f);
+			for (int d = 0; d < 3; ++d) {
+				const float p = (float)res * pos[d];
+				tt[d] = (floorf(p + 0.5f + 0.5f * copysignf(1.0f, dirn[d])) - p) * idir[d];
 			}
+			const float tmin = fminf(fminf(tt[0], tt[1]), tt[2]);
+			target = my_t + fmaxf(tmin / (float)res, 0.0f);
 		}
 		const uint32_t in_mask = __ballot_sync(0xffffffffu, inside), occ_mask = __ballot_sync(0xffffffffu, occ);
-		// Where the serial loop goes after visiting this lane's parameter: the next one if it becomes a sample, else the first
-		// later parameter with t >= target (t grows along the lanes: a binary search over the lanes' my_t).
+		// Where the serial loop goes after visiting this lane's parameter when its cell is empty: the first later parameter
+		// with t >= target (t grows along the lanes: a binary search over the lanes' my_t).
 		uint32_t nxt;
 		{
 			uint32_t lo = (uint32_t)lane + 1u, hi = 32u;
@@ -219,10 +266,11 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 					else hi = mid;
 				}
 			}
-			nxt = occ ? (uint32_t)lane + 1u : lo;
+			nxt = lo;
 		}
-		// Walk the visited parameters only, in ray order, identically in every lane: same visited set, same samples and
-		// the same count as the serial loop.
+		// Walk the visited parameters in ray order, identically in every lane: a run of occupied cells is taken in one go
+		// (every parameter of the run is visited and becomes a sample until the sample limit), an empty cell costs one
+		// shuffle for its jump.  Same visited set, same samples and the same count as the serial loop.
 		uint32_t emit_mask = 0u;
 		int last_empty = -1;
 		const uint32_t j0 = j;
@@ -233,20 +281,22 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 				break;
 			}
 			if ((occ_mask >> k) & 1u) {
-				emit_mask |= 1u << k;
-				++j;
+				const uint32_t inv = ~(occ_mask >> k);
+				const uint32_t run = inv ? (uint32_t)__ffs((int)inv) - 1u : 32u;  // ones from bit k on
+				const uint32_t take = min(run, limit - j);
+				emit_mask |= (take >= 32u ? 0xffffffffu : ((1u << take) - 1u)) << k;
+				j += take;
+				k += take;
 			} else {
 				last_empty = (int)k;
+				k = __shfl_sync(0xffffffffu, nxt, (int)k);
 			}
-			k = __shfl_sync(0xffffffffu, nxt, (int)k);
 		}
 		if (last_empty >= 0) skip_until = __shfl_sync(0xffffffffu, target, last_empty);
 		const bool emit = (emit_mask >> lane) & 1u;
 		const uint32_t slot = j0 + __popc(emit_mask & ((1u << lane) - 1u));
-		t_chunk = t;
 		if (!EMIT && masks && chunk < kMaskWords) {
-			const uint32_t m = __ballot_sync(0xffffffffu, emit);
-			if (lane == 0) masks[chunk] = m;
+			if (lane == 0) masks[chunk] = emit_mask;
 		}
 		if (EMIT && emit) {
 			float* c = coords_out + (size_t)slot * 7;
@@ -257,6 +307,7 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 			}
 			c[3] = warp_dt(my_dt);
 		}
+		cur = next;
 	}
 	if (n_chunks) *n_chunks = chunk;
 	return j;
@@ -273,14 +324,23 @@ __device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, con
 	for (uint32_t chunk = 0; chunk < kMaskWords && j < numsteps; ++chunk) {
 		const uint32_t m = masks[chunk];
 		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
+		if (cone_angle == 0.f) {  // constant step, see chunk_head
+			my_dt = min_cone_stepsize();
 #pragma unroll
-		for (int k = 0; k < 32; ++k) {
-			const float dt = calc_dt(t, cone_angle);
-			if (lane == k) {
-				my_t = t;
-				my_dt = dt;
+			for (int k = 0; k < 32; ++k) {
+				if (lane == k) my_t = t;
+				t += my_dt;
 			}
-			t += dt;
+		} else {
+#pragma unroll
+			for (int k = 0; k < 32; ++k) {
+				const float dt = calc_dt(t, cone_angle);
+				if (lane == k) {
+					my_t = t;
+					my_dt = dt;
+				}
+				t += dt;
+			}
 		}
 		t_chunk = t;
 		if ((m >> lane) & 1u) {
