@@ -573,10 +573,13 @@ __device__ __forceinline__ float warp_incl_scan(float v, int lane) {
 	return v;
 }
 
-// BENT_DIR (:1574-1579): the direction the network saw at the ray's first sample replaces the ray direction
-__device__ __forceinline__ void bent_dir(const __half* __restrict__ mlp_out, uint32_t base, float* dir) {
-	const __half* o = mlp_out + (size_t)base * 16;
-	const float dd[3] = {__half2float(o[8]) * 2.f - 1.f, __half2float(o[9]) * 2.f - 1.f, __half2float(o[10]) * 2.f - 1.f};
+// BENT_DIR (:1574-1579): the direction the network saw at the ray's first sample replaces the ray direction; read from
+// the second 16-byte half of that sample's output row as lane 0 holds it (halves 8..11 = words x, y).
+__device__ __forceinline__ void bent_dir_from_lane0(uint32_t wx, uint32_t wy, float* dir) {
+	wx = __shfl_sync(kFull, wx, 0);
+	wy = __shfl_sync(kFull, wy, 0);
+	const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&wx)), b = __half22float2(*reinterpret_cast<const __half2*>(&wy));
+	const float dd[3] = {a.x * 2.f - 1.f, a.y * 2.f - 1.f, b.x * 2.f - 1.f};
 	const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
 #pragma unroll
 	for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
@@ -593,21 +596,39 @@ __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, co
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_kept; i += warps) {
 		const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
-		float dir[3];
-		bent_dir(mlp_out, base, dir);
 		float T = 1.f, rgb[3] = {0.f, 0.f, 0.f}, ws = 0.f;
 		uint32_t n = 0;
 		bool done = false;
+		// the next 32 samples are in flight while the current 32 are composited (a long ray is a serial chain of chunks)
+		uint4 q0 = make_uint4(0u, 0u, 0u, 0u), q1 = q0;
+		float qdt = 0.f;
+		if ((uint32_t)lane < ns) {
+			const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + lane) * 16);
+			q0 = __ldg(p);
+			q1 = __ldg(p + 1);
+			qdt = coords[(size_t)(base + lane) * 7 + 3];
+		}
+		float dir[3];
+		bent_dir_from_lane0(q1.x, q1.y, dir);  // kept rays have at least one sample
 		for (uint32_t j0 = 0; j0 < ns && !done; j0 += 32) {
 			const uint32_t j = j0 + lane;
 			const bool valid = j < ns;
+			const uint4 c0 = q0, c1 = q1;
+			const float cdt = qdt;
+			if (j + 32u < ns) {
+				const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + j + 32u) * 16);
+				q0 = __ldg(p);
+				q1 = __ldg(p + 1);
+				qdt = coords[(size_t)(base + j + 32u) * 7 + 3];
+			}
 			NeusSample s;
 			s.alpha = 0.f;
 			s.rgb[0] = s.rgb[1] = s.rgb[2] = 0.f;
 			if (valid) {
 				__align__(16) __half o[16];
-				load_out16(mlp_out + (size_t)(base + j) * 16, o);
-				neus_sample(o, coords[(size_t)(base + j) * 7 + 3], dir, cfg.cos_anneal_ratio, s);
+				reinterpret_cast<uint4*>(o)[0] = c0;
+				reinterpret_cast<uint4*>(o)[1] = c1;
+				neus_sample(o, cdt, dir, cfg.cos_anneal_ratio, s);
 			}
 			const float om = 1.f - s.alpha;
 			const float Tb = serial_transmittance(T, om, lane);
@@ -667,6 +688,18 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 			if (ek_loss_out) ek_loss_out[i] = 0.f;
 		}
 		if (cn == 0) continue;
+		// this ray's first 32 samples are requested now, the next 32 always one chunk ahead: they arrive behind the target
+		// pixel fetch and the compositing of the chunk before
+		uint4 q0 = make_uint4(0u, 0u, 0u, 0u), q1 = q0;
+		float qc[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+		if ((uint32_t)lane < cn) {
+			const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + lane) * 16);
+			q0 = __ldg(p);
+			q1 = __ldg(p + 1);
+			const float* cin = coords + (size_t)(base + lane) * 7;
+#pragma unroll
+			for (int e = 0; e < 7; ++e) qc[e] = cin[e];
+		}
 		// target colour (:1619-1667), computed by every lane
 		const uint32_t ray_idx = ray_indices[i] + cfg.ray_index_offset;
 		Pcg32 rng = rng0;
@@ -718,27 +751,34 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 		if (lane == 0 && loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
 		const float loss_scale = cfg.loss_scale / n_rays_f;
 		float dir[3];
-		bent_dir(mlp_out, base, dir);
+		bent_dir_from_lane0(q1.x, q1.y, dir);
 		float rgb2c[3] = {0.f, 0.f, 0.f}, T = 1.f, ek = 0.f;
 		for (uint32_t j0 = 0; j0 < cn; j0 += 32) {
 			const uint32_t j = j0 + lane;
 			const bool valid = j < cn;
+			const uint4 c0 = q0, c1 = q1;
+			float cs[7];
+#pragma unroll
+			for (int e = 0; e < 7; ++e) cs[e] = qc[e];
+			if (j + 32u < cn) {
+				const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + j + 32u) * 16);
+				q0 = __ldg(p);
+				q1 = __ldg(p + 1);
+				const float* cin = coords + (size_t)(base + j + 32u) * 7;
+#pragma unroll
+				for (int e = 0; e < 7; ++e) qc[e] = cin[e];
+			}
 			NeusSample s;
 			s.alpha = 0.f;
 			s.rgb[0] = s.rgb[1] = s.rgb[2] = 0.f;
 			if (valid) {
 				__align__(16) __half o[16];
-				load_out16(mlp_out + (size_t)(base + j) * 16, o);
-				const float* cin = coords + (size_t)(base + j) * 7;
+				reinterpret_cast<uint4*>(o)[0] = c0;
+				reinterpret_cast<uint4*>(o)[1] = c1;
 				float* cout = coords_out + (size_t)(compacted_base + j) * 7;
-				float cdt = 0.f;
 #pragma unroll
-				for (int e = 0; e < 7; ++e) {
-					const float vv = cin[e];
-					cout[e] = vv;
-					if (e == 3) cdt = vv;
-				}
-				neus_sample(o, cdt, dir, cfg.cos_anneal_ratio, s);
+				for (int e = 0; e < 7; ++e) cout[e] = cs[e];
+				neus_sample(o, cs[3], dir, cfg.cos_anneal_ratio, s);
 			}
 			const float om = 1.f - s.alpha;
 			const float Tb = serial_transmittance(T, om, lane);
