@@ -92,18 +92,25 @@ __device__ __forceinline__ uint32_t epilogue16(uint32_t taddr, int row, int c0, 
 	float v[16];
 	tc::tmem_ld16(taddr + c0, v);
 	tc::tmem_ld_wait();
-	__align__(16) __half h[16];
+	__align__(16) uint32_t w[8];  // 8 fp16 pairs
 #pragma unroll
-	for (int e = 0; e < 16; ++e) {
-		float x = v[e];
-		if (ACT == 1) x = fmaxf(x, 0.f);
-		__half hx = __float2half_rn(x);
-		if (ACT == 1 && __half2float(hx) > 0.f) mask_out |= 1u << e;
-		if (ACT == 2 && !((mask_in >> e) & 1u)) hx = __float2half_rn(0.f);
-		h[e] = hx;
+	for (int e = 0; e < 8; ++e) {
+		__half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+		if (ACT == 1) h = __hmax2(h, __floats2half2_rn(0.f, 0.f));  // round(relu(x)) == relu(round(x))
+		uint32_t u = *reinterpret_cast<uint32_t*>(&h);
+		if (ACT == 1) {
+			u &= 0x7fff7fffu;  // nothing negative is left: a -0 becomes +0
+			mask_out |= (uint32_t)((u & 0xffffu) != 0u) << (2 * e);
+			mask_out |= (uint32_t)((u & 0xffff0000u) != 0u) << (2 * e + 1);
+		}
+		if (ACT == 2) {
+			const uint32_t keep = (((mask_in >> (2 * e)) & 1u) ? 0xffffu : 0u) | (((mask_in >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
+			u &= keep;
+		}
+		w[e] = u;
 	}
-	st16(tile, row, c0, 64, h);
-	st16(tile, row, c0 + 8, 64, h + 8);
+	*reinterpret_cast<uint4*>(tile + tc::blk_off(row, c0, 64)) = reinterpret_cast<const uint4*>(w)[0];
+	*reinterpret_cast<uint4*>(tile + tc::blk_off(row, c0 + 8, 64)) = reinterpret_cast<const uint4*>(w)[1];
 	return mask_out;
 }
 
@@ -444,9 +451,16 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 							// the same cell inside the warp (segmented shuffle reduction) and let the run's first lane add the total.
 							const uint32_t px = __shfl_up_sync(0xffffffffu, g2.hx[0], 1), py = __shfl_up_sync(0xffffffffu, g2.hy[0], 1);
 							const uint32_t pz = __shfl_up_sync(0xffffffffu, g2.hz[0], 1);
-							const bool head = lane == 0 || px != g2.hx[0] || py != g2.hy[0] || pz != g2.hz[0];
-							const uint32_t after = (__ballot_sync(0xffffffffu, head) >> lane) >> 1;
-							const uint32_t rest = after ? (uint32_t)__ffs((int)after) - 1u : 31u - (uint32_t)lane;  // lanes behind this one in its run
+							const bool cell_head = lane == 0 || px != g2.hx[0] || py != g2.hy[0] || pz != g2.hz[0];
+							const uint32_t hmask = __ballot_sync(0xffffffffu, cell_head);
+							const uint32_t after = (hmask >> lane) >> 1;
+							const uint32_t run_rest = after ? (uint32_t)__ffs((int)after) - 1u : 31u - (uint32_t)lane;  // lanes behind this one in its run
+							// Runs are cut into pieces of kPiece lanes (a ray leaves about a dozen samples in a batch, fewer per cell on
+							// the middle levels), so log2(kPiece) shuffle steps do.
+							const uint32_t kPiece = j == 0 ? 8u : 4u;  // (j is an unrolled loop index: a constant after unrolling)
+							const uint32_t pos = (uint32_t)lane - (31u - (uint32_t)__clz((int)(hmask & (0xffffffffu >> (31 - lane)))));
+							const bool head = (pos & (kPiece - 1u)) == 0u;
+							const uint32_t rest = min(run_rest, kPiece - 1u - (pos & (kPiece - 1u)));
 #pragma unroll
 							for (uint32_t k = 0; k < 8; ++k) {
 								const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
@@ -456,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 								const float coef = qq * g2.az[bz] + p * bzv[bz];
 								float v0 = valid ? __fmaf_rn(w, dz0, coef * gef.x) : 0.f, v1 = valid ? __fmaf_rn(w, dz1, coef * gef.y) : 0.f;
 #pragma unroll
-								for (uint32_t d = 1; d < 32; d <<= 1) {
+								for (uint32_t d = 1; d < kPiece; d <<= 1) {
 									const float o0 = __shfl_down_sync(0xffffffffu, v0, d), o1 = __shfl_down_sync(0xffffffffu, v1, d);
 									if (d <= rest) {
 										v0 += o0;
