@@ -105,6 +105,10 @@ def set_mma_path(path):
     check(lib().neus2b_set_mma_path(C.c_int(path)))
 
 
+def get_mma_path():
+    return int(lib().neus2b_get_mma_path())
+
+
 def device_error_flags():
     v = C.c_uint32(0)
     check(lib().neus2b_device_error_flags(C.byref(v)))
