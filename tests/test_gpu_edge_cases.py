@@ -1,5 +1,7 @@
 """Edge cases of the path through the C ABI: empty and ragged inputs, a fully occupied and a fully empty occupancy grid
 (maximum and zero samples per ray), meshes without a surface, optimizer steps without gradients, the tensor-core path switch."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -78,8 +80,12 @@ def test_fused_kernels_accept_empty_batches(gpu):
     for path in (L.MMA_TCGEN05, L.MMA_SYNC):
         L.set_mma_path(path)
         assert L.get_mma_path() == path
-        ops.neus_forward(d, params, coords[:0], out=out)
-        ops.neus_train(d, params, coords[:0], dl[:0], 1, gm, gg, gv)
+        # n = 0 through the host argument and through the device-side count
+        L.check(L.lib().neus2b_neus_forward(C.byref(d), L.ptr(params), C.c_float(-0.1), C.c_uint32(0), None, L.ptr(coords), L.ptr(out),
+                                            L.cur_stream()))
+        ops.neus_forward(d, params, coords, n_dev=torch.zeros(1, dtype=torch.int32, device="cuda"), out=out)
+        L.check(L.lib().neus2b_neus_train(C.byref(d), L.ptr(params), C.c_uint32(0), L.ptr(coords), L.ptr(dl), C.c_uint32(1), L.ptr(gm),
+                                          L.ptr(gg), L.ptr(gv), L.cur_stream()))
         torch.cuda.synchronize()
         assert float(out[0, 0]) == 7.0 and float(gm.abs().sum()) == 0.0 and float(gg.float().abs().sum()) == 0.0
     L.set_mma_path(L.MMA_TCGEN05)
@@ -122,5 +128,5 @@ def test_adam_without_gradients_leaves_weights(gpu, oracle):
     grid = slice(12288, 12288 + n_grid)
     assert np.array_equal(t[0].cpu().numpy()[grid], master[grid]) and np.array_equal(t[1].cpu().numpy()[grid], m[grid])
     for got, want in zip(t, ro):
-        assert np.allclose(got.cpu().numpy(), want, rtol=2e-6, atol=1e-9)
+        assert np.allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-7)  # fp32 chains, contraction differs (as in test_adam_step)
     assert (np.abs(P.float().cpu().numpy() - O.bits_f32(p_o)) <= 1e-3 * np.abs(O.bits_f32(p_o)) + 1e-7).all()
