@@ -318,6 +318,15 @@ int neus2b_marching_cubes_scratch_bytes(const uint32_t res[3], uint64_t* bytes);
 int neus2b_marching_cubes(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], float thresh, const float* d_sdf,
                           const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts, uint32_t* d_indices,
                           uint32_t max_indices, uint32_t* d_counts, neus2b_stream_t stream);
+/* The same for one z-slab of the lattice, for extraction sharded over GPUs (the reference extracts on one GPU): lattice
+ * layers z0 .. z0 + n_layers - 1 of the res grid, d_sdf_slab float[n_layers][res[1]][res[0]] holding only those layers
+ * (neus2b_testbed_sdf_grid with z0, z1), scratch sized for {res[0], res[1], n_layers}.  Vertex positions are those of the
+ * whole grid; numbering is local to the slab.  d_counts[4] = {vertices, indices, vertices owned by the layers before the
+ * slab's last, vertices owned by its first layer}: what the host needs to drop the copies of the seam vertices. */
+int neus2b_marching_cubes_slab(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0, uint32_t n_layers,
+                               float thresh, const float* d_sdf_slab, const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts,
+                               uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts,
+                               neus2b_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -78,7 +78,7 @@ EXPORTS = [
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
-    "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes",
+    "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
 ]
 
 

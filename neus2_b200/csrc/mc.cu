@@ -14,6 +14,7 @@ namespace n2b {
 struct McGrid {
 	uint32_t rx, ry, rz;
 	uint64_t res2, res3;
+	uint32_t z_off;  // the slab's first lattice layer in the whole grid (vertex positions are those of the whole grid)
 	float thresh;
 	float scale[3], offset[3];
 };
@@ -133,9 +134,17 @@ __global__ void __launch_bounds__(1024) scan_add_kernel(uint64_t n, uint64_t* __
 		if (k0 + e < n) data[k0 + e] += add;
 }
 
-__global__ void mc_counts_kernel(const uint64_t* __restrict__ grand_total, uint32_t* __restrict__ counts) {
-	counts[0] = (uint32_t)(*grand_total & 0xFFFFFFFFull);
+// counts = {vertices, indices} and, for a slab, {vertices owned by the layers before the last one, vertices owned by the
+// first layer} (read off the scanned keys: a cell's key is the number of vertices owned by the cells before it)
+__global__ void mc_counts_kernel(McGrid g, const uint64_t* __restrict__ keys, const uint64_t* __restrict__ grand_total,
+                                 uint32_t* __restrict__ counts, int slab) {
+	const uint32_t nv = (uint32_t)(*grand_total & 0xFFFFFFFFull);
+	counts[0] = nv;
 	counts[1] = (uint32_t)(*grand_total >> 32);
+	if (slab) {
+		counts[2] = (uint32_t)(keys[(uint64_t)(g.rz - 1) * g.res2] & 0xFFFFFFFFull);
+		counts[3] = g.rz > 1 ? (uint32_t)(keys[g.res2] & 0xFFFFFFFFull) : nv;
+	}
 }
 
 // id of the vertex on the edge of cell `c` along `axis` = the cell's vertex base + rank among its crossing edges
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(256) mc_emit_kernel(McGrid g, const float* __r
 			if (!((m >> e) & 1u)) continue;
 			const float f1 = sdf[idx + step[e]];
 			const float dt = (g.thresh - f0) / (f1 - f0);
-			float q[3] = {(float)x, (float)y, (float)z};
+			float q[3] = {(float)x, (float)y, (float)(z + g.z_off)};
 			q[e] += dt;
 			if (vid < max_verts) {
 #pragma unroll
@@ -218,17 +227,18 @@ extern "C" int neus2b_marching_cubes_scratch_bytes(const uint32_t res[3], uint64
 	return NEUS2B_OK;
 }
 
-extern "C" int neus2b_marching_cubes(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], float thresh, const float* d_sdf,
-                                     const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts,
-                                     uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts, neus2b_stream_t stream) {
+static int marching_cubes_impl(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0, uint32_t n_layers, int slab,
+                               float thresh, const float* d_sdf, const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts,
+                               uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts, cudaStream_t stream) {
 	if (!aabb_min || !aabb_max || !res || !d_sdf || !d_tri_table || !d_scratch || !d_counts) return NEUS2B_E_INVALID;
-	if (res[0] < 2 || res[1] < 2 || res[2] < 2) return NEUS2B_E_INVALID;
+	if (res[0] < 2 || res[1] < 2 || res[2] < 2 || n_layers < 2 || (uint64_t)z0 + n_layers > res[2]) return NEUS2B_E_INVALID;
 	McGrid g;
 	g.rx = res[0];
 	g.ry = res[1];
-	g.rz = res[2];
+	g.rz = n_layers;
+	g.z_off = z0;
 	g.res2 = (uint64_t)res[0] * res[1];
-	g.res3 = g.res2 * res[2];
+	g.res3 = g.res2 * n_layers;
 	if (g.res3 > (1ull << 32)) return NEUS2B_E_TOO_LARGE;
 	g.thresh = thresh;
 	for (int k = 0; k < 3; ++k) {
@@ -250,11 +260,27 @@ extern "C" int neus2b_marching_cubes(const float aabb_min[3], const float aabb_m
 		N2B_CHECK_LAUNCH();
 		scan_add_kernel<<<blocks, 1024, 0, stream>>>(cells, keys, sums);
 		N2B_CHECK_LAUNCH();
-		mc_counts_kernel<<<1, 1, 0, stream>>>(total, d_counts);
+		mc_counts_kernel<<<1, 1, 0, stream>>>(g, keys, total, d_counts, slab);
 		N2B_CHECK_LAUNCH();
 		return NEUS2B_OK;
 	}
 	mc_emit_kernel<<<(uint32_t)((cells + 255u) / 256u), 256, 0, stream>>>(g, d_sdf, d_tri_table, keys, d_verts, max_verts, d_indices, max_indices);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_marching_cubes(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], float thresh, const float* d_sdf,
+                                     const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts,
+                                     uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts, neus2b_stream_t stream) {
+	if (!res) return NEUS2B_E_INVALID;
+	return marching_cubes_impl(aabb_min, aabb_max, res, 0, res[2], 0, thresh, d_sdf, d_tri_table, d_scratch, d_verts, max_verts, d_indices,
+	                           max_indices, d_counts, stream);
+}
+
+extern "C" int neus2b_marching_cubes_slab(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0, uint32_t n_layers,
+                                          float thresh, const float* d_sdf_slab, const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts,
+                                          uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts,
+                                          neus2b_stream_t stream) {
+	return marching_cubes_impl(aabb_min, aabb_max, res, z0, n_layers, 1, thresh, d_sdf_slab, d_tri_table, d_scratch, d_verts, max_verts, d_indices,
+	                           max_indices, d_counts, stream);
 }

@@ -211,3 +211,27 @@ def marching_cubes(sdf, tri_table=None, thresh=0.0, aabb_min=(0.0, 0.0, 0.0), aa
     L.check(L.lib().neus2b_marching_cubes(mn, mx, res, C.c_float(thresh), L.ptr(sdf), L.ptr(tt), L.ptr(scratch), L.ptr(verts), u32(nv),
                                           L.ptr(idx), u32(ni), L.ptr(counts), L.cur_stream()))
     return verts[:nv], idx[:ni]
+
+
+def marching_cubes_slab(sdf_slab, res, z0, tri_table=None, thresh=0.0, aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0)):
+    """One z-slab of a res = (rx, ry, rz) lattice: sdf_slab float32 CUDA tensor [n_layers][ry][rx] = layers z0 .. z0+n_layers-1.
+    Returns a part for neus2_b200.mesh_shard.merge_slab_meshes (host arrays)."""
+    if tri_table is None:
+        from .mc_table import make_table
+        tri_table = torch.from_numpy(make_table())
+    tt = tri_table.to(device=sdf_slab.device, dtype=torch.int8).contiguous()
+    nl = sdf_slab.shape[0]
+    r = (C.c_uint32 * 3)(*[int(v) for v in res])
+    r_slab = (C.c_uint32 * 3)(int(res[0]), int(res[1]), nl)
+    mn, mx = (C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max)
+    nb = C.c_uint64(0)
+    L.check(L.lib().neus2b_marching_cubes_scratch_bytes(r_slab, C.byref(nb)))
+    scratch = torch.empty(nb.value // 8, dtype=torch.int64, device=sdf_slab.device)
+    counts = torch.zeros(4, dtype=torch.int32, device=sdf_slab.device)
+    args = (mn, mx, r, u32(z0), u32(nl), C.c_float(thresh), L.ptr(sdf_slab), L.ptr(tt), L.ptr(scratch))
+    L.check(L.lib().neus2b_marching_cubes_slab(*args, None, u32(0), None, u32(0), L.ptr(counts), L.cur_stream()))
+    nv, ni, nbl, nf = [int(v) for v in counts.cpu()]
+    verts = torch.empty((max(nv, 1), 3), dtype=torch.float32, device=sdf_slab.device)
+    idx = torch.empty(max(ni, 1), dtype=torch.int32, device=sdf_slab.device)
+    L.check(L.lib().neus2b_marching_cubes_slab(*args, L.ptr(verts), u32(nv), L.ptr(idx), u32(ni), L.ptr(counts), L.cur_stream()))
+    return dict(verts=verts[:nv].cpu().numpy(), indices=idx[:ni].cpu().numpy().view("uint32"), nv_before_last=nbl, nv_first=nf)

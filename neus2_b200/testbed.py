@@ -130,3 +130,13 @@ class Testbed:
         EMA parameters, then marching cubes at `thresh`.  Returns (verts, indices) as CUDA tensors."""
         from . import ops
         return ops.marching_cubes(self.sdf_grid(resolution, use_ema=use_ema), tri_table=tri_table, thresh=thresh)
+
+    def compute_marching_cubes_mesh_sharded(self, resolution, rank, world, thresh=0.0, tri_table=None, use_ema=True, gather=None):
+        """The same mesh with the lattice split into z-slabs, one per rank: every rank evaluates the SDF and runs marching cubes
+        on its slab only, the parts are gathered and merged on the host (neus2_b200.mesh_shard).  Returns host arrays."""
+        from . import mesh_shard, ops
+        res = [int(r) for r in (resolution if hasattr(resolution, "__len__") else (resolution,) * 3)]
+
+        def slab(z0, nl):
+            return ops.marching_cubes_slab(self.sdf_grid(res, z0, z0 + nl, use_ema=use_ema), res, z0, tri_table=tri_table, thresh=thresh)
+        return mesh_shard.extract_mesh_sharded(slab, res, rank, world, gather=gather)

@@ -1209,16 +1209,21 @@ void n2o_adam_step(const n2o_adam_cfg* c, uint32_t n, const float* grad, float* 
 }
 
 /* ------------------------------------------------------------------ marching cubes, canonical (cell-linear) order */
-void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint32_t res[3], float thresh, const float* sdf,
-                        const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* n_verts, uint32_t* n_indices) {
-	const uint32_t rx = res[0], ry = res[1], rz = res[2];
+/* The lattice layers z0 .. z0 + nz - 1 of a res[0] x res[1] x res[2] grid (sdf holds only those layers): vertex positions
+ * are those of the whole grid, numbering is local to the slab.  counts = {vertices, indices, vertices owned by the layers
+ * before the slab's last one, vertices owned by its first layer}. */
+void n2o_marching_cubes_slab(const float* aabb_min, const float* aabb_max, const uint32_t res[3], uint32_t z0, uint32_t nz, float thresh,
+                             const float* sdf, const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* counts) {
+	const uint32_t rx = res[0], ry = res[1], rz = nz;
 	const size_t res2 = (size_t)rx * ry, res3 = res2 * rz;
 	int* vgrid = (int*)calloc(res3 * 3, sizeof(int));
 	float scale[3] = {(aabb_max[0] - aabb_min[0]) / (float)rx, (aabb_max[1] - aabb_min[1]) / (float)ry,
-	                  (aabb_max[2] - aabb_min[2]) / (float)rz};
-	uint32_t nv = 0, ni = 0;
+	                  (aabb_max[2] - aabb_min[2]) / (float)res[2]};
+	uint32_t nv = 0, ni = 0, nv_before_last = 0, nv_first = 0;
 	/* gen_vertices, src/marching_cubes.cu:276-329 */
-	for (uint32_t z = 0; z < rz; ++z)
+	for (uint32_t z = 0; z < rz; ++z) {
+		if (z + 1 == rz) nv_before_last = nv;
+		if (z == 1) nv_first = nv;
 		for (uint32_t y = 0; y < ry; ++y)
 			for (uint32_t x = 0; x < rx; ++x) {
 				size_t idx = x + (size_t)y * rx + (size_t)z * res2;
@@ -1232,7 +1237,7 @@ void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint
 					if (inside != (f1 > thresh)) {
 						if (verts) {
 							float dt = (thresh - f0) / (f1 - f0);
-							float q[3] = {(float)x, (float)y, (float)z};
+							float q[3] = {(float)x, (float)y, (float)(z + z0)};
 							q[e] += dt;
 							for (int k = 0; k < 3; ++k) verts[(size_t)nv * 3 + k] = q[k] * scale[k] + aabb_min[k];
 						}
@@ -1241,6 +1246,8 @@ void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint
 					}
 				}
 			}
+	}
+	if (rz == 1) nv_first = nv;
 	/* gen_faces, src/marching_cubes.cu:377-718 */
 	for (uint32_t z = 0; z + 1 < rz; ++z)
 		for (uint32_t y = 0; y + 1 < ry; ++y)
@@ -1269,6 +1276,16 @@ void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint
 				}
 			}
 	free(vgrid);
-	*n_verts = nv;
-	*n_indices = ni;
+	counts[0] = nv;
+	counts[1] = ni;
+	counts[2] = nv_before_last;
+	counts[3] = nv_first;
+}
+
+void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint32_t res[3], float thresh, const float* sdf,
+                        const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* n_verts, uint32_t* n_indices) {
+	uint32_t counts[4];
+	n2o_marching_cubes_slab(aabb_min, aabb_max, res, 0, res[2], thresh, sdf, tri_table, verts, indices, counts);
+	*n_verts = counts[0];
+	*n_indices = counts[1];
 }

@@ -156,6 +156,8 @@ void n2o_adam_step(const n2o_adam_cfg* c, uint32_t n, const float* grad /*loss-s
 
 /* --- marching cubes (src/marching_cubes.cu:276-329, 377-718), canonical cell-linear order. tri_table = the 256x16
  * case table, supplied by the caller. Returns counts via pointers; pass NULL outputs to count only. */
+void n2o_marching_cubes_slab(const float* aabb_min, const float* aabb_max, const uint32_t res[3], uint32_t z0, uint32_t nz, float thresh,
+                             const float* sdf, const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* counts);
 void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint32_t res[3], float thresh, const float* sdf,
                         const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* n_verts, uint32_t* n_indices);
 

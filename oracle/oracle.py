@@ -353,3 +353,18 @@ def marching_cubes(sdf, res, tri_table, thresh=0.0, aabb_min=(0, 0, 0), aabb_max
     idx = np.zeros(ni.value, np.uint32)
     lib().n2o_marching_cubes(mn, mx, r, C.c_float(thresh), _p(sdf), _p(tt), _p(verts), _p(idx), C.byref(nv), C.byref(ni))
     return verts, idx
+
+
+def marching_cubes_slab(sdf_slab, res, z0, nz, tri_table, thresh=0.0, aabb_min=(0, 0, 0), aabb_max=(1, 1, 1)):
+    """Layers z0 .. z0+nz-1 of a res grid.  Returns (verts, indices, nv_before_last_layer, nv_first_layer)."""
+    sdf = _c(sdf_slab, np.float32)
+    r = (C.c_uint32 * 3)(*res)
+    mn = (C.c_float * 3)(*aabb_min)
+    mx = (C.c_float * 3)(*aabb_max)
+    tt = _c(tri_table, np.int8)
+    cnt = (C.c_uint32 * 4)()
+    lib().n2o_marching_cubes_slab(mn, mx, r, C.c_uint32(z0), C.c_uint32(nz), C.c_float(thresh), _p(sdf), _p(tt), None, None, cnt)
+    verts = np.zeros((cnt[0], 3), np.float32)
+    idx = np.zeros(cnt[1], np.uint32)
+    lib().n2o_marching_cubes_slab(mn, mx, r, C.c_uint32(z0), C.c_uint32(nz), C.c_float(thresh), _p(sdf), _p(tt), _p(verts), _p(idx), cnt)
+    return verts, idx, int(cnt[2]), int(cnt[3])
