@@ -132,7 +132,7 @@ def run_ours(args):
     L.lib()
 
     scene = make_scene("cuda")
-    tb = Testbed(batch_size=BATCH, world_size=world, rank=rank)
+    tb = Testbed(batch_size=BATCH, world_size=world, rank=rank, **({"learning_rate": args.lr} if args.lr else {}))
     px = scene["pixels"].cpu().numpy()
     cams = [scene[k].cpu().numpy() for k in ("xforms", "focal", "principal")]
     tb.load_training_data(px, *cams)
@@ -504,6 +504,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--pretrain", type=int, default=500)
+    ap.add_argument("--lr", type=float, default=0.0, help="override the Adam learning rate of BASELINE config 1 (1e-2), e.g. to time late training states")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 18)
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -170,10 +170,12 @@ typedef struct {
 	uint32_t* d_numsteps;    /* [max_rays][2] {n, base} */
 	float* d_coords;         /* [max_samples][7] */
 	uint32_t* d_counters;    /* [8]: 0 kept rays, 1 samples, 2 compacted samples (unclipped), 3 overflow flag */
-	uint64_t* d_scan_tmp;    /* [max_rays + 1024] */
+	uint64_t* d_scan_tmp;    /* [max_rays + 1024]: keys, the total behind them and 1023 entries of scan scratch */
 	float* d_ray_tmp;        /* [max_rays][8] */
 	const uint32_t* d_n_rays_total; /* optional: overrides the n_rays_total argument with a device value */
 	uint32_t* d_march_masks;        /* optional [max_rays][64]: lets the second march pass skip the occupancy lookups */
+	const int32_t* d_occupied_bounds; /* optional int32[6] from neus2b_occupancy_bounds: rays that miss the box of occupied
+	                                     cells are not marched (they cannot take a sample; the result is unchanged) */
 } neus2b_ray_workspace;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is
@@ -214,6 +216,10 @@ int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint16_t* d_para
                             uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp, uint8_t* d_bitfield,
                             float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
                             neus2b_stream_t stream);
+
+/* Smallest box of cell indices {min x, y, z, max x, y, z} around the set bits of the finest level of the occupancy bitfield
+ * (min > max when nothing is occupied); no counterpart in the reference, which marches every ray. */
+int neus2b_occupancy_bounds(const uint8_t* d_bitfield, int32_t* d_bounds, neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- optimizer (Trainer::optimizer_step, src/testbed_nerf.cu:3498) */
 typedef struct {
@@ -288,7 +294,8 @@ int neus2b_testbed_n_params(const neus2b_testbed* tb, uint64_t* n);
  * synchronisation.  If h_stats is non-NULL the stream is synchronised once at the end and the last step's counters
  * and losses are copied back. */
 int neus2b_testbed_train(neus2b_testbed* tb, uint32_t n_steps, neus2b_train_stats* h_stats);
-/* Device views for tests and for the caller's own streams/collectives (valid until destroy). */
+/* Device views for tests and for the caller's own streams/collectives (valid until destroy).  A caller that writes the
+ * occupancy bitfield asks for the pointer again before the next step: the call marks the box of occupied cells stale. */
 int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_params, uint16_t** d_params_ema, float** d_master,
                                float** d_grad_mlp, uint16_t** d_grad_grid, float** d_grad_variance, uint8_t** d_bitfield,
                                float** d_density_grid, neus2b_stream_t* stream);

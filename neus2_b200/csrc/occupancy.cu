@@ -360,3 +360,60 @@ extern "C" int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, f
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }
+
+namespace {
+__global__ void occ_bounds_init_kernel(int32_t* bounds) {
+	if (threadIdx.x < 3) bounds[threadIdx.x] = (int32_t)NEUS2B_GRIDSIZE;
+	else if (threadIdx.x < 6) bounds[threadIdx.x] = -1;
+}
+// one thread per byte of the finest level: cell index = Morton code
+__global__ void __launch_bounds__(256) occ_bounds_kernel(const uint8_t* __restrict__ bitfield, int32_t* __restrict__ bounds) {
+	const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+	int lo[3] = {(int)NEUS2B_GRIDSIZE, (int)NEUS2B_GRIDSIZE, (int)NEUS2B_GRIDSIZE}, hi[3] = {-1, -1, -1};
+	if (b < kCells / 8u) {
+		uint32_t bits = bitfield[b];
+		while (bits) {
+			const uint32_t i = b * 8u + (uint32_t)__ffs((int)bits) - 1u;
+			bits &= bits - 1u;
+			const int c[3] = {(int)morton3d_invert(i >> 0), (int)morton3d_invert(i >> 1), (int)morton3d_invert(i >> 2)};
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				lo[e] = min(lo[e], c[e]);
+				hi[e] = max(hi[e], c[e]);
+			}
+		}
+	}
+	// warp -> CTA -> one atomic per CTA and bound (thousands of same-address atomics would serialise)
+	__shared__ int s_lo[3][8], s_hi[3][8];
+	const int warp = threadIdx.x >> 5;
+#pragma unroll
+	for (int e = 0; e < 3; ++e) {
+		const int l = __reduce_min_sync(0xffffffffu, lo[e]), h = __reduce_max_sync(0xffffffffu, hi[e]);
+		if ((threadIdx.x & 31) == 0) {
+			s_lo[e][warp] = l;
+			s_hi[e][warp] = h;
+		}
+	}
+	__syncthreads();
+	if (threadIdx.x < 3) {
+		const int e = threadIdx.x;
+		int l = s_lo[e][0], h = s_hi[e][0];
+#pragma unroll
+		for (int w = 1; w < 8; ++w) {
+			l = min(l, s_lo[e][w]);
+			h = max(h, s_hi[e][w]);
+		}
+		if (l < (int)NEUS2B_GRIDSIZE) atomicMin(&bounds[e], l);
+		if (h >= 0) atomicMax(&bounds[3 + e], h);
+	}
+}
+}  // namespace
+
+extern "C" int neus2b_occupancy_bounds(const uint8_t* d_bitfield, int32_t* d_bounds, neus2b_stream_t stream) {
+	if (!d_bitfield || !d_bounds) return NEUS2B_E_INVALID;
+	occ_bounds_init_kernel<<<1, 32, 0, stream>>>(d_bounds);
+	N2B_CHECK_LAUNCH();
+	occ_bounds_kernel<<<div_up(kCells / 8u, 256), 256, 0, stream>>>(d_bitfield, d_bounds);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
+}

@@ -224,7 +224,8 @@ template <bool EMIT>
 __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
                                               const uint8_t* __restrict__ bitfield, uint32_t limit, float* __restrict__ coords_out,
                                               int lane, uint32_t* __restrict__ masks = nullptr,
-                                              uint32_t* n_chunks = nullptr) {
+                                              uint32_t* n_chunks = nullptr, float t_lo = -3.402823466e+38f,
+                                              float t_hi = 3.402823466e+38f) {
 	const float idir[3] = {1.0f / dirn[0], 1.0f / dirn[1], 1.0f / dirn[2]};
 	float skip_until = -3.402823466e+38f;
 	uint32_t j = 0;
@@ -232,6 +233,32 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 	// every chunk moves t forward by at least 32 minimum steps, so the ray leaves the box after a bounded number of
 	// chunks; the cap only guards against non-finite inputs
 	uint32_t chunk = 0;
+	// [t_lo, t_hi]: the part of the ray inside the box of occupied cells (one cell of margin), when the caller knows it.
+	// Chunks that end well before t_lo only advance the recurrence: nothing there can become a sample, and the chain of
+	// visits restarted more than a chunk (seven cells) ahead of the box has long fallen in step with the serial loop's when it
+	// gets there -- after a restart the two chains can differ only while they visit different parameters of the same
+	// empty cell, and they meet at the next cell unless a parameter falls between two roundings of one boundary (1e-4).
+	{
+		const float cone_angle = cfg.cone_angle_constant;
+		const float guard = 48.f * calc_dt(fmaxf(t_lo, 0.f), cone_angle);
+		float t = startt;
+		while (chunk < 8192u) {
+			float te = t;
+			if (cone_angle == 0.f) {
+				const float dt = min_cone_stepsize();
+#pragma unroll
+				for (int k = 0; k < 32; ++k) te += dt;
+			} else {
+#pragma unroll
+				for (int k = 0; k < 32; ++k) te += calc_dt(te, cone_angle);
+			}
+			if (!(te + guard < t_lo)) break;
+			if (!EMIT && masks && chunk < kMaskWords && lane == 0) masks[chunk] = 0u;
+			t = te;
+			++chunk;
+		}
+		startt = t;
+	}
 	ChunkHead cur = chunk_head(cfg, o, dirn, startt, bitfield, lane);
 	for (; chunk < 8192u && !stop; ++chunk) {
 		const ChunkHead next = chunk_head(cfg, o, dirn, cur.t_end, bitfield, lane);
@@ -307,6 +334,7 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 			}
 			c[3] = warp_dt(my_dt);
 		}
+		if (cur.t_end > t_hi) stop = true;  // the next chunk starts past the occupied cells: no later parameter can become a sample
 		cur = next;
 	}
 	if (n_chunks) *n_chunks = chunk;
@@ -362,9 +390,25 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
                                                           const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
                                                           const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
                                                           const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
-                                                          uint64_t* __restrict__ scan_in, uint32_t* __restrict__ masks) {
+                                                          uint64_t* __restrict__ scan_in, uint32_t* __restrict__ masks,
+                                                          const int32_t* __restrict__ occ_bounds) {
 	const int lane = threadIdx.x & 31;
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
+	if (blockIdx.x == 0 && threadIdx.x == 0) scan_in[n_rays_max + 512] = 0ull;  // the scan's ticket counter (see scan_kernel)
+	// Box around the occupied cells of the finest occupancy level, one cell of margin: a ray that misses it cannot take a
+	// sample, whatever the march would visit, and is not marched (most rays of a converged scene look past the object).
+	float cull_min[3], cull_max[3];
+	bool cull = false, cull_all = false;
+	if (occ_bounds) {
+		cull = true;
+#pragma unroll
+		for (int e = 0; e < 3; ++e) {
+			const int lo = occ_bounds[e], hi = occ_bounds[3 + e];
+			cull_all = cull_all || lo > hi;  // nothing occupied
+			cull_min[e] = (float)(lo - 1) / (float)NEUS2B_GRIDSIZE;
+			cull_max[e] = (float)(hi + 2) / (float)NEUS2B_GRIDSIZE;
+		}
+	}
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
@@ -403,10 +447,23 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 			float startt = tmin;
 			startt += calc_dt(startt, cfg.cone_angle_constant) * rng.next_float();
 			r.startt = startt;
-			uint32_t n_chunks = 0;
-			r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane,
-			                              masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks);
-			long_ray = n_chunks > kMaskWords;
+			bool may_hit = !cull_all;
+			float t_lo = -3.402823466e+38f, t_hi = 3.402823466e+38f;
+			if (cull && may_hit) {
+				float c0, c1;
+				aabb_ray_intersect(cull_min, cull_max, r.o, dirn, c0, c1);
+				may_hit = !(c0 >= 3.0e38f || c1 < 0.0f);  // (a NaN from a zero direction component keeps the ray)
+				if (may_hit && c0 == c0 && c1 == c1) {
+					t_lo = c0;
+					t_hi = c1;
+				}
+			}
+			if (may_hit) {
+				uint32_t n_chunks = 0;
+				r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane,
+				                              masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks, t_lo, t_hi);
+				long_ray = n_chunks > kMaskWords;
+			}
 		}
 		if (lane == 0) {
 			scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
@@ -416,17 +473,23 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 	}
 }
 
-// Exclusive prefix sum of n 64-bit keys, n read on the device (the live ray count is a few thousand once the batch
-// tuner has converged, 2^18 at most).  One CTA walks tiles of 4096 keys with coalesced 32-byte accesses; the total goes
-// to data[n_max].
+// Exclusive prefix sum of n 64-bit keys in place, n read on the device (2^18 at most); the total goes to data[n_max].
+// Every CTA scans tiles of 4096 keys; the CTA that finishes last (a ticket, no waiting on other CTAs) scans the tile sums
+// and adds the tile offsets.  Scratch lives behind the total: data[n_max + 1 ..] tile sums, data[n_max + 512] the ticket
+// counter, zero before the first launch and left at zero (the buffer has max_rays + 1024 entries).
+constexpr uint32_t kScanTile = 4096u, kScanMaxTiles = 256u;
 __global__ void __launch_bounds__(1024) scan_kernel(uint32_t n_max, const uint32_t* __restrict__ d_n, uint64_t* __restrict__ data) {
 	__shared__ uint64_t warp_sums[32];
 	__shared__ uint64_t tile_total;
+	__shared__ uint64_t offsets[kScanMaxTiles];
+	__shared__ bool is_last;
 	const uint32_t tid = threadIdx.x;
 	const uint32_t n = d_n ? min(*d_n, n_max) : n_max;
-	uint64_t carry = 0;
-	for (uint32_t t0 = 0; t0 < n; t0 += 4096u) {
-		const uint32_t k0 = t0 + tid * 4u;
+	const uint32_t n_tiles = (n + kScanTile - 1u) / kScanTile;
+	uint64_t* tile_sums = data + n_max + 1;
+	unsigned long long* ticket = reinterpret_cast<unsigned long long*>(data + n_max + 512);
+	for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+		const uint32_t k0 = tile * kScanTile + tid * 4u;
 		uint64_t v[4];
 #pragma unroll
 		for (int e = 0; e < 4; ++e) v[e] = (k0 + e < n) ? data[k0 + e] : 0ull;
@@ -451,16 +514,32 @@ __global__ void __launch_bounds__(1024) scan_kernel(uint32_t n_max, const uint32
 			if (tid == 31) tile_total = wi;
 		}
 		__syncthreads();
-		uint64_t run = carry + warp_sums[tid >> 5] + incl - sum;
+		uint64_t run = warp_sums[tid >> 5] + incl - sum;
 #pragma unroll
 		for (int e = 0; e < 4; ++e) {
 			if (k0 + e < n) data[k0 + e] = run;
 			run += v[e];
 		}
-		carry += tile_total;
+		if (tid == 0) tile_sums[tile] = tile_total;
 		__syncthreads();
 	}
-	if (tid == 0) data[n_max] = carry;
+	// ticket: the last CTA to get here sees every tile's sum and local scan
+	__threadfence();
+	if (tid == 0) is_last = atomicAdd(ticket, 1ull) == (unsigned long long)(gridDim.x - 1u);
+	__syncthreads();
+	if (!is_last) return;
+	__threadfence();
+	if (tid == 0) {
+		uint64_t run = 0;
+		for (uint32_t t = 0; t < n_tiles; ++t) {
+			offsets[t] = run;
+			run += tile_sums[t];
+		}
+		data[n_max] = run;
+		*ticket = 0ull;
+	}
+	__syncthreads();
+	for (uint32_t k = kScanTile + tid; k < n; k += 1024u) data[k] += offsets[k / kScanTile];
 }
 
 // Second half of the sample generator (:1410-1445): canonical ranges, then march again and write the coordinates.
@@ -590,8 +669,9 @@ __device__ __forceinline__ void bent_dir_from_lane0(uint32_t wx, uint32_t wy, fl
 __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, const uint32_t* __restrict__ counters,
                                                         const __half* __restrict__ mlp_out, const uint32_t* __restrict__ numsteps,
                                                         const float* __restrict__ coords, CompTmp* __restrict__ tmp,
-                                                        uint64_t* __restrict__ scan_in) {
+                                                        uint64_t* __restrict__ scan_in, uint32_t n_rays_max) {
 	const int lane = threadIdx.x & 31;
+	if (blockIdx.x == 0 && threadIdx.x == 0) scan_in[n_rays_max + 512] = 0ull;  // the scan's ticket counter (see scan_kernel)
 	const uint32_t n_kept = counters[0];
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_kept; i += warps) {
@@ -902,9 +982,9 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
 	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
-	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_march_masks);
+	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_march_masks, ws->d_occupied_bounds);
 	N2B_CHECK_LAUNCH();
-	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
+	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
 	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
@@ -923,9 +1003,9 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 	Pcg32 r{rng.state, rng.inc};
 	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);  // 4 warps per CTA, one warp per ray, grid-stride
 	composite_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, ws->d_counters, (const __half*)d_mlp_out, ws->d_numsteps, ws->d_coords,
-	                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp);
+	                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, n_rays);
 	N2B_CHECK_LAUNCH();
-	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, ws->d_counters, ws->d_scan_tmp);
+	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, ws->d_counters, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	loss_kernel<<<ray_ctas, 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted,
 	                                          ws->d_counters, (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
@@ -999,9 +1079,9 @@ extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const ne
 	N2B_CHECK_CUDA(cudaMemsetAsync(d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
 	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
-	                                                            (RayTmp*)ray_tmp, scan, nullptr);
+	                                                            (RayTmp*)ray_tmp, scan, nullptr, nullptr);
 	N2B_CHECK_LAUNCH();
-	scan_kernel<<<1, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
+	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
 	N2B_CHECK_LAUNCH();
 	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
 	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters, nullptr);

@@ -104,6 +104,8 @@ struct neus2b_testbed {
 	// occupancy
 	float *density_grid = nullptr, *density_tmp = nullptr, *density_mean = nullptr, *occ_pos = nullptr;
 	uint8_t* bitfield = nullptr;
+	int32_t* occ_bounds = nullptr;  // box of occupied cells (finest level)
+	bool occ_bounds_stale = true;   // set by an occupancy update and by handing the bitfield's pointer out
 	uint32_t* occ_idx = nullptr;
 	__half* occ_sdf = nullptr;
 	double* occ_partial = nullptr;
@@ -228,6 +230,7 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	TB_ALLOC(tb->density_tmp, n_occ);
 	TB_ALLOC(tb->density_mean, (size_t)1);
 	TB_ALLOC(tb->bitfield, cells / 8 * NEUS2B_CASCADES);
+	TB_ALLOC(tb->occ_bounds, (size_t)8);
 	TB_ALLOC(tb->occ_pos, n_occ * 3);
 	TB_ALLOC(tb->occ_idx, n_occ);
 	TB_ALLOC(tb->occ_sdf, n_occ);
@@ -339,7 +342,10 @@ extern "C" int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_param
 	if (d_grad_mlp) *d_grad_mlp = tb->grad_mlp;
 	if (d_grad_grid) *d_grad_grid = (uint16_t*)tb->grad_grid;
 	if (d_grad_variance) *d_grad_variance = tb->grad_var;
-	if (d_bitfield) *d_bitfield = tb->bitfield;
+	if (d_bitfield) {
+		*d_bitfield = tb->bitfield;
+		tb->occ_bounds_stale = true;  // the caller may write it
+	}
 	if (d_density_grid) *d_density_grid = tb->density_grid;
 	if (stream) *stream = tb->stream;
 	return NEUS2B_OK;
@@ -375,6 +381,7 @@ static int training_prep(neus2b_testbed* tb) {
 	                                 tb->cfg.density_grid_decay, tb->density_grid, tb->density_tmp, tb->bitfield, tb->density_mean,
 	                                 tb->occ_pos, tb->occ_idx, (uint16_t*)tb->occ_sdf, tb->occ_partial, tb->stream);
 	++tb->ema_step;
+	tb->occ_bounds_stale = true;
 	return rc;
 }
 
@@ -410,6 +417,17 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	const neus2b_train_cfg tc = make_train_cfg(tb);
 	const neus2b_pcg32 rng{tb->rng.state, tb->rng.inc};
 	const uint32_t* d_n_rays = &tb->state->rays_per_batch;
+	// one cascade: positions map straight to the finest level's cells, so rays that miss the box of occupied cells are
+	// not marched; the box is recomputed after every occupancy update (and after the bitfield's pointer was handed out)
+	tb->ws.d_occupied_bounds = nullptr;
+	if (tb->cfg.n_cascades == 1) {
+		if (tb->occ_bounds_stale) {
+			rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, tb->stream);
+			if (rc) return rc;
+			tb->occ_bounds_stale = false;
+		}
+		tb->ws.d_occupied_bounds = tb->occ_bounds;
+	}
 	rc = neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->bitfield, &tb->ws, tb->stream);
 	if (rc) return rc;
 	rc = neus2b_neus_forward(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, tb->max_samples, tb->ws.d_counters + 4, tb->ws.d_coords,

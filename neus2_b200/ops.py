@@ -110,7 +110,7 @@ def neus_sdf(d, params, x, sdf_bias=-0.1):
 class RayBatch:
     """Device scratch of one ray batch (neus2b_ray_workspace) plus the dataset handle."""
 
-    def __init__(self, max_rays, max_samples, device="cuda", march_masks=True):
+    def __init__(self, max_rays, max_samples, device="cuda", march_masks=True, occupied_bounds=None):
         self.max_rays, self.max_samples = max_rays, max_samples
         i32, f32 = torch.int32, torch.float32
         self.ray_indices = torch.zeros(max_rays, dtype=i32, device=device)
@@ -123,7 +123,8 @@ class RayBatch:
         self.march_masks = torch.zeros((max_rays, 64), dtype=i32, device=device) if march_masks else None
         self.ws = L.RayWorkspace(max_rays, max_samples, L.ptr(self.ray_indices), L.ptr(self.rays), L.ptr(self.numsteps),
                                  L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp), None,
-                                 L.ptr(self.march_masks))
+                                 L.ptr(self.march_masks), L.ptr(occupied_bounds))
+        self.occupied_bounds = occupied_bounds
 
 
 def make_dataset(pixels, xforms, focal, principal):
@@ -235,3 +236,10 @@ def marching_cubes_slab(sdf_slab, res, z0, tri_table=None, thresh=0.0, aabb_min=
     idx = torch.empty(max(ni, 1), dtype=torch.int32, device=sdf_slab.device)
     L.check(L.lib().neus2b_marching_cubes_slab(*args, L.ptr(verts), u32(nv), L.ptr(idx), u32(ni), L.ptr(counts), L.cur_stream()))
     return dict(verts=verts[:nv].cpu().numpy(), indices=idx[:ni].cpu().numpy().view("uint32"), nv_before_last=nbl, nv_first=nf)
+
+
+def occupancy_bounds(bitfield):
+    """int32[6] CUDA tensor {min x, y, z, max x, y, z} of the occupied cells of the finest level."""
+    out = torch.zeros(8, dtype=torch.int32, device=bitfield.device)
+    L.check(L.lib().neus2b_occupancy_bounds(L.ptr(bitfield), L.ptr(out), L.cur_stream()))
+    return out

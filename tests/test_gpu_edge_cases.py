@@ -42,9 +42,13 @@ def test_generate_samples_empty_and_full_grid(gpu, oracle, fill):
     bf = np.full(128 ** 3 // 8, fill, np.uint8)
     n_rays, max_samples = 2048, 1 << 21
     ref = O.generate_samples(ods, O.train_cfg(), n_rays, 777, max_samples, O.pcg32(5), bf)
+    bf_gpu = torch.from_numpy(bf).cuda()
+    bounds = ops.occupancy_bounds(bf_gpu)
+    b = bounds.cpu().numpy()[:6]
+    assert (list(b) == [128, 128, 128, -1, -1, -1]) if fill == 0 else (list(b) == [0, 0, 0, 127, 127, 127])
     for masks in (True, False):
-        batch = ops.RayBatch(n_rays, max_samples, march_masks=masks)
-        ops.generate_samples(gds, L.train_cfg(), n_rays, 777, L.pcg32(5), torch.from_numpy(bf).cuda(), batch)
+        batch = ops.RayBatch(n_rays, max_samples, march_masks=masks, occupied_bounds=bounds if masks else None)
+        ops.generate_samples(gds, L.train_cfg(), n_rays, 777, L.pcg32(5), bf_gpu, batch)
         torch.cuda.synchronize()
         cnt = compare_batches(ref, batch)
         if fill == 0:
@@ -130,3 +134,12 @@ def test_adam_without_gradients_leaves_weights(gpu, oracle):
     for got, want in zip(t, ro):
         assert np.allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-7)  # fp32 chains, contraction differs (as in test_adam_step)
     assert (np.abs(P.float().cpu().numpy() - O.bits_f32(p_o)) <= 1e-3 * np.abs(O.bits_f32(p_o)) + 1e-7).all()
+
+
+def test_occupancy_bounds_of_a_ball(gpu, oracle):
+    """The box of occupied cells of a centred ball of radius 0.35 in a 128^3 grid."""
+    _, ops = gpu
+    _, bf, _ = ball_bitfield(oracle, radius=0.35)
+    b = ops.occupancy_bounds(torch.from_numpy(bf).cuda()).cpu().numpy()[:6]
+    # cell centres (c + 0.5) / 128 - 0.5 inside the radius: c in [19, 108]
+    assert list(b) == [19, 19, 19, 108, 108, 108]

@@ -76,8 +76,11 @@ def test_generate_samples_bit_exact(gpu, oracle, n_rays, max_samples, snap, mask
     _, bf, _ = ball_bitfield(O)
     ocfg, gcfg = O.train_cfg(snap_to_pixel_centers=snap), L.train_cfg(snap_to_pixel_centers=snap)
     ref = O.generate_samples(ods, ocfg, n_rays, 12345, max_samples, O.pcg32(1337), bf)
-    batch = ops.RayBatch(n_rays, max_samples, march_masks=masks)
-    ops.generate_samples(gds, gcfg, n_rays, 12345, L.pcg32(1337), torch.from_numpy(bf).cuda(), batch)
+    bf_gpu = torch.from_numpy(bf).cuda()
+    # with the march masks on, also cull the rays that miss the box of occupied cells: the result must not change
+    bounds = ops.occupancy_bounds(bf_gpu) if masks else None
+    batch = ops.RayBatch(n_rays, max_samples, march_masks=masks, occupied_bounds=bounds)
+    ops.generate_samples(gds, gcfg, n_rays, 12345, L.pcg32(1337), bf_gpu, batch)
     torch.cuda.synchronize()
     cnt = batch.counters.cpu().numpy().view(np.uint32)
     k = ref["n_kept"]
