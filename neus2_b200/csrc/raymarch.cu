@@ -385,37 +385,56 @@ __device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, con
 	}
 }
 
-// First half of generate_training_samples_nerf_with_global_movement (:1287-1409): build the ray and count its steps.
-__global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
-                                                          const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
-                                                          const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
-                                                          const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
-                                                          uint64_t* __restrict__ scan_in, uint32_t* __restrict__ masks,
-                                                          const int32_t* __restrict__ occ_bounds) {
-	const int lane = threadIdx.x & 31;
+// Box around the occupied cells of the finest occupancy level, one cell of margin: a ray that misses it cannot take a
+// sample, whatever the march would visit, and is not marched (most rays of a converged scene look past the object).
+struct CullBox {
+	float mn[3], mx[3];
+	bool on, nothing;
+};
+__device__ __forceinline__ CullBox cull_box(const int32_t* __restrict__ occ_bounds) {
+	CullBox c;
+	c.on = occ_bounds != nullptr;
+	c.nothing = false;
+#pragma unroll
+	for (int e = 0; e < 3; ++e) {
+		const int lo = c.on ? occ_bounds[e] : 0, hi = c.on ? occ_bounds[3 + e] : (int)NEUS2B_GRIDSIZE - 1;
+		c.nothing = c.nothing || lo > hi;  // nothing occupied
+		c.mn[e] = (float)(lo - 1) / (float)NEUS2B_GRIDSIZE;
+		c.mx[e] = (float)(hi + 2) / (float)NEUS2B_GRIDSIZE;
+	}
+	return c;
+}
+// may the ray take a sample, and between which ray parameters
+__device__ __forceinline__ bool cull_ray(const CullBox& c, const float* o, const float* dirn, float& t_lo, float& t_hi) {
+	t_lo = -3.402823466e+38f;
+	t_hi = 3.402823466e+38f;
+	if (!c.on) return true;
+	if (c.nothing) return false;
+	float c0, c1;
+	aabb_ray_intersect(c.mn, c.mx, o, dirn, c0, c1);
+	if (c0 >= 3.0e38f || c1 < 0.0f) return false;
+	if (c0 == c0 && c1 == c1) {  // (a NaN from a zero direction component keeps the whole ray)
+		t_lo = c0;
+		t_hi = c1;
+	}
+	return true;
+}
+
+// First half of generate_training_samples_nerf_with_global_movement (:1287-1409), part one: one thread builds one ray
+// (pixel, camera, start parameter) and lists it for the march if it can take samples.
+__global__ void __launch_bounds__(256) ray_setup_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
+                                                        const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
+                                                        const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0, RayTmp* __restrict__ tmp,
+                                                        uint64_t* __restrict__ scan_in, const int32_t* __restrict__ occ_bounds,
+                                                        uint32_t* __restrict__ hit_list, uint32_t* __restrict__ hit_count) {
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
 	if (blockIdx.x == 0 && threadIdx.x == 0) scan_in[n_rays_max + 512] = 0ull;  // the scan's ticket counter (see scan_kernel)
-	// Box around the occupied cells of the finest occupancy level, one cell of margin: a ray that misses it cannot take a
-	// sample, whatever the march would visit, and is not marched (most rays of a converged scene look past the object).
-	float cull_min[3], cull_max[3];
-	bool cull = false, cull_all = false;
-	if (occ_bounds) {
-		cull = true;
-#pragma unroll
-		for (int e = 0; e < 3; ++e) {
-			const int lo = occ_bounds[e], hi = occ_bounds[3 + e];
-			cull_all = cull_all || lo > hi;  // nothing occupied
-			cull_min[e] = (float)(lo - 1) / (float)NEUS2B_GRIDSIZE;
-			cull_max[e] = (float)(hi + 2) / (float)NEUS2B_GRIDSIZE;
-		}
-	}
+	const CullBox box = cull_box(occ_bounds);
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
-	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
+	for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_rays; i += gridDim.x * blockDim.x) {
 		RayTmp r;
 		r.numsteps = 0;
 		r.startt = 0.f;
-		bool long_ray = false;
 #pragma unroll
 		for (int e = 0; e < 3; ++e) r.o[e] = r.d[e] = 0.f;
 		const uint32_t ig = i + cfg.ray_index_offset;
@@ -426,7 +445,8 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 		random_image_pos(rng, ds, cfg.snap_to_pixel_centers != 0, xy);
 		read_rgba(ds, img, xy, rgba);
 		const bool keep = !(rgba[0] <= 0.0f && rng.next_float() >= 0.9f);
-		if (keep) {  // uniform across the warp: every lane computes the same ray
+		bool may_hit = false;
+		if (keep) {
 			(void)rng.next_float();  // motion-blur time (:1307)
 			const float* X = ds.d_xforms + (size_t)img * 12;
 			const float fx = ds.d_focal[img * 2], fy = ds.d_focal[img * 2 + 1];
@@ -447,28 +467,40 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_dataset ds, neu
 			float startt = tmin;
 			startt += calc_dt(startt, cfg.cone_angle_constant) * rng.next_float();
 			r.startt = startt;
-			bool may_hit = !cull_all;
-			float t_lo = -3.402823466e+38f, t_hi = 3.402823466e+38f;
-			if (cull && may_hit) {
-				float c0, c1;
-				aabb_ray_intersect(cull_min, cull_max, r.o, dirn, c0, c1);
-				may_hit = !(c0 >= 3.0e38f || c1 < 0.0f);  // (a NaN from a zero direction component keeps the ray)
-				if (may_hit && c0 == c0 && c1 == c1) {
-					t_lo = c0;
-					t_hi = c1;
-				}
-			}
-			if (may_hit) {
-				uint32_t n_chunks = 0;
-				r.numsteps = march_ray<false>(cfg, r.o, dirn, startt, bitfield, NEUS2B_STEPS, nullptr, lane,
-				                              masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks, t_lo, t_hi);
-				long_ray = n_chunks > kMaskWords;
-			}
+			float t_lo, t_hi;
+			may_hit = cull_ray(box, r.o, dirn, t_lo, t_hi);
 		}
+		tmp[i] = r;
+		scan_in[i] = 0ull;
+		if (may_hit) hit_list[atomicAdd(hit_count, 1u)] = i;  // any order: the march writes its result under the ray's own index
+	}
+}
+
+// Part two: one warp marches one listed ray and counts its steps.
+__global__ void __launch_bounds__(128) count_steps_kernel(neus2b_train_cfg cfg, const uint8_t* __restrict__ bitfield, RayTmp* __restrict__ tmp,
+                                                          uint64_t* __restrict__ scan_in, uint32_t* __restrict__ masks,
+                                                          const int32_t* __restrict__ occ_bounds, const uint32_t* __restrict__ hit_list,
+                                                          const uint32_t* __restrict__ hit_count) {
+	const int lane = threadIdx.x & 31;
+	const CullBox box = cull_box(occ_bounds);
+	const uint32_t n_hit = *hit_count;
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); h < n_hit; h += warps) {
+		const uint32_t i = hit_list[h];
+		RayTmp r = tmp[i];
+		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+		float dirn[3];
+#pragma unroll
+		for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+		float t_lo, t_hi;
+		(void)cull_ray(box, r.o, dirn, t_lo, t_hi);
+		uint32_t n_chunks = 0;
+		r.numsteps = march_ray<false>(cfg, r.o, dirn, r.startt, bitfield, NEUS2B_STEPS, nullptr, lane,
+		                              masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks, t_lo, t_hi);
 		if (lane == 0) {
 			scan_in[i] = r.numsteps ? ((1ull << 32) | (uint64_t)r.numsteps) : 0ull;
-			if (long_ray) r.numsteps |= 0x80000000u;  // the mask record does not cover this ray: the emit pass marches again
-			tmp[i] = r;
+			if (n_chunks > kMaskWords) r.numsteps |= 0x80000000u;  // the mask record does not cover this ray: the emit pass marches again
+			tmp[i].numsteps = r.numsteps;
 		}
 	}
 }
@@ -981,8 +1013,14 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	if (n_rays == 0 || n_rays > ws->max_rays || ds->n_images == 0) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
-	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, d_bitfield,
-	                                                            (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_march_masks, ws->d_occupied_bounds);
+	// (the hit list borrows d_ray_indices, which the emit pass fills afterwards; its length is counter 6)
+	ray_setup_kernel<<<min(div_up(n_rays, 256), (uint32_t)kSMs * 8u), 256, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r,
+	                                                                          (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_occupied_bounds,
+	                                                                          ws->d_ray_indices, ws->d_counters + 6);
+	N2B_CHECK_LAUNCH();
+	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, d_bitfield, (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp,
+	                                                                           ws->d_march_masks, ws->d_occupied_bounds, ws->d_ray_indices,
+	                                                                           ws->d_counters + 6);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
@@ -1078,8 +1116,11 @@ extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const ne
 	if (rc) return rc;
 	N2B_CHECK_CUDA(cudaMemsetAsync(d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
-	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, d_bitfield,
-	                                                            (RayTmp*)ray_tmp, scan, nullptr, nullptr);
+	ray_setup_kernel<<<min(div_up(n_rays, 256), (uint32_t)kSMs * 8u), 256, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, nullptr, r, (RayTmp*)ray_tmp, scan,
+	                                                                          nullptr, d_ray_indices, d_counters + 6);
+	N2B_CHECK_LAUNCH();
+	count_steps_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, d_bitfield, (RayTmp*)ray_tmp, scan, nullptr, nullptr, d_ray_indices,
+	                                                                           d_counters + 6);
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
 	N2B_CHECK_LAUNCH();
