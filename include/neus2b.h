@@ -335,6 +335,83 @@ int neus2b_marching_cubes_slab(const float aabb_min[3], const float aabb_max[3],
                                uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts,
                                neus2b_stream_t stream);
 
+/* ---------------------------------------------------------------- inference rendering (NerfTracer, Testbed::render_nerf) */
+
+typedef struct {
+	uint32_t width, height;
+	float focal_length[2];  /* in pixels: Testbed::calc_focal_length (src/testbed.cu:2728) */
+	float screen_center[2]; /* Testbed::render_screen_center (src/testbed.cu:2732); 0.5, 0.5 = centred */
+	float camera[12];       /* 3x4 camera-to-world, column major (camera_matrix1 of render_nerf) */
+	float pixel_offset[2];  /* position inside the pixel: ld_random_pixel_offset(sample_index), random_val.cuh:317-322;
+	                           {0.5, 0.5} when snapping to pixel centres */
+	uint32_t sample_index;  /* index of the sample per pixel (render_buffer.spp()): seeds the jitter of the first ray parameter */
+	float aabb_min[3], aabb_max[3]; /* m_render_aabb, taken equal to the training box m_aabb */
+	float cone_angle_constant;
+	float min_transmittance; /* Testbed::Nerf::rendering_min_transmittance (testbed.h:686), 0.01 */
+	float cos_anneal_ratio;
+	uint32_t linear_colors; /* Nerf::Training::linear_colors (testbed.h:612); 0: the network's colours are sRGB, the frame
+	                           buffer receives srgb_to_linear of them (shade_kernel_nerf) */
+	uint32_t max_steps;     /* samples per ray at most; 0 = 10000 (MARCH_ITER, src/testbed_nerf.cu:68, bounds the reference's
+	                           rounds) */
+} neus2b_render_cfg;
+
+/* Scratch of the renderer; every array is caller-allocated device memory.  max_rays pixels (whole rows, at most 2^20) are
+ * handled at once, max_samples (a multiple of 128) samples go through the network at once. */
+typedef struct {
+	uint32_t max_rays, max_samples;
+	float* d_ray_tmp;      /* [max_rays][8] */
+	uint64_t* d_scan_tmp;  /* [max_rays + 1024], zero before the first use */
+	float* d_state;        /* [max_rays][8] */
+	uint32_t* d_hit_list;  /* [max_rays] */
+	float* d_coords;       /* [max_samples][7] */
+	uint16_t* d_out;       /* [max_samples][16] */
+	uint32_t* d_counters;  /* [8] */
+	const int32_t* d_occupied_bounds; /* optional int32[6] from neus2b_occupancy_bounds (one-cascade scenes): rays that miss
+	                                     the box of occupied cells are not marched */
+} neus2b_render_workspace;
+
+/* Testbed::render_nerf, ERenderMode::Shade (src/testbed_nerf.cu:2671-2812): NerfTracer::init_rays_from_camera (:2398-2478,
+ * pinhole camera; no depth of field, lens distortion, environment map, rolling shutter or slice plane), NerfTracer::trace
+ * (:2480-2601) and shade_kernel_nerf (:2147-2180).  Blends one sample per pixel into d_frame float[height][width][4]
+ * (linear, alpha premultiplied; the caller clears it like CudaRenderBuffer::clear_frame) and writes d_depth
+ * float[height][width].  d_params are the weights to render with (the reference renders with its inference = EMA
+ * weights).  Instead of the reference's rounds of at most 8 steps with a blocking read of the live-ray count after
+ * each, every ray's whole march is counted first and the samples go through the network in windows of max_samples; the
+ * host reads one number per band of max_rays pixels.  h_n_samples (optional) receives the number of samples evaluated. */
+int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, const neus2b_render_cfg* cfg,
+                        const uint8_t* d_bitfield, neus2b_render_workspace* ws, float* d_frame, float* d_depth, uint64_t* h_n_samples,
+                        neus2b_stream_t stream);
+/* CudaRenderBuffer::accumulate, EColorSpace::Linear (src/render_buffer.cu:217-259, 540-560): running mean of the frames,
+ * sample_count = frames accumulated so far (0 overwrites).  Buffers are float[n_pixels][4]. */
+int neus2b_render_accumulate(uint32_t n_pixels, const float* d_frame, float* d_accumulate, uint32_t sample_count,
+                             neus2b_stream_t stream);
+/* CudaRenderBuffer::tonemap with the identity curve (src/render_buffer.cu:474-500, 562-577): background (sRGB, with alpha)
+ * behind the premultiplied colour, exposure in stops, conversion to sRGB when to_srgb. */
+int neus2b_render_tonemap(uint32_t n_pixels, const float* d_accumulate, float exposure, const float background[4], int to_srgb,
+                          float* d_out, neus2b_stream_t stream);
+/* ld_random_pixel_offset (include/neural-graphics-primitives/random_val.cuh:317-322): where inside its pixel the spp-th
+ * sample of every pixel lies (Owen-scrambled Sobol point, Burley 2020); host computation. */
+void neus2b_ld_random_pixel_offset(uint32_t spp, float out_xy[2]);
+
+typedef struct {
+	uint32_t width, height, spp;
+	float camera[12];               /* Testbed::m_camera: 3x4 camera-to-world, column major */
+	float relative_focal_length[2]; /* Testbed::m_relative_focal_length (set_fov: 0.5 / tan(fov / 2)) */
+	uint32_t fov_axis;              /* Testbed::m_fov_axis, 1 */
+	float zoom;                     /* Testbed::m_zoom, 1 */
+	float screen_center[2];         /* Testbed::m_screen_center, 0.5 0.5 */
+	uint32_t snap_to_pixel_centers; /* Testbed::m_snap_to_pixel_centers */
+	float exposure;                 /* Testbed::m_exposure, stops */
+	float background_color[4];      /* Testbed::m_background_color, sRGB + alpha; 0 0 0 1 */
+	uint32_t linear;                /* the `linear` argument of Testbed::render: 1 = linear output, 0 = sRGB */
+	float min_transmittance;        /* Testbed::Nerf::rendering_min_transmittance, 0.01 */
+	uint32_t use_ema;               /* 1: the EMA (inference) weights, like the reference; 0: the training weights */
+} neus2b_render_request;
+/* Testbed::render_to_cpu for a fixed camera (src/python_api.cu:123-169 -> Testbed::render_frame src/testbed.cu:2810-2826):
+ * spp frames, each cleared, rendered, accumulated; then tone mapping; h_rgba float[height][width][4] on the host,
+ * h_depth float[height][width] (optional, of the last frame). */
+int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_request* req, float* h_rgba, float* h_depth);
+
 #ifdef __cplusplus
 }
 #endif

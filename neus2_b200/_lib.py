@@ -39,6 +39,28 @@ class RayWorkspace(C.Structure):
                 ("d_ray_tmp", C.c_void_p), ("d_n_rays_total", C.c_void_p), ("d_march_masks", C.c_void_p), ("d_occupied_bounds", C.c_void_p)]
 
 
+class RenderCfg(C.Structure):
+    _fields_ = [("width", C.c_uint32), ("height", C.c_uint32), ("focal_length", C.c_float * 2), ("screen_center", C.c_float * 2),
+                ("camera", C.c_float * 12), ("pixel_offset", C.c_float * 2), ("sample_index", C.c_uint32),
+                ("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
+                ("min_transmittance", C.c_float), ("cos_anneal_ratio", C.c_float), ("linear_colors", C.c_uint32),
+                ("max_steps", C.c_uint32)]
+
+
+class RenderWorkspace(C.Structure):
+    _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_tmp", C.c_void_p), ("d_scan_tmp", C.c_void_p),
+                ("d_state", C.c_void_p), ("d_hit_list", C.c_void_p), ("d_coords", C.c_void_p), ("d_out", C.c_void_p),
+                ("d_counters", C.c_void_p), ("d_occupied_bounds", C.c_void_p)]
+
+
+class RenderRequest(C.Structure):
+    _fields_ = [("width", C.c_uint32), ("height", C.c_uint32), ("spp", C.c_uint32), ("camera", C.c_float * 12),
+                ("relative_focal_length", C.c_float * 2), ("fov_axis", C.c_uint32), ("zoom", C.c_float),
+                ("screen_center", C.c_float * 2), ("snap_to_pixel_centers", C.c_uint32), ("exposure", C.c_float),
+                ("background_color", C.c_float * 4), ("linear", C.c_uint32), ("min_transmittance", C.c_float),
+                ("use_ema", C.c_uint32)]
+
+
 class AdamCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
                 ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("loss_scale", C.c_float), ("step", C.c_uint32),
@@ -79,6 +101,7 @@ EXPORTS = [
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
+    "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render",
 ]
 
 
@@ -94,6 +117,7 @@ def lib():
         _lib.neus2b_pcg32_advance.restype = None
         _lib.neus2b_testbed_default_config.restype = None
         _lib.neus2b_testbed_destroy.restype = None
+        _lib.neus2b_ld_random_pixel_offset.restype = None
         _lib.neus2b_testbed_destroy.argtypes = [C.c_void_p]
     return _lib
 
@@ -124,6 +148,8 @@ def ptr(t):
     """Device pointer of a torch tensor (or None)."""
     if t is None:
         return C.c_void_p(0)
+    if isinstance(t, int):  # a raw device address, e.g. from Testbed.device_ptrs()
+        return C.c_void_p(t)
     assert t.is_cuda and t.is_contiguous(), "neus2b takes contiguous CUDA tensors"
     return C.c_void_p(t.data_ptr())
 

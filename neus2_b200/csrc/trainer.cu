@@ -123,6 +123,11 @@ struct neus2b_testbed {
 	std::vector<cudaEvent_t> prof_events;
 	uint32_t prof_used = 0;
 	bool prof_on = false;
+	// renderer: buffers for the last requested resolution
+	std::vector<void*> render_allocs;
+	uint32_t render_pixels = 0;
+	neus2b_render_workspace render_ws{};
+	float *render_frame = nullptr, *render_depth = nullptr, *render_acc = nullptr, *render_out = nullptr;
 };
 
 template <typename T>
@@ -176,6 +181,7 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	if (!tb) return;
 	if (tb->stream) cudaStreamSynchronize(tb->stream);
 	for (void* p : tb->allocs) cudaFree(p);
+	for (void* p : tb->render_allocs) cudaFree(p);
 	if (tb->h_state) cudaFreeHost(tb->h_state);
 	if (tb->h_cam) cudaFreeHost(tb->h_cam);
 	for (cudaEvent_t e : tb->prof_events) cudaEventDestroy(e);
@@ -541,6 +547,110 @@ extern "C" int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3]
 		half_to_float_kernel<<<div_up(n, 256), 256, 0, tb->stream>>>(n, tb->occ_sdf, d_out + off);
 		N2B_CHECK_LAUNCH();
 	}
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ rendering
+
+template <typename T>
+static int render_alloc(neus2b_testbed* tb, T** p, size_t n) {
+	void* q = nullptr;
+	cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+	if (e != cudaSuccess) return (int)e;
+	e = cudaMemsetAsync(q, 0, n * sizeof(T), tb->stream);
+	if (e != cudaSuccess) {
+		cudaFree(q);
+		return (int)e;
+	}
+	tb->render_allocs.push_back(q);
+	*p = (T*)q;
+	return NEUS2B_OK;
+}
+
+static int render_reserve(neus2b_testbed* tb, uint32_t width, uint32_t height) {
+	const uint32_t n_pix = width * height;
+	if (tb->render_pixels == n_pix && tb->render_ws.max_rays >= width) return NEUS2B_OK;
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	for (void* p : tb->render_allocs) cudaFree(p);
+	tb->render_allocs.clear();
+	tb->render_pixels = 0;
+	neus2b_render_workspace& ws = tb->render_ws;
+	ws = neus2b_render_workspace{};
+	const uint32_t band = (1u << 20) / width * width;  // whole rows
+	ws.max_rays = n_pix < band ? n_pix : band;
+	ws.max_samples = 1u << 22;
+	int rc = NEUS2B_OK;
+	if (!rc) rc = render_alloc(tb, &ws.d_ray_tmp, (size_t)ws.max_rays * 8);
+	if (!rc) rc = render_alloc(tb, &ws.d_scan_tmp, (size_t)ws.max_rays + 1024);
+	if (!rc) rc = render_alloc(tb, &ws.d_state, (size_t)ws.max_rays * 8);
+	if (!rc) rc = render_alloc(tb, &ws.d_hit_list, (size_t)ws.max_rays);
+	if (!rc) rc = render_alloc(tb, &ws.d_coords, (size_t)ws.max_samples * 7);
+	if (!rc) rc = render_alloc(tb, &ws.d_out, (size_t)ws.max_samples * 16);
+	if (!rc) rc = render_alloc(tb, &ws.d_counters, (size_t)8);
+	if (!rc) rc = render_alloc(tb, &tb->render_frame, (size_t)n_pix * 4);
+	if (!rc) rc = render_alloc(tb, &tb->render_depth, (size_t)n_pix);
+	if (!rc) rc = render_alloc(tb, &tb->render_acc, (size_t)n_pix * 4);
+	if (!rc) rc = render_alloc(tb, &tb->render_out, (size_t)n_pix * 4);
+	if (rc) {
+		for (void* p : tb->render_allocs) cudaFree(p);
+		tb->render_allocs.clear();
+		return rc;
+	}
+	tb->render_pixels = n_pix;
+	return NEUS2B_OK;
+}
+
+// Testbed::render_to_cpu (src/python_api.cu:123-169) for a fixed camera: spp frames of render_frame
+// (src/testbed.cu:2810-2826: clear, render_nerf, accumulate, tonemap), then the surface goes to the host.
+extern "C" int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_request* req, float* h_rgba, float* h_depth) {
+	if (!tb || !req || !h_rgba || req->width == 0 || req->height == 0 || req->spp == 0 || req->fov_axis > 1) return NEUS2B_E_INVALID;
+	if ((uint64_t)req->width * req->height > (1ull << 28) || req->width > (1u << 20)) return NEUS2B_E_TOO_LARGE;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	int rc = render_reserve(tb, req->width, req->height);
+	if (rc) return rc;
+	const uint32_t n_pix = req->width * req->height;
+	if (tb->cfg.n_cascades == 1 && tb->occ_bounds_stale) {
+		rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, tb->stream);
+		if (rc) return rc;
+		tb->occ_bounds_stale = false;
+	}
+	tb->render_ws.d_occupied_bounds = tb->cfg.n_cascades == 1 ? tb->occ_bounds : nullptr;
+	neus2b_render_cfg c{};
+	c.width = req->width;
+	c.height = req->height;
+	const uint32_t res[2] = {req->width, req->height};
+	for (int e = 0; e < 2; ++e) {
+		c.focal_length[e] = req->relative_focal_length[e] * (float)res[req->fov_axis] * req->zoom;  // calc_focal_length
+		c.screen_center[e] = (0.5f - req->screen_center[e]) * req->zoom + 0.5f;                    // render_screen_center
+	}
+	memcpy(c.camera, req->camera, sizeof(c.camera));
+	const neus2b_train_cfg t = make_train_cfg(tb);
+	for (int e = 0; e < 3; ++e) {
+		c.aabb_min[e] = t.aabb_min[e];
+		c.aabb_max[e] = t.aabb_max[e];
+	}
+	c.cone_angle_constant = t.cone_angle_constant;
+	c.cos_anneal_ratio = t.cos_anneal_ratio;
+	c.min_transmittance = req->min_transmittance;
+	c.linear_colors = 0;
+	c.max_steps = 0;
+	neus2b_grid_desc d = tb->cfg.grid;  // every level, like the SDF lattice
+	const uint16_t* params = (const uint16_t*)(req->use_ema ? tb->params_ema : tb->params);
+	for (uint32_t s = 0; s < req->spp; ++s) {
+		c.sample_index = s;
+		neus2b_ld_random_pixel_offset(req->snap_to_pixel_centers ? 0u : s, c.pixel_offset);
+		N2B_CHECK_CUDA(cudaMemsetAsync(tb->render_frame, 0, (size_t)n_pix * 16, tb->stream));
+		rc = neus2b_render_frame(&d, params, tb->cfg.sdf_bias, &c, tb->bitfield, &tb->render_ws, tb->render_frame, tb->render_depth, nullptr,
+		                         tb->stream);
+		if (rc) return rc;
+		rc = neus2b_render_accumulate(n_pix, tb->render_frame, tb->render_acc, s, tb->stream);
+		if (rc) return rc;
+	}
+	rc = neus2b_render_tonemap(n_pix, tb->render_acc, req->exposure, req->background_color, req->linear ? 0 : 1, tb->render_out, tb->stream);
+	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaMemcpyAsync(h_rgba, tb->render_out, (size_t)n_pix * 16, cudaMemcpyDeviceToHost, tb->stream));
+	if (h_depth) N2B_CHECK_CUDA(cudaMemcpyAsync(h_depth, tb->render_depth, (size_t)n_pix * 4, cudaMemcpyDeviceToHost, tb->stream));
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	return NEUS2B_OK;
 }

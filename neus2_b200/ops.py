@@ -243,3 +243,95 @@ def occupancy_bounds(bitfield):
     out = torch.zeros(8, dtype=torch.int32, device=bitfield.device)
     L.check(L.lib().neus2b_occupancy_bounds(L.ptr(bitfield), L.ptr(out), L.cur_stream()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------ inference rendering
+
+def _owen_scramble(x, seed):
+    def rev(v):
+        return int(f"{v & 0xffffffff:032b}"[::-1], 2)
+    x = (rev(x) + seed) & 0xffffffff
+    for m in (0x6c50b47c, 0xb82f1e52, 0xc7afe638, 0x8d22f6e6):
+        x ^= (x * m) & 0xffffffff
+    return rev(x)
+
+
+def _sobol(index, dim):
+    """Sobol point (32-bit) of `index` in dimension 0 or 1: direction numbers 2^(31-k) and, for dimension 1 (primitive
+    polynomial x + 1), v_k = v_(k-1) xor (v_(k-1) >> 1)."""
+    v, x = 0x80000000, 0
+    for bit in range(32):
+        if (index >> bit) & 1:
+            x ^= v
+        v = (v >> 1) if dim == 0 else (v ^ (v >> 1))
+    return x
+
+
+def ld_random_val_2d(index, seed):
+    """ld_random_val_2d (include/neural-graphics-primitives/random_val.cuh:278-282): a 2-D point of the Owen-scrambled Sobol
+    sequence (Burley 2020)."""
+    import numpy as np
+    index = _owen_scramble(index, seed)
+    out = []
+    for dim in range(2):
+        sd = (seed ^ ((dim + ((seed << 6) & 0xffffffff) + (seed >> 2)) & 0xffffffff)) & 0xffffffff
+        out.append(np.float32(_owen_scramble(_sobol(index, dim), sd)) * np.float32(1.0 / 4294967296.0))
+    return out
+
+
+def ld_random_pixel_offset(spp):
+    """ld_random_pixel_offset (random_val.cuh:317-322): where inside its pixel the spp-th sample of every pixel lies."""
+    import numpy as np
+    a, b = ld_random_val_2d(0, 0xdeadbeef), ld_random_val_2d(spp, 0xdeadbeef)
+    off = [np.float32(0.5) - a[e] + b[e] for e in range(2)]
+    return [float(o - np.floor(o)) for o in off]
+
+
+class RenderBuffers:
+    """Scratch of the renderer for up to max_rays pixels and max_samples samples at a time (neus2b_render_workspace)."""
+
+    def __init__(self, max_rays, max_samples, device="cuda", occupied_bounds=None):
+        max_samples = (int(max_samples) + 127) // 128 * 128
+        self.ray_tmp = torch.empty((max_rays, 8), dtype=torch.float32, device=device)
+        self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
+        self.state = torch.empty((max_rays, 8), dtype=torch.float32, device=device)
+        self.hit_list = torch.empty(max_rays, dtype=torch.int32, device=device)
+        self.coords = torch.empty((max_samples, 7), dtype=torch.float32, device=device)
+        self.out = torch.empty((max_samples, 16), dtype=torch.float16, device=device)
+        self.counters = torch.zeros(8, dtype=torch.int32, device=device)
+        self.occupied_bounds = occupied_bounds
+        self.ws = L.RenderWorkspace(u32(max_rays), u32(max_samples), L.ptr(self.ray_tmp), L.ptr(self.scan_tmp), L.ptr(self.state),
+                                    L.ptr(self.hit_list), L.ptr(self.coords), L.ptr(self.out), L.ptr(self.counters),
+                                    L.ptr(occupied_bounds))
+
+
+def render_cfg(width, height, focal_length, camera, screen_center=(0.5, 0.5), pixel_offset=(0.5, 0.5), sample_index=0,
+               aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0), cone_angle_constant=0.0, min_transmittance=0.01,
+               cos_anneal_ratio=1.0, linear_colors=False, max_steps=0):
+    """camera: 3x4 camera-to-world (array-like, row i column j = camera[i][j])."""
+    import numpy as np
+    cam = np.asarray(camera, dtype=np.float32).reshape(3, 4)
+    return L.RenderCfg(u32(width), u32(height), (C.c_float * 2)(*focal_length), (C.c_float * 2)(*screen_center),
+                       (C.c_float * 12)(*cam.T.reshape(-1).tolist()), (C.c_float * 2)(*pixel_offset), u32(sample_index),
+                       (C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max), C.c_float(cone_angle_constant),
+                       C.c_float(min_transmittance), C.c_float(cos_anneal_ratio), u32(1 if linear_colors else 0), u32(max_steps))
+
+
+def render_frame(desc, params, sdf_bias, cfg, bitfield, buffers, frame, depth):
+    """neus2b_render_frame: blends one sample per pixel into frame [h][w][4] (float32 CUDA) and writes depth [h][w].
+    Returns the number of samples that went through the network."""
+    n = C.c_uint64(0)
+    L.check(L.lib().neus2b_render_frame(C.byref(desc), L.ptr(params), C.c_float(sdf_bias), C.byref(cfg), L.ptr(bitfield),
+                                        C.byref(buffers.ws), L.ptr(frame), L.ptr(depth), C.byref(n), L.cur_stream()))
+    return int(n.value)
+
+
+def render_accumulate(frame, accumulate, sample_count):
+    L.check(L.lib().neus2b_render_accumulate(u32(frame.numel() // 4), L.ptr(frame), L.ptr(accumulate), u32(sample_count), L.cur_stream()))
+
+
+def render_tonemap(accumulate, exposure=0.0, background=(0.0, 0.0, 0.0, 0.0), to_srgb=True):
+    out = torch.empty_like(accumulate)
+    L.check(L.lib().neus2b_render_tonemap(u32(accumulate.numel() // 4), L.ptr(accumulate), C.c_float(exposure),
+                                          (C.c_float * 4)(*background), C.c_int(1 if to_srgb else 0), L.ptr(out), L.cur_stream()))
+    return out

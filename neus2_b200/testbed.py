@@ -28,6 +28,16 @@ class Testbed:
         L.check(L.lib().neus2b_testbed_create(C.byref(cfg), C.byref(self._h)))
         self.stats = L.TrainStats()
         self.shall_train = True
+        # camera and display state of the reference's Testbed (include/neural-graphics-primitives/testbed.h:489-510, 686, 833)
+        self.camera_matrix = np.array([[1, 0, 0, 0.5], [0, -1, 0, 0.5], [0, 0, -1, 0.5]], np.float32)
+        self.relative_focal_length = np.ones(2, np.float32)
+        self.fov_axis = 1
+        self.zoom = 1.0
+        self.screen_center = np.array([0.5, 0.5], np.float32)
+        self.snap_to_pixel_centers = False
+        self.exposure = 0.0
+        self.background_color = np.array([0.0, 0.0, 0.0, 1.0], np.float32)
+        self.rendering_min_transmittance = 0.01
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
@@ -117,6 +127,39 @@ class Testbed:
         L.check(L.lib().neus2b_testbed_sdf_grid(self._h, (C.c_uint32 * 3)(*res), C.c_uint32(z0), C.c_uint32(z1), C.c_int(int(use_ema)),
                                                 C.c_void_p(out.data_ptr())))
         return out
+
+    # --- rendering
+    @property
+    def fov(self):
+        """Field of view in degrees along fov_axis (Testbed::fov, src/testbed.cu:1820)."""
+        return float(2.0 * 180.0 / np.pi * np.arctan(1.0 / (self.relative_focal_length[self.fov_axis] * 2.0)))
+
+    @fov.setter
+    def fov(self, degrees):
+        self.relative_focal_length[:] = 0.5 / np.tan(0.5 * degrees * np.pi / 180.0)
+
+    def render(self, width, height, spp=1, linear=True, use_ema=True, return_depth=False):
+        """``Testbed.render(width, height, spp, linear)`` (src/python_api.cu:123-169, 333) with the camera in
+        ``camera_matrix`` (3x4 camera-to-world in the scene's own coordinates, like ``Testbed::m_camera``): float32
+        [height][width][4], alpha premultiplied."""
+        req = L.RenderRequest()
+        req.width, req.height, req.spp = int(width), int(height), int(spp)
+        cam = np.asarray(self.camera_matrix, np.float32).reshape(3, 4)
+        req.camera = (C.c_float * 12)(*cam.T.reshape(-1).tolist())
+        req.relative_focal_length = (C.c_float * 2)(*[float(v) for v in self.relative_focal_length])
+        req.fov_axis, req.zoom = int(self.fov_axis), float(self.zoom)
+        req.screen_center = (C.c_float * 2)(*[float(v) for v in self.screen_center])
+        req.snap_to_pixel_centers = int(bool(self.snap_to_pixel_centers))
+        req.exposure = float(self.exposure)
+        req.background_color = (C.c_float * 4)(*[float(v) for v in self.background_color])
+        req.linear = int(bool(linear))
+        req.min_transmittance = float(self.rendering_min_transmittance)
+        req.use_ema = int(bool(use_ema))
+        out = np.empty((int(height), int(width), 4), np.float32)
+        depth = np.empty((int(height), int(width)), np.float32) if return_depth else None
+        L.check(L.lib().neus2b_testbed_render(self._h, C.byref(req), out.ctypes.data_as(C.c_void_p),
+                                              depth.ctypes.data_as(C.c_void_p) if return_depth else None))
+        return (out, depth) if return_depth else out
 
     def profile_train_kernel(self, max_steps=0):
         """Arms timing of the fused forward+backward kernel for the next `max_steps` steps (0 = off) and returns

@@ -1080,6 +1080,256 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 }
 
 /* fill_rollover: pad [n_valid, n_target) by wrap-around copies of [0, n_valid) (call sites :3908-3916; body un-vendored) */
+/* ---------------------------------------------------------------- inference rendering */
+
+/* ld_random_val, dimension 0 (include/neural-graphics-primitives/random_val.cuh:235-290): hash-based Owen scrambling of
+ * the Sobol sequence (Burley 2020) with the Laine-Karras permutation; the Sobol point of an index in dimension 0 is its
+ * bit reversal. */
+static inline uint32_t reverse_bits(uint32_t x) {
+	x = ((x & 0xaaaaaaaau) >> 1) | ((x & 0x55555555u) << 1);
+	x = ((x & 0xccccccccu) >> 2) | ((x & 0x33333333u) << 2);
+	x = ((x & 0xf0f0f0f0u) >> 4) | ((x & 0x0f0f0f0fu) << 4);
+	x = ((x & 0xff00ff00u) >> 8) | ((x & 0x00ff00ffu) << 8);
+	return (x >> 16) | (x << 16);
+}
+static inline uint32_t laine_karras(uint32_t x, uint32_t seed) {
+	x += seed;
+	x ^= x * 0x6c50b47cu;
+	x ^= x * 0xb82f1e52u;
+	x ^= x * 0xc7afe638u;
+	x ^= x * 0x8d22f6e6u;
+	return x;
+}
+static inline uint32_t owen_scramble(uint32_t x, uint32_t seed) { return reverse_bits(laine_karras(reverse_bits(x), seed)); }
+float n2o_ld_random_val(uint32_t index, uint32_t seed) {
+	index = owen_scramble(index, seed);
+	uint32_t seed0 = seed ^ (0u + (seed << 6) + (seed >> 2)); /* hash_combine(seed, 0) */
+	return (float)owen_scramble(reverse_bits(index), seed0) * (float)(1.0 / 4294967296.0);
+}
+
+typedef struct {
+	float o[3], d[3], t;
+	int alive;
+} render_ray;
+
+/* init_rays_with_payload_kernel_nerf (src/testbed_nerf.cu:2207-2332) for a pinhole camera, then the jitter of
+ * advance_pos_nerf (:812-818).  The walk to the first occupied cell that follows in advance_pos_nerf is the head of the
+ * sampling loop below and is done there. */
+static void render_init_ray(const n2o_render_cfg* rc, uint32_t x, uint32_t y, render_ray* r) {
+	const uint32_t idx = x + rc->width * y;
+	const float u = ((float)x + rc->pixel_offset[0]) / (float)rc->width, v = ((float)y + rc->pixel_offset[1]) / (float)rc->height;
+	const float dl[3] = {(u - rc->screen_center[0]) * (float)rc->width / rc->focal_length[0],
+	                     (v - rc->screen_center[1]) * (float)rc->height / rc->focal_length[1], 1.0f};
+	float d[3];
+	for (int e = 0; e < 3; ++e) {
+		r->o[e] = rc->camera[9 + e];
+		d[e] = rc->camera[0 + e] * dl[0] + rc->camera[3 + e] * dl[1] + rc->camera[6 + e] * dl[2];
+	}
+	const float norm = sqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
+	for (int e = 0; e < 3; ++e) r->d[e] = d[e] / norm;
+	float tmin, tmax;
+	aabb_ray_intersect(rc->aabb_min, rc->aabb_max, r->o, r->d, &tmin, &tmax);
+	float t = fmaxf(tmin, 0.2f) + 1e-6f; /* NERF_RENDERING_NEAR_DISTANCE */
+	const float p0[3] = {r->o[0] + r->d[0] * t, r->o[1] + r->d[1] * t, r->o[2] + r->d[2] * t};
+	r->alive = aabb_contains(rc->aabb_min, rc->aabb_max, p0);
+	if (r->alive) t += n2o_ld_random_val(rc->sample_index, idx * 786433u) * calc_dt(t, rc->cone_angle_constant);
+	r->t = t;
+}
+
+/* generate_next_nerf_network_inputs (:867-924): up to n_steps samples from the ray's current parameter; returns how many
+ * were taken; *left is set when the ray left the box. */
+static uint32_t render_next_inputs(const n2o_render_cfg* rc, render_ray* r, const uint8_t* bitfield, uint32_t n_steps, float* coords,
+                                   int* left) {
+	const float idir[3] = {1.0f / r->d[0], 1.0f / r->d[1], 1.0f / r->d[2]};
+	const float cone_angle = rc->cone_angle_constant;
+	float t = r->t;
+	*left = 0;
+	for (uint32_t j = 0; j < n_steps; ++j) {
+		float pos[3], dt;
+		for (;;) {
+			for (int e = 0; e < 3; ++e) pos[e] = r->o[e] + t * r->d[e];
+			if (!aabb_contains(rc->aabb_min, rc->aabb_max, pos)) {
+				*left = 1;
+				return j;
+			}
+			dt = calc_dt(t, cone_angle);
+			uint32_t mip = (uint32_t)mip_from_dt(dt, pos);
+			if (occupied_at(pos, bitfield, mip)) break;
+			t = advance_to_next_voxel(t, cone_angle, pos, r->d, idir, N2O_GRIDSIZE >> mip);
+		}
+		if (coords) {
+			float* c = coords + (size_t)j * 7;
+			for (int e = 0; e < 3; ++e) {
+				c[e] = (pos[e] - rc->aabb_min[e]) / (rc->aabb_max[e] - rc->aabb_min[e]);
+				c[4 + e] = (r->d[e] + 1.f) * 0.5f;
+			}
+			c[3] = warp_dt(dt);
+		}
+		t += dt;
+	}
+	r->t = t;
+	return n_steps;
+}
+
+/* Every pixel's whole march (all rounds of NerfTracer::trace, no early termination by opacity), canonical order by pixel
+ * index: what the network would be asked for if no ray ever became opaque. */
+void n2o_render_march(const n2o_render_cfg* rc, const uint8_t* bitfield, uint64_t max_samples, uint32_t* numsteps, float* coords,
+                      uint64_t* n_samples) {
+	const uint32_t limit = rc->max_steps ? rc->max_steps : 10000u;
+	const int64_t n_pix = (int64_t)rc->width * rc->height;
+#pragma omp parallel for schedule(dynamic, 64)
+	for (int64_t i = 0; i < n_pix; ++i) {
+		render_ray r;
+		render_init_ray(rc, (uint32_t)(i % rc->width), (uint32_t)(i / rc->width), &r);
+		int left;
+		numsteps[i] = r.alive ? render_next_inputs(rc, &r, bitfield, limit, NULL, &left) : 0u;
+	}
+	uint64_t base = 0;
+	for (int64_t i = 0; i < n_pix; ++i) base += numsteps[i];
+	*n_samples = base;
+	if (!coords || base > max_samples) return;
+	uint64_t* bases = (uint64_t*)malloc(sizeof(uint64_t) * (size_t)n_pix);
+	base = 0;
+	for (int64_t i = 0; i < n_pix; ++i) {
+		bases[i] = base;
+		base += numsteps[i];
+	}
+#pragma omp parallel for schedule(dynamic, 64)
+	for (int64_t i = 0; i < n_pix; ++i) {
+		if (!numsteps[i]) continue;
+		render_ray r;
+		render_init_ray(rc, (uint32_t)(i % rc->width), (uint32_t)(i / rc->width), &r);
+		int left;
+		render_next_inputs(rc, &r, bitfield, numsteps[i], coords + bases[i] * 7, &left);
+	}
+	free(bases);
+}
+
+/* Testbed::render_nerf in ERenderMode::Shade (:2671-2812): init_rays_from_camera, the rounds of NerfTracer::trace
+ * (:2480-2601: next inputs -> network -> composite_kernel_nerf :926-1171 -> drop finished rays) with 8 steps per round,
+ * shade_kernel_nerf (:2147-2180) for the rays whose opacity passed 0.001 (compact_kernel_nerf :2182-2205).  frame is
+ * blended into (float[h][w][4]), depth written (float[h][w]). */
+void n2o_render_frame(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias, const n2o_render_cfg* rc, const uint8_t* bitfield,
+                      float* frame, float* depth, uint64_t* n_samples_out) {
+	const uint32_t limit = rc->max_steps ? rc->max_steps : 10000u;
+	const int64_t n_pix = (int64_t)rc->width * rc->height;
+	const uint32_t R = 8; /* MAX_STEPS_INBETWEEN_COMPACTION */
+	render_ray* rays = (render_ray*)malloc(sizeof(render_ray) * (size_t)n_pix);
+	float* rgba = (float*)calloc((size_t)n_pix * 4, sizeof(float));
+	float* dep = (float*)calloc((size_t)n_pix, sizeof(float));
+	float* max_weight = (float*)calloc((size_t)n_pix, sizeof(float));
+	uint32_t* taken = (uint32_t*)calloc((size_t)n_pix, sizeof(uint32_t));
+	uint32_t* nsteps = (uint32_t*)calloc((size_t)n_pix, sizeof(uint32_t));
+	uint32_t* alive_list = (uint32_t*)malloc(sizeof(uint32_t) * (size_t)n_pix);
+#pragma omp parallel for schedule(static)
+	for (int64_t i = 0; i < n_pix; ++i) {
+		render_init_ray(rc, (uint32_t)(i % rc->width), (uint32_t)(i / rc->width), &rays[i]);
+		depth[i] = 1e10f;
+	}
+	const float cam_fwd[3] = {rc->camera[6], rc->camera[7], rc->camera[8]};
+	const float cam_pos[3] = {rc->camera[9], rc->camera[10], rc->camera[11]};
+	uint64_t n_samples = 0;
+	float* coords = NULL;
+	uint16_t* out = NULL;
+	size_t cap = 0;
+	for (;;) {
+		size_t n_alive = 0;
+		for (int64_t i = 0; i < n_pix; ++i)
+			if (rays[i].alive) alive_list[n_alive++] = (uint32_t)i;
+		if (!n_alive) break;
+		if (n_alive * R > cap) {
+			cap = n_alive * R;
+			free(coords);
+			free(out);
+			coords = (float*)malloc(cap * 7 * sizeof(float));
+			out = (uint16_t*)malloc(cap * 16 * sizeof(uint16_t));
+		}
+		/* like the reference, sample j of ray a sits at a + j * n_alive */
+#pragma omp parallel for schedule(dynamic, 64)
+		for (int64_t a = 0; a < (int64_t)n_alive; ++a) {
+			const uint32_t i = alive_list[a];
+			float c8[8 * 7];
+			int left;
+			uint32_t want = R;
+			if (taken[i] + want > limit) want = limit - taken[i];
+			nsteps[i] = render_next_inputs(rc, &rays[i], bitfield, want, c8, &left);
+			if (want < R) left = 1; /* step budget used up */
+			for (uint32_t j = 0; j < nsteps[i]; ++j) memcpy(coords + ((size_t)a + (size_t)j * n_alive) * 7, c8 + j * 7, 28);
+			for (uint32_t j = nsteps[i]; j < R; ++j) memset(coords + ((size_t)a + (size_t)j * n_alive) * 7, 0, 28);
+			if (left) rays[i].alive = 2; /* leaves after this round's compositing */
+		}
+		n2o_neus_forward(d, params, sdf_bias, (uint32_t)(n_alive * R), coords, out);
+#pragma omp parallel for schedule(dynamic, 64)
+		for (int64_t a = 0; a < (int64_t)n_alive; ++a) {
+			const uint32_t i = alive_list[a];
+			float* px = rgba + (size_t)i * 4;
+			uint32_t j = 0;
+			for (; j < nsteps[i]; ++j) {
+				const size_t k = (size_t)a + (size_t)j * n_alive;
+				const uint16_t* o = out + k * 16;
+				const float* c = coords + k * 7;
+				float dd[3] = {h2f(o[8]) * 2.f - 1.f, h2f(o[9]) * 2.f - 1.f, h2f(o[10]) * 2.f - 1.f}, dir[3];
+				const float nn = sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+				for (int e = 0; e < 3; ++e) dir[e] = dd[e] / nn; /* BENT_DIR (:999-1002) */
+				neus_sample_t ns;
+				neus_sample(o, c, dir, rc->cos_anneal_ratio, &ns);
+				const float T = 1.f - px[3];
+				const float weight = ns.alpha * T;
+				for (int e = 0; e < 3; ++e) px[e] += ns.rgb[e] * weight;
+				px[3] += weight;
+				if (weight > max_weight[i]) {
+					max_weight[i] = weight;
+					float dp = 0.f;
+					for (int e = 0; e < 3; ++e) {
+						const float pos = c[e] * (rc->aabb_max[e] - rc->aabb_min[e]) + rc->aabb_min[e];
+						dp += cam_fwd[e] * (pos - cam_pos[e]);
+					}
+					dep[i] = dp;
+				}
+				if (px[3] > 1.0f - rc->min_transmittance) {
+					const float w = px[3];
+					for (int e = 0; e < 4; ++e) px[e] /= w;
+					break;
+				}
+			}
+			taken[i] += nsteps[i];
+			if (j < nsteps[i] || rays[i].alive == 2) rays[i].alive = 0;
+		}
+		for (size_t a = 0; a < n_alive; ++a) n_samples += nsteps[alive_list[a]];
+	}
+	for (int64_t i = 0; i < n_pix; ++i) {
+		float tmp[4] = {rgba[i * 4], rgba[i * 4 + 1], rgba[i * 4 + 2], rgba[i * 4 + 3]};
+		if (!(tmp[3] > 0.001f)) continue;
+		if (!rc->linear_colors)
+			for (int e = 0; e < 3; ++e) tmp[e] = srgb_to_linear(tmp[e]);
+		const float k = 1.0f - tmp[3];
+		for (int e = 0; e < 4; ++e) frame[i * 4 + e] = tmp[e] + frame[i * 4 + e] * k;
+		if (tmp[3] > 0.2f) depth[i] = dep[i];
+	}
+	if (n_samples_out) *n_samples_out = n_samples;
+	free(rays); free(rgba); free(dep); free(max_weight); free(taken); free(nsteps); free(alive_list); free(coords); free(out);
+}
+
+/* accumulate_kernel (EColorSpace::Linear) and tonemap_kernel with the identity curve (src/render_buffer.cu:217-259, 474-500) */
+void n2o_render_accumulate(uint32_t n_pixels, const float* frame, float* acc, uint32_t sample_count) {
+	const float sc = (float)sample_count;
+	for (size_t i = 0; i < (size_t)n_pixels * 4; ++i) acc[i] = ((sample_count ? acc[i] : 0.f) * sc + frame[i]) / (sc + 1.f);
+}
+void n2o_render_tonemap(uint32_t n_pixels, const float* acc, float exposure, const float* background, int to_srgb, float* out) {
+	const float bg[3] = {srgb_to_linear(background[0]), srgb_to_linear(background[1]), srgb_to_linear(background[2])};
+	const float scale = exp2f(exposure);
+	for (size_t i = 0; i < n_pixels; ++i) {
+		float c[4] = {acc[i * 4], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]};
+		const float weight = (1.f - c[3]) * background[3];
+		for (int e = 0; e < 3; ++e) {
+			c[e] = (c[e] + bg[e] * weight) * scale;
+			if (to_srgb) c[e] = linear_to_srgb(c[e]);
+		}
+		c[3] += weight;
+		memcpy(out + i * 4, c, 16);
+	}
+}
+
 void n2o_fill_rollover(uint32_t n_target, uint32_t width, uint32_t n_valid, float* data) {
 	if (n_valid == 0 || n_valid >= n_target) return;
 	for (size_t i = (size_t)n_valid * width; i < (size_t)n_target * width; ++i) data[i] = data[i % ((size_t)n_valid * width)];

@@ -134,6 +134,27 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 void n2o_fill_rollover(uint32_t n_target, uint32_t width, uint32_t n_valid, float* data);
 void n2o_fill_rollover_and_rescale_half(uint32_t n_target, uint32_t width, uint32_t n_valid, uint16_t* data);
 
+/* --- inference rendering (src/testbed_nerf.cu:787-1171, 2147-2332, 2398-2601, 2671-2812; src/render_buffer.cu) --- */
+typedef struct {
+	uint32_t width, height;
+	float focal_length[2], screen_center[2];
+	float camera[12];      /* 3x4 camera-to-world, column major */
+	float pixel_offset[2]; /* ld_random_pixel_offset(sample_index) */
+	uint32_t sample_index;
+	float aabb_min[3], aabb_max[3];
+	float cone_angle_constant, min_transmittance, cos_anneal_ratio;
+	uint32_t linear_colors;
+	uint32_t max_steps;    /* 0 = 10000 */
+} n2o_render_cfg;
+float n2o_ld_random_val(uint32_t index, uint32_t seed); /* random_val.cuh:284-288, dimension 0 */
+void n2o_render_march(const n2o_render_cfg* rc, const uint8_t* bitfield, uint64_t max_samples, uint32_t* numsteps /*[h*w]*/,
+                      float* coords /*[max_samples][7] or NULL*/, uint64_t* n_samples);
+void n2o_render_frame(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias, const n2o_render_cfg* rc, const uint8_t* bitfield,
+                      float* frame /*[h][w][4], blended into*/, float* depth /*[h][w]*/, uint64_t* n_samples);
+void n2o_render_accumulate(uint32_t n_pixels, const float* frame, float* acc, uint32_t sample_count);
+void n2o_render_tonemap(uint32_t n_pixels, const float* acc, float exposure, const float* background /*[4] sRGB*/, int to_srgb,
+                        float* out);
+
 /* --- occupancy grid (src/testbed_nerf.cu:630-785, 3287-3391) --- */
 uint32_t n2o_morton3d(uint32_t x, uint32_t y, uint32_t z);
 uint32_t n2o_morton3d_invert(uint32_t x);

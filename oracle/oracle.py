@@ -50,6 +50,14 @@ class TrainCfg(C.Structure):
                 ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32)]
 
 
+class RenderCfg(C.Structure):
+    _fields_ = [("width", C.c_uint32), ("height", C.c_uint32), ("focal_length", C.c_float * 2), ("screen_center", C.c_float * 2),
+                ("camera", C.c_float * 12), ("pixel_offset", C.c_float * 2), ("sample_index", C.c_uint32),
+                ("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
+                ("min_transmittance", C.c_float), ("cos_anneal_ratio", C.c_float), ("linear_colors", C.c_uint32),
+                ("max_steps", C.c_uint32)]
+
+
 class AdamCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
                 ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("loss_scale", C.c_float), ("step", C.c_uint32),
@@ -72,6 +80,7 @@ def lib():
         _lib.n2o_pcg32_next_float.restype = C.c_float
         _lib.n2o_morton3d.restype = C.c_uint32
         _lib.n2o_morton3d_invert.restype = C.c_uint32
+        _lib.n2o_ld_random_val.restype = C.c_float
     return _lib
 
 
@@ -368,3 +377,56 @@ def marching_cubes_slab(sdf_slab, res, z0, nz, tri_table, thresh=0.0, aabb_min=(
     idx = np.zeros(cnt[1], np.uint32)
     lib().n2o_marching_cubes_slab(mn, mx, r, C.c_uint32(z0), C.c_uint32(nz), C.c_float(thresh), _p(sdf), _p(tt), _p(verts), _p(idx), cnt)
     return verts, idx, int(cnt[2]), int(cnt[3])
+
+
+def ld_random_val(index, seed):
+    return float(lib().n2o_ld_random_val(C.c_uint32(index), C.c_uint32(seed)))
+
+
+def render_cfg(width, height, focal_length, camera, screen_center=(0.5, 0.5), pixel_offset=(0.5, 0.5), sample_index=0,
+               aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0), cone_angle_constant=0.0, min_transmittance=0.01,
+               cos_anneal_ratio=1.0, linear_colors=False, max_steps=0):
+    """camera: 3x4 camera-to-world, camera[i][j] = row i, column j."""
+    cam = np.asarray(camera, dtype=np.float32).reshape(3, 4)
+    return RenderCfg(width, height, (C.c_float * 2)(*focal_length), (C.c_float * 2)(*screen_center),
+                     (C.c_float * 12)(*cam.T.reshape(-1).tolist()), (C.c_float * 2)(*pixel_offset), sample_index,
+                     (C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max), cone_angle_constant, min_transmittance,
+                     cos_anneal_ratio, 1 if linear_colors else 0, max_steps)
+
+
+def render_march(cfg, bitfield, want_coords=True):
+    """Every pixel's whole march: (numsteps [h*w], coords [n][7] or None, n)."""
+    n_pix = cfg.width * cfg.height
+    numsteps = np.zeros(n_pix, np.uint32)
+    n = C.c_uint64(0)
+    bf = _c(bitfield, np.uint8)
+    lib().n2o_render_march(C.byref(cfg), _p(bf), C.c_uint64(0), _p(numsteps), None, C.byref(n))
+    if not want_coords:
+        return numsteps, None, int(n.value)
+    coords = np.zeros((max(int(n.value), 1), 7), np.float32)
+    lib().n2o_render_march(C.byref(cfg), _p(bf), C.c_uint64(coords.shape[0]), _p(numsteps), _p(coords), C.byref(n))
+    return numsteps, coords[:int(n.value)], int(n.value)
+
+
+def render_frame(d, params, cfg, bitfield, sdf_bias=-0.1, frame=None):
+    """(frame [h][w][4], depth [h][w], samples the rounds evaluated)."""
+    h, w = cfg.height, cfg.width
+    frame = np.zeros((h, w, 4), np.float32) if frame is None else _c(frame, np.float32)
+    depth = np.zeros((h, w), np.float32)
+    n = C.c_uint64(0)
+    lib().n2o_render_frame(C.byref(d), _p(_c(params, np.uint16)), C.c_float(sdf_bias), C.byref(cfg), _p(_c(bitfield, np.uint8)),
+                           _p(frame), _p(depth), C.byref(n))
+    return frame, depth, int(n.value)
+
+
+def render_accumulate(frame, acc, sample_count):
+    frame = _c(frame, np.float32)
+    lib().n2o_render_accumulate(C.c_uint32(frame.size // 4), _p(frame), _p(acc), C.c_uint32(sample_count))
+
+
+def render_tonemap(acc, exposure=0.0, background=(0.0, 0.0, 0.0, 0.0), to_srgb=True):
+    acc = _c(acc, np.float32)
+    out = np.empty_like(acc)
+    lib().n2o_render_tonemap(C.c_uint32(acc.size // 4), _p(acc), C.c_float(exposure), (C.c_float * 4)(*background), C.c_int(int(to_srgb)),
+                             _p(out))
+    return out
