@@ -354,6 +354,29 @@ def run_kernel_only(args):
         print(json.dumps({"kernel": "mesh", "res": res, "runs": out}))
         tb.close()
         return
+    if args.kernel == "render":
+        # one frame of Testbed.render (1 sample per pixel) of the briefly trained config-1 scene, host image out
+        import time
+        from neus2_b200.testbed import Testbed
+        scene = S.render_sphere_views(64, 512, 512, device="cuda", seed=0)
+        tb = Testbed(batch_size=1 << 18, **({"learning_rate": args.lr} if args.lr else {}))
+        tb.load_training_data(scene["pixels"].cpu().numpy(), *[scene[k].cpu().numpy() for k in ("xforms", "focal", "principal")])
+        tb.set_params(S.init_params(ng, seed=1337))
+        tb.train(args.pretrain)
+        X = scene["xforms"][7].cpu().numpy()
+        tb.camera_matrix = np.stack([X[0:3], X[3:6], X[6:9], X[9:12]], 1)
+        tb.fov = args.render_fov
+        tb.background_color = [0.0, 0.0, 0.0, 0.0]
+        w, h = args.render_res
+        out = []
+        for it in range(args.kernel_iters):
+            t0 = time.perf_counter()
+            img = tb.render(w, h, spp=1, linear=False)
+            out.append({"wall_ms": (time.perf_counter() - t0) * 1e3, "device_ms": tb.last_render_device_ms,
+                        "samples": tb.last_render_samples, "coverage": float((img[..., 3] > 0.5).mean())})
+        print(json.dumps({"kernel": "render", "width": w, "height": h, "runs": out}))
+        tb.close()
+        return
     p = S.init_params(ng, seed=1337)
     rng = np.random.default_rng(9)
     p[12288:12288 + ng] = rng.uniform(-1e-2, 1e-2, ng)
@@ -508,10 +531,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render"], help="run one fused kernel alone (profiling)")
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
     ap.add_argument("--mesh-res", type=int, default=512)
+    ap.add_argument("--render-res", type=int, nargs=2, default=[1600, 1200], help="width height of --kernel render (DTU images are 1600x1200)")
+    ap.add_argument("--render-fov", type=float, default=30.0)
     args = ap.parse_args()
     if args.kernel:
         run_kernel_only(args)

@@ -368,6 +368,8 @@ typedef struct {
 	uint32_t* d_counters;  /* [8] */
 	const int32_t* d_occupied_bounds; /* optional int32[6] from neus2b_occupancy_bounds (one-cascade scenes): rays that miss
 	                                     the box of occupied cells are not marched */
+	uint32_t* d_march_masks;          /* optional [max_rays][64]: the counting pass records which ray parameters became
+	                                     samples, so that writing their coordinates needs no second march */
 } neus2b_render_workspace;
 
 /* Testbed::render_nerf, ERenderMode::Shade (src/testbed_nerf.cu:2671-2812): NerfTracer::init_rays_from_camera (:2398-2478,
@@ -411,6 +413,9 @@ typedef struct {
  * spp frames, each cleared, rendered, accumulated; then tone mapping; h_rgba float[height][width][4] on the host,
  * h_depth float[height][width] (optional, of the last frame). */
 int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_request* req, float* h_rgba, float* h_depth);
+/* Of the last neus2b_testbed_render call: samples that went through the network (all spp frames) and the time on the
+ * device from the first clear to the end of tone mapping (the copy to the host not included). */
+int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n_samples, float* device_ms);
 
 #ifdef __cplusplus
 }

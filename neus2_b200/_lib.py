@@ -50,7 +50,7 @@ class RenderCfg(C.Structure):
 class RenderWorkspace(C.Structure):
     _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_tmp", C.c_void_p), ("d_scan_tmp", C.c_void_p),
                 ("d_state", C.c_void_p), ("d_hit_list", C.c_void_p), ("d_coords", C.c_void_p), ("d_out", C.c_void_p),
-                ("d_counters", C.c_void_p), ("d_occupied_bounds", C.c_void_p)]
+                ("d_counters", C.c_void_p), ("d_occupied_bounds", C.c_void_p), ("d_march_masks", C.c_void_p)]
 
 
 class RenderRequest(C.Structure):
@@ -101,7 +101,7 @@ EXPORTS = [
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
-    "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render",
+    "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
 ]
 
 

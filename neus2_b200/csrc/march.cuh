@@ -154,6 +154,37 @@ struct RayTmp {  // 8 floats per ray
 // visited set, same samples, same count.
 constexpr uint32_t kMaskWords = 64;  // per-ray record of the count pass: one bit per ray parameter that became a sample
 
+// Shortcut for the recurrence t <- t + dt with a constant dt.  While t stays in one binade every t is a multiple of
+// u = ulp(t), so t + dt rounds to t + D where D is dt rounded to a multiple of u: the same D at every step, unless dt lies
+// exactly halfway between two multiples (then the rounding depends on the parity of t).  If all 32 steps from t0 stay in
+// t0's binade, the value after k steps is therefore t0 + k * D, and both the product and the sum are exact in fp32: the
+// shortcut returns the very numbers the 32 serial additions produce.  Returns false when it does not apply (a binade
+// boundary within the 32 steps, a tie, t0 not a positive normal number); the caller then adds serially.
+__device__ __forceinline__ bool const_step_increment(float t0, float dt, float& D, float& t32) {
+	const uint32_t b = __float_as_uint(t0);
+	const uint32_t e = b & 0x7f800000u;
+	if ((b >> 31) != 0u || e < (64u << 23) || e > (190u << 23)) return false;
+	const float u = __uint_as_float(e - (23u << 23));
+	D = (t0 + dt) - t0;
+	t32 = t0 + 32.f * D;
+	if ((__float_as_uint(t32) & 0x7f800000u) != e) return false;
+	return fabsf(dt - D) * 2.f != u;
+}
+// t after 32 steps of the recurrence (any cone angle)
+__device__ __forceinline__ float advance32(float t, float cone_angle) {
+	if (cone_angle == 0.f) {
+		const float dt = min_cone_stepsize();
+		float D, t32;
+		if (const_step_increment(t, dt, D, t32)) return t32;
+#pragma unroll
+		for (int k = 0; k < 32; ++k) t += dt;
+		return t;
+	}
+#pragma unroll
+	for (int k = 0; k < 32; ++k) t += calc_dt(t, cone_angle);
+	return t;
+}
+
 // First half of a chunk: this lane's ray parameter (t after `lane` steps of the recurrence from the chunk start), its
 // position, and the occupancy byte on its way from memory.  Nothing here depends on the visit / jump decisions of earlier
 // chunks, so the next chunk's first half is issued before the current chunk is walked and the lookup latency hides there.
@@ -174,10 +205,16 @@ __device__ __forceinline__ ChunkHead chunk_head(const neus2b_train_cfg& cfg, con
 		// dependent operations
 		const float dt = min_cone_stepsize();
 		h.my_dt = dt;
+		float D, t32;
+		if (const_step_increment(t, dt, D, t32)) {
+			h.my_t = t + (float)lane * D;
+			t = t32;
+		} else {
 #pragma unroll
-		for (int k = 0; k < 32; ++k) {
-			if (lane == k) h.my_t = t;
-			t += dt;
+			for (int k = 0; k < 32; ++k) {
+				if (lane == k) h.my_t = t;
+				t += dt;
+			}
 		}
 	} else {
 #pragma unroll
@@ -239,15 +276,7 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 		const float guard = 48.f * calc_dt(fmaxf(t_lo, 0.f), cone_angle);
 		float t = startt;
 		while (chunk < 8192u) {
-			float te = t;
-			if (cone_angle == 0.f) {
-				const float dt = min_cone_stepsize();
-#pragma unroll
-				for (int k = 0; k < 32; ++k) te += dt;
-			} else {
-#pragma unroll
-				for (int k = 0; k < 32; ++k) te += calc_dt(te, cone_angle);
-			}
+			const float te = advance32(t, cone_angle);
 			if (!(te + guard < t_lo)) break;
 			if (!EMIT && masks && chunk < kMaskWords && lane == 0) masks[chunk] = 0u;
 			t = te;
@@ -341,7 +370,7 @@ __device__ __forceinline__ uint32_t march_ray(const neus2b_train_cfg& cfg, const
 // only the t recurrence and the coordinate writes.
 __device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, const float* o, const float* dirn, float startt,
                                                 const uint32_t* __restrict__ masks, uint32_t numsteps, float* __restrict__ coords_out,
-                                                int lane) {
+                                                int lane, uint32_t slot_lo = 0u, uint32_t slot_hi = 0xffffffffu) {
 	const float cone_angle = cfg.cone_angle_constant;
 	float t_chunk = startt;
 	uint32_t j = 0;
@@ -350,10 +379,16 @@ __device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, con
 		float t = t_chunk, my_t = t_chunk, my_dt = 0.f;
 		if (cone_angle == 0.f) {  // constant step, see chunk_head
 			my_dt = min_cone_stepsize();
+			float D, t32;
+			if (const_step_increment(t, my_dt, D, t32)) {
+				my_t = t + (float)lane * D;
+				t = t32;
+			} else {
 #pragma unroll
-			for (int k = 0; k < 32; ++k) {
-				if (lane == k) my_t = t;
-				t += my_dt;
+				for (int k = 0; k < 32; ++k) {
+					if (lane == k) my_t = t;
+					t += my_dt;
+				}
 			}
 		} else {
 #pragma unroll
@@ -367,8 +402,9 @@ __device__ __forceinline__ void emit_from_masks(const neus2b_train_cfg& cfg, con
 			}
 		}
 		t_chunk = t;
-		if ((m >> lane) & 1u) {
-			float* c = coords_out + (size_t)(j + __popc(m & ((1u << lane) - 1u))) * 7;
+		const uint32_t slot = j + __popc(m & ((1u << lane) - 1u));
+		if (((m >> lane) & 1u) && slot >= slot_lo && slot < slot_hi) {
+			float* c = coords_out + (ptrdiff_t)slot * 7;
 #pragma unroll
 			for (int e = 0; e < 3; ++e) {
 				const float pos = o[e] + my_t * dirn[e];

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) render_setup_kernel(neus2b_render_cfg rc,
 __global__ void __launch_bounds__(128) render_count_kernel(neus2b_render_cfg rc, uint32_t limit, const uint8_t* __restrict__ bitfield,
                                                            RayTmp* __restrict__ tmp, uint64_t* __restrict__ scan_in,
                                                            const int32_t* __restrict__ occ_bounds, const uint32_t* __restrict__ hit_list,
-                                                           const uint32_t* __restrict__ counters) {
+                                                           const uint32_t* __restrict__ counters, uint32_t* __restrict__ masks) {
 	const int lane = threadIdx.x & 31;
 	const neus2b_train_cfg cfg = march_cfg(rc);
 	const CullBox box = cull_box(occ_bounds);
@@ -122,10 +122,13 @@ __global__ void __launch_bounds__(128) render_count_kernel(neus2b_render_cfg rc,
 		const RayTmp r = tmp[i];
 		float t_lo, t_hi;
 		(void)cull_ray(box, r.o, r.d, t_lo, t_hi);
-		const uint32_t n = march_ray<false>(cfg, r.o, r.d, r.startt, bitfield, limit, nullptr, lane, nullptr, nullptr, t_lo, t_hi);
+		uint32_t n_chunks = 0;
+		const uint32_t n = march_ray<false>(cfg, r.o, r.d, r.startt, bitfield, limit, nullptr, lane,
+		                                    masks ? masks + (size_t)i * kMaskWords : nullptr, &n_chunks, t_lo, t_hi);
 		if (lane == 0) {
 			scan_in[i] = (uint64_t)n;
-			tmp[i].numsteps = n;
+			// (top bit: the mask record does not cover this ray, the emit pass marches it again)
+			tmp[i].numsteps = n | (n_chunks > kMaskWords ? 0x80000000u : 0u);
 		}
 	}
 }
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(128) render_emit_kernel(neus2b_render_cfg rc, 
                                                           const uint8_t* __restrict__ bitfield, const RayTmp* __restrict__ tmp,
                                                           const uint64_t* __restrict__ scan, const int32_t* __restrict__ occ_bounds,
                                                           const uint32_t* __restrict__ hit_list, uint32_t* __restrict__ counters,
-                                                          float* __restrict__ coords) {
+                                                          float* __restrict__ coords, const uint32_t* __restrict__ masks) {
 	const int lane = threadIdx.x & 31;
 	const neus2b_train_cfg cfg = march_cfg(rc);
 	const CullBox box = cull_box(occ_bounds);
@@ -145,14 +148,20 @@ __global__ void __launch_bounds__(128) render_emit_kernel(neus2b_render_cfg rc, 
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); h < n_hit; h += warps) {
 		const uint32_t i = hit_list[h];
-		const RayTmp r = tmp[i];
+		RayTmp r = tmp[i];
+		const bool long_ray = (r.numsteps & 0x80000000u) != 0;
+		r.numsteps &= 0x7fffffffu;
 		const uint32_t base = (uint32_t)scan[i];
 		if (r.numsteps == 0 || base + r.numsteps <= s0 || base >= s0 + window) continue;
 		const uint32_t lo = s0 > base ? s0 - base : 0u, hi = min(r.numsteps, s0 + window - base);
+		float* out = coords + ((ptrdiff_t)base - (ptrdiff_t)s0) * 7;
+		if (masks && !long_ray) {
+			emit_from_masks(cfg, r.o, r.d, r.startt, masks + (size_t)i * kMaskWords, hi, out, lane, lo, hi);
+			continue;
+		}
 		float t_lo, t_hi;
 		(void)cull_ray(box, r.o, r.d, t_lo, t_hi);
-		march_ray<true>(cfg, r.o, r.d, r.startt, bitfield, hi, coords + ((ptrdiff_t)base - (ptrdiff_t)s0) * 7, lane, nullptr, nullptr, t_lo,
-		                t_hi, lo, hi);
+		march_ray<true>(cfg, r.o, r.d, r.startt, bitfield, hi, out, lane, nullptr, nullptr, t_lo, t_hi, lo, hi);
 	}
 }
 
@@ -168,15 +177,26 @@ __global__ void __launch_bounds__(128) render_composite_kernel(neus2b_render_cfg
 	const float cam_pos[3] = {rc.camera[9], rc.camera[10], rc.camera[11]};
 	for (uint32_t h = blockIdx.x * blockDim.x + threadIdx.x; h < n_hit; h += gridDim.x * blockDim.x) {
 		const uint32_t i = hit_list[h];
-		const uint32_t n = tmp[i].numsteps, base = (uint32_t)scan[i];
+		const uint32_t n = tmp[i].numsteps & 0x7fffffffu, base = (uint32_t)scan[i];
 		if (n == 0 || base + n <= s0 || base >= s0 + window) continue;
 		RenderState s = state[i];
 		if (s.done) continue;
 		const uint32_t lo = s0 > base ? s0 - base : 0u, hi = min(n, s0 + window - base);
+		// the next sample's rows are on their way while this one is composited (the loop is a chain of dependent steps)
+		const size_t k0 = (size_t)(base + lo - s0);
+		uint4 nx0 = __ldg(reinterpret_cast<const uint4*>(out + k0 * 16)), nx1 = __ldg(reinterpret_cast<const uint4*>(out + k0 * 16) + 1);
+		float ndt = __ldg(coords + k0 * 7 + 3);
 		for (uint32_t j = lo; j < hi; ++j) {
 			const size_t k = (size_t)(base + j - s0);
 			__half o[16];
-			load_out16(out + k * 16, o);
+			reinterpret_cast<uint4*>(o)[0] = nx0;
+			reinterpret_cast<uint4*>(o)[1] = nx1;
+			const float dt_warped = ndt;
+			if (j + 1 < hi) {
+				nx0 = __ldg(reinterpret_cast<const uint4*>(out + (k + 1) * 16));
+				nx1 = __ldg(reinterpret_cast<const uint4*>(out + (k + 1) * 16) + 1);
+				ndt = __ldg(coords + (k + 1) * 7 + 3);
+			}
 			const float* c = coords + k * 7;
 			// BENT_DIR (:999-1002): the direction the network saw, renormalised
 			float dir[3];
@@ -187,7 +207,7 @@ __global__ void __launch_bounds__(128) render_composite_kernel(neus2b_render_cfg
 				for (int e = 0; e < 3; ++e) dir[e] = dd[e] / nn;
 			}
 			NeusSample ns;
-			neus_sample(o, __ldg(c + 3), dir, rc.cos_anneal_ratio, ns);
+			neus_sample(o, dt_warped, dir, rc.cos_anneal_ratio, ns);
 			const float T = 1.f - s.rgba[3];
 			const float weight = ns.alpha * T;
 #pragma unroll
@@ -306,7 +326,7 @@ extern "C" int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t*
 		N2B_CHECK_LAUNCH();
 		const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);
 		render_count_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, limit, d_bitfield, (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_occupied_bounds,
-		                                                 ws->d_hit_list, ws->d_counters);
+		                                                 ws->d_hit_list, ws->d_counters, ws->d_march_masks);
 		N2B_CHECK_LAUNCH();
 		launch_scan(n_rays, nullptr, ws->d_scan_tmp, stream);
 		N2B_CHECK_LAUNCH();
@@ -318,7 +338,8 @@ extern "C" int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t*
 		n_samples += total;
 		for (uint64_t s0 = 0; s0 < total; s0 += ws->max_samples) {
 			render_emit_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, n_rays, (uint32_t)s0, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
-			                                                ws->d_scan_tmp, ws->d_occupied_bounds, ws->d_hit_list, ws->d_counters, ws->d_coords);
+			                                                ws->d_scan_tmp, ws->d_occupied_bounds, ws->d_hit_list, ws->d_counters, ws->d_coords,
+			                                                ws->d_march_masks);
 			N2B_CHECK_LAUNCH();
 			const int rc = neus2b_neus_forward(desc, d_params, sdf_bias, ws->max_samples, ws->d_counters + 2, ws->d_coords, ws->d_out, stream_);
 			if (rc != NEUS2B_OK) return rc;

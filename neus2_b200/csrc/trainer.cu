@@ -128,6 +128,9 @@ struct neus2b_testbed {
 	uint32_t render_pixels = 0;
 	neus2b_render_workspace render_ws{};
 	float *render_frame = nullptr, *render_depth = nullptr, *render_acc = nullptr, *render_out = nullptr;
+	uint64_t render_samples = 0;  // of the last call
+	float render_ms = 0.f;
+	cudaEvent_t render_ev[2] = {nullptr, nullptr};
 };
 
 template <typename T>
@@ -185,6 +188,8 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	if (tb->h_state) cudaFreeHost(tb->h_state);
 	if (tb->h_cam) cudaFreeHost(tb->h_cam);
 	for (cudaEvent_t e : tb->prof_events) cudaEventDestroy(e);
+	for (cudaEvent_t e : tb->render_ev)
+		if (e) cudaEventDestroy(e);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
 }
@@ -588,6 +593,7 @@ static int render_reserve(neus2b_testbed* tb, uint32_t width, uint32_t height) {
 	if (!rc) rc = render_alloc(tb, &ws.d_coords, (size_t)ws.max_samples * 7);
 	if (!rc) rc = render_alloc(tb, &ws.d_out, (size_t)ws.max_samples * 16);
 	if (!rc) rc = render_alloc(tb, &ws.d_counters, (size_t)8);
+	if (!rc) rc = render_alloc(tb, &ws.d_march_masks, (size_t)ws.max_rays * 64);
 	if (!rc) rc = render_alloc(tb, &tb->render_frame, (size_t)n_pix * 4);
 	if (!rc) rc = render_alloc(tb, &tb->render_depth, (size_t)n_pix);
 	if (!rc) rc = render_alloc(tb, &tb->render_acc, (size_t)n_pix * 4);
@@ -637,20 +643,35 @@ extern "C" int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_req
 	c.max_steps = 0;
 	neus2b_grid_desc d = tb->cfg.grid;  // every level, like the SDF lattice
 	const uint16_t* params = (const uint16_t*)(req->use_ema ? tb->params_ema : tb->params);
+	for (cudaEvent_t& e : tb->render_ev)
+		if (!e) N2B_CHECK_CUDA(cudaEventCreate(&e));
+	tb->render_samples = 0;
+	N2B_CHECK_CUDA(cudaEventRecord(tb->render_ev[0], tb->stream));
 	for (uint32_t s = 0; s < req->spp; ++s) {
 		c.sample_index = s;
 		neus2b_ld_random_pixel_offset(req->snap_to_pixel_centers ? 0u : s, c.pixel_offset);
 		N2B_CHECK_CUDA(cudaMemsetAsync(tb->render_frame, 0, (size_t)n_pix * 16, tb->stream));
-		rc = neus2b_render_frame(&d, params, tb->cfg.sdf_bias, &c, tb->bitfield, &tb->render_ws, tb->render_frame, tb->render_depth, nullptr,
+		uint64_t n_samples = 0;
+		rc = neus2b_render_frame(&d, params, tb->cfg.sdf_bias, &c, tb->bitfield, &tb->render_ws, tb->render_frame, tb->render_depth, &n_samples,
 		                         tb->stream);
 		if (rc) return rc;
+		tb->render_samples += n_samples;
 		rc = neus2b_render_accumulate(n_pix, tb->render_frame, tb->render_acc, s, tb->stream);
 		if (rc) return rc;
 	}
 	rc = neus2b_render_tonemap(n_pix, tb->render_acc, req->exposure, req->background_color, req->linear ? 0 : 1, tb->render_out, tb->stream);
 	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaEventRecord(tb->render_ev[1], tb->stream));
 	N2B_CHECK_CUDA(cudaMemcpyAsync(h_rgba, tb->render_out, (size_t)n_pix * 16, cudaMemcpyDeviceToHost, tb->stream));
 	if (h_depth) N2B_CHECK_CUDA(cudaMemcpyAsync(h_depth, tb->render_depth, (size_t)n_pix * 4, cudaMemcpyDeviceToHost, tb->stream));
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	N2B_CHECK_CUDA(cudaEventElapsedTime(&tb->render_ms, tb->render_ev[0], tb->render_ev[1]));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n_samples, float* device_ms) {
+	if (!tb) return NEUS2B_E_INVALID;
+	if (n_samples) *n_samples = tb->render_samples;
+	if (device_ms) *device_ms = tb->render_ms;
 	return NEUS2B_OK;
 }

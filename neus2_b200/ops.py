@@ -290,7 +290,7 @@ def ld_random_pixel_offset(spp):
 class RenderBuffers:
     """Scratch of the renderer for up to max_rays pixels and max_samples samples at a time (neus2b_render_workspace)."""
 
-    def __init__(self, max_rays, max_samples, device="cuda", occupied_bounds=None):
+    def __init__(self, max_rays, max_samples, device="cuda", occupied_bounds=None, masks=False):
         max_samples = (int(max_samples) + 127) // 128 * 128
         self.ray_tmp = torch.empty((max_rays, 8), dtype=torch.float32, device=device)
         self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
@@ -300,9 +300,10 @@ class RenderBuffers:
         self.out = torch.empty((max_samples, 16), dtype=torch.float16, device=device)
         self.counters = torch.zeros(8, dtype=torch.int32, device=device)
         self.occupied_bounds = occupied_bounds
+        self.masks = torch.empty((max_rays, 64), dtype=torch.int32, device=device) if masks else None
         self.ws = L.RenderWorkspace(u32(max_rays), u32(max_samples), L.ptr(self.ray_tmp), L.ptr(self.scan_tmp), L.ptr(self.state),
                                     L.ptr(self.hit_list), L.ptr(self.coords), L.ptr(self.out), L.ptr(self.counters),
-                                    L.ptr(occupied_bounds))
+                                    L.ptr(occupied_bounds), L.ptr(self.masks))
 
 
 def render_cfg(width, height, focal_length, camera, screen_center=(0.5, 0.5), pixel_offset=(0.5, 0.5), sample_index=0,

@@ -159,6 +159,9 @@ class Testbed:
         depth = np.empty((int(height), int(width)), np.float32) if return_depth else None
         L.check(L.lib().neus2b_testbed_render(self._h, C.byref(req), out.ctypes.data_as(C.c_void_p),
                                               depth.ctypes.data_as(C.c_void_p) if return_depth else None))
+        n, ms = C.c_uint64(0), C.c_float(0.0)
+        L.check(L.lib().neus2b_testbed_render_stats(self._h, C.byref(n), C.byref(ms)))
+        self.last_render_samples, self.last_render_device_ms = int(n.value), float(ms.value)
         return (out, depth) if return_depth else out
 
     def profile_train_kernel(self, max_steps=0):

@@ -35,11 +35,11 @@ def cfg_kwargs(w, h, fov=40.0, **kw):
     return d
 
 
-def gpu_frame(L, ops, d, params_bits, cfg, bf, max_rays=None, max_samples=1 << 21, bounds=False):
+def gpu_frame(L, ops, d, params_bits, cfg, bf, max_rays=None, max_samples=1 << 21, bounds=False, masks=False):
     n_pix = cfg.width * cfg.height
     bf_gpu = torch.from_numpy(bf).cuda()
     ob = ops.occupancy_bounds(bf_gpu) if bounds else None
-    buf = ops.RenderBuffers(max_rays or n_pix, max_samples, occupied_bounds=ob)
+    buf = ops.RenderBuffers(max_rays or n_pix, max_samples, occupied_bounds=ob, masks=masks)
     frame = torch.zeros((cfg.height, cfg.width, 4), dtype=torch.float32, device="cuda")
     depth = torch.zeros((cfg.height, cfg.width), dtype=torch.float32, device="cuda")
     gd = L.GridDesc(d.n_levels, d.log2_hashmap_size, d.base_resolution, d.per_level_scale, d.n_active_levels)
@@ -48,9 +48,9 @@ def gpu_frame(L, ops, d, params_bits, cfg, bf, max_rays=None, max_samples=1 << 2
     return frame.cpu().numpy(), depth.cpu().numpy(), n, buf
 
 
-@pytest.mark.parametrize("bounds", [False, True])
+@pytest.mark.parametrize("bounds,masks", [(False, False), (True, False), (True, True), (False, True)])
 @pytest.mark.parametrize("w,h,offset,spp", [(96, 64, (0.5, 0.5), 0), (61, 47, (0.794, 0.19), 3)])
-def test_render_march_bit_exact(gpu, oracle, w, h, offset, spp, bounds):
+def test_render_march_bit_exact(gpu, oracle, w, h, offset, spp, bounds, masks):
     L, ops = gpu
     O = oracle
     _, bf, _ = ball_bitfield(O)
@@ -58,9 +58,9 @@ def test_render_march_bit_exact(gpu, oracle, w, h, offset, spp, bounds):
     kw = cfg_kwargs(w, h, pixel_offset=offset, sample_index=spp)
     numsteps, coords, n = O.render_march(O.render_cfg(**kw), bf)
     assert n > 1000
-    _, _, n_gpu, buf = gpu_frame(L, ops, d, pb, ops.render_cfg(**kw), bf, bounds=bounds)
+    _, _, n_gpu, buf = gpu_frame(L, ops, d, pb, ops.render_cfg(**kw), bf, bounds=bounds, masks=masks)
     assert n_gpu == n
-    got_steps = buf.ray_tmp.cpu().numpy().view(np.uint32)[:, 7]
+    got_steps = buf.ray_tmp.cpu().numpy().view(np.uint32)[:, 7] & 0x7fffffff
     np.testing.assert_array_equal(got_steps, numsteps)
     np.testing.assert_array_equal(buf.coords.cpu().numpy()[:n].view(np.uint32), coords.view(np.uint32))
 
@@ -125,6 +125,10 @@ def test_render_windows_and_bands_identical(gpu, oracle):
     cfg = ops.render_cfg(**cfg_kwargs(72, 56, pixel_offset=(0.3, 0.7), sample_index=1))
     one, one_depth, n, _ = gpu_frame(L, ops, d, pb, cfg, bf)
     win, win_depth, n2, _ = gpu_frame(L, ops, d, pb, cfg, bf, max_samples=4096)       # many windows, rays split across them
+    wm, wm_depth, n4, _ = gpu_frame(L, ops, d, pb, cfg, bf, max_samples=4096, masks=True, bounds=True)
+    assert n4 == n
+    np.testing.assert_array_equal(one.view(np.uint32), wm.view(np.uint32))
+    np.testing.assert_array_equal(one_depth.view(np.uint32), wm_depth.view(np.uint32))
     band, band_depth, n3, _ = gpu_frame(L, ops, d, pb, cfg, bf, max_rays=72 * 5 + 10)  # bands of 5 rows
     assert n > 3 * 4096 and n == n2 == n3
     np.testing.assert_array_equal(one.view(np.uint32), win.view(np.uint32))
