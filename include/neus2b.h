@@ -28,6 +28,7 @@ typedef struct CUstream_st* neus2b_stream_t;
 #define NEUS2B_E_NO_DEVICE (-3)
 #define NEUS2B_E_OVERFLOW (-4)    /* a device-side capacity was exceeded (flag read back by the caller) */
 #define NEUS2B_E_TOO_LARGE (-5)   /* request beyond a fixed compiled-in capacity */
+#define NEUS2B_E_IO (-6)          /* a file could not be opened or written */
 
 #define NEUS2B_MAX_LEVELS 16
 #define NEUS2B_GRIDSIZE 128u /* NERF_GRIDSIZE  include/neural-graphics-primitives/nerf.h:24 */
@@ -416,6 +417,28 @@ int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_request* req, 
 /* Of the last neus2b_testbed_render call: samples that went through the network (all spp frames) and the time on the
  * device from the first clear to the end of tone mapping (the copy to the host not included). */
 int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n_samples, float* device_ms);
+
+/* ---------------------------------------------------------------- mesh post-processing and export */
+
+/* compute_mesh_1ring (src/marching_cubes.cu:331-375, 720-735): per vertex the homogeneous sum of its 1-ring neighbours
+ * d_ring float[n_verts][4] (xyz sum, count; optional) and the area-weighted normal d_normals float[n_verts][3] (not
+ * normalised; optional).  Both are zeroed first. */
+int neus2b_mesh_1ring(uint32_t n_verts, const float* d_verts, uint32_t n_indices, const uint32_t* d_indices, float* d_ring,
+                      float* d_normals, neus2b_stream_t stream);
+/* Testbed::compute_mesh_vertex_colors (src/testbed_nerf.cu:4057-4080): the network's colour at every vertex, seen from the
+ * direction that points away from the centre of the unit cube; logistic activation, then linear_to_srgb when
+ * linear_colors (extract_srgb_with_activation, :522-535).  d_colors float[n_verts][3].  Scratch: d_coords_scratch
+ * float[scratch_samples][7], d_out_scratch fp16 [scratch_samples][16], scratch_samples >= 128 vertices per network call. */
+int neus2b_mesh_vertex_colors(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n_verts,
+                              const float* d_verts, const float aabb_min[3], const float aabb_max[3], int linear_colors,
+                              float* d_coords_scratch, uint16_t* d_out_scratch, uint32_t scratch_samples, float* d_colors,
+                              neus2b_stream_t stream);
+/* save_mesh without texture unwrap (src/marching_cubes.cu:824-976): HOST arrays in, Wavefront OBJ (or ASCII PLY when the
+ * path ends in ".ply") out, the same text as the reference's writer: positions (v - nerf_offset) / nerf_scale, unit
+ * normals, colours clamped to [0, 1] (OBJ) or bytes (PLY), triangles reversed unless invert_normals
+ * (dataset.from_na, src/testbed.cu:305).  The lines are formatted by all host threads. */
+int neus2b_save_mesh(const char* path, uint32_t n_verts, const float* h_verts, const float* h_normals, const float* h_colors,
+                     uint32_t n_indices, const uint32_t* h_indices, float nerf_scale, const float nerf_offset[3], int invert_normals);
 
 #ifdef __cplusplus
 }

@@ -102,6 +102,7 @@ EXPORTS = [
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
     "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
+    "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh",
 ]
 
 

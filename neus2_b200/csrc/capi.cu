@@ -11,6 +11,7 @@ extern "C" const char* neus2b_error_string(int code) {
 		case NEUS2B_E_NO_DEVICE: return "no CUDA device";
 		case NEUS2B_E_OVERFLOW: return "device-side capacity exceeded";
 		case NEUS2B_E_TOO_LARGE: return "request exceeds a compiled-in capacity";
+		case NEUS2B_E_IO: return "file could not be opened or written";
 		default: break;
 	}
 	if (code > 0) return cudaGetErrorString((cudaError_t)code);

@@ -336,3 +336,39 @@ def render_tonemap(accumulate, exposure=0.0, background=(0.0, 0.0, 0.0, 0.0), to
     L.check(L.lib().neus2b_render_tonemap(u32(accumulate.numel() // 4), L.ptr(accumulate), C.c_float(exposure),
                                           (C.c_float * 4)(*background), C.c_int(1 if to_srgb else 0), L.ptr(out), L.cur_stream()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------ mesh post-processing
+
+def mesh_1ring(verts, indices, want_ring=False):
+    """Area-weighted vertex normals [n][3] (not normalised) and, if asked, the homogeneous 1-ring sums [n][4]."""
+    n = verts.shape[0]
+    normals = torch.empty((n, 3), dtype=torch.float32, device=verts.device)
+    ring = torch.empty((n, 4), dtype=torch.float32, device=verts.device) if want_ring else None
+    L.check(L.lib().neus2b_mesh_1ring(u32(n), L.ptr(verts), u32(indices.numel()), L.ptr(indices), L.ptr(ring), L.ptr(normals), L.cur_stream()))
+    return (normals, ring) if want_ring else normals
+
+
+def mesh_vertex_colors(desc, params, sdf_bias, verts, linear_colors=False, aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0),
+                       chunk=1 << 20):
+    n = verts.shape[0]
+    colors = torch.empty((n, 3), dtype=torch.float32, device=verts.device)
+    chunk = max(128, min(chunk, (n + 127) // 128 * 128))
+    coords = torch.empty((chunk, 7), dtype=torch.float32, device=verts.device)
+    out = torch.empty((chunk, 16), dtype=torch.float16, device=verts.device)
+    L.check(L.lib().neus2b_mesh_vertex_colors(C.byref(desc), L.ptr(params), C.c_float(sdf_bias), u32(n), L.ptr(verts), (C.c_float * 3)(*aabb_min),
+                                              (C.c_float * 3)(*aabb_max), C.c_int(int(linear_colors)), L.ptr(coords), L.ptr(out), u32(chunk),
+                                              L.ptr(colors), L.cur_stream()))
+    return colors
+
+
+def save_mesh(path, verts, normals, colors, indices, nerf_scale=1.0, nerf_offset=(0.0, 0.0, 0.0), invert_normals=False):
+    """Host arrays (numpy) to an .obj or .ply file."""
+    import numpy as np
+    v = np.ascontiguousarray(verts, dtype=np.float32)
+    nr = np.ascontiguousarray(normals, dtype=np.float32)
+    c = np.ascontiguousarray(colors, dtype=np.float32)
+    idx = np.ascontiguousarray(indices).astype(np.uint32, copy=False)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    L.check(L.lib().neus2b_save_mesh(str(path).encode(), u32(v.shape[0]), p(v), p(nr), p(c), u32(idx.size), p(idx), C.c_float(nerf_scale),
+                                     (C.c_float * 3)(*nerf_offset), C.c_int(int(invert_normals))))

@@ -177,6 +177,22 @@ class Testbed:
         from . import ops
         return ops.marching_cubes(self.sdf_grid(resolution, use_ema=use_ema), tri_table=tri_table, thresh=thresh)
 
+    def compute_and_save_marching_cubes_mesh(self, filename, resolution=256, thresh=0.0, tri_table=None, use_ema=True,
+                                             nerf_scale=1.0, nerf_offset=(0.0, 0.0, 0.0), invert_normals=False):
+        """Testbed::compute_and_save_marching_cubes_mesh (src/testbed.cu:298-306; python_api.cu:352): marching cubes on the
+        SDF lattice, 1-ring normals, vertex colours from the network, OBJ or PLY file.  Returns the mesh as host arrays."""
+        import torch
+        from . import ops
+        verts, indices = self.compute_marching_cubes_mesh(resolution, thresh, tri_table, use_ema)
+        ptrs = self.device_ptrs()
+        normals = ops.mesh_1ring(verts, indices)
+        colors = ops.mesh_vertex_colors(self.config.grid, ptrs["params_ema" if use_ema else "params"], self.config.sdf_bias, verts)
+        torch.cuda.synchronize()
+        mesh = dict(verts=verts.cpu().numpy(), normals=normals.cpu().numpy(), colors=colors.cpu().numpy(),
+                    indices=indices.cpu().numpy().view(np.uint32))
+        ops.save_mesh(filename, mesh["verts"], mesh["normals"], mesh["colors"], mesh["indices"], nerf_scale, nerf_offset, invert_normals)
+        return mesh
+
     def compute_marching_cubes_mesh_sharded(self, resolution, rank, world, thresh=0.0, tri_table=None, use_ema=True, gather=None):
         """The same mesh with the lattice split into z-slabs, one per rank: every rank evaluates the SDF and runs marching cubes
         on its slab only, the parts are gathered and merged on the host (neus2_b200.mesh_shard).  Returns host arrays."""

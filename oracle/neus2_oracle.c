@@ -7,6 +7,7 @@
 #include <math.h>
 #include <omp.h>
 #include <stdlib.h>
+#include <stdio.h>
 #include <string.h>
 
 void n2o_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
@@ -1538,4 +1539,105 @@ void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint
 	n2o_marching_cubes_slab(aabb_min, aabb_max, res, 0, res[2], thresh, sdf, tri_table, verts, indices, counts);
 	*n_verts = counts[0];
 	*n_indices = counts[1];
+}
+
+/* --- mesh post-processing (src/marching_cubes.cu:331-375, 720-735, 824-976; src/testbed_nerf.cu:522-535, 838-844, 4057-4080) */
+
+/* accumulate_1ring: ring [n][4] and normals [n][3] (either may be NULL), accumulated in double and rounded once */
+void n2o_mesh_1ring(uint32_t n_verts, const float* verts, uint32_t n_indices, const uint32_t* indices, float* ring, float* normals) {
+	double* r = (double*)calloc((size_t)n_verts * 4 + 1, sizeof(double));
+	double* nr = (double*)calloc((size_t)n_verts * 3 + 1, sizeof(double));
+	for (uint32_t t = 0; t + 2 < n_indices; t += 3) {
+		const uint32_t id[3] = {indices[t], indices[t + 1], indices[t + 2]};
+		const float* p[3] = {verts + (size_t)id[0] * 3, verts + (size_t)id[1] * 3, verts + (size_t)id[2] * 3};
+		for (int k = 0; k < 3; ++k) {
+			const int a = (k + 1) % 3, b = (k + 2) % 3;
+			for (int e = 0; e < 3; ++e) r[(size_t)id[k] * 4 + e] += (double)(p[a][e] + p[b][e]);
+			r[(size_t)id[k] * 4 + 3] += 2.0;
+		}
+		const float u[3] = {p[1][0] - p[0][0], p[1][1] - p[0][1], p[1][2] - p[0][2]};
+		const float v[3] = {p[0][0] - p[2][0], p[0][1] - p[2][1], p[0][2] - p[2][2]};
+		const float n[3] = {u[1] * v[2] - u[2] * v[1], u[2] * v[0] - u[0] * v[2], u[0] * v[1] - u[1] * v[0]}; /* (pb-pa) x (pa-pc) */
+		for (int k = 0; k < 3; ++k)
+			for (int e = 0; e < 3; ++e) nr[(size_t)id[k] * 3 + e] += (double)n[e];
+	}
+	if (ring)
+		for (size_t i = 0; i < (size_t)n_verts * 4; ++i) ring[i] = (float)r[i];
+	if (normals)
+		for (size_t i = 0; i < (size_t)n_verts * 3; ++i) normals[i] = (float)nr[i];
+	free(r);
+	free(nr);
+}
+
+/* compute_mesh_vertex_colors: generate_nerf_network_inputs_from_positions -> network -> extract_srgb_with_activation */
+void n2o_mesh_vertex_colors(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias, uint32_t n_verts, const float* verts,
+                            const float* aabb_min, const float* aabb_max, int linear_colors, float* colors) {
+	float* coords = (float*)calloc((size_t)(n_verts + 1) * 7, sizeof(float));
+	uint16_t* out = (uint16_t*)malloc((size_t)(n_verts + 1) * 16 * sizeof(uint16_t));
+	for (uint32_t i = 0; i < n_verts; ++i) {
+		const float* p = verts + (size_t)i * 3;
+		float dd[3] = {p[0] - 0.5f, p[1] - 0.5f, p[2] - 0.5f};
+		const float nn = sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
+		float* c = coords + (size_t)i * 7;
+		for (int e = 0; e < 3; ++e) {
+			if (nn > 0.f) dd[e] /= nn;
+			c[e] = (p[e] - aabb_min[e]) / (aabb_max[e] - aabb_min[e]);
+			c[4 + e] = (dd[e] + 1.f) * 0.5f;
+		}
+		c[3] = warp_dt(min_cone_stepsize());
+	}
+	n2o_neus_forward(d, params, sdf_bias, n_verts, coords, out);
+	for (size_t i = 0; i < (size_t)n_verts * 3; ++i) {
+		float c = logisticf(h2f(out[(i / 3) * 16 + i % 3]));
+		colors[i] = linear_colors ? linear_to_srgb(c) : c;
+	}
+	free(coords);
+	free(out);
+}
+
+/* save_mesh without unwrap: the reference's fprintf calls, one after another.  Returns 0 on success. */
+int n2o_save_mesh(const char* path, uint32_t n_verts, const float* verts, const float* normals, const float* colors, uint32_t n_indices,
+                  const uint32_t* indices, float nerf_scale, const float* nerf_offset, int invert_normals) {
+	const size_t len = strlen(path);
+	const int ply = len >= 4 && strcmp(path + len - 4, ".ply") == 0;
+	FILE* f = fopen(path, "wb");
+	if (!f) return -1;
+	if (ply)
+		fprintf(f,
+		        "ply\nformat ascii 1.0\ncomment output from https://github.com/NVlabs/instant-ngp\nelement vertex %u\n"
+		        "property float x\nproperty float y\nproperty float z\nproperty float nx\nproperty float ny\nproperty float nz\n"
+		        "property uchar red\nproperty uchar green\nproperty uchar blue\nelement face %u\n"
+		        "property list uchar int vertex_index\nend_header\n",
+		        n_verts, n_indices / 3);
+	for (uint32_t i = 0; i < n_verts; ++i) {
+		float p[3], n[3];
+		const float* v = normals + (size_t)i * 3;
+		const float z = v[0] * v[0] + v[1] * v[1] + v[2] * v[2];
+		for (int e = 0; e < 3; ++e) {
+			p[e] = (verts[(size_t)i * 3 + e] - nerf_offset[e]) / nerf_scale;
+			n[e] = z > 0.f ? v[e] / sqrtf(z) : v[e];
+		}
+		const float* c = colors + (size_t)i * 3;
+		if (ply) {
+			unsigned char c8[3];
+			for (int e = 0; e < 3; ++e) c8[e] = (unsigned char)clampf(c[e] * 255.f, 0.f, 255.f);
+			fprintf(f, "%0.5f %0.5f %0.5f %0.3f %0.3f %0.3f %d %d %d\n", p[0], p[1], p[2], n[0], n[1], n[2], c8[0], c8[1], c8[2]);
+		} else {
+			fprintf(f, "v %0.5f %0.5f %0.5f %0.3f %0.3f %0.3f\n", p[0], p[1], p[2], clampf(c[0], 0.f, 1.f), clampf(c[1], 0.f, 1.f),
+			        clampf(c[2], 0.f, 1.f));
+		}
+	}
+	if (!ply)
+		for (uint32_t i = 0; i < n_verts; ++i) {
+			const float* v = normals + (size_t)i * 3;
+			const float z = v[0] * v[0] + v[1] * v[1] + v[2] * v[2];
+			const float s = z > 0.f ? sqrtf(z) : 1.f;
+			fprintf(f, "vn %0.5f %0.5f %0.5f\n", v[0] / s, v[1] / s, v[2] / s);
+		}
+	for (uint32_t t = 0; t + 2 < n_indices; t += 3) {
+		const uint32_t a = invert_normals ? indices[t] : indices[t + 2], b = indices[t + 1], c = invert_normals ? indices[t + 2] : indices[t];
+		if (ply) fprintf(f, "3 %d %d %d\n", (int)a, (int)b, (int)c);
+		else fprintf(f, "f %u//%u %u//%u %u//%u\n", a + 1, a + 1, b + 1, b + 1, c + 1, c + 1);
+	}
+	return fclose(f);
 }

@@ -182,6 +182,14 @@ void n2o_marching_cubes_slab(const float* aabb_min, const float* aabb_max, const
 void n2o_marching_cubes(const float* aabb_min, const float* aabb_max, const uint32_t res[3], float thresh, const float* sdf,
                         const int8_t* tri_table, float* verts, uint32_t* indices, uint32_t* n_verts, uint32_t* n_indices);
 
+/* --- mesh post-processing and export (src/marching_cubes.cu:331-375, 824-976; src/testbed_nerf.cu:4057-4080) --- */
+void n2o_mesh_1ring(uint32_t n_verts, const float* verts, uint32_t n_indices, const uint32_t* indices, float* ring /*[n][4] or NULL*/,
+                    float* normals /*[n][3] or NULL*/);
+void n2o_mesh_vertex_colors(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias, uint32_t n_verts, const float* verts,
+                            const float* aabb_min, const float* aabb_max, int linear_colors, float* colors /*[n][3]*/);
+int n2o_save_mesh(const char* path, uint32_t n_verts, const float* verts, const float* normals, const float* colors, uint32_t n_indices,
+                  const uint32_t* indices, float nerf_scale, const float* nerf_offset, int invert_normals);
+
 #ifdef __cplusplus
 }
 #endif

@@ -430,3 +430,30 @@ def render_tonemap(acc, exposure=0.0, background=(0.0, 0.0, 0.0, 0.0), to_srgb=T
     lib().n2o_render_tonemap(C.c_uint32(acc.size // 4), _p(acc), C.c_float(exposure), (C.c_float * 4)(*background), C.c_int(int(to_srgb)),
                              _p(out))
     return out
+
+
+def mesh_1ring(verts, indices):
+    """(normals [n][3], ring [n][4])"""
+    v = _c(verts, np.float32)
+    idx = _c(indices, np.uint32)
+    normals = np.zeros((v.shape[0], 3), np.float32)
+    ring = np.zeros((v.shape[0], 4), np.float32)
+    lib().n2o_mesh_1ring(C.c_uint32(v.shape[0]), _p(v), C.c_uint32(idx.size), _p(idx), _p(ring), _p(normals))
+    return normals, ring
+
+
+def mesh_vertex_colors(d, params, verts, sdf_bias=-0.1, linear_colors=False, aabb_min=(0, 0, 0), aabb_max=(1, 1, 1)):
+    v = _c(verts, np.float32)
+    colors = np.zeros((v.shape[0], 3), np.float32)
+    lib().n2o_mesh_vertex_colors(C.byref(d), _p(_c(params, np.uint16)), C.c_float(sdf_bias), C.c_uint32(v.shape[0]), _p(v),
+                                 (C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max), C.c_int(int(linear_colors)), _p(colors))
+    return colors
+
+
+def save_mesh(path, verts, normals, colors, indices, nerf_scale=1.0, nerf_offset=(0.0, 0.0, 0.0), invert_normals=False):
+    v, n, c = _c(verts, np.float32), _c(normals, np.float32), _c(colors, np.float32)
+    idx = _c(indices, np.uint32)
+    rc = lib().n2o_save_mesh(str(path).encode(), C.c_uint32(v.shape[0]), _p(v), _p(n), _p(c), C.c_uint32(idx.size), _p(idx),
+                             C.c_float(nerf_scale), (C.c_float * 3)(*nerf_offset), C.c_int(int(invert_normals)))
+    if rc != 0:
+        raise OSError(f"n2o_save_mesh({path}) failed")
