@@ -221,6 +221,10 @@ int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint16_t* d_para
 /* Smallest box of cell indices {min x, y, z, max x, y, z} around the set bits of the finest level of the occupancy bitfield
  * (min > max when nothing is occupied); no counterpart in the reference, which marches every ray. */
 int neus2b_occupancy_bounds(const uint8_t* d_bitfield, int32_t* d_bounds, neus2b_stream_t stream);
+/* update_density_grid_mean_and_bitfield alone (src/testbed_nerf.cu:3371-3391): mean of the finest level, occupancy bits of
+ * every level from d_grid float[128^3 * n_cascades]; d_partial double[1024] scratch. */
+int neus2b_occupancy_mean_and_bitfield(uint32_t n_cascades, const float* d_grid, uint8_t* d_bitfield, float* d_mean, double* d_partial,
+                                       neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- optimizer (Trainer::optimizer_step, src/testbed_nerf.cu:3498) */
 typedef struct {
@@ -439,6 +443,32 @@ int neus2b_mesh_vertex_colors(const neus2b_grid_desc* desc, const uint16_t* d_pa
  * (dataset.from_na, src/testbed.cu:305).  The lines are formatted by all host threads. */
 int neus2b_save_mesh(const char* path, uint32_t n_verts, const float* h_verts, const float* h_normals, const float* h_colors,
                      uint32_t n_indices, const uint32_t* h_indices, float nerf_scale, const float nerf_offset[3], int invert_normals);
+
+/* ---------------------------------------------------------------- state for snapshots (Testbed::save_snapshot / load_snapshot,
+ * src/testbed.cu:3134-3244: Trainer::serialize + density grid + counters) */
+
+typedef struct {
+	uint32_t training_step;          /* snapshot["training_step"] */
+	uint32_t density_grid_ema_step;  /* Nerf::density_grid_ema_step */
+	uint32_t rays_per_batch, measured_batch_size, measured_batch_size_before_compaction; /* snapshot["nerf"]["rgb"] */
+	uint32_t n_rays_total;           /* Counters::n_rays_total */
+	float loss, ek_loss;             /* snapshot["loss"] */
+	neus2b_pcg32 rng, density_rng;   /* m_rng, m_nerf.density_grid_rng */
+} neus2b_training_state;
+int neus2b_testbed_get_training_state(neus2b_testbed* tb, neus2b_training_state* out);
+int neus2b_testbed_set_training_state(neus2b_testbed* tb, const neus2b_training_state* in);
+/* The arrays a snapshot holds, copied to / from HOST memory; `bytes` must be the array's size.  Trainer::serialize stores
+ * the fp16 parameters and, with include_optimizer_state, the optimizer's arrays; load_snapshot converts the stored fp16
+ * density grid back to fp32 and rebuilds mean and bitfield, which setting NEUS2B_ARRAY_DENSITY_GRID does here too. */
+#define NEUS2B_ARRAY_MASTER 0       /* float[n_params]  Trainer::params_full_precision */
+#define NEUS2B_ARRAY_ADAM_M 1       /* float[n_params] */
+#define NEUS2B_ARRAY_ADAM_V 2       /* float[n_params] */
+#define NEUS2B_ARRAY_EMA_MASTER 3   /* float[n_params] */
+#define NEUS2B_ARRAY_PARAMS 4       /* fp16[n_params]   Trainer::params */
+#define NEUS2B_ARRAY_PARAMS_EMA 5   /* fp16[n_params]   Trainer::params_inference */
+#define NEUS2B_ARRAY_DENSITY_GRID 6 /* float[128^3 * n_cascades] */
+int neus2b_testbed_get_array(neus2b_testbed* tb, int which, void* h_out, uint64_t bytes);
+int neus2b_testbed_set_array(neus2b_testbed* tb, int which, const void* h_in, uint64_t bytes);
 
 #ifdef __cplusplus
 }

@@ -78,6 +78,12 @@ class TestbedConfig(C.Structure):
                 ("progressive_steps_per_increment", C.c_uint32), ("world_size", C.c_uint32), ("rank", C.c_uint32)]
 
 
+class TrainingState(C.Structure):
+    _fields_ = [("training_step", C.c_uint32), ("density_grid_ema_step", C.c_uint32), ("rays_per_batch", C.c_uint32),
+                ("measured_batch_size", C.c_uint32), ("measured_batch_size_before_compaction", C.c_uint32),
+                ("n_rays_total", C.c_uint32), ("loss", C.c_float), ("ek_loss", C.c_float), ("rng", Pcg32), ("density_rng", Pcg32)]
+
+
 class TrainStats(C.Structure):
     _fields_ = [("training_step", C.c_uint32), ("rays_per_batch", C.c_uint32), ("n_rays_kept", C.c_uint32),
                 ("measured_batch_size_before_compaction", C.c_uint32), ("measured_batch_size", C.c_uint32),
@@ -102,7 +108,8 @@ EXPORTS = [
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward",
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
     "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
-    "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh",
+    "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh", "neus2b_occupancy_mean_and_bitfield",
+    "neus2b_testbed_get_training_state", "neus2b_testbed_set_training_state", "neus2b_testbed_get_array", "neus2b_testbed_set_array",
 ]
 
 

@@ -311,6 +311,13 @@ extern "C" int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint1
 	}
 	occ_ema_kernel<<<div_up(n_elements, 256), 256, 0, stream>>>(n_elements, decay, d_grid, d_grid_tmp);
 	N2B_CHECK_LAUNCH();
+	return neus2b_occupancy_mean_and_bitfield(n_cascades, d_grid, d_bitfield, d_mean, d_partial, stream);
+}
+
+extern "C" int neus2b_occupancy_mean_and_bitfield(uint32_t n_cascades, const float* d_grid, uint8_t* d_bitfield, float* d_mean,
+                                                  double* d_partial, neus2b_stream_t stream_) {
+	cudaStream_t stream = (cudaStream_t)stream_;
+	if (!d_grid || !d_bitfield || !d_mean || !d_partial || n_cascades == 0 || n_cascades > NEUS2B_CASCADES) return NEUS2B_E_INVALID;
 	occ_mean_partial_kernel<<<1024, 256, 0, stream>>>(d_grid, d_partial);
 	N2B_CHECK_LAUNCH();
 	occ_mean_final_kernel<<<1, 32, 0, stream>>>(d_partial, d_mean);

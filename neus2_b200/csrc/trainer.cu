@@ -675,3 +675,90 @@ extern "C" int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n
 	if (device_ms) *device_ms = tb->render_ms;
 	return NEUS2B_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ snapshot state
+
+extern "C" int neus2b_testbed_get_training_state(neus2b_testbed* tb, neus2b_training_state* out) {
+	if (!tb || !out) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->h_state, tb->state, sizeof(TrainState), cudaMemcpyDeviceToHost, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	out->training_step = tb->training_step;
+	out->density_grid_ema_step = tb->ema_step;
+	out->rays_per_batch = tb->h_state->rays_per_batch;
+	out->n_rays_total = tb->h_state->n_rays_total;
+	out->measured_batch_size = tb->h_state->measured;
+	out->measured_batch_size_before_compaction = tb->h_state->measured_pre;
+	out->loss = tb->h_state->loss;
+	out->ek_loss = tb->h_state->ek_loss;
+	out->rng = neus2b_pcg32{tb->rng.state, tb->rng.inc};
+	out->density_rng = neus2b_pcg32{tb->density_rng.state, tb->density_rng.inc};
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_set_training_state(neus2b_testbed* tb, const neus2b_training_state* in) {
+	if (!tb || !in || in->rays_per_batch == 0 || in->rays_per_batch > tb->max_rays) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	tb->training_step = in->training_step;
+	tb->ema_step = in->density_grid_ema_step;
+	tb->rng = Pcg32{in->rng.state, in->rng.inc};
+	tb->density_rng = Pcg32{in->density_rng.state, in->density_rng.inc};
+	TrainState st{};
+	st.rays_per_batch = in->rays_per_batch;
+	st.n_rays_total = in->n_rays_total;
+	st.measured = in->measured_batch_size;
+	st.measured_pre = in->measured_batch_size_before_compaction;
+	st.loss = in->loss;
+	st.ek_loss = in->ek_loss;
+	*tb->h_state = st;
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->state, tb->h_state, sizeof(TrainState), cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+static int state_array(neus2b_testbed* tb, int which, void** ptr, uint64_t* bytes) {
+	const uint64_t cells = (uint64_t)NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * tb->cfg.n_cascades;
+	switch (which) {
+		case NEUS2B_ARRAY_MASTER: *ptr = tb->master; *bytes = tb->n_params * 4; return NEUS2B_OK;
+		case NEUS2B_ARRAY_ADAM_M: *ptr = tb->adam_m; *bytes = tb->n_params * 4; return NEUS2B_OK;
+		case NEUS2B_ARRAY_ADAM_V: *ptr = tb->adam_v; *bytes = tb->n_params * 4; return NEUS2B_OK;
+		case NEUS2B_ARRAY_EMA_MASTER: *ptr = tb->ema_master; *bytes = tb->n_params * 4; return NEUS2B_OK;
+		case NEUS2B_ARRAY_PARAMS: *ptr = tb->params; *bytes = tb->n_params * 2; return NEUS2B_OK;
+		case NEUS2B_ARRAY_PARAMS_EMA: *ptr = tb->params_ema; *bytes = tb->n_params * 2; return NEUS2B_OK;
+		case NEUS2B_ARRAY_DENSITY_GRID: *ptr = tb->density_grid; *bytes = cells * 4; return NEUS2B_OK;
+		default: return NEUS2B_E_INVALID;
+	}
+}
+
+extern "C" int neus2b_testbed_get_array(neus2b_testbed* tb, int which, void* h_out, uint64_t bytes) {
+	if (!tb || !h_out) return NEUS2B_E_INVALID;
+	void* p = nullptr;
+	uint64_t n = 0;
+	int rc = state_array(tb, which, &p, &n);
+	if (rc) return rc;
+	if (bytes != n) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(h_out, p, n, cudaMemcpyDeviceToHost, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_set_array(neus2b_testbed* tb, int which, const void* h_in, uint64_t bytes) {
+	if (!tb || !h_in) return NEUS2B_E_INVALID;
+	void* p = nullptr;
+	uint64_t n = 0;
+	int rc = state_array(tb, which, &p, &n);
+	if (rc) return rc;
+	if (bytes != n) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(p, h_in, n, cudaMemcpyHostToDevice, tb->stream));
+	if (which == NEUS2B_ARRAY_DENSITY_GRID) {  // update_density_grid_mean_and_bitfield, as load_snapshot does (src/testbed.cu:3228-3230)
+		rc = neus2b_occupancy_mean_and_bitfield(tb->cfg.n_cascades, tb->density_grid, tb->bitfield, tb->density_mean, tb->occ_partial, tb->stream);
+		if (rc) return rc;
+		tb->occ_bounds_stale = true;
+	}
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+

@@ -128,6 +128,17 @@ class Testbed:
                                                 C.c_void_p(out.data_ptr())))
         return out
 
+    # --- snapshots
+    def save_snapshot(self, path, include_optimizer_state=False):
+        """``Testbed.save_snapshot`` (src/python_api.cu:347, src/testbed.cu:3134): msgpack file in the reference's layout."""
+        from . import snapshot
+        snapshot.save_snapshot(self, path, include_optimizer_state)
+
+    def load_snapshot(self, path):
+        """``Testbed.load_snapshot`` (src/testbed.cu:3187)."""
+        from . import snapshot
+        return snapshot.load_snapshot(self, path)
+
     # --- rendering
     @property
     def fov(self):

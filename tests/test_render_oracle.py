@@ -89,3 +89,16 @@ def test_accumulate_and_tonemap_identities(oracle):
     np.testing.assert_allclose(out[:, :3], acc[:, :3] * 2, rtol=1e-6)
     white = O.render_tonemap(np.zeros((3, 4), np.float32), 0.0, (1, 1, 1, 1), to_srgb=True)
     np.testing.assert_allclose(white, 1.0, rtol=1e-5)
+
+
+def test_snapshot_network_config_uses_reference_keys():
+    import ctypes as C
+    from neus2_b200 import _lib as L
+    from neus2_b200 import snapshot as SN
+    cfg = L.TestbedConfig()
+    L.lib().neus2b_testbed_default_config(C.byref(cfg))
+    doc = SN.network_config(cfg)
+    assert doc["encoding"]["otype"] == "HashGrid" and doc["encoding"]["n_levels"] == 16 and doc["encoding"]["log2_hashmap_size"] == 19
+    opt = doc["optimizer"]
+    assert opt["otype"] == "Ema" and opt["nested"]["otype"] == "ExponentialDecay" and opt["nested"]["nested"]["otype"] == "Adam"
+    assert abs(opt["nested"]["nested"]["learning_rate"] - 1e-2) < 1e-9
