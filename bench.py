@@ -143,8 +143,8 @@ def run_ours(args):
     from neus2_b200.parallel import DataParallelTrainer
     dp = DataParallelTrainer(tb, ng)
 
-    def step(read_stats=False):
-        return dp.step(read_stats=read_stats)
+    def step(read_stats=False, next_cameras=None):
+        return dp.step(read_stats=read_stats, next_cameras=next_cameras)
 
     def barrier():
         torch.cuda.synchronize()
@@ -184,9 +184,16 @@ def run_ours(args):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         tb.profile_train_kernel(nb)  # CUDA-event pairs around the fused forward+backward launch of these steps
         t0.record(stream)
-        for _ in range(nb):
+        if world > 1:
+            # data parallel: the camera block of the NEXT step is uploaded behind this step's backward pass, so that the
+            # samples drawn during the gradient exchange already use it (one upload per step, as on one GPU)
             tb.update_cameras(*cams)
-            st = step(read_stats=True)
+            for _ in range(nb):
+                st = step(read_stats=True, next_cameras=cams)
+        else:
+            for _ in range(nb):
+                tb.update_cameras(*cams)
+                st = step(read_stats=True)
         t1.record(stream)
         barrier()
         ms_e2e += t0.elapsed_time(t1)

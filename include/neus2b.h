@@ -308,6 +308,13 @@ int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_params, uint16_t
  * (NCCL) on the returned stream, then optimizer_step applies Adam.  neus2b_testbed_train == both halves back to back. */
 int neus2b_testbed_train_backward(neus2b_testbed* tb);
 int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats);
+/* Optional, between the two calls above: runs the pending step's batch tuner and draws the NEXT step's rays and samples
+ * already (they depend on the occupancy bits and the ray count, not on the parameters), so that this work overlaps the
+ * gradient all-reduce running on another stream.  Returns 1 without doing anything when the next step begins with an
+ * occupancy-grid update.  The next neus2b_testbed_train_backward then skips its sample generation; camera updates,
+ * state changes and handing out the bitfield's address discard the samples drawn ahead.  Results are those of the
+ * plain sequence. */
+int neus2b_testbed_train_pregenerate(neus2b_testbed* tb);
 /* Times the fused forward+backward kernel inside the step (the reference keeps a moving average of the whole step only,
  * m_training_ms, src/testbed.cu:2707-2721): arms CUDA-event pairs around that launch for the next max_steps steps on
  * the training stream (0 = off).  When h_ms_sum and h_n are given, first returns the sum of the durations recorded

@@ -118,6 +118,7 @@ struct neus2b_testbed {
 	// dataset
 	neus2b_dataset ds{};
 	float* h_cam = nullptr;  // pinned staging for the camera block
+	cudaEvent_t cam_event = nullptr;  // behind the last upload from h_cam
 	std::vector<void*> allocs;
 	// optional timing of the fused forward+backward kernel inside the step (event pairs on the training stream)
 	std::vector<cudaEvent_t> prof_events;
@@ -128,6 +129,8 @@ struct neus2b_testbed {
 	uint32_t render_pixels = 0;
 	neus2b_render_workspace render_ws{};
 	float *render_frame = nullptr, *render_depth = nullptr, *render_acc = nullptr, *render_out = nullptr;
+	bool tuned = false;         // the batch tuner already ran for the step whose optimizer pass is pending
+	bool pregenerated = false;  // the next step's samples are already in the ray workspace
 	uint64_t render_samples = 0;  // of the last call
 	float render_ms = 0.f;
 	cudaEvent_t render_ev[2] = {nullptr, nullptr};
@@ -190,6 +193,7 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	for (cudaEvent_t e : tb->prof_events) cudaEventDestroy(e);
 	for (cudaEvent_t e : tb->render_ev)
 		if (e) cudaEventDestroy(e);
+	if (tb->cam_event) cudaEventDestroy(tb->cam_event);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
 }
@@ -233,8 +237,8 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	TB_ALLOC(tb->ema_master, tb->n_params);
 	TB_ALLOC(tb->adam_m, tb->n_params);
 	TB_ALLOC(tb->adam_v, tb->n_params);
-	TB_ALLOC(tb->grad_mlp, (size_t)NEUS2B_MLP_N);
-	TB_ALLOC(tb->grad_var, (size_t)4);
+	TB_ALLOC(tb->grad_mlp, (size_t)NEUS2B_MLP_N + 4);  // the variance gradient sits right behind: one fp32 exchange for both
+	tb->grad_var = tb->grad_mlp + NEUS2B_MLP_N;
 	const size_t cells = (size_t)NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE;
 	const size_t n_occ = cells * cfg->n_cascades;
 	TB_ALLOC(tb->density_grid, n_occ);
@@ -290,11 +294,16 @@ extern "C" int neus2b_testbed_n_params(const neus2b_testbed* tb, uint64_t* n) {
 extern "C" int neus2b_testbed_update_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal) {
 	if (!tb || !tb->ds.n_images || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
 	const uint32_t n = tb->ds.n_images;
+	tb->pregenerated = false;  // samples drawn ahead used the previous cameras
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (!tb->cam_event) N2B_CHECK_CUDA(cudaEventCreateWithFlags(&tb->cam_event, cudaEventDisableTiming));
+	else N2B_CHECK_CUDA(cudaEventSynchronize(tb->cam_event));  // the previous upload may still be reading the staging buffer
 	memcpy(tb->h_cam, h_xforms, sizeof(float) * 12 * n);
 	memcpy(tb->h_cam + 12 * n, h_focal, sizeof(float) * 2 * n);
 	memcpy(tb->h_cam + 14 * n, h_principal, sizeof(float) * 2 * n);
 	// the three arrays are one allocation, in this order
 	N2B_CHECK_CUDA(cudaMemcpyAsync((void*)tb->ds.d_xforms, tb->h_cam, sizeof(float) * 16 * n, cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaEventRecord(tb->cam_event, tb->stream));
 	return NEUS2B_OK;
 }
 
@@ -356,6 +365,7 @@ extern "C" int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_param
 	if (d_bitfield) {
 		*d_bitfield = tb->bitfield;
 		tb->occ_bounds_stale = true;  // the caller may write it
+		tb->pregenerated = false;
 	}
 	if (d_density_grid) *d_density_grid = tb->density_grid;
 	if (stream) *stream = tb->stream;
@@ -415,12 +425,31 @@ static neus2b_train_cfg make_train_cfg(const neus2b_testbed* tb) {
 	return c;
 }
 
+static uint32_t occupancy_skip(uint32_t step) { return step / 16u < 1u ? 1u : (step / 16u > 16u ? 16u : step / 16u); }
+
+// The step's rays and samples (first half of train_nerf_step, src/testbed_nerf.cu:3782-3830).  Depends on the occupancy
+// bits, the batch tuner's ray count and the step's random stream, not on the parameters.
+static int generate_step_samples(neus2b_testbed* tb, const neus2b_train_cfg& tc, const neus2b_pcg32& rng) {
+	// one cascade: positions map straight to the finest level's cells, so rays that miss the box of occupied cells are
+	// not marched; the box is recomputed after every occupancy update (and after the bitfield's pointer was handed out)
+	tb->ws.d_occupied_bounds = nullptr;
+	if (tb->cfg.n_cascades == 1) {
+		if (tb->occ_bounds_stale) {
+			int rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, tb->stream);
+			if (rc) return rc;
+			tb->occ_bounds_stale = false;
+		}
+		tb->ws.d_occupied_bounds = tb->occ_bounds;
+	}
+	return neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, &tb->state->rays_per_batch, 0, rng, tb->bitfield, &tb->ws, tb->stream);
+}
+
 extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	int rc;
-	const uint32_t skip = tb->training_step / 16u < 1u ? 1u : (tb->training_step / 16u > 16u ? 16u : tb->training_step / 16u);
-	if (tb->training_step % skip == 0) {
+	if (tb->training_step % occupancy_skip(tb->training_step) == 0) {
+		if (tb->pregenerated) return NEUS2B_E_INVALID;  // (pregenerate refuses steps that start with an occupancy update)
 		rc = training_prep(tb);
 		if (rc) return rc;
 	}
@@ -428,19 +457,12 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	const neus2b_train_cfg tc = make_train_cfg(tb);
 	const neus2b_pcg32 rng{tb->rng.state, tb->rng.inc};
 	const uint32_t* d_n_rays = &tb->state->rays_per_batch;
-	// one cascade: positions map straight to the finest level's cells, so rays that miss the box of occupied cells are
-	// not marched; the box is recomputed after every occupancy update (and after the bitfield's pointer was handed out)
-	tb->ws.d_occupied_bounds = nullptr;
-	if (tb->cfg.n_cascades == 1) {
-		if (tb->occ_bounds_stale) {
-			rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, tb->stream);
-			if (rc) return rc;
-			tb->occ_bounds_stale = false;
-		}
-		tb->ws.d_occupied_bounds = tb->occ_bounds;
+	if (tb->pregenerated) {
+		tb->pregenerated = false;  // neus2b_testbed_train_pregenerate already drew this step's samples
+	} else {
+		rc = generate_step_samples(tb, tc, rng);
+		if (rc) return rc;
 	}
-	rc = neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->bitfield, &tb->ws, tb->stream);
-	if (rc) return rc;
 	rc = neus2b_neus_forward(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, tb->max_samples, tb->ws.d_counters + 4, tb->ws.d_coords,
 	                         (uint16_t*)tb->mlp_out, tb->stream);
 	if (rc) return rc;
@@ -457,6 +479,29 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 		tb->prof_used += 2;
 	}
 	tb->rng.advance(1ull << 32);  // m_rng.advance() (src/testbed_nerf.cu:3981)
+	return NEUS2B_OK;
+}
+
+// Between neus2b_testbed_train_backward and neus2b_testbed_train_optimizer_step: draws the NEXT step's rays and samples
+// now, so that this work overlaps a gradient exchange running on another stream (data-parallel training).  The batch
+// tuner of the pending step runs first (it reads the counters the generator is about to reuse).  Returns 1 and does
+// nothing when the next step starts with an occupancy-grid update, which needs the updated parameters first.
+extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
+	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
+	if (tb->pregenerated) return NEUS2B_OK;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	const uint32_t next = tb->training_step + 1;
+	if (next % occupancy_skip(next) == 0) return 1;
+	if (!tb->tuned) {
+		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
+		N2B_CHECK_LAUNCH();
+		tb->tuned = true;
+	}
+	const neus2b_train_cfg tc = make_train_cfg(tb);  // (nothing the generator reads depends on the step number)
+	const neus2b_pcg32 rng{tb->rng.state, tb->rng.inc};  // already advanced to the next step's stream
+	int rc = generate_step_samples(tb, tc, rng);
+	if (rc) return rc;
+	tb->pregenerated = true;
 	return NEUS2B_OK;
 }
 
@@ -504,8 +549,11 @@ extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_tr
 	int rc = neus2b_adam_step(&ac, tb->n_params, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->master, tb->adam_m, tb->adam_v,
 	                          (uint16_t*)tb->params, (uint16_t*)tb->params_ema, tb->ema_master, tb->stream);
 	if (rc) return rc;
-	tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
-	N2B_CHECK_LAUNCH();
+	if (!tb->tuned) {
+		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
+		N2B_CHECK_LAUNCH();
+	}
+	tb->tuned = false;
 	++tb->training_step;
 	if (h_stats) {
 		loss_reduce_kernel<<<1, 1024, 0, tb->stream>>>(tb->state, tb->loss, tb->ek_loss, tb->target);
@@ -701,6 +749,7 @@ extern "C" int neus2b_testbed_set_training_state(neus2b_testbed* tb, const neus2
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	tb->training_step = in->training_step;
+	tb->pregenerated = tb->tuned = false;
 	tb->ema_step = in->density_grid_ema_step;
 	tb->rng = Pcg32{in->rng.state, in->rng.inc};
 	tb->density_rng = Pcg32{in->density_rng.state, in->density_rng.inc};

@@ -44,22 +44,44 @@ def device_view(ptr, nbytes, dtype):
 
 def gradient_views(testbed, grid_n_params):
     p = testbed.device_ptrs()
+    if p["grad_variance"] == p["grad_mlp"] + 12288 * 4:  # adjacent: one fp32 collective for both
+        return [device_view(p["grad_grid"], grid_n_params * 2, torch.float16), device_view(p["grad_mlp"], 12288 * 4 + 16, torch.float32)]
     return [device_view(p["grad_grid"], grid_n_params * 2, torch.float16), device_view(p["grad_mlp"], 12288 * 4, torch.float32),
             device_view(p["grad_variance"], 16, torch.float32)]
 
 
 class DataParallelTrainer:
-    """Drives one testbed per process; `step()` = local backward, gradient all-reduce, optimizer."""
+    """Drives one testbed per process; `step()` = local backward, gradient all-reduce, optimizer.  With `overlap` the next
+    step's sample generation runs while the gradients are exchanged."""
 
-    def __init__(self, testbed, grid_n_params):
+    def __init__(self, testbed, grid_n_params, overlap=True):
         self.tb = testbed
+        self.overlap = overlap
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.grads = gradient_views(testbed, grid_n_params) if self.world > 1 else None
         self.stream = torch.cuda.ExternalStream(testbed.device_ptrs()["stream"])
 
-    def step(self, read_stats=False):
+    def step(self, read_stats=False, next_cameras=None):
+        """`next_cameras` = (xforms, focal, principal) host arrays for the step AFTER this one: uploaded behind this step's
+        backward pass so that the samples drawn ahead already use them."""
         if self.world == 1:
-            return self.tb.train(1, read_stats=read_stats)
+            st = self.tb.train(1, read_stats=read_stats)
+            if next_cameras is not None:
+                self.tb.update_cameras(*next_cameras)
+            return st
         self.tb.train_backward()
-        allreduce_gradients(self.grads, stream=self.stream)
+        if not self.overlap:
+            allreduce_gradients(self.grads, stream=self.stream)
+            if next_cameras is not None:
+                self.tb.update_cameras(*next_cameras)
+            return self.tb.optimizer_step(read_stats=read_stats)
+        # the collectives start behind the backward kernels on NCCL's own stream; the training stream meanwhile draws the
+        # next step's samples and only then waits for the summed gradients
+        with torch.cuda.stream(self.stream):
+            works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
+            if next_cameras is not None:
+                self.tb.update_cameras(*next_cameras)
+            self.tb.train_pregenerate()
+            for w in works:
+                w.wait()
         return self.tb.optimizer_step(read_stats=read_stats)

@@ -93,6 +93,14 @@ class Testbed:
     def train_backward(self):
         L.check(L.lib().neus2b_testbed_train_backward(self._h))
 
+    def train_pregenerate(self):
+        """Draws the next step's samples between train_backward and optimizer_step; False if the next step starts with an
+        occupancy update and nothing was done."""
+        rc = L.lib().neus2b_testbed_train_pregenerate(self._h)
+        if rc not in (0, 1):
+            L.check(rc)
+        return rc == 0
+
     def optimizer_step(self, read_stats=True):
         L.check(L.lib().neus2b_testbed_train_optimizer_step(self._h, C.byref(self.stats) if read_stats else None))
         return self.stats

@@ -100,3 +100,46 @@ def test_refuses_other_architectures_and_files(trained_pair, tmp_path):
     with pytest.raises(ValueError, match="does not contain a snapshot"):
         b.load_snapshot(tmp_path / "nosnap.msgpack")
     b.close()
+
+
+def test_pregenerated_samples_equal_the_plain_sequence(tmp_path):
+    """Drawing the next step's samples between backward and optimizer pass (what data-parallel training overlaps with the
+    gradient exchange) leaves the step unchanged: from one saved state, the plain and the reordered sequence generate the
+    same rays and samples."""
+    a = make()
+    a.train(42)
+    a.save_snapshot(tmp_path / "s.msgpack", include_optimizer_state=True)
+    a.close()
+
+    def run(reordered):
+        tb = make()
+        tb.load_snapshot(tmp_path / "s.msgpack")
+        drew = []
+        for _ in range(3):  # steps 42, 43, 44: step 44 starts with an occupancy update, 43 does not
+            tb.train_backward()
+            if reordered:
+                drew.append(tb.train_pregenerate())
+            st = tb.optimizer_step()
+            out = (st.training_step, st.rays_per_batch, st.n_rays_kept, st.measured_batch_size_before_compaction,
+                   st.measured_batch_size, st.loss)
+            if st.training_step == 44:
+                keep = out
+        tb.close()
+        return keep, drew
+    plain, _ = run(False)
+    ahead, drew = run(True)
+    assert drew == [True, False, True]
+    # ray count, kept rays and generated samples of step 43 do not depend on the (non-deterministic) gradient sums
+    assert plain[:4] == ahead[:4]
+    assert abs(plain[4] - ahead[4]) <= 0.01 * plain[4] and abs(plain[5] - ahead[5]) <= 0.2 * plain[5]
+    # a camera update discards samples drawn ahead
+    tb = make()
+    tb.load_snapshot(tmp_path / "s.msgpack")
+    tb.train_backward()
+    assert tb.train_pregenerate()
+    tb.update_cameras()
+    st = tb.optimizer_step()
+    tb.train_backward()
+    st2 = tb.optimizer_step()
+    assert st2.training_step == 44 and (st2.rays_per_batch, st2.n_rays_kept, st2.measured_batch_size_before_compaction) == plain[1:4]
+    tb.close()
