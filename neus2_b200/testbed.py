@@ -59,6 +59,23 @@ class Testbed:
                                                           pixels.ctypes.data_as(C.c_void_p),
                                                           *[a.ctypes.data_as(C.c_void_p) for a in self._cams]))
 
+    def load_training_data_from_json(self, json_paths):
+        """``Testbed.load_training_data(path)`` for a transforms file of a static scene (src/testbed.cu:155, src/nerf_loader.cu:197):
+        images and cameras through ``neus2_b200.loader``.  Returns the loaded dataset description."""
+        from . import loader
+        ds = loader.load_nerf_dataset(json_paths)
+        if ds["aabb_scale"] != 1 << (int(self.config.n_cascades) - 1):
+            raise ValueError(f"the dataset's aabb_scale {ds['aabb_scale']} needs n_cascades = {int(ds['aabb_scale']).bit_length()}")
+        self.dataset = ds
+        self.load_training_data(ds["pixels"], ds["xforms"], ds["focal"], ds["principal"])
+        return ds
+
+    def set_nerf_camera_matrix(self, nerf_matrix):
+        """``Testbed.set_nerf_camera_matrix`` (src/python_api.cu:430): a camera in the dataset's own convention."""
+        from . import loader
+        ds = getattr(self, "dataset", None) or dict(scale=loader.NERF_SCALE, offset=[0.5, 0.5, 0.5], from_na=False, from_mitsuba=False)
+        self.camera_matrix = loader.nerf_matrix_to_ngp(nerf_matrix, ds["scale"], ds["offset"], ds["from_na"], ds["from_mitsuba"])
+
     def update_cameras(self, xforms=None, focal=None, principal=None):
         cams = [np.ascontiguousarray(a, dtype=np.float32) if a is not None else b
                 for a, b in zip((xforms, focal, principal), self._cams)]
