@@ -184,16 +184,12 @@ def run_ours(args):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         tb.profile_train_kernel(nb)  # CUDA-event pairs around the fused forward+backward launch of these steps
         t0.record(stream)
-        if world > 1:
-            # data parallel: the camera block of the NEXT step is uploaded behind this step's backward pass, so that the
-            # samples drawn during the gradient exchange already use it (one upload per step, as on one GPU)
-            tb.update_cameras(*cams)
-            for _ in range(nb):
-                st = step(read_stats=True, next_cameras=cams)
-        else:
-            for _ in range(nb):
-                tb.update_cameras(*cams)
-                st = step(read_stats=True)
+        # one camera upload and one statistics read-back per step; the camera block of the NEXT step is uploaded behind this
+        # step's backward pass, so that the samples drawn ahead (during the gradient exchange on several GPUs, during the
+        # host's wait for the statistics on one) already use it
+        tb.update_cameras(*cams)
+        for _ in range(nb):
+            st = step(read_stats=True, next_cameras=cams)
         t1.record(stream)
         barrier()
         ms_e2e += t0.elapsed_time(t1)

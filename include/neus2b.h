@@ -310,11 +310,24 @@ int neus2b_testbed_train_backward(neus2b_testbed* tb);
 int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats);
 /* Optional, between the two calls above: runs the pending step's batch tuner and draws the NEXT step's rays and samples
  * already (they depend on the occupancy bits and the ray count, not on the parameters), so that this work overlaps the
- * gradient all-reduce running on another stream.  Returns 1 without doing anything when the next step begins with an
+ * gradient all-reduce running on another stream (it may also be called after the optimizer step, before the next
+ * neus2b_testbed_train_backward).  Returns 1 without doing anything when the next step begins with an
  * occupancy-grid update.  The next neus2b_testbed_train_backward then skips its sample generation; camera updates,
  * state changes and handing out the bitfield's address discard the samples drawn ahead.  Results are those of the
  * plain sequence. */
 int neus2b_testbed_train_pregenerate(neus2b_testbed* tb);
+/* neus2b_testbed_train_optimizer_step in two halves, for hosts that want the step's statistics every step without
+ * leaving the GPU idle while they wait: _async enqueues the optimizer pass, the batch tuner, the loss reduction and the
+ * copy of the statistics to the host and returns; the host can then enqueue more work (the next step's camera upload and
+ * neus2b_testbed_train_pregenerate, which may also follow the optimizer pass) before _wait_stats blocks on an event
+ * behind that copy only, not on the stream. */
+int neus2b_testbed_train_optimizer_step_async(neus2b_testbed* tb);
+int neus2b_testbed_train_wait_stats(neus2b_testbed* tb, neus2b_train_stats* h_stats);
+/* One training step through those halves in one call: backward, optimizer pass and statistics copy enqueued, the NEXT
+ * step's cameras uploaded (optional: three host arrays as in neus2b_testbed_update_cameras, or NULLs), the next step's
+ * samples drawn, then the wait for this step's statistics (h_stats may be NULL: nothing is waited for). */
+int neus2b_testbed_train_step(neus2b_testbed* tb, const float* h_next_xforms, const float* h_next_focal, const float* h_next_principal,
+                              neus2b_train_stats* h_stats);
 /* Times the fused forward+backward kernel inside the step (the reference keeps a moving average of the whole step only,
  * m_training_ms, src/testbed.cu:2707-2721): arms CUDA-event pairs around that launch for the next max_steps steps on
  * the training stream (0 = off).  When h_ms_sum and h_n are given, first returns the sum of the durations recorded

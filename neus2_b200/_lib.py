@@ -105,7 +105,7 @@ EXPORTS = [
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_occupancy_bounds", "neus2b_adam_step", "neus2b_adam_step_packed",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
-    "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward", "neus2b_testbed_train_pregenerate",
+    "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward", "neus2b_testbed_train_pregenerate", "neus2b_testbed_train_optimizer_step_async", "neus2b_testbed_train_wait_stats", "neus2b_testbed_train_step",
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
     "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
     "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh", "neus2b_occupancy_mean_and_bitfield",

@@ -129,6 +129,9 @@ struct neus2b_testbed {
 	uint32_t render_pixels = 0;
 	neus2b_render_workspace render_ws{};
 	float *render_frame = nullptr, *render_depth = nullptr, *render_acc = nullptr, *render_out = nullptr;
+	bool step_pending = false;  // between a step's backward pass and its optimizer pass
+	cudaEvent_t stats_event = nullptr;  // behind the last copy of the step statistics to the host
+	uint32_t stats_step = 0;
 	bool tuned = false;         // the batch tuner already ran for the step whose optimizer pass is pending
 	bool pregenerated = false;  // the next step's samples are already in the ray workspace
 	uint64_t render_samples = 0;  // of the last call
@@ -194,6 +197,7 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	for (cudaEvent_t e : tb->render_ev)
 		if (e) cudaEventDestroy(e);
 	if (tb->cam_event) cudaEventDestroy(tb->cam_event);
+	if (tb->stats_event) cudaEventDestroy(tb->stats_event);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
 }
@@ -479,6 +483,7 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 		tb->prof_used += 2;
 	}
 	tb->rng.advance(1ull << 32);  // m_rng.advance() (src/testbed_nerf.cu:3981)
+	tb->step_pending = true;
 	return NEUS2B_OK;
 }
 
@@ -490,9 +495,9 @@ extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
 	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
 	if (tb->pregenerated) return NEUS2B_OK;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
-	const uint32_t next = tb->training_step + 1;
+	const uint32_t next = tb->training_step + (tb->step_pending ? 1u : 0u);
 	if (next % occupancy_skip(next) == 0) return 1;
-	if (!tb->tuned) {
+	if (tb->step_pending && !tb->tuned) {
 		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
 		N2B_CHECK_LAUNCH();
 		tb->tuned = true;
@@ -529,8 +534,7 @@ extern "C" int neus2b_testbed_profile(neus2b_testbed* tb, uint32_t max_steps, fl
 	return NEUS2B_OK;
 }
 
-extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats) {
-	if (!tb) return NEUS2B_E_INVALID;
+static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	const neus2b_testbed_config& c = tb->cfg;
 	neus2b_adam_cfg ac{};
@@ -554,22 +558,60 @@ extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_tr
 		N2B_CHECK_LAUNCH();
 	}
 	tb->tuned = false;
+	tb->step_pending = false;
 	++tb->training_step;
-	if (h_stats) {
+	if (want_stats) {
 		loss_reduce_kernel<<<1, 1024, 0, tb->stream>>>(tb->state, tb->loss, tb->ek_loss, tb->target);
 		N2B_CHECK_LAUNCH();
 		N2B_CHECK_CUDA(cudaMemcpyAsync(tb->h_state, tb->state, sizeof(TrainState), cudaMemcpyDeviceToHost, tb->stream));
-		N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
-		h_stats->training_step = tb->training_step;
-		h_stats->rays_per_batch = tb->h_state->rays_per_batch;
-		h_stats->n_rays_kept = tb->h_state->n_kept;
-		h_stats->measured_batch_size_before_compaction = tb->h_state->measured_pre;
-		h_stats->measured_batch_size = tb->h_state->measured;
-		h_stats->overflow = tb->h_state->overflow;
-		h_stats->loss = tb->h_state->loss;
-		h_stats->ek_loss = tb->h_state->ek_loss;
+		if (!tb->stats_event) N2B_CHECK_CUDA(cudaEventCreateWithFlags(&tb->stats_event, cudaEventDisableTiming));
+		N2B_CHECK_CUDA(cudaEventRecord(tb->stats_event, tb->stream));
+		tb->stats_step = tb->training_step;
 	}
 	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_train_wait_stats(neus2b_testbed* tb, neus2b_train_stats* h_stats) {
+	if (!tb || !h_stats || !tb->stats_event) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaEventSynchronize(tb->stats_event));
+	h_stats->training_step = tb->stats_step;
+	h_stats->rays_per_batch = tb->h_state->rays_per_batch;
+	h_stats->n_rays_kept = tb->h_state->n_kept;
+	h_stats->measured_batch_size_before_compaction = tb->h_state->measured_pre;
+	h_stats->measured_batch_size = tb->h_state->measured;
+	h_stats->overflow = tb->h_state->overflow;
+	h_stats->loss = tb->h_state->loss;
+	h_stats->ek_loss = tb->h_state->ek_loss;
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats) {
+	if (!tb) return NEUS2B_E_INVALID;
+	const int rc = optimizer_enqueue(tb, h_stats != nullptr);
+	if (rc || !h_stats) return rc;
+	return neus2b_testbed_train_wait_stats(tb, h_stats);
+}
+
+extern "C" int neus2b_testbed_train_optimizer_step_async(neus2b_testbed* tb) {
+	if (!tb) return NEUS2B_E_INVALID;
+	return optimizer_enqueue(tb, true);
+}
+
+extern "C" int neus2b_testbed_train_step(neus2b_testbed* tb, const float* h_next_xforms, const float* h_next_focal,
+                                         const float* h_next_principal, neus2b_train_stats* h_stats) {
+	if (!tb) return NEUS2B_E_INVALID;
+	int rc = neus2b_testbed_train_backward(tb);
+	if (rc) return rc;
+	rc = optimizer_enqueue(tb, h_stats != nullptr);
+	if (rc) return rc;
+	if (h_next_xforms && h_next_focal && h_next_principal) {
+		rc = neus2b_testbed_update_cameras(tb, h_next_xforms, h_next_focal, h_next_principal);
+		if (rc) return rc;
+	}
+	rc = neus2b_testbed_train_pregenerate(tb);
+	if (rc != NEUS2B_OK && rc != 1) return rc;
+	return h_stats ? neus2b_testbed_train_wait_stats(tb, h_stats) : NEUS2B_OK;
 }
 
 extern "C" int neus2b_testbed_train(neus2b_testbed* tb, uint32_t n_steps, neus2b_train_stats* h_stats) {

@@ -65,10 +65,14 @@ class DataParallelTrainer:
         """`next_cameras` = (xforms, focal, principal) host arrays for the step AFTER this one: uploaded behind this step's
         backward pass so that the samples drawn ahead already use them."""
         if self.world == 1:
-            st = self.tb.train(1, read_stats=read_stats)
-            if next_cameras is not None:
-                self.tb.update_cameras(*next_cameras)
-            return st
+            if not self.overlap:
+                st = self.tb.train(1, read_stats=read_stats)
+                if next_cameras is not None:
+                    self.tb.update_cameras(*next_cameras)
+                return st
+            # the next step's camera upload and sample generation are enqueued before the host waits for this step's
+            # statistics, so the GPU has work while the host wakes up and issues the next launches
+            return self.tb.train_step(next_cameras, read_stats=read_stats)
         self.tb.train_backward()
         if not self.overlap:
             allreduce_gradients(self.grads, stream=self.stream)

@@ -118,6 +118,22 @@ class Testbed:
             L.check(rc)
         return rc == 0
 
+    def train_step(self, next_cameras=None, read_stats=True):
+        """One step with the next step's cameras (three float32 arrays, already contiguous) uploaded and its samples drawn
+        before the host waits for this step's statistics."""
+        keep = [np.ascontiguousarray(a, dtype=np.float32) for a in next_cameras] if next_cameras is not None else None
+        cams = [a.ctypes.data_as(C.c_void_p) for a in keep] if keep else [None, None, None]
+        L.check(L.lib().neus2b_testbed_train_step(self._h, *cams, C.byref(self.stats) if read_stats else None))
+        return self.stats
+
+    def optimizer_step_async(self):
+        """Enqueues the optimizer pass and the copy of the step statistics; `wait_stats` returns them."""
+        L.check(L.lib().neus2b_testbed_train_optimizer_step_async(self._h))
+
+    def wait_stats(self):
+        L.check(L.lib().neus2b_testbed_train_wait_stats(self._h, C.byref(self.stats)))
+        return self.stats
+
     def optimizer_step(self, read_stats=True):
         L.check(L.lib().neus2b_testbed_train_optimizer_step(self._h, C.byref(self.stats) if read_stats else None))
         return self.stats

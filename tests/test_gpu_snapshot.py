@@ -117,21 +117,28 @@ def test_pregenerated_samples_equal_the_plain_sequence(tmp_path):
         drew = []
         for _ in range(3):  # steps 42, 43, 44: step 44 starts with an occupancy update, 43 does not
             tb.train_backward()
-            if reordered:
+            if reordered == "between":
                 drew.append(tb.train_pregenerate())
-            st = tb.optimizer_step()
+                st = tb.optimizer_step()
+            elif reordered == "after":  # optimizer pass enqueued, next samples drawn, only then the host waits for the statistics
+                tb.optimizer_step_async()
+                drew.append(tb.train_pregenerate())
+                st = tb.wait_stats()
+            else:
+                st = tb.optimizer_step()
             out = (st.training_step, st.rays_per_batch, st.n_rays_kept, st.measured_batch_size_before_compaction,
                    st.measured_batch_size, st.loss)
             if st.training_step == 44:
                 keep = out
         tb.close()
         return keep, drew
-    plain, _ = run(False)
-    ahead, drew = run(True)
-    assert drew == [True, False, True]
-    # ray count, kept rays and generated samples of step 43 do not depend on the (non-deterministic) gradient sums
-    assert plain[:4] == ahead[:4]
-    assert abs(plain[4] - ahead[4]) <= 0.01 * plain[4] and abs(plain[5] - ahead[5]) <= 0.2 * plain[5]
+    plain, _ = run(None)
+    for mode in ("between", "after"):
+        ahead, drew = run(mode)
+        assert drew == [True, False, True]
+        # ray count, kept rays and generated samples of step 43 do not depend on the (non-deterministic) gradient sums
+        assert plain[:4] == ahead[:4], mode
+        assert abs(plain[4] - ahead[4]) <= 0.01 * plain[4] and abs(plain[5] - ahead[5]) <= 0.2 * plain[5]
     # a camera update discards samples drawn ahead
     tb = make()
     tb.load_snapshot(tmp_path / "s.msgpack")
