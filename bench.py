@@ -357,6 +357,40 @@ def run_kernel_only(args):
         print(json.dumps({"kernel": "mesh", "res": res, "runs": out}))
         tb.close()
         return
+    if args.kernel == "config2":
+        # BASELINE config 2 stand-in: torus + rounded box, 49 views at 1600x1200, batch 2^19, progressive levels (8 + 2 per 500
+        # steps); device time per step over --steps steps after --pretrain steps, then the mesh against the analytic surface
+        from neus2_b200.testbed import Testbed
+        scene = S.render_csg_views(49, 1600, 1200, device="cuda", seed=0)
+        tb = Testbed(batch_size=1 << 19, progressive_start_levels=8, progressive_levels_per_increment=2, progressive_steps_per_increment=500,
+                     **({"learning_rate": args.lr} if args.lr else {}))
+        tb.load_training_data(scene["pixels"].cpu().numpy(), *[scene[k].cpu().numpy() for k in ("xforms", "focal", "principal")])
+        del scene
+        tb.set_params(S.init_params(ng, seed=1337))
+        stream = torch.cuda.ExternalStream(tb.device_ptrs()["stream"])
+        runs = []
+        for block in range(args.kernel_iters):
+            tb.train(args.pretrain, read_stats=False)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            tb.train(args.steps, read_stats=False)
+            e1.record(stream)
+            st = tb.train(1)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            runs.append({"training_step": int(st.training_step), "ms_per_step": ms, "samples_per_s": (1 << 19) / (ms * 1e-3),
+                         "rays_per_batch": int(st.rays_per_batch), "samples_before_compaction": int(st.measured_batch_size_before_compaction),
+                         "samples_after_compaction": int(st.measured_batch_size), "loss": float(st.loss), "ek_loss": float(st.ek_loss),
+                         "overflow": int(st.overflow)})
+        v, i = tb.compute_marching_cubes_mesh(256)
+        err = S.csg_sdf(v).abs()
+        seen = v[:, 2] > 0.5  # the cameras sit on a cap above the object: its underside is never observed
+        print(json.dumps({"kernel": "config2", "runs": runs, "mesh": {"res": 256, "verts": int(v.shape[0]), "triangles": int(i.shape[0]) // 3,
+                                                                        "mean_abs_sdf": float(err.mean()), "p99_abs_sdf": float(err.quantile(0.99)),
+                                                                        "upper_half_mean_abs_sdf": float(err[seen].mean()),
+                                                                        "upper_half_p99_abs_sdf": float(err[seen].quantile(0.99))}}))
+        tb.close()
+        return
     if args.kernel == "render":
         # one frame of Testbed.render (1 sample per pixel) of the briefly trained config-1 scene, host image out
         import time
@@ -534,7 +568,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render", "config2"], help="run one fused kernel alone (profiling)")
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
     ap.add_argument("--mesh-res", type=int, default=512)

@@ -100,6 +100,82 @@ def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=
     return dict(pixels=pixels, xforms=xforms, focal=focal, principal=principal, width=width, height=height)
 
 
+def csg_sdf(p, center=(0.5, 0.5, 0.5)):
+    """Signed distance of the union of a torus (R 0.25, r 0.08, axis z) and a rounded box (half-extent 0.15, corner radius
+    0.02), both centred in the unit cube; p is [n][3] (torch)."""
+    q = p - torch.tensor(center, device=p.device, dtype=p.dtype)
+    ring = torch.sqrt(q[:, 0] ** 2 + q[:, 1] ** 2) - 0.25
+    torus = torch.sqrt(ring ** 2 + q[:, 2] ** 2) - 0.08
+    d = q.abs() - (0.15 - 0.02)
+    box = d.clamp_min(0).norm(dim=1) + d.max(dim=1).values.clamp_max(0) - 0.02
+    return torch.minimum(torus, box)
+
+
+def cap_cameras(n_views, radius=2.5, cap_deg=60.0, center=(0.5, 0.5, 0.5)):
+    """[n][12] camera-to-world matrices on a spherical cap of half-angle cap_deg around +z, looking at the centre."""
+    out = np.zeros((n_views, 12), np.float32)
+    golden = math.pi * (3.0 - math.sqrt(5.0))
+    c = np.asarray(center, np.float64)
+    zmin = math.cos(math.radians(cap_deg))
+    for i in range(n_views):
+        z = 1.0 - (1.0 - zmin) * (i + 0.5) / n_views
+        r = math.sqrt(max(0.0, 1.0 - z * z))
+        th = golden * i
+        n = np.array([r * math.cos(th), r * math.sin(th), z])
+        fwd = -n
+        up = np.array([0.0, 0.0, 1.0]) if abs(n[2]) < 0.99 else np.array([0.0, 1.0, 0.0])
+        right = np.cross(fwd, up)
+        right /= np.linalg.norm(right)
+        down = np.cross(fwd, right)
+        out[i, 0:3], out[i, 3:6], out[i, 6:9], out[i, 9:12] = right, down, fwd, c + radius * n
+    return out
+
+
+def render_csg_views(n_views=49, width=1600, height=1200, fov_deg=30.0, seed=0, device="cpu", cam_radius=2.5, chunk=1 << 21):
+    """The DTU-shaped stand-in scene: torus + rounded box (csg_sdf) with a checker / value-noise albedo, sphere-traced from
+    cameras on a 60-degree cap.  Same dict as render_sphere_views."""
+    xforms = torch.from_numpy(cap_cameras(n_views, cam_radius)).to(device)
+    focal_px = 0.5 * width / math.tan(0.5 * math.radians(fov_deg))
+    focal = torch.full((n_views, 2), focal_px, dtype=torch.float32, device=device)
+    principal = torch.full((n_views, 2), 0.5, dtype=torch.float32, device=device)
+    ys, xs = torch.meshgrid(torch.arange(height, device=device), torch.arange(width, device=device), indexing="ij")
+    u = ((xs.float() + 0.5) / width).reshape(-1)
+    v = ((ys.float() + 0.5) / height).reshape(-1)
+    dl = torch.stack([(u - 0.5) * width / focal_px, (v - 0.5) * height / focal_px, torch.ones_like(u)], 1)
+    light = torch.tensor([0.4, -0.5, 0.77], device=device)
+    light = light / light.norm()
+    pixels = torch.zeros((n_views, height * width), dtype=torch.int32, device=device)
+    eps = 1e-3
+    for i in range(n_views):
+        X = xforms[i]
+        R = torch.stack([X[0:3], X[3:6], X[6:9]], 1)
+        o = X[9:12]
+        for c0 in range(0, height * width, chunk):
+            d = dl[c0:c0 + chunk] @ R.T
+            d = d / d.norm(dim=1, keepdim=True)
+            t = torch.full((d.shape[0],), cam_radius - 0.75, device=device)
+            for _ in range(96):  # sphere tracing
+                t = t + csg_sdf(o + t[:, None] * d)
+                t = t.clamp_max(cam_radius + 0.75)
+            p = o + t[:, None] * d
+            hit = csg_sdf(p).abs() < 2e-4
+            g = torch.stack([csg_sdf(p + torch.tensor(e, device=device)) - csg_sdf(p - torch.tensor(e, device=device))
+                             for e in ((eps, 0, 0), (0, eps, 0), (0, 0, eps))], 1)
+            nrm = g / g.norm(dim=1, keepdim=True).clamp_min(1e-12)
+            pc = p.clamp(0, 1)
+            checker = ((torch.floor(pc[:, 0] * 8) + torch.floor(pc[:, 1] * 8) + torch.floor(pc[:, 2] * 8)) % 2)[:, None]
+            albedo = (0.15 + 0.8 * _value_noise(pc, seed)) * (0.6 + 0.4 * checker)
+            shade = 0.3 + 0.7 * (nrm @ light).clamp_min(0)
+            col = _linear_to_srgb((albedo * shade[:, None]).clamp(0, 1))
+            rgb8 = (col * 255.0 + 0.5).clamp(0, 255).to(torch.int64)
+            rgb8 = torch.where(hit[:, None], rgb8, torch.zeros_like(rgb8))
+            a8 = torch.where(hit, 255, 0).to(torch.int64)
+            packed = rgb8[:, 0] | (rgb8[:, 1] << 8) | (rgb8[:, 2] << 16) | (a8 << 24)
+            packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed)
+            pixels[i, c0:c0 + chunk] = packed.to(torch.int32)
+    return dict(pixels=pixels.reshape(n_views, height, width), xforms=xforms, focal=focal, principal=principal, width=width, height=height)
+
+
 def geometric_init_sdf_weights(seed=7, in_width=48, bias_radius=None):
     """Sphere-like initialisation of the one-hidden-layer SDF net (the role utils/mlp_weights.txt plays in the
     reference, nerf_network.h:774-823): first layer ~ N(0, sqrt(2)/sqrt(64)) on the xyz columns only, last layer
