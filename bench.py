@@ -335,8 +335,31 @@ def run_kernel_only(args):
         import time
         from neus2_b200.testbed import Testbed
         res = args.mesh_res
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
         tb = Testbed(batch_size=1 << 18)
         tb.set_params(S.init_params(ng, seed=1337))  # geometric initialisation: a sphere-like SDF
+        if world > 1:
+            # sharded by z-slab: every rank evaluates its layers and runs marching cubes on them, the parts are gathered
+            # (pickled host arrays over the process group) and merged on the host; time = the slowest rank
+            rank = int(os.environ.get("RANK", "0"))
+            out = []
+            for it in range(args.kernel_iters):
+                dist.barrier()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                v, i = tb.compute_marching_cubes_mesh_sharded(res, rank, world, use_ema=False)
+                t = torch.tensor([time.perf_counter() - t0], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                out.append({"wall_s": float(t.item()), "verts": int(len(v)), "triangles": int(len(i)) // 3})
+            if rank == 0:
+                print(json.dumps({"kernel": "mesh", "res": res, "n_gpus": world, "sharded_by": "z-slab", "runs": out}))
+            tb.close()
+            dist.destroy_process_group()
+            return
         e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         stream = torch.cuda.ExternalStream(tb.device_ptrs()["stream"])
         out = []
