@@ -9,7 +9,7 @@ _METRICS = {}
 
 
 def record(name, **kw):
-    """Keeps the measured errors of the GPU parity tests next to the run (gpurun_out/parity_metrics.json)."""
+    """Keeps the measured errors of the GPU parity tests next to the run (parity_metrics.json in the run's output folder)."""
     out = os.path.join(ROOT, "gpurun_out")
     path = os.path.join(out, "parity_metrics.json")
     if not _METRICS and os.path.exists(path):
