@@ -29,6 +29,8 @@ typedef struct CUstream_st* neus2b_stream_t;
 #define NEUS2B_E_OVERFLOW (-4)    /* a device-side capacity was exceeded (flag read back by the caller) */
 #define NEUS2B_E_TOO_LARGE (-5)   /* request beyond a fixed compiled-in capacity */
 #define NEUS2B_E_IO (-6)          /* a file could not be opened or written */
+#define NEUS2B_E_DEVICE (-7)      /* a kernel raised the sticky device error flag (neus2b_device_error_flags) */
+#define NEUS2B_E_TIMEOUT (-8)     /* a bounded wait on the host ran out */
 
 #define NEUS2B_MAX_LEVELS 16
 #define NEUS2B_GRIDSIZE 128u /* NERF_GRIDSIZE  include/neural-graphics-primitives/nerf.h:24 */
@@ -118,6 +120,9 @@ int neus2b_set_mma_path(int path);
 int neus2b_get_mma_path(void);
 /* Sticky device-side error bits (bit 0: a bounded completion wait inside a tcgen05 kernel ran out). Synchronises. */
 int neus2b_device_error_flags(uint32_t* h_flags);
+/* Overwrites the sticky bits (0 clears them).  For hosts that recovered from an error, and for tests of the error path:
+ * the training loop reports NEUS2B_E_DEVICE from its statistics call while a bit is set. */
+int neus2b_set_device_error_flags(uint32_t flags);
 
 /* NerfNetwork::inference_mixed_precision == forward_impl (nerf_network.h:87-90,132-315), static scene.
  * d_coords [n][7] fp32 (xyz, dt, dir in [0,1]); d_out [n][16] fp16 rows: 0-2 raw rgb, 3 sdf+bias, 4-6 normal,
@@ -163,7 +168,9 @@ typedef struct {
 	uint32_t ray_index_offset, ray_count_scale;
 } neus2b_train_cfg;
 
-/* Scratch for one batch of rays; every array is caller-allocated device memory. */
+/* Scratch for one batch of rays; every array is caller-allocated device memory.  One call handles at most
+ * NEUS2B_MAX_RAYS_PER_CALL rays (the capacity of the ray-order prefix sum); more returns NEUS2B_E_TOO_LARGE. */
+#define NEUS2B_MAX_RAYS_PER_CALL (1u << 20)
 typedef struct {
 	uint32_t max_rays, max_samples;
 	uint32_t* d_ray_indices; /* [max_rays] */
@@ -227,10 +234,21 @@ int neus2b_occupancy_mean_and_bitfield(uint32_t n_cascades, const float* d_grid,
                                        neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- optimizer (Trainer::optimizer_step, src/testbed_nerf.cu:3498) */
+/* What the optimizer does where the un-vendored tiny-cuda-nn fork cannot be read; 0 = the default behaviour of this
+ * library (Adam of the public tiny-cuda-nn: weight decay on the matrix weights only, entries without a gradient left
+ * alone, bias-corrected EMA).  The flags exist so that each choice can be switched on its own. */
+#define NEUS2B_ADAM_UPDATE_UNTOUCHED 1u /* also update non-matrix entries whose gradient is exactly zero (moments decay) */
+#define NEUS2B_ADAM_L2_ALL 2u           /* weight decay on every parameter, not only the matrix weights */
+#define NEUS2B_ADAM_EMA_NO_DEBIAS 4u    /* plain EMA ema = d * ema + (1 - d) * w, without the 1 / (1 - d^t) correction */
 typedef struct {
 	float learning_rate, beta1, beta2, epsilon, l2_reg, ema_decay, loss_scale;
 	uint32_t step;     /* 1-based */
 	uint32_t n_matrix; /* leading MLP-weight entries */
+	uint32_t flags;    /* NEUS2B_ADAM_* */
+	/* optional device counter: a gradient that is NaN or infinite (an overflowed fp16 sum, a poisoned exchange buffer) is
+	 * treated as absent -- that parameter keeps its weight and moments this step, the gradient slot is cleared -- and the
+	 * number of such entries is added here, so that one bad value cannot reach the fp32 master weights unnoticed */
+	uint32_t* d_nonfinite;
 } neus2b_adam_cfg;
 /* Ema o ExponentialDecay o Adam (configs/nerf/dtu.json:5-27) over the flat parameter block.  Gradients: d_grad_mlp fp32
  * for [0, n_matrix), d_grad_grid fp16 for [n_matrix, n - 4), d_grad_variance fp32 for the last 4; all are zeroed after
@@ -265,7 +283,22 @@ typedef struct {
 	/* progressive level mask: n_active = min(L, start + per_increment * (step / steps_per_increment)); 0 steps = off */
 	uint32_t progressive_start_levels, progressive_levels_per_increment, progressive_steps_per_increment;
 	uint32_t world_size, rank;     /* ray sharding for data-parallel training (one process per GPU) */
+	/* The reference's own keys for the progressive mask ("encoding" block, configs/nerf/base.json:36-38, dtu.json:35-37;
+	 * consumed by Encoding::set_training_step, src/testbed.cu:2643-2647, inside the un-vendored tiny-cuda-nn fork).
+	 * base_training_step > 0 switches this schedule on (it then takes precedence over the triple above):
+	 *   fraction = min(1, base_valid_level_scale + valid_level_scale * (step / base_training_step))   (integer division)
+	 *   n_active = clamp(round(n_levels * fraction), 1, n_levels)
+	 * The formula is this library's reading of the key names; the fork's source is not available. */
+	float valid_level_scale, base_valid_level_scale;
+	uint32_t base_training_step;
+	uint32_t adam_flags;           /* NEUS2B_ADAM_* */
+	float loss_scale;              /* LOSS_SCALE (include/neural-graphics-primitives/testbed.h:237): 128 */
 } neus2b_testbed_config;
+/* "top_resolution" -> per_level_scale when the config gives none (src/testbed.cu:2173-2177):
+ * exp(log(top_resolution * aabb_scale / base_resolution) / (n_levels - 1)). */
+float neus2b_per_level_scale_from_top_resolution(uint32_t n_levels, uint32_t base_resolution, float top_resolution, uint32_t aabb_scale);
+/* Active levels at a training step under the testbed's configured schedule (what the step's kernels are launched with). */
+uint32_t neus2b_testbed_config_active_levels(const neus2b_testbed_config* cfg, uint32_t training_step);
 
 typedef struct {
 	uint32_t training_step;
@@ -275,6 +308,8 @@ typedef struct {
 	uint32_t measured_batch_size;
 	uint32_t overflow;
 	float loss, ek_loss;                           /* Testbed.loss / ek_loss (python_api.cu:447-449) */
+	uint32_t nonfinite_gradients;                  /* gradient entries the optimizer refused so far (NaN / infinite), cumulative */
+	uint32_t device_error;                         /* sticky device error bits at the end of the step (neus2b_device_error_flags) */
 } neus2b_train_stats;
 
 typedef struct neus2b_testbed neus2b_testbed;

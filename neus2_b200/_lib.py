@@ -64,7 +64,10 @@ class RenderRequest(C.Structure):
 class AdamCfg(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float),
                 ("l2_reg", C.c_float), ("ema_decay", C.c_float), ("loss_scale", C.c_float), ("step", C.c_uint32),
-                ("n_matrix", C.c_uint32)]
+                ("n_matrix", C.c_uint32), ("flags", C.c_uint32), ("d_nonfinite", C.c_void_p)]
+
+
+ADAM_UPDATE_UNTOUCHED, ADAM_L2_ALL, ADAM_EMA_NO_DEBIAS = 1, 2, 4
 
 
 class TestbedConfig(C.Structure):
@@ -75,7 +78,9 @@ class TestbedConfig(C.Structure):
                 ("mask_loss_weight", C.c_float), ("anneal_end", C.c_uint32), ("density_grid_decay", C.c_float),
                 ("random_bg_color", C.c_uint32), ("snap_to_pixel_centers", C.c_uint32),
                 ("progressive_start_levels", C.c_uint32), ("progressive_levels_per_increment", C.c_uint32),
-                ("progressive_steps_per_increment", C.c_uint32), ("world_size", C.c_uint32), ("rank", C.c_uint32)]
+                ("progressive_steps_per_increment", C.c_uint32), ("world_size", C.c_uint32), ("rank", C.c_uint32),
+                ("valid_level_scale", C.c_float), ("base_valid_level_scale", C.c_float), ("base_training_step", C.c_uint32),
+                ("adam_flags", C.c_uint32), ("loss_scale", C.c_float)]
 
 
 class TrainingState(C.Structure):
@@ -87,7 +92,8 @@ class TrainingState(C.Structure):
 class TrainStats(C.Structure):
     _fields_ = [("training_step", C.c_uint32), ("rays_per_batch", C.c_uint32), ("n_rays_kept", C.c_uint32),
                 ("measured_batch_size_before_compaction", C.c_uint32), ("measured_batch_size", C.c_uint32),
-                ("overflow", C.c_uint32), ("loss", C.c_float), ("ek_loss", C.c_float)]
+                ("overflow", C.c_uint32), ("loss", C.c_float), ("ek_loss", C.c_float), ("nonfinite_gradients", C.c_uint32),
+                ("device_error", C.c_uint32)]
 
 
 class Neus2bError(RuntimeError):
@@ -101,7 +107,8 @@ EXPORTS = [
     "neus2b_version", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
     "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
     "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
-    "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
+    "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_set_device_error_flags",
+    "neus2b_per_level_scale_from_top_resolution", "neus2b_testbed_config_active_levels", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_occupancy_bounds", "neus2b_adam_step", "neus2b_adam_step_packed",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
@@ -127,6 +134,9 @@ def lib():
         _lib.neus2b_testbed_destroy.restype = None
         _lib.neus2b_ld_random_pixel_offset.restype = None
         _lib.neus2b_testbed_destroy.argtypes = [C.c_void_p]
+        _lib.neus2b_per_level_scale_from_top_resolution.restype = C.c_float
+        _lib.neus2b_per_level_scale_from_top_resolution.argtypes = [C.c_uint32, C.c_uint32, C.c_float, C.c_uint32]
+        _lib.neus2b_testbed_config_active_levels.restype = C.c_uint32
     return _lib
 
 
@@ -145,6 +155,10 @@ def device_error_flags():
     v = C.c_uint32(0)
     check(lib().neus2b_device_error_flags(C.byref(v)))
     return int(v.value)
+
+
+def set_device_error_flags(flags):
+    check(lib().neus2b_set_device_error_flags(C.c_uint32(flags)))
 
 
 def check(rc):

@@ -12,6 +12,8 @@ extern "C" const char* neus2b_error_string(int code) {
 		case NEUS2B_E_OVERFLOW: return "device-side capacity exceeded";
 		case NEUS2B_E_TOO_LARGE: return "request exceeds a compiled-in capacity";
 		case NEUS2B_E_IO: return "file could not be opened or written";
+		case NEUS2B_E_DEVICE: return "a kernel raised the device error flag";
+		case NEUS2B_E_TIMEOUT: return "a bounded wait ran out";
 		default: break;
 	}
 	if (code > 0) return cudaGetErrorString((cudaError_t)code);

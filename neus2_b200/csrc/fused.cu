@@ -557,6 +557,7 @@ static int fill_common(NeusArgs& a, const neus2b_grid_desc* desc, const uint16_t
 int launch_neus_tc_forward(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream);
 int launch_neus_tc_train(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream);
 int read_tc_error(uint32_t* h_flags);
+int write_tc_error(uint32_t flags);
 static int g_mma_path = NEUS2B_MMA_TCGEN05;
 
 }  // namespace n2b
@@ -573,6 +574,7 @@ extern "C" int neus2b_device_error_flags(uint32_t* h_flags) {
 	if (!h_flags) return NEUS2B_E_INVALID;
 	return read_tc_error(h_flags);
 }
+extern "C" int neus2b_set_device_error_flags(uint32_t flags) { return write_tc_error(flags); }
 
 extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
                                    const uint32_t* d_n, const float* d_coords, uint16_t* d_out, neus2b_stream_t stream) {

@@ -54,7 +54,9 @@ struct Smem {
 	unsigned char X1[T64];  // S -> H1 -> (training) S again
 	unsigned char X2[MODE == MODE_TRAIN ? T64 : 16];  // H2 -> dH1
 	unsigned char X3[MODE == MODE_TRAIN ? T64 : 16];  // dH2 -> dHs -> T
-	unsigned char dY[MODE == MODE_TRAIN ? T16 : 16];  // dY3 -> dYs -> e0
+	unsigned char dY[MODE == MODE_TRAIN ? T16 : 16];  // dY3 -> dYs
+	unsigned char E0[MODE == MODE_TRAIN ? T16 : 16];  // second-order seed e0 (its own tile: the GEMM that reads dYs may still run)
+	__half gst[MODE == MODE_TRAIN ? 128 : 1][8];      // rows 3..10 of a sample's output gradient, from part 0 to part 1
 	float nrm[kParts][128][3];
 	float vbuf[128][4];
 	float red[kThreads / 32];
@@ -192,6 +194,20 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		BODY;                                            \
 		tc::commit(mbar);                                \
 	}
+// BODY is waited for, TAIL (weight-gradient GEMMs, read at the end of the kernel only) runs on behind the wait: the tensor
+// pipe works through it while the threads do the stage's epilogue.  MMAs of one thread complete in issue order, so the
+// next stage's wait also covers this TAIL.
+#define N2B_ISSUE_TAIL(BODY, TAIL)                       \
+	tc::fence_async_smem();                              \
+	tc::fence_before_sync();                             \
+	__syncthreads();                                     \
+	if (tid == 0) {                                      \
+		tc::fence_after_sync();                          \
+		BODY;                                            \
+		tc::commit(mbar);                                \
+		TAIL;                                            \
+	}                                                    \
+	N2B_WAIT()
 #define N2B_WAIT()                                       \
 	if (ok) ok = tc::mbar_wait(mbar, phase);             \
 	phase ^= 1u;                                         \
@@ -213,9 +229,28 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			dir[1] = c[a.dir_offset + 1];
 			dir[2] = c[a.dir_offset + 2];
 		}
-		// ---- gather: features of this thread's 4 levels -> Zs, Jacobian d enc / d x kept in registers
+		// ---- gather: features of this thread's 4 levels -> Zs, Jacobian d enc / d x kept in registers.
+		// All 32 table loads of the thread are issued before the first is used: one trip to L2 per tile instead of one per level.
 		float J[4][6];
 		__half2 feats[4];
+		__half2 th[4][8];
+		float fr[4][3];
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const uint32_t l = (uint32_t)(part + 4 * j);
+			if (l < a.lv.n_active) {
+				const LevelGeom g = level_geom(a.lv, l, x);
+				fr[j][0] = g.ax[1];
+				fr[j][1] = g.ay[1];
+				fr[j][2] = g.az[1];
+#pragma unroll
+				for (uint32_t k = 0; k < 8; ++k) th[j][k] = ldg_h2(grid, geom_index(g, k));
+			} else {
+				fr[j][0] = fr[j][1] = fr[j][2] = 0.f;
+#pragma unroll
+				for (uint32_t k = 0; k < 8; ++k) th[j][k] = __floats2half2_rn(0.f, 0.f);
+			}
+		}
 #pragma unroll
 		for (int j = 0; j < 4; ++j) {
 			const uint32_t l = (uint32_t)(part + 4 * j);
@@ -223,26 +258,23 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 #pragma unroll
 			for (int e = 0; e < 6; ++e) J[j][e] = 0.f;
 			if (l < a.lv.n_active) {
-				const LevelGeom g = level_geom(a.lv, l, x);
-				__half2 th[8];
-#pragma unroll
-				for (uint32_t k = 0; k < 8; ++k) th[k] = ldg_h2(grid, geom_index(g, k));
+				const float gax[2] = {1.0f - fr[j][0], fr[j][0]}, gay[2] = {1.0f - fr[j][1], fr[j][1]}, gaz[2] = {1.0f - fr[j][2], fr[j][2]};
 				const float scale = a.lv.scale[l];
 				// Trilinear value and its gradient, factored: along an axis the derivative is the difference of the two faces
 				// weighted by the other two axes' products (fp32 throughout, one rounding of the value to fp16).
 				float2 t[8];
 #pragma unroll
-				for (int k = 0; k < 8; ++k) t[k] = __half22float2(th[k]);
+				for (int k = 0; k < 8; ++k) t[k] = __half22float2(th[j][k]);
 				float a0 = 0.f, a1 = 0.f;
 				float jx0 = 0.f, jx1 = 0.f, jy0 = 0.f, jy1 = 0.f, jz0 = 0.f, jz1 = 0.f;
 #pragma unroll
 				for (int u = 0; u < 2; ++u)
 #pragma unroll
 					for (int v = 0; v < 2; ++v) {
-						const float pyz = g.ay[u] * g.az[v], pxz = g.ax[u] * g.az[v], pxy = g.ax[u] * g.ay[v];
+						const float pyz = gay[u] * gaz[v], pxz = gax[u] * gaz[v], pxy = gax[u] * gay[v];
 						const float2 x0 = t[2 * u + 4 * v], x1 = t[1 + 2 * u + 4 * v];  // bx = 0 | 1 at (by, bz) = (u, v)
-						a0 = __fmaf_rn(pyz, __fmaf_rn(g.ax[1], x1.x, g.ax[0] * x0.x), a0);
-						a1 = __fmaf_rn(pyz, __fmaf_rn(g.ax[1], x1.y, g.ax[0] * x0.y), a1);
+						a0 = __fmaf_rn(pyz, __fmaf_rn(gax[1], x1.x, gax[0] * x0.x), a0);
+						a1 = __fmaf_rn(pyz, __fmaf_rn(gax[1], x1.y, gax[0] * x0.y), a1);
 						jx0 = __fmaf_rn(pyz, x1.x - x0.x, jx0);
 						jx1 = __fmaf_rn(pyz, x1.y - x0.y, jx1);
 						const float2 y0 = t[u + 4 * v], y1 = t[u + 2 + 4 * v];  // by = 0 | 1 at (bx, bz) = (u, v)
@@ -343,6 +375,15 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			h[6] = h[7] = __float2half_rn(0.f);
 			st16(sm.Zc, s, 32, 48, h);
 		}
+		// (training: this sample's output gradient is requested now and used behind the colour net's forward pass)
+		uint4 gq0 = make_uint4(0u, 0u, 0u, 0u), gq1 = gq0;
+		if constexpr (MODE == MODE_TRAIN) {
+			if (part == 0 && valid) {
+				const uint4* src = reinterpret_cast<const uint4*>(a.dL_dout + (size_t)i * 16);
+				gq0 = __ldg(src);
+				gq1 = __ldg(src + 1);
+			}
+		}
 		// ---- colour net
 		N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.Zc, 48), kmaj(sm.W1c, 48), 3, false));
 		const uint32_t m_h1 = epilogue16<1>(R1, s, part * 16, sm.X1, 0u);
@@ -376,30 +417,29 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		} else {
 			// ---- B1: dY3 = rows 0-2 of dL_dout (nerf_network.h:331-340)
 			__align__(16) __half g[16];
-#pragma unroll
-			for (int k = 0; k < 16; ++k) g[k] = __float2half_rn(0.f);
+			reinterpret_cast<uint4*>(g)[0] = gq0;
+			reinterpret_cast<uint4*>(g)[1] = gq1;
 			if (part == 0) {
-				if (valid) {
-					const uint4* src = reinterpret_cast<const uint4*>(a.dL_dout + (size_t)i * 16);
-					reinterpret_cast<uint4*>(g)[0] = __ldg(src);
-					reinterpret_cast<uint4*>(g)[1] = __ldg(src + 1);
-				}
 				__align__(16) __half d3[16];
 #pragma unroll
 				for (int k = 0; k < 16; ++k) d3[k] = k < 3 ? g[k] : __float2half_rn(0.f);
 				st16(sm.dY, s, 0, 16, d3);
 				st16(sm.dY, s, 8, 16, d3 + 8);
+				__align__(16) __half gs[8];
+#pragma unroll
+				for (int e = 0; e < 8; ++e) gs[e] = g[3 + e];
+				*reinterpret_cast<uint4*>(&sm.gst[s][0]) = *reinterpret_cast<const uint4*>(gs);  // (read by part 1 behind B3's barrier)
 			}
-			N2B_ISSUE(gemm<64>(tm + 64, kmaj(sm.dY, 16), mnmaj(sm.W3c, 64), 1, false);
-			          gemm<16>(WG_W3cT, mnmaj(sm.X2, 64), mnmaj(sm.dY, 16), 8, !first));
+			N2B_ISSUE_TAIL(gemm<64>(tm + 64, kmaj(sm.dY, 16), mnmaj(sm.W3c, 64), 1, false),
+			               gemm<16>(WG_W3cT, mnmaj(sm.X2, 64), mnmaj(sm.dY, 16), 8, !first));
 			epilogue16<2>(R1, s, part * 16, sm.X3, m_h2);  // dH2
 			// ---- B2
-			N2B_ISSUE(gemm<64>(tm, kmaj(sm.X3, 64), mnmaj(sm.W2c, 64), 4, false);
-			          gemm<64>(WG_W2c, mnmaj(sm.X3, 64), mnmaj(sm.X1, 64), 8, !first));
+			N2B_ISSUE_TAIL(gemm<64>(tm, kmaj(sm.X3, 64), mnmaj(sm.W2c, 64), 4, false),
+			               gemm<64>(WG_W2c, mnmaj(sm.X3, 64), mnmaj(sm.X1, 64), 8, !first));
 			epilogue16<2>(R0, s, part * 16, sm.X2, m_h1);  // dH1 (over H2)
 			// ---- B3
-			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X2, 64), mnmaj(sm.W1c, 48), 4, false);
-			          gemm<48>(WG_W1c, mnmaj(sm.X2, 64), mnmaj(sm.Zc, 48), 8, !first));
+			N2B_ISSUE_TAIL(gemm<48>(tm + 64, kmaj(sm.X2, 64), mnmaj(sm.W1c, 48), 4, false),
+			               gemm<48>(WG_W1c, mnmaj(sm.X2, 64), mnmaj(sm.Zc, 48), 8, !first));
 			// ---- B4: SDF-net output gradient = colour-net input gradient rows 0-15 (+ dL/dsdf), v = dL/dnormal (:388-395, :465-491)
 			if (part == 0) {
 				float v[16];
@@ -411,33 +451,68 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				h[0] = __hadd(h[0], g[3]);
 				st16(sm.dY, s, 0, 16, h);
 				st16(sm.dY, s, 8, 16, h + 8);
-				tc::tmem_ld16(R1 + 32, v);
+				var_grad += __half2float(g[7]);
+			} else if (part == 1) {
+				float v[8];
+				tmem_ld8(R1 + 32, v);
 				tc::tmem_ld_wait();
+				__align__(16) __half gs[8];  // rows 3..10 of the output gradient
+				*reinterpret_cast<uint4*>(gs) = *reinterpret_cast<const uint4*>(&sm.gst[s][0]);
 #pragma unroll
 				for (int e = 0; e < 3; ++e)
-					sm.vbuf[s][e] = __half2float(__float2half_rn(v[3 + e])) + __half2float(g[4 + e]) / a.batch_size + __half2float(g[8 + e]);
-				var_grad += __half2float(g[7]);
+					sm.vbuf[s][e] = __half2float(__float2half_rn(v[3 + e])) + __half2float(gs[1 + e]) / a.batch_size + __half2float(gs[5 + e]);
 			}
-			N2B_ISSUE(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false);
-			          gemm<16>(WG_W2sT, mnmaj(sm.Hs, 64), mnmaj(sm.dY, 16), 8, !first));
+			N2B_ISSUE_TAIL(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false),
+			               gemm<16>(WG_W2sT, mnmaj(sm.Hs, 64), mnmaj(sm.dY, 16), 8, !first));
 			epilogue16<2>(R0, s, part * 16, sm.X3, m_hs);  // dHs
-			// ---- B5
-			N2B_ISSUE(gemm<48>(tm + 64, kmaj(sm.X3, 64), mnmaj(sm.W1s, 48), 4, false);
-			          gemm<48>(WG_W1s, mnmaj(sm.X3, 64), mnmaj(sm.Zs, 48), 8, !first));
-			// ---- B6: grid gradient (first + second order merged, one reduction per corner); U = [J v | v | 0] over Zs
+			// ---- B5 + B7: U = [J v | v | 0] (dL / d(dy0/dz), :547-557) goes over the colour-net input tile, which is free since B3, so
+			// that the second-order GEMMs need not wait for B5: T' = U W1s^T and dW1s += S^T U (:560-571) are issued with it.
 			const float v3[3] = {sm.vbuf[s][0], sm.vbuf[s][1], sm.vbuf[s][2]};
 			{
-				float dzv[8];
-				tmem_ld8(R1 + 8 * part, dzv);
-				tc::tmem_ld_wait();
 				__align__(16) __half u8[8];
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
 					const uint32_t l = (uint32_t)(part + 4 * j);
 					__half2 dy = __floats2half2_rn(0.f, 0.f);
-					if (l < a.lv.n_active) {
+					if (l < a.lv.n_active)
 						dy = __floats2half2_rn(J[j][0] * v3[0] + J[j][2] * v3[1] + J[j][4] * v3[2],
 						                       J[j][1] * v3[0] + J[j][3] * v3[1] + J[j][5] * v3[2]);
+					u8[2 * j] = __low2half(dy);
+					u8[2 * j + 1] = __high2half(dy);
+				}
+				st16(sm.Zc, s, 8 * part, 48, u8);
+			}
+			if (part == 0) {
+				__align__(16) __half h[8];
+#pragma unroll
+				for (int e = 0; e < 8; ++e) h[e] = __float2half_rn(e < 3 ? v3[e] : 0.f);
+				st16(sm.Zc, s, 32, 48, h);
+			} else if (part == 1) {
+				// second-order seed dy = e0 for every live sample (:497-503)
+				__align__(16) __half e0[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k) e0[k] = __float2half_rn((k == 0 && valid) ? 1.f : 0.f);
+				st16(sm.E0, s, 0, 16, e0);
+				st16(sm.E0, s, 8, 16, e0 + 8);
+			}
+			write_S(sm.W2s, sm.X1, s, part * 16, m_hs);
+			N2B_ISSUE_TAIL(gemm<48>(tm + 64, kmaj(sm.X3, 64), mnmaj(sm.W1s, 48), 4, false);
+			               gemm<48>(WG_W1s, mnmaj(sm.X3, 64), mnmaj(sm.Zs, 48), 8, !first);
+			               gemm<64>(tm, kmaj(sm.Zc, 48), kmaj(sm.W1s, 48), 3, false),
+			               gemm<48>(WG_W1s, mnmaj(sm.X1, 64), mnmaj(sm.Zc, 48), 8, true));
+			epilogue16<2>(R0, s, part * 16, sm.X3, m_hs);  // T = D .* T'
+			// dW2s[0,:] += sum_b T
+			N2B_ISSUE_NOWAIT(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.E0, 16), 8, true));
+			// ---- B6: grid gradient (first + second order merged, one reduction per corner); runs while the tensor pipe
+			// finishes the tile's last weight-gradient GEMM
+			{
+				float dzv[8];
+				tmem_ld8(R1 + 8 * part, dzv);
+				tc::tmem_ld_wait();
+#pragma unroll
+				for (int j = 0; j < 4; ++j) {
+					const uint32_t l = (uint32_t)(part + 4 * j);
+					if (l < a.lv.n_active) {
 						const float dz0 = __half2float(__float2half_rn(dzv[2 * j]));
 						const float dz1 = __half2float(__float2half_rn(dzv[2 * j + 1]));
 						const float2 gef = __half22float2(ge[j]);
@@ -480,39 +555,38 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 								if (head && (v0 != 0.f || v1 != 0.f)) red_add_h2(a.grad_grid, geom_index(g2, k), v0, v1);
 							}
 						} else if (valid) {
+							// Fine levels: the two x-neighbours of a corner pair are one aligned 8-byte pair of entries whenever their
+							// indices differ in bit 0 only (dense: an even index; hashed: an even x, because x ^ h and (x + 1) ^ h then
+							// differ in bit 0 only): one vector reduction instead of two.
 #pragma unroll
-							for (uint32_t k = 0; k < 8; ++k) {
-								const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
-								const float p = g2.ax[bx] * g2.ay[by];
-								const float qq = bxv[bx] * g2.ay[by] + g2.ax[bx] * byv[by];
-								const float w = p * g2.az[bz];
-								const float coef = qq * g2.az[bz] + p * bzv[bz];
-								red_add_h2(a.grad_grid, geom_index(g2, k), __fmaf_rn(w, dz0, coef * gef.x), __fmaf_rn(w, dz1, coef * gef.y));
+							for (uint32_t k = 0; k < 8; k += 2) {
+								const uint32_t by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+								float v[2][2];
+#pragma unroll
+								for (uint32_t bx = 0; bx < 2; ++bx) {
+									const float p = g2.ax[bx] * g2.ay[by];
+									const float qq = bxv[bx] * g2.ay[by] + g2.ax[bx] * byv[by];
+									const float w = p * g2.az[bz];
+									const float coef = qq * g2.az[bz] + p * bzv[bz];
+									v[bx][0] = __fmaf_rn(w, dz0, coef * gef.x);
+									v[bx][1] = __fmaf_rn(w, dz1, coef * gef.y);
+								}
+								const uint32_t e0 = geom_index(g2, k), e1 = geom_index(g2, k + 1u);
+#ifndef N2B_NO_V2
+								if ((e0 ^ e1) == 1u) {
+									if (e0 & 1u) red_add_h2x2(a.grad_grid, e1, v[1][0], v[1][1], v[0][0], v[0][1]);
+									else red_add_h2x2(a.grad_grid, e0, v[0][0], v[0][1], v[1][0], v[1][1]);
+								} else
+#endif
+								{
+									red_add_h2(a.grad_grid, e0, v[0][0], v[0][1]);
+									red_add_h2(a.grad_grid, e1, v[1][0], v[1][1]);
+								}
 							}
 						}
 					}
-					u8[2 * j] = __low2half(dy);
-					u8[2 * j + 1] = __high2half(dy);
 				}
-				st16(sm.Zs, s, 8 * part, 48, u8);
 			}
-			if (part == 0) {
-#pragma unroll
-				for (int e = 0; e < 3; ++e) *reinterpret_cast<__half*>(sm.Zs + tc::blk_off(s, 32 + e, 48)) = __float2half_rn(v3[e]);
-			} else if (part == 1) {
-				// second-order seed dy = e0 for every live sample (:497-503)
-				__align__(16) __half e0[16];
-#pragma unroll
-				for (int k = 0; k < 16; ++k) e0[k] = __float2half_rn((k == 0 && valid) ? 1.f : 0.f);
-				st16(sm.dY, s, 0, 16, e0);
-				st16(sm.dY, s, 8, 16, e0 + 8);
-			}
-			write_S(sm.W2s, sm.X1, s, part * 16, m_hs);
-			// ---- B7: T = D .* (U W1s^T);  dW2s[0,:] += sum_b T;  dW1s += S^T U  (:560-571)
-			N2B_ISSUE(gemm<64>(tm, kmaj(sm.Zs, 48), kmaj(sm.W1s, 48), 3, false));
-			epilogue16<2>(R0, s, part * 16, sm.X3, m_hs);  // T
-			N2B_ISSUE_NOWAIT(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.dY, 16), 8, true);
-			                 gemm<48>(WG_W1s, mnmaj(sm.X1, 64), mnmaj(sm.Zs, 48), 8, true));
 			pending = true;
 			first = false;
 		}
@@ -525,6 +599,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		N2B_WAIT();
 	}
 #undef N2B_ISSUE
+#undef N2B_ISSUE_TAIL
 #undef N2B_ISSUE_NOWAIT
 #undef N2B_WAIT
 	if (!ok) atomicOr(&g_tc_error, 1u);
@@ -614,6 +689,18 @@ int read_tc_error(uint32_t* h_flags) {
 	cudaError_t e = cudaMemcpyFromSymbol(&v, tcf::g_tc_error, sizeof(v));
 	if (e != cudaSuccess) return (int)e;
 	*h_flags = v;
+	return NEUS2B_OK;
+}
+int write_tc_error(uint32_t flags) {
+	cudaError_t e = cudaMemcpyToSymbol(tcf::g_tc_error, &flags, sizeof(flags));
+	return e == cudaSuccess ? NEUS2B_OK : (int)e;
+}
+// Device address of the error word on the current device (for kernels of other translation units that report it).
+int tc_error_device_ptr(const uint32_t** d_ptr) {
+	void* p = nullptr;
+	cudaError_t e = cudaGetSymbolAddress(&p, tcf::g_tc_error);
+	if (e != cudaSuccess) return (int)e;
+	*d_ptr = (const uint32_t*)p;
 	return NEUS2B_OK;
 }
 

@@ -468,10 +468,15 @@ __device__ __forceinline__ void neus_sample(const __half* o, float dt_warped, co
 #pragma unroll
 	for (int e = 0; e < 3; ++e) s.nrm[e] = __half2float(o[4 + e]);
 	s.true_cos = dir[0] * s.nrm[0] + dir[1] * s.nrm[1] + dir[2] * s.nrm[2];
-	const float r1 = -s.true_cos * 0.5f + 0.5f, r2 = -s.true_cos;
-	s.iter_cos = -(fmaxf(r1, 0.f) * (1.0f - anneal) + fmaxf(r2, 0.f) * anneal);
-	s.next_sdf = sdf + s.iter_cos * s.dt * 0.5f;
-	const float prev_sdf = sdf - s.iter_cos * s.dt * 0.5f;
+	// The reference writes these lines with double literals (0.5, 1.0): the intermediates are fp64 and each line rounds to
+	// fp32 once (src/testbed_nerf.cu:1594-1598).  r1 is rounded where it is passed to activation_function(float), the
+	// product with the annealing ratio is a float product, the sum and the two sdf estimates are fp64 sums.
+	const float r1 = (float)((double)(-s.true_cos) * 0.5 + 0.5), r2 = -s.true_cos;
+	const float relu2a = fmaxf(r2, 0.f) * anneal;
+	s.iter_cos = (float)(-((double)fmaxf(r1, 0.f) * (1.0 - (double)anneal) + (double)relu2a));
+	const float half_step = s.iter_cos * s.dt;  // float product, then * 0.5 in fp64 (exact)
+	s.next_sdf = (float)((double)sdf + (double)half_step * 0.5);
+	const float prev_sdf = (float)((double)sdf - (double)half_step * 0.5);
 	const float next_cdf = logisticf(s.next_sdf * s.inv_s), prev_cdf = logisticf(prev_sdf * s.inv_s);
 	s.p_div_c = (prev_cdf - next_cdf + 1e-5f) / (prev_cdf + 1e-5f);
 	s.alpha = clampf(s.p_div_c, 0.0f, 1.0f);
@@ -486,6 +491,6 @@ __device__ __forceinline__ void load_out16(const __half* src, __half* dst) {
 // Exclusive prefix sum of n (<= 2^20) 64-bit keys in place, n read on the device when d_n is given; the total goes to
 // data[n_max], data[n_max + 1 .. n_max + 1023] is scratch and data[n_max + 512] must be zero before the launch (it is left
 // at zero).
-void launch_scan(uint32_t n_max, const uint32_t* d_n, uint64_t* data, cudaStream_t stream);
+int launch_scan(uint32_t n_max, const uint32_t* d_n, uint64_t* data, cudaStream_t stream);
 
 }  // namespace n2b

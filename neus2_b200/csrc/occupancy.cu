@@ -115,11 +115,20 @@ __global__ void occ_maxpool_kernel(uint32_t n, const uint8_t* __restrict__ prev,
 
 // ------------------------------------------------------------------------------------------------ Adam
 // One element of the Ema o Adam update.  Returns the new weight; m/v are updated in place.
-__device__ __forceinline__ float adam_element(const neus2b_adam_cfg& c, float lr_t, bool matrix, float g, float w, float& m, float& v) {
+// A gradient that is NaN or infinite counts as absent (bad = true): the parameter keeps its weight and moments.
+__device__ __forceinline__ float adam_element(const neus2b_adam_cfg& c, float lr_t, bool matrix, float g, float w, float& m, float& v,
+                                              bool& bad) {
+	if (!(fabsf(g) <= 3.402823466e+38f)) {
+		bad = true;
+		return w;
+	}
 	g = __fdividef(g, c.loss_scale);
 	bool upd = true;
 	if (matrix) g += c.l2_reg * w;
-	else if (g == 0.0f) upd = false;  // grid entries no sample touched keep their weight and moments
+	else {
+		if (g == 0.0f && !(c.flags & NEUS2B_ADAM_UPDATE_UNTOUCHED)) upd = false;  // grid entries no sample touched keep their weight and moments
+		if (c.flags & NEUS2B_ADAM_L2_ALL) g += c.l2_reg * w;
+	}
 	if (upd) {
 		m = c.beta1 * m + (1.0f - c.beta1) * g;
 		v = c.beta2 * v + (1.0f - c.beta2) * g * g;
@@ -163,8 +172,15 @@ __global__ void __launch_bounds__(256, 8) adam_kernel(neus2b_adam_cfg c, float l
 			const float4 e4 = *reinterpret_cast<const float4*>(ema_master + i0);
 			em[0] = e4.x; em[1] = e4.y; em[2] = e4.z; em[3] = e4.w;
 		}
+		bool bad = false;
 #pragma unroll
-		for (int e = 0; e < 4; ++e) w[e] = adam_element(c, lr_t, matrix, g[e], w[e], mm[e], vv[e]);
+		for (int e = 0; e < 4; ++e) w[e] = adam_element(c, lr_t, matrix, g[e], w[e], mm[e], vv[e], bad);
+		if (bad && c.d_nonfinite) {
+			uint32_t nb = 0;
+#pragma unroll
+			for (int e = 0; e < 4; ++e) nb += !(fabsf(g[e]) <= 3.402823466e+38f);
+			atomicAdd(c.d_nonfinite, nb);
+		}
 		*reinterpret_cast<float4*>(master + i0) = make_float4(w[0], w[1], w[2], w[3]);
 		*reinterpret_cast<float4*>(m + i0) = make_float4(mm[0], mm[1], mm[2], mm[3]);
 		*reinterpret_cast<float4*>(v + i0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
@@ -172,7 +188,7 @@ __global__ void __launch_bounds__(256, 8) adam_kernel(neus2b_adam_cfg c, float l
 		*reinterpret_cast<uint2*>(params + i0) = make_uint2(*reinterpret_cast<uint32_t*>(&p01), *reinterpret_cast<uint32_t*>(&p23));
 		if (params_ema) {
 #pragma unroll
-			for (int e = 0; e < 4; ++e) em[e] = ((1.0f - c.ema_decay) * w[e] + c.ema_decay * em[e] * ema_old) * ema_new_inv;
+			for (int e = 0; e < 4; ++e) em[e] = ((1.0f - c.ema_decay) * w[e] + c.ema_decay * em[e] * ema_old) * ema_new_inv;  // (1, 1 without debiasing)
 			*reinterpret_cast<float4*>(ema_master + i0) = make_float4(em[0], em[1], em[2], em[3]);
 			__half2 e01 = __floats2half2_rn(em[0], em[1]), e23 = __floats2half2_rn(em[2], em[3]);
 			*reinterpret_cast<uint2*>(params_ema + i0) = make_uint2(*reinterpret_cast<uint32_t*>(&e01), *reinterpret_cast<uint32_t*>(&e23));
@@ -210,8 +226,10 @@ __global__ void __launch_bounds__(256, 8) adam_packed_kernel(neus2b_adam_cfg c, 
 			g[1] = grad_var[i0 - n_grid_end + 1];
 		}
 		float4 s0 = state[i0], s1 = state[i0 + 1];
-		s0.x = adam_element(c, lr_t, matrix, g[0], s0.x, s0.y, s0.z);
-		s1.x = adam_element(c, lr_t, matrix, g[1], s1.x, s1.y, s1.z);
+		bool bad = false;
+		s0.x = adam_element(c, lr_t, matrix, g[0], s0.x, s0.y, s0.z, bad);
+		s1.x = adam_element(c, lr_t, matrix, g[1], s1.x, s1.y, s1.z, bad);
+		if (bad && c.d_nonfinite) atomicAdd(c.d_nonfinite, (uint32_t)!(fabsf(g[0]) <= 3.402823466e+38f) + (uint32_t)!(fabsf(g[1]) <= 3.402823466e+38f));
 		s0.w = ((1.0f - c.ema_decay) * s0.x + c.ema_decay * s0.w * ema_old) * ema_new_inv;
 		s1.w = ((1.0f - c.ema_decay) * s1.x + c.ema_decay * s1.w * ema_old) * ema_new_inv;
 		state[i0] = s0;
@@ -343,8 +361,9 @@ extern "C" int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d
 	     (uintptr_t)d_params_ema | (uintptr_t)d_ema_master) & 15u)
 		return NEUS2B_E_INVALID;
 	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
-	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
-	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
+	const bool debias = !(cfg->flags & NEUS2B_ADAM_EMA_NO_DEBIAS);
+	const float ema_old = debias ? 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1)) : 1.0f;
+	const float ema_new_inv = debias ? 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step)) : 1.0f;
 	adam_kernel<<<div_up((n + 3) / 4, 256), 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
 	                                          d_master, d_m, d_v, (__half*)d_params, (__half*)d_params_ema, d_ema_master);
 	N2B_CHECK_LAUNCH();
@@ -360,8 +379,9 @@ extern "C" int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, f
 	     (uintptr_t)d_params_ema) & 15u)
 		return NEUS2B_E_INVALID;
 	const float lr_t = cfg->learning_rate * sqrtf(1.0f - powf(cfg->beta2, (float)cfg->step)) / (1.0f - powf(cfg->beta1, (float)cfg->step));
-	const float ema_old = 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1));
-	const float ema_new_inv = 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step));
+	const bool debias = !(cfg->flags & NEUS2B_ADAM_EMA_NO_DEBIAS);
+	const float ema_old = debias ? 1.0f - powf(cfg->ema_decay, (float)(cfg->step - 1)) : 1.0f;
+	const float ema_new_inv = debias ? 1.0f / (1.0f - powf(cfg->ema_decay, (float)cfg->step)) : 1.0f;
 	adam_packed_kernel<<<kSMs * 16, 256, 0, stream>>>(*cfg, lr_t, ema_old, ema_new_inv, n, d_grad_mlp, (__half*)d_grad_grid, d_grad_variance,
 	                                                  (float4*)d_state, (__half*)d_params, (__half*)d_params_ema);
 	N2B_CHECK_LAUNCH();

@@ -155,21 +155,29 @@ __global__ void __launch_bounds__(1024) scan_kernel(uint32_t n_max, const uint32
 	__syncthreads();
 	if (!is_last) return;
 	__threadfence();
+	// (what the other CTAs wrote is read through L2, past this SM's L1)
 	if (tid == 0) {
 		uint64_t run = 0;
 		for (uint32_t t = 0; t < n_tiles; ++t) {
 			offsets[t] = run;
-			run += tile_sums[t];
+			run += __ldcg(tile_sums + t);
 		}
 		data[n_max] = run;
 		*ticket = 0ull;
 	}
 	__syncthreads();
-	for (uint32_t k = kScanTile + tid; k < n; k += 1024u) data[k] += offsets[k / kScanTile];
+	for (uint32_t k = kScanTile + tid; k < n; k += 1024u) data[k] = __ldcg(data + k) + offsets[k / kScanTile];
 }
 
-void launch_scan(uint32_t n_max, const uint32_t* d_n, uint64_t* data, cudaStream_t stream) {
+// The scan holds one offset per tile in shared memory and keeps its tile sums and ticket behind the keys: 2^20 keys at most.
+constexpr uint32_t kScanMaxKeys = kScanTile * kScanMaxTiles;
+static_assert(kScanMaxKeys == NEUS2B_MAX_RAYS_PER_CALL, "the header states the scan's capacity");
+
+int launch_scan(uint32_t n_max, const uint32_t* d_n, uint64_t* data, cudaStream_t stream) {
+	if (n_max > kScanMaxKeys) return NEUS2B_E_TOO_LARGE;
 	scan_kernel<<<64, 1024, 0, stream>>>(n_max, d_n, data);
+	N2B_CHECK_LAUNCH();
+	return NEUS2B_OK;
 }
 
 // Second half of the sample generator (:1410-1445): canonical ranges, then march again and write the coordinates.
@@ -414,13 +422,14 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 			lgl[e] = (ad > al ? (ad - 0.5f * al) : 0.5f / al * diff * diff) / 5.0f;
 			lgg[e] = (ad > al ? (diff > 0 ? 1.0f : -1.0f) : diff / al) / 5.0f;
 		}
-		const float mask_gt = tex[3] > 0.9999f ? 1.f : 0.f;
+		// double literals in the reference (:1690-1702): the comparisons are fp64, the assigned constants round to fp32
+		const float mask_gt = (double)tex[3] > 0.9999 ? 1.f : 0.f;
 		float gws, ws = c.weight_sum;
-		if (ws >= 1.0f - 1e-4f) {
-			ws = 1.0f - 1e-4f;
+		if ((double)ws >= 1.0 - 1e-4) {
+			ws = (float)(1.0 - 1e-4);
 			gws = 0.f;
-		} else if (ws <= 1e-4f) {
-			ws = 1e-4f;
+		} else if ((double)ws <= 1e-4) {
+			ws = (float)1e-4;
 			gws = 0.f;
 		} else {
 			const float sg = 1.0f / (1.0f + expf(-ws));
@@ -477,14 +486,14 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 					g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
 					dla += lgg[e] * (Ta * s.rgb[e] - suffix);
 				}
-				dla /= (1.0f - s.alpha + 1e-5f);
+				dla = (float)((double)dla / ((double)(1.0f - s.alpha) + 1e-5));  // "/ (1.0f - alpha + 1e-5)": fp64 divide (:1829-1832)
 				float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
 				if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {
 					const float P = __expf(s.inv_s * s.iter_cos * s.dt);
 					const float E = __expf(-s.next_sdf * s.inv_s);
 					dE_dsdf = -s.inv_s * E;
 					dE_ds = -s.next_sdf * E;
-					const float a = 1 + E, b = 1 + P * E, cc = 1e-5f + 1 / (1 + P * E);
+					const float a = 1 + E, b = 1 + P * E, cc = (float)(1e-5 + (double)(1 / (1 + P * E)));  // fp64 sum (:1862)
 					const float delta = a * (b * b) * (cc * cc);
 					da_dE = -(P / delta - 1 / (a * a * cc));
 					da_dP = -E / delta;
@@ -495,7 +504,8 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 				const float dl_dinvs = dla * (da_dE * dE_ds + da_dP * dP_ds);
 				const float dl_dvar = dl_dinvs * s.inv_s * 10;
 				const float dic_dcos = s.true_cos >= 0 ? 0.0f : 1.0f;
-				const float gn = sqrtf(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2] + 1e-6f);
+				// std::sqrt(float sum + 1e-6): the sum of squares is fp32, the offset and the root are fp64 (:1884)
+				const float gn = (float)sqrt((double)(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2]) + 1e-6);
 				const float gni = 1 - 1 / gn;
 				const float dl_dnn = dla * (da_dE * dE_dic + dP_dic * da_dP) * dic_dcos;
 				g[3] = loss_scale * (dla * da_dE * dE_dsdf);
@@ -578,6 +588,7 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
                                        neus2b_stream_t stream) {
 	if (!ds || !cfg || !d_bitfield || check_ws(ws)) return NEUS2B_E_INVALID;
 	if (n_rays == 0 || n_rays > ws->max_rays || ds->n_images == 0) return NEUS2B_E_INVALID;
+	if (n_rays > kScanMaxKeys) return NEUS2B_E_TOO_LARGE;
 	N2B_CHECK_CUDA(cudaMemsetAsync(ws->d_counters, 0, 8 * sizeof(uint32_t), stream));
 	Pcg32 r{rng.state, rng.inc};
 	// (the hit list borrows d_ray_indices, which the emit pass fills afterwards; its length is counter 6)
@@ -604,6 +615,7 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
                                    int rollover, neus2b_stream_t stream) {
 	if (!ds || !cfg || !d_mlp_out || !d_coords_out || !d_dloss_dout || check_ws(ws)) return NEUS2B_E_INVALID;
 	if (n_rays == 0 || n_rays > ws->max_rays || max_compacted == 0) return NEUS2B_E_INVALID;
+	if (n_rays > kScanMaxKeys) return NEUS2B_E_TOO_LARGE;
 	if (((uintptr_t)d_mlp_out | (uintptr_t)d_dloss_dout) & 15u) return NEUS2B_E_INVALID;
 	Pcg32 r{rng.state, rng.inc};
 	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);  // 4 warps per CTA, one warp per ray, grid-stride

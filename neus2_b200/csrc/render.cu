@@ -328,7 +328,10 @@ extern "C" int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t*
 		render_count_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, limit, d_bitfield, (RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_occupied_bounds,
 		                                                 ws->d_hit_list, ws->d_counters, ws->d_march_masks);
 		N2B_CHECK_LAUNCH();
-		launch_scan(n_rays, nullptr, ws->d_scan_tmp, stream);
+		{
+			const int src = launch_scan(n_rays, nullptr, ws->d_scan_tmp, stream);
+			if (src) return src;
+		}
 		N2B_CHECK_LAUNCH();
 		// the one read per band: how many windows of max_samples the band's samples fill
 		uint64_t total = 0;

@@ -15,11 +15,17 @@ struct TrainState {  // device resident, one per testbed
 	uint32_t n_rays_total;
 	uint32_t measured_pre, measured, n_kept, overflow;
 	float loss, ek_loss;
+	uint32_t nonfinite;     // gradient entries the optimizer pass refused (cumulative; adam_kernel adds to it)
+	uint32_t device_error;  // copy of the sticky device error word, taken by the batch tuner
 };
 
+int tc_error_device_ptr(const uint32_t** d_ptr);  // fused_tc.cu
+
 // Counters::update_after_training (src/testbed_nerf.cu:3406-3432) on the device.
-__global__ void tune_kernel(TrainState* st, const uint32_t* __restrict__ counters, uint32_t target, uint32_t max_rays) {
+__global__ void tune_kernel(TrainState* st, const uint32_t* __restrict__ counters, uint32_t target, uint32_t max_rays,
+                            const uint32_t* __restrict__ device_error) {
 	if (threadIdx.x != 0 || blockIdx.x != 0) return;
+	st->device_error = *device_error;
 	const uint32_t rays = st->rays_per_batch;
 	st->n_rays_total += rays;
 	st->measured_pre = counters[1];
@@ -115,6 +121,7 @@ struct neus2b_testbed {
 	float *coords_compacted = nullptr, *loss = nullptr, *ek_loss = nullptr;
 	TrainState* state = nullptr;
 	TrainState* h_state = nullptr;  // pinned
+	const uint32_t* d_device_error = nullptr;  // the kernels' sticky error word on this device
 	// dataset
 	neus2b_dataset ds{};
 	float* h_cam = nullptr;  // pinned staging for the camera block
@@ -184,6 +191,7 @@ extern "C" void neus2b_testbed_default_config(neus2b_testbed_config* c) {
 	c->snap_to_pixel_centers = 0;
 	c->world_size = 1;
 	c->rank = 0;
+	c->loss_scale = 128.f;
 }
 
 extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
@@ -208,7 +216,7 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	int rc = make_levels(&cfg->grid, &lv);
 	if (rc) return rc;
 	if (cfg->batch_size == 0 || cfg->batch_size % 128u || cfg->n_cascades == 0 || cfg->n_cascades > NEUS2B_CASCADES ||
-	    cfg->world_size == 0 || cfg->rank >= cfg->world_size)
+	    cfg->world_size == 0 || cfg->rank >= cfg->world_size || !(cfg->loss_scale > 0.f))
 		return NEUS2B_E_INVALID;
 	int ndev = 0;
 	if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return NEUS2B_E_NO_DEVICE;
@@ -271,6 +279,13 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	TB_ALLOC(tb->ek_loss, (size_t)tb->max_rays);
 	TB_ALLOC(tb->state, (size_t)1);
 	tb->ws.d_n_rays_total = &tb->state->n_rays_total;
+	{
+		const int erc = tc_error_device_ptr(&tb->d_device_error);
+		if (erc) {
+			neus2b_testbed_destroy(tb);
+			return erc;
+		}
+	}
 	e = cudaMallocHost((void**)&tb->h_state, sizeof(TrainState));
 	if (e != cudaSuccess) {
 		neus2b_testbed_destroy(tb);
@@ -376,13 +391,40 @@ extern "C" int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_param
 	return NEUS2B_OK;
 }
 
+extern "C" float neus2b_per_level_scale_from_top_resolution(uint32_t n_levels, uint32_t base_resolution, float top_resolution,
+                                                           uint32_t aabb_scale) {
+	if (n_levels < 2 || base_resolution == 0 || !(top_resolution > 0.f) || aabb_scale == 0) return 0.f;
+	return expf(logf(top_resolution * (float)aabb_scale / (float)base_resolution) / (float)(n_levels - 1));
+}
+
+extern "C" uint32_t neus2b_testbed_config_active_levels(const neus2b_testbed_config* c, uint32_t training_step) {
+	if (!c) return 0;
+	const uint32_t L = c->grid.n_levels;
+	uint32_t n = c->grid.n_active_levels < L ? c->grid.n_active_levels : L;
+	if (c->base_training_step) {  // the reference's keys (configs/nerf/dtu.json:35-37)
+		float frac = c->base_valid_level_scale + c->valid_level_scale * (float)(training_step / c->base_training_step);
+		if (!(frac < 1.0f)) frac = 1.0f;
+		if (!(frac > 0.f)) frac = 0.f;
+		n = (uint32_t)((float)L * frac + 0.5f);  // to the nearest level: 0.2 * 14 = 2.8 -> 3
+		n = n < 1u ? 1u : (n > L ? L : n);
+	} else if (c->progressive_steps_per_increment) {
+		n = c->progressive_start_levels + c->progressive_levels_per_increment * (training_step / c->progressive_steps_per_increment);
+		n = n < L ? n : L;
+	}
+	return n;
+}
+
+// After a synchronisation: has any kernel raised the sticky error word (a bounded wait that ran out)?
+static int device_error_status() {
+	uint32_t flags = 0;
+	const int rc = neus2b_device_error_flags(&flags);
+	if (rc) return rc;
+	return flags ? NEUS2B_E_DEVICE : NEUS2B_OK;
+}
+
 static neus2b_grid_desc active_desc(const neus2b_testbed* tb) {
 	neus2b_grid_desc d = tb->cfg.grid;
-	const neus2b_testbed_config& c = tb->cfg;
-	if (c.progressive_steps_per_increment) {
-		uint32_t n = c.progressive_start_levels + c.progressive_levels_per_increment * (tb->training_step / c.progressive_steps_per_increment);
-		d.n_active_levels = n < d.n_levels ? n : d.n_levels;
-	}
+	d.n_active_levels = neus2b_testbed_config_active_levels(&tb->cfg, tb->training_step);
 	return d;
 }
 
@@ -419,7 +461,7 @@ static neus2b_train_cfg make_train_cfg(const neus2b_testbed* tb) {
 	c.cone_angle_constant = 0.f;  // aabb_scale <= 1 (src/testbed_nerf.cu:3084)
 	c.snap_to_pixel_centers = tb->cfg.snap_to_pixel_centers;
 	c.random_bg_color = tb->cfg.random_bg_color;
-	c.loss_scale = 128.f;
+	c.loss_scale = tb->cfg.loss_scale;  // LOSS_SCALE (testbed.h:237) = 128 by default
 	c.mask_loss_weight = tb->cfg.mask_loss_weight;
 	c.ek_loss_weight = tb->cfg.ek_loss_weight;
 	// NerfNetwork::cos_anneal_ratio (nerf_network.h:1109-1118)
@@ -498,7 +540,7 @@ extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
 	const uint32_t next = tb->training_step + (tb->step_pending ? 1u : 0u);
 	if (next % occupancy_skip(next) == 0) return 1;
 	if (tb->step_pending && !tb->tuned) {
-		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
+		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
 		N2B_CHECK_LAUNCH();
 		tb->tuned = true;
 	}
@@ -547,14 +589,16 @@ static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 	ac.epsilon = c.epsilon;
 	ac.l2_reg = c.l2_reg;
 	ac.ema_decay = c.ema_decay;
-	ac.loss_scale = 128.f;  // LOSS_SCALE (testbed.h:237)
+	ac.loss_scale = c.loss_scale;
 	ac.step = step;
 	ac.n_matrix = NEUS2B_MLP_N;
+	ac.flags = c.adam_flags;
+	ac.d_nonfinite = &tb->state->nonfinite;
 	int rc = neus2b_adam_step(&ac, tb->n_params, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->master, tb->adam_m, tb->adam_v,
 	                          (uint16_t*)tb->params, (uint16_t*)tb->params_ema, tb->ema_master, tb->stream);
 	if (rc) return rc;
 	if (!tb->tuned) {
-		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays);
+		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
 		N2B_CHECK_LAUNCH();
 	}
 	tb->tuned = false;
@@ -583,7 +627,10 @@ extern "C" int neus2b_testbed_train_wait_stats(neus2b_testbed* tb, neus2b_train_
 	h_stats->overflow = tb->h_state->overflow;
 	h_stats->loss = tb->h_state->loss;
 	h_stats->ek_loss = tb->h_state->ek_loss;
-	return NEUS2B_OK;
+	h_stats->nonfinite_gradients = tb->h_state->nonfinite;
+	h_stats->device_error = tb->h_state->device_error;
+	// a bounded wait inside a kernel ran out: that step's gradients are not to be trusted
+	return tb->h_state->device_error ? NEUS2B_E_DEVICE : NEUS2B_OK;
 }
 
 extern "C" int neus2b_testbed_train_optimizer_step(neus2b_testbed* tb, neus2b_train_stats* h_stats) {
@@ -643,7 +690,7 @@ extern "C" int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3]
 		N2B_CHECK_LAUNCH();
 	}
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
-	return NEUS2B_OK;
+	return device_error_status();
 }
 
 // ------------------------------------------------------------------------------------------------ rendering
@@ -756,7 +803,7 @@ extern "C" int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_req
 	if (h_depth) N2B_CHECK_CUDA(cudaMemcpyAsync(h_depth, tb->render_depth, (size_t)n_pix * 4, cudaMemcpyDeviceToHost, tb->stream));
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	N2B_CHECK_CUDA(cudaEventElapsedTime(&tb->render_ms, tb->render_ev[0], tb->render_ev[1]));
-	return NEUS2B_OK;
+	return device_error_status();
 }
 
 extern "C" int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n_samples, float* device_ms) {
@@ -848,6 +895,7 @@ extern "C" int neus2b_testbed_set_array(neus2b_testbed* tb, int which, const voi
 		rc = neus2b_occupancy_mean_and_bitfield(tb->cfg.n_cascades, tb->density_grid, tb->bitfield, tb->density_mean, tb->occ_partial, tb->stream);
 		if (rc) return rc;
 		tb->occ_bounds_stale = true;
+		tb->pregenerated = false;  // samples drawn ahead were marched through the previous occupancy bits
 	}
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	return NEUS2B_OK;

@@ -122,7 +122,12 @@ def load_snapshot(tb, path):
         set_array(tb, "adam_m", np.frombuffer(opt["nested"]["first_moments_binary"], np.float32))
         set_array(tb, "adam_v", np.frombuffer(opt["nested"]["second_moments_binary"], np.float32))
     else:
+        # the reference resets the network before it deserialises (src/testbed.cu:3215): a file without optimizer state
+        # leaves a fresh optimizer behind, whatever the testbed had trained before
         tb.set_params(half_bits.view(np.float16).astype(np.float32))
+        zeros = np.zeros(tb.n_params, np.float32)
+        set_array(tb, "adam_m", zeros)
+        set_array(tb, "adam_v", zeros)
     grid = np.frombuffer(snap["density_grid_binary"], np.float16).astype(np.float32)
     if grid.size == GRIDSIZE ** 3 * int(tb.config.n_cascades):
         set_array(tb, "density_grid", grid)

@@ -9,11 +9,15 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("NEUS2_REFERENCE", "/root/reference")
+# the checkout of 19reborn/NeuS2 to read: NEUS2_REFERENCE, else a folder named "reference" beside this repository;
+# without either nothing is extracted
+REF = os.environ.get("NEUS2_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 OUT = os.path.join(HERE, "_ref", "mc_tri_table.npy")
 
 
 def extract():
+    if not REF:
+        return None
     path = os.path.join(REF, "src", "marching_cubes.cu")
     if not os.path.exists(path):
         return None

@@ -919,10 +919,15 @@ static inline void neus_sample(const uint16_t* o, const float* c, const float* d
 	float sdf = h2f(o[3]);
 	for (int e = 0; e < 3; ++e) s->nrm[e] = h2f(o[4 + e]);
 	s->true_cos = dir[0] * s->nrm[0] + dir[1] * s->nrm[1] + dir[2] * s->nrm[2];
-	float r1 = -s->true_cos * 0.5f + 0.5f, r2 = -s->true_cos;
-	s->iter_cos = -((r1 > 0.f ? r1 : 0.f) * (1.0f - anneal) + (r2 > 0.f ? r2 : 0.f) * anneal);
-	s->next_sdf = sdf + s->iter_cos * s->dt * 0.5f;
-	float prev_sdf = sdf - s->iter_cos * s->dt * 0.5f;
+	/* The reference writes these lines with double literals (0.5, 1.0), so the intermediates are fp64 and each line rounds
+	 * to fp32 once (:1594-1598): r1 is rounded when it is passed to activation_function(float), the product with the
+	 * annealing ratio is a float product, the sum and the two sdf estimates are fp64 sums. */
+	float r1 = (float)((double)(-s->true_cos) * 0.5 + 0.5), r2 = -s->true_cos;
+	float relu2a = (r2 > 0.f ? r2 : 0.f) * anneal;
+	s->iter_cos = (float)(-((double)(r1 > 0.f ? r1 : 0.f) * (1.0 - (double)anneal) + (double)relu2a));
+	float half_step = s->iter_cos * s->dt; /* float product, then * 0.5 in fp64 (exact) */
+	s->next_sdf = (float)((double)sdf + (double)half_step * 0.5);
+	float prev_sdf = (float)((double)sdf - (double)half_step * 0.5);
 	float next_cdf = logisticf(s->next_sdf * s->inv_s), prev_cdf = logisticf(prev_sdf * s->inv_s);
 	s->p_div_c = (prev_cdf - next_cdf + 1e-5f) / (prev_cdf + 1e-5f);
 	s->alpha = clampf(s->p_div_c, 0.0f, 1.0f);
@@ -1007,9 +1012,10 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 			lgl[e] = (ad > al ? (ad - 0.5f * al) : 0.5f / al * diff * diff) / 5.0f;
 			lgg[e] = (ad > al ? (diff > 0 ? 1.0f : -1.0f) : diff / al) / 5.0f;
 		}
-		float mask_gt = tex[3] > 0.9999f ? 1.f : 0.f, gws, ws = c.weight_sum;
-		if (ws >= 1.0f - 1e-4f) { ws = 1.0f - 1e-4f; gws = 0.f; }
-		else if (ws <= 1e-4f) { ws = 1e-4f; gws = 0.f; }
+		/* double literals in the reference (:1690-1702): the comparisons are fp64, the assigned constants round to fp32 */
+		float mask_gt = (double)tex[3] > 0.9999 ? 1.f : 0.f, gws, ws = c.weight_sum;
+		if ((double)ws >= 1.0 - 1e-4) { ws = (float)(1.0 - 1e-4); gws = 0.f; }
+		else if ((double)ws <= 1e-4) { ws = (float)1e-4; gws = 0.f; }
 		else { float sg = 1.0f / (1.0f + expf(-ws)); gws = (mask_gt - sg) * ws * cfg->mask_loss_weight; }
 		const float n_rays_f = (float)n_rays * (float)(cfg->ray_count_scale ? cfg->ray_count_scale : 1u);
 		if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
@@ -1042,14 +1048,14 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 				g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
 				dla += lgg[e] * (T * s.rgb[e] - suffix);
 			}
-			dla /= (1.0f - s.alpha + 1e-5f);
+			dla = (float)((double)dla / ((double)(1.0f - s.alpha) + 1e-5)); /* "/ (1.0f - alpha + 1e-5)": fp64 divide (:1829-1832) */
 			float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
 			if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {
 				float P = expf(s.inv_s * s.iter_cos * s.dt);
 				float E = expf(-s.next_sdf * s.inv_s);
 				dE_dsdf = -s.inv_s * E;
 				dE_ds = -s.next_sdf * E;
-				float a = 1 + E, b = 1 + P * E, cc = 1e-5f + 1 / (1 + P * E);
+				float a = 1 + E, b = 1 + P * E, cc = (float)(1e-5 + (double)(1 / (1 + P * E))); /* "1e-5 + 1/(...)": fp64 sum (:1862) */
 				float delta = a * (b * b) * (cc * cc);
 				da_dE = -(P / delta - 1 / (a * a * cc));
 				da_dP = -E / delta;
@@ -1060,7 +1066,8 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 			float dl_dinvs = dla * (da_dE * dE_ds + da_dP * dP_ds);
 			float dl_dvar = dl_dinvs * s.inv_s * 10;
 			float dic_dcos = s.true_cos >= 0 ? 0.0f : 1.0f;
-			float gn = sqrtf(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2] + 1e-6f);
+			/* std::sqrt(float sum + 1e-6): the sum of squares is fp32, the offset and the root are fp64 (:1884) */
+			float gn = (float)sqrt((double)(s.nrm[0] * s.nrm[0] + s.nrm[1] * s.nrm[1] + s.nrm[2] * s.nrm[2]) + 1e-6);
 			float gni = 1 - 1 / gn;
 			float dl_dnn = dla * (da_dE * dE_dic + dP_dic * da_dP) * dic_dcos;
 			g[3] = loss_scale * (dla * da_dE * dE_dsdf);

@@ -2,7 +2,7 @@
 utils/mlp_weights.txt, the sphere-initialised SDF-MLP weights (64x48 + 16x64 floats, row-major [out][in],
 include/neural-graphics-primitives/nerf_network.h:774-823).
 
-Run in the build container, where the reference is mounted:  python tests/golden/make_geometric_init_golden.py
+Run where a checkout of the reference is at hand:  NEUS2_REFERENCE=<checkout> python tests/golden/make_geometric_init_golden.py
 
 The golden file holds (a) the weights rounded to fp16 (the precision the networks run in), (b) 256 seeded query points,
 (c) the SDF-net output of the CPU oracle for them with an all-zero hash grid, and (d) structural facts of the file that
@@ -15,10 +15,12 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("NEUS2_REFERENCE", "/root/reference")
+REF = os.environ.get("NEUS2_REFERENCE") or (sys.argv[1] if len(sys.argv) > 1 else None)
 
 
 def main():
+    if not REF:
+        raise SystemExit("set NEUS2_REFERENCE (or pass the path) to a checkout of 19reborn/NeuS2")
     from oracle import oracle as O
     w = np.loadtxt(os.path.join(REF, "utils", "mlp_weights.txt"), dtype=np.float64)
     assert w.size == 64 * 48 + 16 * 64

@@ -56,3 +56,48 @@ def test_pcg32_host(oracle):
     assert (a.state, a.inc) == (b.state, b.inc)
     a, b = L.pcg32_advance(a, 2 ** 40 + 5), oracle.pcg32_advance(b, 2 ** 40 + 5)
     assert a.state == b.state
+
+
+def test_ray_count_beyond_the_scan_capacity_is_refused_without_a_gpu():
+    """neus2b_generate_samples / neus2b_compute_loss take at most NEUS2B_MAX_RAYS_PER_CALL rays (the ray-order prefix sum
+    holds one shared-memory offset per tile of 4096 keys, 256 tiles): more is refused before anything is launched."""
+    import ctypes as C
+    from neus2_b200 import _lib as L
+    fake = C.c_void_p(256)  # never dereferenced: the refusal comes first
+    n = (1 << 20) + 128
+    ws = L.RayWorkspace(n, 1 << 20, fake, fake, fake, fake, fake, fake, fake, None, None, None)
+    ds = L.Dataset(1, 8, 8, fake, fake, fake, fake)
+    cfg = L.train_cfg()
+    rng = L.pcg32(1)
+    assert L.lib().neus2b_generate_samples(C.byref(ds), C.byref(cfg), C.c_uint32(n), None, C.c_uint32(0), rng, fake, C.byref(ws), None) == -5
+    assert L.lib().neus2b_compute_loss(C.byref(ds), C.byref(cfg), C.c_uint32(n), None, C.c_uint32(0), rng, C.c_uint32(1 << 18), fake,
+                                       C.byref(ws), fake, fake, None, None, C.c_int(0), None) == -5
+    assert L.lib().neus2b_error_string(-5) == b"request exceeds a compiled-in capacity"
+
+
+def test_progressive_level_schedules():
+    """The level mask as a function of the step: the reference's keys (configs/nerf/dtu.json:35-37, this library's reading
+    of them), BASELINE config 2's wording, and neither."""
+    import ctypes as C
+    from neus2_b200 import _lib as L
+    cfg = L.TestbedConfig()
+    L.lib().neus2b_testbed_default_config(C.byref(cfg))
+    act = lambda step: int(L.lib().neus2b_testbed_config_active_levels(C.byref(cfg), C.c_uint32(step)))
+    assert [act(s) for s in (0, 5000, 10 ** 6)] == [16, 16, 16]
+    # the literal values of the reference's dtu.json: 14 levels, top_resolution 2048 -> per_level_scale, mask keys
+    cfg.grid.n_levels = cfg.grid.n_active_levels = 14
+    scale = L.lib().neus2b_per_level_scale_from_top_resolution(14, 16, 2048.0, 1)
+    assert abs(scale - np.exp(np.log(2048.0 / 16.0) / 13.0)) < 1e-6
+    cfg.grid.per_level_scale = scale
+    off, res, sc, hashed = L.grid_level_table(cfg.grid)
+    assert res[13] in (2048, 2049)  # the top resolution by the rule of src/testbed.cu:2177 (2048 up to rounding of b^13)
+    cfg.base_training_step, cfg.valid_level_scale, cfg.base_valid_level_scale = 200, 0.02, 0.2
+    want = lambda step: max(1, min(14, int(np.float32(14) * min(np.float32(1.0), np.float32(0.2) + np.float32(0.02) * np.float32(step // 200)) + np.float32(0.5))))
+    for step in (0, 199, 200, 1000, 1999, 2000, 5000, 7999, 8000, 20000):
+        assert act(step) == want(step), step
+    assert act(0) == 3 and act(8000) == 14 and act(6000) < 14
+    # BASELINE config 2: 8 levels, 2 more every 500 steps
+    cfg.base_training_step = 0
+    cfg.grid.n_levels = cfg.grid.n_active_levels = 16
+    cfg.progressive_start_levels, cfg.progressive_levels_per_increment, cfg.progressive_steps_per_increment = 8, 2, 500
+    assert [act(s) for s in (0, 499, 500, 1999, 2000, 9999)] == [8, 8, 10, 14, 16, 16]

@@ -189,13 +189,13 @@ def test_fused_forward(gpu, oracle, case, path):
     out = f32(ops.neus_forward(to_lib_desc(L, d), half(params), dev(coords), sdf_bias=-0.1))
     assert L.device_error_flags() == 0
     tag = "fused_fwd_p%d_n%d_L%d_a%d" % (path, coords.shape[0], d.n_levels, d.n_active_levels)
-    check_fp16(tag + "_rgb", out[:, 0:3], ref[:, 0:3], min_frac=0.995, min_cos=0.999)
-    check_fp16(tag + "_sdf", out[:, 3], ref[:, 3], min_frac=0.995, min_cos=0.9999)
-    check_fp16(tag + "_normal", out[:, 4:7], ref[:, 4:7], min_frac=0.995, min_cos=0.999)
+    check_fp16(tag + "_rgb", out[:, 0:3], ref[:, 0:3], min_frac=0.9999, min_cos=0.99999)
+    check_fp16(tag + "_sdf", out[:, 3], ref[:, 3], min_frac=0.9999, min_cos=0.99999)
+    check_fp16(tag + "_normal", out[:, 4:7], ref[:, 4:7], min_frac=0.9999, min_cos=0.99999)
     assert np.array_equal(out[:, 7:11], ref[:, 7:11])
     sdf = f32(ops.neus_sdf(to_lib_desc(L, d), half(params), dev(coords[:, :3].copy()), sdf_bias=-0.1))
     sref = O.bits_f32(O.neus_sdf(d, params, coords[:, :3]))
-    check_fp16(tag + "_sdf_only", sdf, sref, min_frac=0.995)
+    check_fp16(tag + "_sdf_only", sdf, sref, min_frac=0.9999)
 
 
 def test_fused_forward_device_count(gpu, oracle):

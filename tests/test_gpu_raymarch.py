@@ -144,7 +144,7 @@ def test_loss_and_compaction(gpu, oracle, n_rays, target, variance):
     assert np.array_equal(coords_out.cpu().numpy()[:nv].view(np.uint32), ref["coords"][:nv].view(np.uint32))
     got, want = dloss.float().cpu().numpy()[:nv], O.bits_f32(ref["dloss"])[:nv]
     for name, sl in [("rgb", slice(0, 3)), ("sdf", slice(3, 4)), ("eik", slice(4, 7)), ("var", slice(7, 8)), ("cos", slice(8, 11))]:
-        check_fp16("dloss_%s_%d" % (name, n_rays), got[:, sl], want[:, sl], rel=2e-3, min_frac=0.995, min_cos=0.9995)
+        check_fp16("dloss_%s_%d" % (name, n_rays), got[:, sl], want[:, sl], rel=2e-3, min_frac=0.998, min_cos=0.9999)
     assert np.allclose(loss.cpu().numpy()[:k], ref["loss"][:k], rtol=2e-3, atol=1e-9)
     assert np.allclose(ek.cpu().numpy()[:k], ref["ek_loss"][:k], rtol=2e-3, atol=1e-9)
     # roll-over: pad to the target batch by wrap-around and rescale the gradient
@@ -197,7 +197,7 @@ def test_occupancy_update_matches_oracle(gpu, oracle):
         # density from the GPU's SDF values: the splat / EMA / threshold chain is what is under test here
         sdf_gpu = bits(occ.sdf[:2 * n])
         sref = O.neus_sdf(d, params, pos)
-        check_fp16("occ_sdf_step%d" % step, O.bits_f32(sdf_gpu), O.bits_f32(sref), min_frac=0.995)
+        check_fp16("occ_sdf_step%d" % step, O.bits_f32(sdf_gpu), O.bits_f32(sref), min_frac=0.9999)
         dens = O.sdf_to_density(sdf_gpu, params[O.GRID_OFF + O.grid_n_params(d)])
         grid = O.occ_splat_ema(idx, dens, grid, 0.95)
         got = occ.grid.cpu().numpy()

@@ -43,3 +43,52 @@ def test_generated_table_matches_reference_counts():
         pytest.skip("reference case table not extracted on this machine")
     t = make_table()
     assert ((t >= 0).sum(1) == (ref >= 0).sum(1)).all()
+
+
+def _triangles(row):
+    r = [int(x) for x in row if x >= 0]
+    return [tuple(r[k:k + 3]) for k in range(0, len(r), 3)]
+
+
+def _boundary_loops(tris):
+    """Oriented boundary polygons of a triangle list: the directed edges without a reversed partner, chained."""
+    edges = set()
+    for a, b, c in tris:
+        edges.update(((a, b), (b, c), (c, a)))
+    nxt = {}
+    for u, v in edges:
+        if (v, u) not in edges:
+            assert u not in nxt
+            nxt[u] = v
+    loops, seen = [], set()
+    for s in sorted(nxt):
+        if s in seen:
+            continue
+        loop, cur = [], s
+        while cur not in seen:
+            seen.add(cur)
+            loop.append(cur)
+            cur = nxt[cur]
+        assert cur == s
+        loops.append(tuple(loop))
+    return sorted(loops)
+
+
+def test_generated_table_has_the_reference_polygons():
+    """In each of the 256 cases the generated table cuts the cube along the same oriented polygons as the reference's table
+    (same resolution of the ambiguous faces, same winding): the two meshes are the same polygon surface, and differ only in
+    the diagonals that split a polygon of four to seven vertices into triangles."""
+    from neus2_b200.mc_table import make_table
+    from oracle import extract_mc_table as X
+    ref = X.load()
+    if ref is None:
+        import pytest
+        pytest.skip("reference case table not extracted on this machine")
+    t = make_table()
+    n_same_triangles = 0
+    for case in range(256):
+        a, b = _triangles(ref[case]), _triangles(t[case])
+        assert _boundary_loops(a) == _boundary_loops(b), case
+        canon = lambda tr: sorted(min((x[k:] + x[:k] for k in range(3))) for x in tr)
+        n_same_triangles += canon(a) == canon(b)
+    assert n_same_triangles >= 96  # the cases whose polygons are all triangles, and those where the diagonals happen to agree

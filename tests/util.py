@@ -9,8 +9,11 @@ _METRICS = {}
 
 
 def record(name, **kw):
-    """Keeps the measured errors of the GPU parity tests next to the run (parity_metrics.json in the run's output folder)."""
-    out = os.path.join(ROOT, "gpurun_out")
+    """Keeps the measured errors of the GPU parity tests in parity_metrics.json in the folder NEUS2B_METRICS_DIR names
+    (nothing is written when the variable is unset)."""
+    out = os.environ.get("NEUS2B_METRICS_DIR")
+    if not out:
+        return
     path = os.path.join(out, "parity_metrics.json")
     if not _METRICS and os.path.exists(path):
         try:
