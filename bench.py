@@ -172,6 +172,8 @@ def run_ours(args):
     sizes = [args.steps // n_blocks + (1 if b < args.steps % n_blocks else 0) for b in range(n_blocks)]
     ms = ms_e2e = 0.0
     kernel_ms_sum, kernel_launches = 0.0, 0
+    launches_before = L.launch_count()
+    step_first = int(st.training_step) + max(args.warmup - 1, 0)
     for nb in sizes:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -203,20 +205,27 @@ def run_ours(args):
     ms_step = ms / args.steps
     value = BATCH * world * args.steps / (ms * 1e-3)
     e2e_value = BATCH * world * args.steps / (ms_e2e * 1e-3)
-    n_occ = occupancy_updates_between(first_step, 2 * args.steps)
-    launches = (2 * args.steps * 12 + n_occ * 16) // 2  # per arm
+    # kernels of libneus2b.so launched inside the two timed arms (counted by the library at every launch site); NCCL's
+    # all-reduce kernels on several GPUs are not the library's and are not counted
+    launches = L.launch_count() - launches_before
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
             "data": "synthetic", "config": workload_config(world),
+            "gpu_launches_note": "libneus2b.so kernels inside both timed arms (2 x steps training steps)",
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": int(sum(c.nbytes for c in cams)), "d2h_bytes_per_step": 32},
             "gpu_launches": launches, "clocks": clocks,
-            "train_state": {"training_step": int(st.training_step), "rays_per_batch": int(st.rays_per_batch),
+            "train_state": {"timed_steps": [step_first, int(st.training_step)], "training_step": int(st.training_step),
+                            "rays_per_batch": int(st.rays_per_batch),
                             "samples_before_compaction": int(st.measured_batch_size_before_compaction),
                             "samples_after_compaction": int(st.measured_batch_size), "loss": float(st.loss),
                             "ek_loss": float(st.ek_loss), "overflow": int(st.overflow)}}
 
+    # ---- mesh extraction at 512^3, sharded by z-slab over the ranks (SDF lattice with the EMA weights, marching cubes with
+    # global numbering, counters all-gathered, slices gathered into rank 0): not part of `value`
+    if not args.no_mesh:
+        line["mesh_512"] = mesh_record(tb, rank, world, args.mesh_res)
     if rank == 0:
         # ---- roofline of the dominant kernel (fused forward+backward over the 2^18 compacted samples), timed alone
         line["roofline"] = roofline_train_kernel(tb, ptrs, st, ng, kernel_ms_sum / max(kernel_launches, 1), kernel_launches)
@@ -229,10 +238,49 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM traffic of one launch of the fused forward+backward kernel at 2^18 samples (dram__bytes_read.sum +
-# dram__bytes_write.sum of the `ncu --set full` capture summarised in profiles/): the hash table and its gradient table
-# stay in L2, what reaches HBM is their first touch plus the sample streams.
+def mesh_record(tb, rank, world, res):
+    """Times the sharded extraction (max over ranks, CUDA events) and checks on rank 0 that it equals this GPU's own
+    extraction of the whole lattice."""
+    import hashlib
+    import torch
+    import torch.distributed as dist
+
+    def run():
+        return tb.compute_marching_cubes_mesh_sharded_device(res, rank, world, use_ema=True)
+    run()  # warm-up (allocations, NCCL point-to-point connections)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    v, i = run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    rec = {"res": res, "ms": float(ms.item()), "n_gpus": world, "sharding": "z-slab per rank, global numbering on the devices"}
+    if rank == 0:
+        def digest(a, b):
+            return hashlib.sha1(a.contiguous().cpu().numpy().tobytes() + b.contiguous().cpu().numpy().tobytes()).hexdigest()[:16]
+        rec.update(verts=int(v.shape[0]), triangles=int(i.shape[0] // 3), sha1=digest(v, i))
+        if world > 1:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            v1, i1 = tb.compute_marching_cubes_mesh(res, use_ema=True)
+            t1.record()
+            torch.cuda.synchronize()
+            rec.update(single_gpu_ms=t0.elapsed_time(t1), equal_to_single_gpu=bool(digest(v1, i1.view(torch.int32)) == rec["sha1"]))
+    return rec
+
+
+# Figures of one launch of the fused forward+backward kernel at 2^18 samples from the `ncu --set full` capture summarised
+# in profiles/neus_tc_kernel_train_2p18_samples.txt (constants copied from that capture, not measured by this run):
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum: the hash table and its gradient table stay in L2, what
+# reaches HBM is their first touch plus the sample streams), L2 sectors requested by the SMs, tensor-pipe activity.
 TRAIN_KERNEL_DRAM_BYTES = 59969536 + 534016
+TRAIN_KERNEL_L2_SECTORS = 30405708
+TRAIN_KERNEL_TENSOR_PIPE_PCT = 4.6
 
 
 def roofline_train_kernel(tb, ptrs, st, ng, ms_in_step, launches_in_step):
@@ -244,10 +292,12 @@ def roofline_train_kernel(tb, ptrs, st, ng, ms_in_step, launches_in_step):
     import torch
     from neus2_b200 import ops
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peak, src = 6650.0, "fallback"
+    peak, src, tensor_peak = 6650.0, "fallback", 1400.0
     if os.path.exists(peaks_path):
         try:
-            peak, src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+            pk = json.load(open(peaks_path))
+            peak, src = float(pk["hbm_gbs"]), "measured"
+            tensor_peak = float(pk.get("bf16_tflops_sustained", tensor_peak))  # the kernel is timed inside a long step
         except (KeyError, ValueError, OSError):
             pass
     g = torch.Generator(device="cuda")
@@ -289,7 +339,15 @@ def roofline_train_kernel(tb, ptrs, st, ng, ms_in_step, launches_in_step):
     return {"kernel": "neus_tc_kernel<TRAIN> (tcgen05 fused forward+backward, 2^18 samples per launch)", "bound": "hbm",
             "achieved": achieved, "peak": peak,
             "peak_source": src + " (MEASURED_PEAKS.json hbm_gbs)" if src == "measured" else "fallback 6.65 TB/s",
-            "unit": "GB/s", "frac": achieved / peak, "traffic": TRAIN_KERNEL_DRAM_BYTES, "ms_per_launch": ms,
+            "unit": "GB/s", "frac": achieved / peak, "traffic": TRAIN_KERNEL_DRAM_BYTES,
+            "traffic_source": "constant from the ncu capture summarised in profiles/neus_tc_kernel_train_2p18_samples.txt",
+            "bound_note": "the denominator is the HBM copy peak, but the kernel is not HBM-bound: its algorithmic bytes are table "
+                          "gathers and reductions served by L1/L2 (DRAM traffic is 0.2x the algorithmic bytes); what limits it is the "
+                          "latency of those gathers and reductions at 16 resident warps per SM and the per-sample arithmetic around them",
+            "l2_sector_gbs": TRAIN_KERNEL_L2_SECTORS * 32 / (ms * 1e-3) / 1e9,
+            "tensor_pipe_active_pct_ncu": TRAIN_KERNEL_TENSOR_PIPE_PCT,
+            "tensor_frac": 96256 * n / (ms * 1e-3) / 1e12 / tensor_peak,
+            "tensor_peak_tflops": tensor_peak, "ms_per_launch": ms,
             "launches_timed": launches_in_step, "ms_per_launch_cold_l2": ms_cold,
             "algorithmic_bytes_per_sample": bytes_per_sample, "flop_per_sample": 96256,
             "achieved_tflops": 96256 * n / (ms * 1e-3) / 1e12}
@@ -595,6 +653,7 @@ def main():
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
     ap.add_argument("--mesh-res", type=int, default=512)
+    ap.add_argument("--no-mesh", action="store_true", help="skip the 512^3 mesh extraction record behind the timed steps")
     ap.add_argument("--render-res", type=int, nargs=2, default=[1600, 1200], help="width height of --kernel render (DTU images are 1600x1200)")
     ap.add_argument("--render-fov", type=float, default=30.0)
     args = ap.parse_args()

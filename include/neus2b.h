@@ -62,6 +62,9 @@ typedef struct {
 #define NEUS2B_GRID_OFF 12288
 
 const char* neus2b_version(void);
+/* Kernel launches this library has issued in this process so far (a counter every launch site increments; for callers that
+ * want to state how many of the library's kernels ran inside a timed region). */
+uint64_t neus2b_launch_count(void);
 const char* neus2b_error_string(int code);
 
 /* GridEncoding::level_n_params / level_params_offset (src/testbed.cu:1861-1877).  offsets[17] in grid ENTRIES (2 fp16). */
@@ -200,6 +203,8 @@ int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_train_cfg* cf
  * (more returns NEUS2B_E_TOO_LARGE).  The first call on a device looks the arrays' addresses up
  * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls on a device share the arrays:
  * calls that overlap on the GPU race, so issue them one after another on one stream.
+ * This is the plain form of the generator: it takes neither the optional record of march masks nor the box of occupied
+ * cells that neus2b_ray_workspace can carry, so every ray is marched twice and none is culled (same result, more time).
  * Outputs (caller-allocated): d_ray_indices [n_rays], d_rays [n_rays][6], d_numsteps [n_rays][2],
  * d_coords [max_samples][7], d_counters [8] (layout as in neus2b_ray_workspace). */
 #define NEUS2B_STATIC_MAX_RAYS 65536u
@@ -394,6 +399,22 @@ int neus2b_marching_cubes_slab(const float aabb_min[3], const float aabb_max[3],
                                float thresh, const float* d_sdf_slab, const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts,
                                uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts,
                                neus2b_stream_t stream);
+
+/* One z-slab with GLOBAL numbering, for extraction sharded over GPUs without a merge on the host (the reference extracts on
+ * one GPU, src/marching_cubes.cu:794-822).  A slab that is followed by another (halo = 1) gets n_layers + 1 layers of SDF:
+ * with the extra layer it can number the vertices of its last own layer exactly as the next slab numbers them (that slab
+ * owns and writes them), so every index it writes is already the vertex's final id once vertex_offset = the number of
+ * vertices the slabs before it own.  The last slab passes halo = 0 and owns all its vertices.
+ * Pass 1 (d_verts == NULL): d_counts[0] = vertex ids the slab refers to, [1] = indices it writes, [2] = vertices it owns.
+ * Between the passes the caller exchanges counts [1] and [2] of all slabs (an all-gather of two numbers per rank) and forms
+ * the exclusive prefix sums.  Pass 2: d_verts float[owned][3] and d_indices uint32[counts[1]] are this slab's slices of the
+ * whole mesh: concatenated in slab order they equal neus2b_marching_cubes on the undivided lattice bit for bit.
+ * Scratch sized for {res[0], res[1], n_layers + halo}. */
+int neus2b_marching_cubes_slab_global(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0,
+                                      uint32_t n_layers, uint32_t halo, float thresh, const float* d_sdf_slab,
+                                      const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts,
+                                      uint32_t* d_indices, uint32_t max_indices, uint32_t vertex_offset, uint32_t* d_counts,
+                                      neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- inference rendering (NerfTracer, Testbed::render_nerf) */
 

@@ -104,7 +104,7 @@ _lib = None
 
 # every symbol include/neus2b.h declares
 EXPORTS = [
-    "neus2b_version", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
+    "neus2b_version", "neus2b_launch_count", "neus2b_error_string", "neus2b_grid_level_table", "neus2b_grid_n_params", "neus2b_model_n_params",
     "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
     "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
     "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_set_device_error_flags",
@@ -113,7 +113,7 @@ EXPORTS = [
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
     "neus2b_testbed_train", "neus2b_testbed_device_ptrs", "neus2b_testbed_train_backward", "neus2b_testbed_train_pregenerate", "neus2b_testbed_train_optimizer_step_async", "neus2b_testbed_train_wait_stats", "neus2b_testbed_train_step",
-    "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab",
+    "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab", "neus2b_marching_cubes_slab_global",
     "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
     "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh", "neus2b_occupancy_mean_and_bitfield",
     "neus2b_testbed_get_training_state", "neus2b_testbed_set_training_state", "neus2b_testbed_get_array", "neus2b_testbed_set_array",
@@ -137,6 +137,7 @@ def lib():
         _lib.neus2b_per_level_scale_from_top_resolution.restype = C.c_float
         _lib.neus2b_per_level_scale_from_top_resolution.argtypes = [C.c_uint32, C.c_uint32, C.c_float, C.c_uint32]
         _lib.neus2b_testbed_config_active_levels.restype = C.c_uint32
+        _lib.neus2b_launch_count.restype = C.c_uint64
     return _lib
 
 
@@ -155,6 +156,10 @@ def device_error_flags():
     v = C.c_uint32(0)
     check(lib().neus2b_device_error_flags(C.byref(v)))
     return int(v.value)
+
+
+def launch_count():
+    return int(lib().neus2b_launch_count())
 
 
 def set_device_error_flags(flags):

@@ -19,3 +19,11 @@ extern "C" const char* neus2b_error_string(int code) {
 	if (code > 0) return cudaGetErrorString((cudaError_t)code);
 	return "unknown error";
 }
+
+// Kernel launches issued by this library in this process (every launch site counts itself through N2B_CHECK_LAUNCH).
+#include <atomic>
+namespace n2b {
+static std::atomic<uint64_t> g_launch_count{0};
+void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace n2b
+extern "C" uint64_t neus2b_launch_count(void) { return n2b::g_launch_count.load(std::memory_order_relaxed); }

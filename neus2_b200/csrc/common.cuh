@@ -14,9 +14,14 @@
 	} while (0)
 #define N2B_CHECK_LAUNCH()                        \
 	do {                                          \
+		n2b::count_launch();                      \
 		cudaError_t _e = cudaGetLastError();      \
 		if (_e != cudaSuccess) return (int)_e;    \
 	} while (0)
+
+namespace n2b {
+void count_launch();  // capi.cu: every kernel launch of the library passes here (neus2b_launch_count)
+}
 
 namespace n2b {
 
@@ -124,22 +129,12 @@ __device__ __forceinline__ __half2 ldg_h2(const __half* grid, uint32_t entry) {
 // is an `atom` with a result that travels back from L2 and holds a register until it arrives, whether it is used or not.
 __device__ __forceinline__ void red_add_h2(__half* grid_grad, uint32_t entry, float g0, float g1) {
 	const __half2 v = __floats2half2_rn(g0, g1);
-#ifdef N2B_ABL_NOSCATTER
-	if (entry == 0xffffffffu)
-#endif
-#ifdef N2B_ATOM_H2
-	atomicAdd(reinterpret_cast<__half2*>(grid_grad) + entry, v);
-#else
 	asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(reinterpret_cast<__half2*>(grid_grad) + entry), "r"(*reinterpret_cast<const uint32_t*>(&v))
 	             : "memory");
-#endif
 }
 // Two neighbouring entries (entry even: 8-byte aligned) in one reduction.
 __device__ __forceinline__ void red_add_h2x2(__half* grid_grad, uint32_t entry, float a0, float a1, float b0, float b1) {
 	const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
-#ifdef N2B_ABL_NOSCATTER
-	if (entry == 0xffffffffu)
-#endif
 	asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1, %2};" ::"l"(reinterpret_cast<__half2*>(grid_grad) + entry),
 	             "r"(*reinterpret_cast<const uint32_t*>(&va)), "r"(*reinterpret_cast<const uint32_t*>(&vb))
 	             : "memory");

@@ -572,13 +572,10 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 									v[bx][1] = __fmaf_rn(w, dz1, coef * gef.y);
 								}
 								const uint32_t e0 = geom_index(g2, k), e1 = geom_index(g2, k + 1u);
-#ifndef N2B_NO_V2
 								if ((e0 ^ e1) == 1u) {
 									if (e0 & 1u) red_add_h2x2(a.grad_grid, e1, v[1][0], v[1][1], v[0][0], v[0][1]);
 									else red_add_h2x2(a.grad_grid, e0, v[0][0], v[0][1], v[1][0], v[1][1]);
-								} else
-#endif
-								{
+								} else {
 									red_add_h2(a.grad_grid, e0, v[0][0], v[0][1]);
 									red_add_h2(a.grad_grid, e1, v[1][0], v[1][1]);
 								}

@@ -15,6 +15,11 @@ struct McGrid {
 	uint32_t rx, ry, rz;
 	uint64_t res2, res3;
 	uint32_t z_off;  // the slab's first lattice layer in the whole grid (vertex positions are those of the whole grid)
+	// A slab that is followed by another one carries that slab's first layer pair as a halo: the layers [count_rz, rz) own no
+	// vertices, the cells from layer face_rz - 1 on emit no triangles, and the vertices of the layers [own_rz, count_rz) are
+	// numbered (exactly as the next slab numbers them) but not written.  Without a halo all four equal rz.
+	uint32_t face_rz, count_rz, own_rz;
+	uint32_t vertex_offset;  // added to every vertex id written into the index buffer (global numbering)
 	float thresh;
 	float scale[3], offset[3];
 };
@@ -48,8 +53,8 @@ __global__ void __launch_bounds__(256) mc_count_kernel(McGrid g, const float* __
 	const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (idx >= g.res3) return;
 	const uint32_t x = (uint32_t)(idx % g.rx), y = (uint32_t)((idx / g.rx) % g.ry), z = (uint32_t)(idx / g.res2);
-	uint64_t key = (uint64_t)__popc(cell_crossings(g, sdf, idx, x, y, z));
-	if (x + 1 < g.rx && y + 1 < g.ry && z + 1 < g.rz) {
+	uint64_t key = z < g.count_rz ? (uint64_t)__popc(cell_crossings(g, sdf, idx, x, y, z)) : 0ull;
+	if (x + 1 < g.rx && y + 1 < g.ry && z + 1 < g.face_rz) {
 		const int mask = cube_mask(g, sdf, idx);
 		if (mask && mask != 255) {
 			const int8_t* tri = tri_table + mask * 16;
@@ -141,9 +146,12 @@ __global__ void mc_counts_kernel(McGrid g, const uint64_t* __restrict__ keys, co
 	const uint32_t nv = (uint32_t)(*grand_total & 0xFFFFFFFFull);
 	counts[0] = nv;
 	counts[1] = (uint32_t)(*grand_total >> 32);
-	if (slab) {
+	if (slab == 1) {
 		counts[2] = (uint32_t)(keys[(uint64_t)(g.rz - 1) * g.res2] & 0xFFFFFFFFull);
 		counts[3] = g.rz > 1 ? (uint32_t)(keys[g.res2] & 0xFFFFFFFFull) : nv;
+	} else if (slab == 2) {  // globally numbered slab: vertices this slab owns (= writes)
+		counts[2] = g.own_rz < g.rz ? (uint32_t)(keys[(uint64_t)g.own_rz * g.res2] & 0xFFFFFFFFull) : nv;
+		counts[3] = 0;
 	}
 }
 
@@ -152,7 +160,7 @@ __device__ __forceinline__ uint32_t edge_vertex(const McGrid& g, const float* __
                                                 uint32_t axis) {
 	const uint32_t x = (uint32_t)(c % g.rx), y = (uint32_t)((c / g.rx) % g.ry), z = (uint32_t)(c / g.res2);
 	const uint32_t m = cell_crossings(g, sdf, c, x, y, z);
-	return (uint32_t)(keys[c] & 0xFFFFFFFFull) + __popc(m & ((1u << axis) - 1u));
+	return g.vertex_offset + (uint32_t)(keys[c] & 0xFFFFFFFFull) + __popc(m & ((1u << axis) - 1u));
 }
 
 __global__ void __launch_bounds__(256) mc_emit_kernel(McGrid g, const float* __restrict__ sdf, const int8_t* __restrict__ tri_table,
@@ -163,7 +171,7 @@ __global__ void __launch_bounds__(256) mc_emit_kernel(McGrid g, const float* __r
 	const uint32_t x = (uint32_t)(idx % g.rx), y = (uint32_t)((idx / g.rx) % g.ry), z = (uint32_t)(idx / g.res2);
 	const uint64_t key = keys[idx];
 	// gen_vertices (:276-329)
-	const uint32_t m = cell_crossings(g, sdf, idx, x, y, z);
+	const uint32_t m = z < g.own_rz ? cell_crossings(g, sdf, idx, x, y, z) : 0u;
 	if (m) {
 		uint32_t vid = (uint32_t)(key & 0xFFFFFFFFull);
 		const float f0 = sdf[idx];
@@ -183,7 +191,7 @@ __global__ void __launch_bounds__(256) mc_emit_kernel(McGrid g, const float* __r
 		}
 	}
 	// gen_faces (:377-718)
-	if (x + 1 < g.rx && y + 1 < g.ry && z + 1 < g.rz) {
+	if (x + 1 < g.rx && y + 1 < g.ry && z + 1 < g.face_rz) {
 		const int mask = cube_mask(g, sdf, idx);
 		if (mask && mask != 255) {
 			const int8_t* tri = tri_table + mask * 16;
@@ -229,16 +237,21 @@ extern "C" int neus2b_marching_cubes_scratch_bytes(const uint32_t res[3], uint64
 
 static int marching_cubes_impl(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0, uint32_t n_layers, int slab,
                                float thresh, const float* d_sdf, const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts,
-                               uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts, cudaStream_t stream) {
+                               uint32_t max_verts, uint32_t* d_indices, uint32_t max_indices, uint32_t* d_counts, cudaStream_t stream,
+                               uint32_t halo = 0, uint32_t vertex_offset = 0) {
 	if (!aabb_min || !aabb_max || !res || !d_sdf || !d_tri_table || !d_scratch || !d_counts) return NEUS2B_E_INVALID;
-	if (res[0] < 2 || res[1] < 2 || res[2] < 2 || n_layers < 2 || (uint64_t)z0 + n_layers > res[2]) return NEUS2B_E_INVALID;
+	if (res[0] < 2 || res[1] < 2 || res[2] < 2 || n_layers < 2 || (uint64_t)z0 + n_layers + halo > res[2] || halo > 1) return NEUS2B_E_INVALID;
 	McGrid g;
 	g.rx = res[0];
 	g.ry = res[1];
-	g.rz = n_layers;
+	g.rz = n_layers + halo;
+	g.face_rz = n_layers;
+	g.count_rz = n_layers;
+	g.own_rz = halo ? n_layers - 1 : n_layers;
+	g.vertex_offset = vertex_offset;
 	g.z_off = z0;
 	g.res2 = (uint64_t)res[0] * res[1];
-	g.res3 = g.res2 * n_layers;
+	g.res3 = g.res2 * g.rz;
 	if (g.res3 > (1ull << 32)) return NEUS2B_E_TOO_LARGE;
 	g.thresh = thresh;
 	for (int k = 0; k < 3; ++k) {
@@ -283,4 +296,13 @@ extern "C" int neus2b_marching_cubes_slab(const float aabb_min[3], const float a
                                           neus2b_stream_t stream) {
 	return marching_cubes_impl(aabb_min, aabb_max, res, z0, n_layers, 1, thresh, d_sdf_slab, d_tri_table, d_scratch, d_verts, max_verts, d_indices,
 	                           max_indices, d_counts, stream);
+}
+
+extern "C" int neus2b_marching_cubes_slab_global(const float aabb_min[3], const float aabb_max[3], const uint32_t res[3], uint32_t z0,
+                                                 uint32_t n_layers, uint32_t halo, float thresh, const float* d_sdf_slab,
+                                                 const int8_t* d_tri_table, uint64_t* d_scratch, float* d_verts, uint32_t max_verts,
+                                                 uint32_t* d_indices, uint32_t max_indices, uint32_t vertex_offset, uint32_t* d_counts,
+                                                 neus2b_stream_t stream) {
+	return marching_cubes_impl(aabb_min, aabb_max, res, z0, n_layers, 2, thresh, d_sdf_slab, d_tri_table, d_scratch, d_verts, max_verts, d_indices,
+	                           max_indices, d_counts, stream, halo, vertex_offset);
 }

@@ -332,7 +332,6 @@ extern "C" int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t*
 			const int src = launch_scan(n_rays, nullptr, ws->d_scan_tmp, stream);
 			if (src) return src;
 		}
-		N2B_CHECK_LAUNCH();
 		// the one read per band: how many windows of max_samples the band's samples fill
 		uint64_t total = 0;
 		N2B_CHECK_CUDA(cudaMemcpyAsync(&total, ws->d_scan_tmp + n_rays, sizeof(uint64_t), cudaMemcpyDeviceToHost, stream));

@@ -238,6 +238,37 @@ def marching_cubes_slab(sdf_slab, res, z0, tri_table=None, thresh=0.0, aabb_min=
     return dict(verts=verts[:nv].cpu().numpy(), indices=idx[:ni].cpu().numpy().view("uint32"), nv_before_last=nbl, nv_first=nf)
 
 
+class SlabGlobal:
+    """neus2b_marching_cubes_slab_global in its two passes: `count()` -> (ids referred to, indices written, vertices owned) on the
+    device, then `emit(vertex_offset)` -> (verts [owned][3], indices [n]) CUDA tensors with global vertex ids."""
+
+    def __init__(self, sdf_slab, res, z0, n_layers, halo, tri_table=None, thresh=0.0, aabb_min=(0.0, 0.0, 0.0), aabb_max=(1.0, 1.0, 1.0)):
+        if tri_table is None:
+            from .mc_table import make_table
+            tri_table = torch.from_numpy(make_table())
+        assert sdf_slab.shape[0] == n_layers + halo and sdf_slab.is_contiguous()
+        self.dev = sdf_slab.device
+        self.sdf, self.tt = sdf_slab, tri_table.to(device=self.dev, dtype=torch.int8).contiguous()
+        r_slab = (C.c_uint32 * 3)(int(res[0]), int(res[1]), n_layers + halo)
+        nb = C.c_uint64(0)
+        L.check(L.lib().neus2b_marching_cubes_scratch_bytes(r_slab, C.byref(nb)))
+        self.scratch = torch.empty(nb.value // 8, dtype=torch.int64, device=self.dev)
+        self.counts = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.args = ((C.c_float * 3)(*aabb_min), (C.c_float * 3)(*aabb_max), (C.c_uint32 * 3)(*[int(v) for v in res]), u32(z0),
+                     u32(n_layers), u32(halo), C.c_float(thresh), L.ptr(self.sdf), L.ptr(self.tt), L.ptr(self.scratch))
+
+    def count(self):
+        L.check(L.lib().neus2b_marching_cubes_slab_global(*self.args, None, u32(0), None, u32(0), u32(0), L.ptr(self.counts), L.cur_stream()))
+        return self.counts
+
+    def emit(self, vertex_offset, n_owned, n_indices):
+        verts = torch.empty((max(n_owned, 1), 3), dtype=torch.float32, device=self.dev)
+        idx = torch.empty(max(n_indices, 1), dtype=torch.int32, device=self.dev)
+        L.check(L.lib().neus2b_marching_cubes_slab_global(*self.args, L.ptr(verts), u32(n_owned), L.ptr(idx), u32(n_indices), u32(vertex_offset),
+                                                          L.ptr(self.counts), L.cur_stream()))
+        return verts[:n_owned], idx[:n_indices]
+
+
 def occupancy_bounds(bitfield):
     """int32[6] CUDA tensor {min x, y, z, max x, y, z} of the occupied cells of the finest level."""
     out = torch.zeros(8, dtype=torch.int32, device=bitfield.device)

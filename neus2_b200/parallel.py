@@ -19,10 +19,74 @@ def ray_shard(rank, max_rays=1 << 18):
     return rank * max_rays
 
 
-def allreduce_gradients(tensors, group=None, stream=None):
+class PeerFailure(RuntimeError):
+    """Another rank left the job, or did not reach the exchange in time.  The step's collective was not entered (or was
+    abandoned): local gradients are intact, parameters have not been updated."""
+
+
+class StepGuard:
+    """Host-side agreement before a step's gradient exchange, through the process group's key-value store (no GPU work, no
+    collective): every rank counts itself in for the step; a rank that finds a peer gone, or not there within
+    `timeout_s`, raises PeerFailure instead of entering a collective that could never complete.  A rank that stops
+    between steps calls `leave()` first, with none of its kernels or collectives in flight.
+
+    One store round trip per checked step: check every `every` steps (1 = every step)."""
+
+    def __init__(self, store, rank, world, timeout_s=30.0, every=1, prefix="neus2b"):
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s, self.every, self.prefix = float(timeout_s), max(1, int(every)), prefix
+
+    def leave(self, reason="left"):
+        self.store.add(f"{self.prefix}/left", 1)
+        self.store.set(f"{self.prefix}/left_by/{self.rank}", reason)
+
+    def peers_left(self):
+        return int(self.store.add(f"{self.prefix}/left", 0))
+
+    def check(self, step):
+        """All ranks present for `step`?  Returns once they are; raises PeerFailure otherwise."""
+        import time
+        if step % self.every:
+            return
+        key = f"{self.prefix}/step/{step}"
+        try:
+            self.store.add(key, 1)
+            deadline = time.monotonic() + self.timeout_s
+            while True:
+                if self.peers_left():
+                    raise PeerFailure(f"rank {self.rank}: a peer left the job before step {step}")
+                if int(self.store.add(key, 0)) >= self.world:
+                    return
+                if time.monotonic() > deadline:
+                    raise PeerFailure(f"rank {self.rank}: {self.world - int(self.store.add(key, 0))} peer(s) did not reach step {step} "
+                                      f"within {self.timeout_s:g} s")
+                time.sleep(0.0005)
+        except PeerFailure:
+            raise
+        except Exception as e:  # the store's host is gone
+            raise PeerFailure(f"rank {self.rank}: the job's store cannot be reached before step {step}: {e}") from e
+
+
+def allreduce_gradients(tensors, group=None, stream=None, timeout_s=None):
     """Sum every gradient buffer over the ranks, in place.  On CUDA the collectives are enqueued behind `stream` (the
-    training stream of the testbed), so they run between the backward kernels and the optimizer pass without a host sync."""
+    training stream of the testbed), so they run between the backward kernels and the optimizer pass without a host sync.
+    With `timeout_s` the host waits for the collectives and raises PeerFailure if they do not complete in time (a peer
+    that stalled or died inside the exchange) instead of waiting for ever."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    if timeout_s is not None:
+        import datetime
+        ctx = torch.cuda.stream(stream) if stream is not None else _null()
+        with ctx:
+            works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True) for t in tensors]
+            try:
+                for w in works:
+                    if not w.wait(timeout=datetime.timedelta(seconds=float(timeout_s))):
+                        raise PeerFailure("gradient all-reduce did not complete")
+            except PeerFailure:
+                raise
+            except Exception as e:  # the backends report a timed-out wait as RuntimeError / DistBackendError
+                raise PeerFailure(f"gradient all-reduce failed or timed out after {timeout_s:g} s: {e}") from e
         return
     if stream is not None:
         with torch.cuda.stream(stream):
@@ -31,6 +95,14 @@ def allreduce_gradients(tensors, group=None, stream=None):
     else:
         for t in tensors:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
 
 
 def device_view(ptr, nbytes, dtype):
@@ -54,9 +126,13 @@ class DataParallelTrainer:
     """Drives one testbed per process; `step()` = local backward, gradient all-reduce, optimizer.  With `overlap` the next
     step's sample generation runs while the gradients are exchanged."""
 
-    def __init__(self, testbed, grid_n_params, overlap=True):
+    def __init__(self, testbed, grid_n_params, overlap=True, guard=None, exchange_timeout_s=None):
+        """`guard` (a StepGuard) makes every rank agree on the host that all peers are present before the step's
+        collectives are launched; `exchange_timeout_s` bounds the wait for the collectives themselves.  Both raise
+        PeerFailure; both are off by default (one store round trip, one host wait per step)."""
         self.tb = testbed
         self.overlap = overlap
+        self.guard, self.exchange_timeout_s, self.steps = guard, exchange_timeout_s, 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.grads = gradient_views(testbed, grid_n_params) if self.world > 1 else None
         self.stream = torch.cuda.ExternalStream(testbed.device_ptrs()["stream"])
@@ -73,9 +149,12 @@ class DataParallelTrainer:
             # the next step's camera upload and sample generation are enqueued before the host waits for this step's
             # statistics, so the GPU has work while the host wakes up and issues the next launches
             return self.tb.train_step(next_cameras, read_stats=read_stats)
+        if self.guard is not None:
+            self.guard.check(self.steps)  # before anything of this step is launched: a missing peer costs no GPU state
+        self.steps += 1
         self.tb.train_backward()
-        if not self.overlap:
-            allreduce_gradients(self.grads, stream=self.stream)
+        if not self.overlap or self.exchange_timeout_s is not None:
+            allreduce_gradients(self.grads, stream=self.stream, timeout_s=self.exchange_timeout_s)
             if next_cameras is not None:
                 self.tb.update_cameras(*next_cameras)
             return self.tb.optimizer_step(read_stats=read_stats)

@@ -39,6 +39,13 @@ class Testbed:
         self.background_color = np.array([0.0, 0.0, 0.0, 1.0], np.float32)
         self.rendering_min_transmittance = 0.01
 
+    @classmethod
+    def from_network_config(cls, network_config, aabb_scale=1, **overrides):
+        """A testbed configured by one of the reference's network configuration files (configs/nerf/*.json) or the parsed
+        dict: what ``Testbed.reload_network_from_file`` (src/python_api.cu:339, src/testbed.cu:2093-2339) sets up."""
+        from . import config
+        return cls(config=config.testbed_config_from_json(network_config, aabb_scale=aabb_scale), **overrides)
+
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
             L.lib().neus2b_testbed_destroy(self._h)
@@ -254,3 +261,17 @@ class Testbed:
         def slab(z0, nl):
             return ops.marching_cubes_slab(self.sdf_grid(res, z0, z0 + nl, use_ema=use_ema), res, z0, tri_table=tri_table, thresh=thresh)
         return mesh_shard.extract_mesh_sharded(slab, res, rank, world, gather=gather)
+
+    def compute_marching_cubes_mesh_sharded_device(self, resolution, rank, world, thresh=0.0, tri_table=None, use_ema=True, group=None,
+                                                   dst=0):
+        """The same mesh with every slab numbered on its own device: SDF of the slab (and of one halo layer when another slab
+        follows), count pass, all-gather of the counters over the process group, emit pass at the global offsets, gather of
+        the slices into rank `dst` (point-to-point).  No merge or re-indexing on the host.  Returns CUDA tensors
+        (verts [n][3] float32, indices [m] int32) on rank `dst`, (None, None) on the others."""
+        from . import mesh_shard, ops
+        res = [int(r) for r in (resolution if hasattr(resolution, "__len__") else (resolution,) * 3)]
+
+        def slab(z0, nl, halo):
+            return ops.SlabGlobal(self.sdf_grid(res, z0, z0 + nl + halo, use_ema=use_ema), res, z0, nl, halo, tri_table=tri_table,
+                                  thresh=thresh)
+        return mesh_shard.extract_mesh_sharded_device(slab, res, rank, world, group=group, dst=dst)

@@ -86,3 +86,68 @@ def test_ray_shard_offsets():
     sys.path.insert(0, ROOT)
     from neus2_b200 import parallel as P
     assert [P.ray_shard(r) for r in range(4)] == [0, 1 << 18, 2 << 18, 3 << 18]
+
+
+# ------------------------------------------------------------------------------------------------ failures, made on the host
+
+def _failure_worker(rank, world, port, q, mode):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import datetime
+    import time
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=datetime.timedelta(seconds=60))
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    sys.path.insert(0, ROOT)
+    from neus2_b200 import parallel as P
+    guard = P.StepGuard(store, rank, world, timeout_s=2.0)
+    grad = torch.full((1024,), float(rank + 1))
+    out = {"rank": rank, "steps_done": 0, "error": None}
+    t0 = time.monotonic()
+    try:
+        for step in range(6):
+            if mode == "leaves" and rank == 1 and step == 3:
+                guard.leave("done early")  # between steps: nothing of this rank is in flight
+                break
+            if mode == "never_arrives" and rank == 1 and step == 3:
+                time.sleep(6.0)  # stalls on the host past the others' patience, then finds them gone
+            if mode != "stalls_in_exchange":
+                guard.check(step)
+            if mode == "stalls_in_exchange" and rank == 1 and step == 3:
+                time.sleep(5.0)
+                break
+            g = grad.clone()
+            P.allreduce_gradients([g], timeout_s=1.5 if mode == "stalls_in_exchange" else None)
+            assert float(g[0]) == 3.0
+            out["steps_done"] = step + 1
+    except P.PeerFailure as e:
+        out["error"] = "PeerFailure: " + str(e)
+    out["seconds"] = time.monotonic() - t0
+    q.put(out)
+    q.close()
+    q.join_thread()
+    os._exit(0)  # the process group may be unusable after a failed collective: leave without its destructor
+
+
+@pytest.mark.parametrize("mode", ["leaves", "never_arrives", "stalls_in_exchange"])
+def test_a_missing_peer_gives_an_error_not_a_hang(mode):
+    """One of two ranks leaves between steps, never arrives at a step, or stalls inside the exchange: the other rank's step
+    raises PeerFailure within its timeout instead of waiting for ever.  The failure is made on the host (CPU ranks over gloo)."""
+    world, port = 2, 31000 + (os.getpid() * 7 + len(mode)) % 2000
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_failure_worker, args=(r, world, port, q, mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        o = q.get(timeout=120)
+        res[o["rank"]] = o
+    for p in procs:
+        p.join(timeout=60)
+    r0 = res[0]
+    assert r0["steps_done"] == 3 and r0["error"] and r0["error"].startswith("PeerFailure"), res
+    assert r0["seconds"] < 20, res
+    if mode == "leaves":
+        assert res[1]["error"] is None and res[1]["steps_done"] == 3
+        assert "left" in r0["error"]
+    if mode == "never_arrives":
+        assert "did not reach step 3" in r0["error"]

@@ -102,6 +102,36 @@ def test_sharded_extraction_equals_the_whole_grid(world):
     assert np.array_equal(i, i_ref.cpu().numpy().view(np.uint32))
 
 
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+@pytest.mark.parametrize("kind,res", [("torus_box", (44, 36, 40)), ("noise", (17, 13, 9))])
+def test_globally_numbered_slabs_concatenate_to_the_whole_mesh(world, kind, res):
+    """Each slab counts, learns its offsets from the counters of the slabs before it, and writes its slice with final vertex
+    ids: the slices put one after another are the undivided mesh, bit for bit (ranks emulated one after another here)."""
+    from neus2_b200 import mesh_shard as M
+    from neus2_b200 import ops
+    sdf = sdf_field((res[2], res[1], res[0]), kind)
+    g = torch.from_numpy(sdf).cuda()
+    v_ref, i_ref = ops.marching_cubes(g)
+    slabs, counts = [], []
+    for z0, nl in M.slab_ranges(res[2], world):
+        halo = 1 if nl > 1 and z0 + nl < res[2] else 0
+        sl = ops.SlabGlobal(g[z0:z0 + nl + halo].contiguous(), res, z0, nl, halo) if nl > 1 else None
+        slabs.append(sl)
+        counts.append(sl.count().cpu().tolist() if sl is not None else [0, 0, 0, 0])
+    v_off, i_off, nv, ni = M.global_offsets(counts)
+    assert nv == v_ref.shape[0] and ni == i_ref.shape[0]
+    vs, is_ = [], []
+    for r, sl in enumerate(slabs):
+        if sl is None:
+            continue
+        v, i = sl.emit(v_off[r], counts[r][2], counts[r][1])
+        vs.append(v)
+        is_.append(i)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat(vs).view(torch.int32), v_ref.view(torch.int32))
+    assert torch.equal(torch.cat(is_), i_ref)
+
+
 def test_testbed_sharded_mesh_matches_single_pass(oracle):
     from neus2_b200 import synthetic as S
     from neus2_b200 import _lib as L

@@ -32,13 +32,14 @@ def _setup(oracle):
     c = np.stack([inv(idx), inv(idx >> 1), inv(idx >> 2)], 1).astype(np.float32)
     grid = (np.linalg.norm((c + 0.5) / 128.0 - 0.5, axis=1) < 0.33).astype(np.float32)
     bits, _ = oracle.occ_bitfield(grid, 1)
-    return L, ops, ds, torch.from_numpy(bits).cuda()
+    ods = oracle.make_dataset(sc["pixels"].numpy().view(np.uint32), sc["xforms"].numpy(), sc["focal"].numpy(), sc["principal"].numpy())
+    return L, ops, ds, torch.from_numpy(bits).cuda(), ods, bits
 
 
 def test_static_scratch_entry_point_matches_the_allocating_one(oracle):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
-    L, ops, ds, bitfield = _setup(oracle)
+    L, ops, ds, bitfield, ods, bits_host = _setup(oracle)
     cfg = L.train_cfg()
     max_samples = 1 << 19
     for call, (n_rays, total, seed) in enumerate([(8192, 111, 7), (3000, 99999, 8)]):  # two calls in a row, shared scratch
@@ -50,9 +51,13 @@ def test_static_scratch_entry_point_matches_the_allocating_one(oracle):
         numsteps = torch.zeros((n_rays, 2), dtype=i32, device="cuda")
         coords = torch.zeros((max_samples, 7), dtype=f32, device="cuda")
         counters = torch.full((8,), -1, dtype=i32, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         ops.generate_samples_static(ds, cfg, n_rays, total, L.pcg32(seed), bitfield, max_samples, ray_indices, rays, numsteps,
                                     coords, counters)
         torch.cuda.synchronize()
+        if call > 0:  # (the first call on a device looks the scratch arrays' addresses up, which may load the module)
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call must not change the device's free memory"
         cnt = batch.counters.cpu().numpy()
         assert cnt[0] > 0 and cnt[1] > 0, "the case must generate samples"
         assert np.array_equal(counters.cpu().numpy(), cnt), call
@@ -62,12 +67,17 @@ def test_static_scratch_entry_point_matches_the_allocating_one(oracle):
         assert torch.equal(numsteps[:k], batch.numsteps[:k])
         assert torch.equal(rays[:k].view(i32), batch.rays[:k].view(i32))
         assert torch.equal(coords[:used].view(i32), batch.coords[:used].view(i32))
+        # and directly against the CPU restatement of the reference's generator
+        ref = oracle.generate_samples(ods, oracle.train_cfg(), n_rays, total, max_samples, oracle.pcg32(seed), bits_host)
+        assert k == ref["n_kept"] and int(cnt[1]) == ref["n_samples"]
+        assert np.array_equal(numsteps.cpu().numpy().view(np.uint32)[:k], ref["numsteps"][:k])
+        assert np.array_equal(coords.cpu().numpy()[:used].view(np.uint32), ref["coords"][:used].view(np.uint32))
 
 
 def test_static_scratch_entry_point_rejects_oversized_batches(oracle):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
-    L, ops, ds, bitfield = _setup(oracle)
+    L, ops, ds, bitfield, _, _ = _setup(oracle)
     one = torch.zeros(64, dtype=torch.int32, device="cuda")
     with pytest.raises(L.Neus2bError, match="-5"):
         ops.generate_samples_static(ds, L.train_cfg(), 65537, 0, L.pcg32(1), bitfield, 1024, one, one.float(), one, one.float(), one)
