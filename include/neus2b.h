@@ -113,6 +113,8 @@ int neus2b_mlp_backward_backward_input(uint32_t n, uint32_t in_width, const uint
 /* SphericalHarmonics degree 4 of 2*dir-1 (configs/nerf/base.json:48-62; nerf_network.h:251). */
 int neus2b_sh4_forward(uint32_t n, const float* d_dir01, uint32_t stride, uint16_t* d_out, neus2b_stream_t stream);
 
+typedef struct neus2b_motion neus2b_motion; /* dynamic sequences: the frame's learned rigid motion, defined below */
+
 /* ---------------------------------------------------------------- fused NeuS graph (NerfNetwork) */
 
 /* Two implementations of the fused graph kernels exist: tcgen05.mma on 128-sample CTA tiles with accumulators in tensor
@@ -138,6 +140,41 @@ int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t* d_params, 
 int neus2b_neus_train(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
                       const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp, uint16_t* d_grad_grid,
                       float* d_grad_variance, neus2b_stream_t stream);
+/* ---- dynamic sequences: the DeltaNetwork (include/neural-graphics-primitives/transform_network.h:26-170), a learned rigid
+ * motion applied to every sample ahead of the encoding while the frames after the first are trained (NerfNetwork::forward_impl
+ * with m_use_delta, nerf_network.h:149-169; backward :589-625).  d_delta: 12 fp16 parameters in the network's own order,
+ * transition [0..3] (xyz, one unused) then the 6-D rotation [4..11] (two 3-vectors, two unused); identity = 0 0 0 0 | 1 0 0 0 1 0 0 0.
+ * A sample moves as x' = R (x + t - first_frame_offset) + first_frame_offset, dir' = (R (2 dir - 1) + 1) / 2. */
+struct neus2b_motion {
+	const uint16_t* d_delta;     /* NULL: no motion (the first frame; m_use_delta false) */
+	float first_frame_offset[3]; /* Testbed::m_first_frame_offset (testbed.h:455), 0 */
+	float* d_sums;               /* training only, optional: float[12], the backward's batch sums are ADDED here:
+	                                [0..2] sum of dL/dx', [3..11] sum of dL/dx' (x) (x + t) row-major; neus2b_delta_optimizer_step
+	                                turns them into the parameters' gradients (NULL: m_train_delta false) */
+};
+/* neus2b_neus_forward / _train / _sdf with the motion applied first (motion may be NULL = the plain call).  In the training
+ * call the three canonical gradient pointers may all be NULL: the canonical model is frozen and only motion->d_sums is
+ * produced (the reference's m_train_canonical = false while it predicts a frame's global movement). */
+int neus2b_neus_forward_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
+                              const uint32_t* d_n, const float* d_coords, const neus2b_motion* motion, uint16_t* d_out,
+                              neus2b_stream_t stream);
+int neus2b_neus_train_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
+                            const neus2b_motion* motion, const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp,
+                            uint16_t* d_grad_grid, float* d_grad_variance, neus2b_stream_t stream);
+int neus2b_neus_sdf_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
+                          uint32_t x_stride, const neus2b_motion* motion, uint16_t* d_sdf, neus2b_stream_t stream);
+/* DeltaNetwork::forward_impl alone (add_global_movement_with_rotation_6d, common_operation.cuh:419-474): coords [n][7]. */
+int neus2b_delta_forward(const uint16_t* d_delta, const float first_frame_offset[3], uint32_t n, const float* d_coords_in,
+                         float* d_coords_out, neus2b_stream_t stream);
+/* DeltaNetwork::backward_impl's per-sample part (add_loss_to_rotation_6d_each, common_operation.cuh:793-849) reduced over the
+ * batch on the device: d_dL_dx [n][3] is the gradient w.r.t. the moved positions; the twelve sums are added to d_sums. */
+int neus2b_delta_backward(const uint16_t* d_delta, uint32_t n, const float* d_coords_in, const float* d_dL_dx, float* d_sums,
+                          neus2b_stream_t stream);
+/* NerfNetwork::accumulate_global_movement (nerf_network.h:1153-1167; accumulate_global_movement_rotation_6d_kernel,
+ * common_operation.cuh:555-589) on the host: rotation [9] row-major <- R rotation, transition [3] <- R (transition + t), both
+ * rounded to fp16-representable values (the reference keeps them in fp16 buffers). */
+int neus2b_movement_accumulate(const uint16_t h_delta[12], float rotation[9], float transition[3]);
+
 /* NerfNetwork::sdf (nerf_network.h:643-709): d_sdf [n] fp16 = y0 + bias. */
 int neus2b_neus_sdf(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
                     uint32_t x_stride, uint16_t* d_sdf, neus2b_stream_t stream);
@@ -169,6 +206,12 @@ typedef struct {
 	/* data-parallel ray sharding: this process draws rays [ray_index_offset, ray_index_offset + n_rays) of a logical
 	 * batch that is ray_count_scale times larger (loss normalisation uses n_rays * ray_count_scale); 0 / 1 = single GPU */
 	uint32_t ray_index_offset, ray_count_scale;
+	/* dynamic sequences: the accumulated global movement of the earlier frames, applied to every ray before the march
+	 * (global_movement_with_rotation_6d, src/testbed_nerf.cu:183-203; call sites :1370-1378, :1550-1558):
+	 * o = R (o - first_frame_offset) + t, dir = R dir with dir normalised before and not again after.  rotation row-major.
+	 * With it the rays written to d_rays are the moved ones (origin, unit direction). */
+	uint32_t use_global_movement;
+	float rotation[9], transition[3], first_frame_offset[3];
 } neus2b_train_cfg;
 
 /* Scratch for one batch of rays; every array is caller-allocated device memory.  One call handles at most
@@ -230,6 +273,14 @@ int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint16_t* d_para
                             float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
                             neus2b_stream_t stream);
 
+/* The same while a later frame of a dynamic sequence is trained: the SDF is queried through the frame's motion
+ * (NerfNetwork::density applies the DeltaNetwork, nerf_network.h:651-662).  motion may be NULL. */
+int neus2b_occupancy_update_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n_cascades,
+                                  uint32_t n_uniform, uint32_t n_nonuniform, neus2b_pcg32 rng_uniform, neus2b_pcg32 rng_nonuniform,
+                                  uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp, uint8_t* d_bitfield,
+                                  float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
+                                  const neus2b_motion* motion, neus2b_stream_t stream);
+
 /* Smallest box of cell indices {min x, y, z, max x, y, z} around the set bits of the finest level of the occupancy bitfield
  * (min > max when nothing is occupied); no counterpart in the reference, which marches every ray. */
 int neus2b_occupancy_bounds(const uint8_t* d_bitfield, int32_t* d_bounds, neus2b_stream_t stream);
@@ -267,6 +318,13 @@ int neus2b_adam_step(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, 
 int neus2b_adam_step_packed(const neus2b_adam_cfg* cfg, uint64_t n, float* d_grad_mlp, uint16_t* d_grad_grid,
                             float* d_grad_variance, float* d_state, uint16_t* d_params, uint16_t* d_params_ema,
                             neus2b_stream_t stream);
+
+/* DeltaNetwork's optimizer (dynamic sequences).  The sums -> the 12 parameters' gradients (transition: R^T sum dL/dx'; rotation: backward of the Gram-Schmidt construction,
+ * gradient_rotation_matrix_to_6d, common_operation.cuh:96-158) -> one step of the motion's own optimizer (the "globalmove"
+ * block of configs/nerf/base.json:84-110; m_global_move.trainer->optimizer_step, src/testbed_nerf.cu:3500-3502).  d_sums is
+ * cleared.  d_grad_out (optional, float[12]) receives the gradients; with d_master == NULL only they are computed. */
+int neus2b_delta_optimizer_step(const neus2b_adam_cfg* cfg, float* d_sums, float* d_master, float* d_m, float* d_v, uint16_t* d_delta,
+                                uint16_t* d_delta_ema, float* d_ema_master, float* d_grad_out, neus2b_stream_t stream);
 
 /* ---------------------------------------------------------------- training loop (Testbed, src/testbed.cu / src/testbed_nerf.cu) */
 
@@ -434,6 +492,11 @@ typedef struct {
 	                           buffer receives srgb_to_linear of them (shade_kernel_nerf) */
 	uint32_t max_steps;     /* samples per ray at most; 0 = 10000 (MARCH_ITER, src/testbed_nerf.cu:68, bounds the reference's
 	                           rounds) */
+	/* dynamic sequences: accumulated global movement applied to the camera rays (src/testbed_nerf.cu:2286-2296), as in
+	 * neus2b_train_cfg */
+	uint32_t use_global_movement;
+	float rotation[9], transition[3], first_frame_offset[3];
+	const uint16_t* d_delta; /* the current frame's learned motion applied to the samples (neus2b_motion::d_delta), or NULL */
 } neus2b_render_cfg;
 
 /* Scratch of the renderer; every array is caller-allocated device memory.  max_rays pixels (whole rows, at most 2^20) are

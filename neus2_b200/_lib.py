@@ -30,7 +30,13 @@ class TrainCfg(C.Structure):
     _fields_ = [("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
                 ("snap_to_pixel_centers", C.c_uint32), ("random_bg_color", C.c_uint32), ("background_color", C.c_float * 3),
                 ("loss_scale", C.c_float), ("mask_loss_weight", C.c_float), ("ek_loss_weight", C.c_float),
-                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32)]
+                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32),
+                ("use_global_movement", C.c_uint32), ("rotation", C.c_float * 9), ("transition", C.c_float * 3),
+                ("first_frame_offset", C.c_float * 3)]
+
+
+class Motion(C.Structure):
+    _fields_ = [("d_delta", C.c_void_p), ("first_frame_offset", C.c_float * 3), ("d_sums", C.c_void_p)]
 
 
 class RayWorkspace(C.Structure):
@@ -44,7 +50,8 @@ class RenderCfg(C.Structure):
                 ("camera", C.c_float * 12), ("pixel_offset", C.c_float * 2), ("sample_index", C.c_uint32),
                 ("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
                 ("min_transmittance", C.c_float), ("cos_anneal_ratio", C.c_float), ("linear_colors", C.c_uint32),
-                ("max_steps", C.c_uint32)]
+                ("max_steps", C.c_uint32), ("use_global_movement", C.c_uint32), ("rotation", C.c_float * 9),
+                ("transition", C.c_float * 3), ("first_frame_offset", C.c_float * 3), ("d_delta", C.c_void_p)]
 
 
 class RenderWorkspace(C.Structure):
@@ -108,7 +115,9 @@ EXPORTS = [
     "neus2b_grid_forward", "neus2b_grid_backward_input", "neus2b_grid_backward_params", "neus2b_grid_backward_backward_input",
     "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
     "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_set_device_error_flags",
-    "neus2b_per_level_scale_from_top_resolution", "neus2b_testbed_config_active_levels", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
+    "neus2b_per_level_scale_from_top_resolution", "neus2b_testbed_config_active_levels", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf",
+    "neus2b_neus_forward_moved", "neus2b_neus_train_moved", "neus2b_neus_sdf_moved", "neus2b_delta_forward", "neus2b_delta_backward",
+    "neus2b_delta_optimizer_step", "neus2b_movement_accumulate", "neus2b_occupancy_update_moved", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_occupancy_bounds", "neus2b_adam_step", "neus2b_adam_step_packed",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
@@ -226,8 +235,13 @@ def pcg32_advance(r, delta):
 
 def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, snap_to_pixel_centers=False,
               cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0), ray_index_offset=0,
-              ray_count_scale=1):
+              ray_count_scale=1, rotation=None, transition=None, first_frame_offset=(0.0, 0.0, 0.0)):
     c = TrainCfg()
+    if rotation is not None:
+        c.use_global_movement = 1
+        c.rotation[:] = [float(v) for v in rotation]
+        c.transition[:] = [float(v) for v in transition]
+        c.first_frame_offset[:] = list(first_frame_offset)
     c.aabb_min[:] = [0.0, 0.0, 0.0]
     c.aabb_max[:] = [1.0, 1.0, 1.0]
     c.cone_angle_constant = 0.0

@@ -15,6 +15,7 @@
 // permuted to match while they are staged), so the per-level feature pair is 4-byte aligned.
 #include "common.cuh"
 #include "fused_common.cuh"
+#include "delta.cuh"
 #include "mma_tile.cuh"
 
 namespace n2b {
@@ -220,6 +221,10 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == MODE_TRAIN ? 1 : 2) neus_
 				dir[1] = c[a.dir_offset + 1];
 				dir[2] = c[a.dir_offset + 2];
 			}
+		}
+		if (a.delta) {  // dynamic sequences: the frame's rigid motion comes first (only the SDF query supports it on this path)
+			const RigidMotion rm = load_rigid_motion(a.delta);
+			move_sample(rm.R, rm.t, a.first_frame_offset, x, dir);
 		}
 		// ---- F1: encoding -> Zs[:, 0:32], xyz - 0.5 -> Zs[:, 32:35]
 		float J[8][6];
@@ -576,12 +581,28 @@ extern "C" int neus2b_device_error_flags(uint32_t* h_flags) {
 }
 extern "C" int neus2b_set_device_error_flags(uint32_t flags) { return write_tc_error(flags); }
 
+static void fill_motion(NeusArgs& a, const neus2b_motion* motion) {
+	if (!motion || !motion->d_delta) return;
+	a.delta = (const __half*)motion->d_delta;
+	for (int e = 0; e < 3; ++e) a.first_frame_offset[e] = motion->first_frame_offset[e];
+	a.delta_sums = motion->d_sums;
+}
+
 extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
                                    const uint32_t* d_n, const float* d_coords, uint16_t* d_out, neus2b_stream_t stream) {
+	return neus2b_neus_forward_moved(desc, d_params, sdf_bias, n, d_n, d_coords, nullptr, d_out, stream);
+}
+
+extern "C" int neus2b_neus_forward_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
+                                         const uint32_t* d_n, const float* d_coords, const neus2b_motion* motion, uint16_t* d_out,
+                                         neus2b_stream_t stream) {
 	NeusArgs a = {};
 	int rc = fill_common(a, desc, d_params);
 	if (rc) return rc;
 	if (!d_coords || !d_out || ((uintptr_t)d_out & 15u)) return NEUS2B_E_INVALID;
+	fill_motion(a, motion);
+	a.delta_sums = nullptr;
+	if (a.delta && g_mma_path != NEUS2B_MMA_TCGEN05) return NEUS2B_E_UNSUPPORTED;
 	a.sdf_bias = sdf_bias;
 	a.n = n;
 	a.d_n = d_n;
@@ -596,12 +617,24 @@ extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t*
 extern "C" int neus2b_neus_train(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
                                  const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp, uint16_t* d_grad_grid,
                                  float* d_grad_variance, neus2b_stream_t stream) {
+	if (!d_grad_mlp || !d_grad_grid || !d_grad_variance) return NEUS2B_E_INVALID;
+	return neus2b_neus_train_moved(desc, d_params, n, d_coords, nullptr, d_dL_dout, indeed_batch_size, d_grad_mlp, d_grad_grid, d_grad_variance,
+	                               stream);
+}
+
+extern "C" int neus2b_neus_train_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
+                                       const neus2b_motion* motion, const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp,
+                                       uint16_t* d_grad_grid, float* d_grad_variance, neus2b_stream_t stream) {
 	NeusArgs a = {};
 	int rc = fill_common(a, desc, d_params);
 	if (rc) return rc;
-	if (!d_coords || !d_dL_dout || !d_grad_mlp || !d_grad_grid || !d_grad_variance || ((uintptr_t)d_dL_dout & 15u) ||
-	    indeed_batch_size == 0)
-		return NEUS2B_E_INVALID;
+	if (!d_coords || !d_dL_dout || ((uintptr_t)d_dL_dout & 15u) || indeed_batch_size == 0) return NEUS2B_E_INVALID;
+	// the canonical gradients are all there or all absent (a frame's first steps train the motion alone)
+	const bool canonical = d_grad_mlp && d_grad_grid && d_grad_variance;
+	if (!canonical && (d_grad_mlp || d_grad_grid || d_grad_variance)) return NEUS2B_E_INVALID;
+	fill_motion(a, motion);
+	if (!canonical && !a.delta_sums) return NEUS2B_E_INVALID;
+	if ((a.delta || !canonical) && g_mma_path != NEUS2B_MMA_TCGEN05) return NEUS2B_E_UNSUPPORTED;
 	a.n = n;
 	a.coords = d_coords;
 	a.coord_stride = 7;
@@ -617,10 +650,17 @@ extern "C" int neus2b_neus_train(const neus2b_grid_desc* desc, const uint16_t* d
 
 extern "C" int neus2b_neus_sdf(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
                                uint32_t x_stride, uint16_t* d_sdf, neus2b_stream_t stream) {
+	return neus2b_neus_sdf_moved(desc, d_params, sdf_bias, n, d_x, x_stride, nullptr, d_sdf, stream);
+}
+
+extern "C" int neus2b_neus_sdf_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n, const float* d_x,
+                                     uint32_t x_stride, const neus2b_motion* motion, uint16_t* d_sdf, neus2b_stream_t stream) {
 	NeusArgs a = {};
 	int rc = fill_common(a, desc, d_params);
 	if (rc) return rc;
 	if (!d_x || !d_sdf || x_stride < 3) return NEUS2B_E_INVALID;
+	fill_motion(a, motion);
+	a.delta_sums = nullptr;
 	a.sdf_bias = sdf_bias;
 	a.n = n;
 	a.coords = d_x;

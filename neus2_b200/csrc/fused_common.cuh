@@ -23,6 +23,11 @@ struct NeusArgs {
 	__half* grad_grid;
 	float* grad_var;
 	__half* sdf_out;
+	// dynamic sequences: the frame's learned rigid motion (DeltaNetwork, nerf_network.h:149-169) is applied to every sample
+	// before anything else when delta != nullptr; training adds the twelve sums of its backward to delta_sums when given
+	const __half* delta;
+	float first_frame_offset[3];
+	float* delta_sums;
 };
 
 // original column of the SDF-net input for internal column k

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "fused_common.cuh"
 #include "tc05.cuh"
+#include "delta.cuh"
 
 namespace n2b {
 namespace tcf {
@@ -59,6 +60,9 @@ struct Smem {
 	__half gst[MODE == MODE_TRAIN ? 128 : 1][8];      // rows 3..10 of a sample's output gradient, from part 0 to part 1
 	float nrm[kParts][128][3];
 	float vbuf[128][4];
+	float dxc[MODE == MODE_TRAIN ? 128 : 1][3];  // xyz rows of the colour-net input gradient (for the DeltaNetwork's dL/dx)
+	float motion[12];                            // the frame's rigid motion: R row-major, t
+	float dsum[12];                              // this CTA's share of the DeltaNetwork's backward sums
 	float red[kThreads / 32];
 	uint64_t mbar;
 	uint32_t tmem_base;
@@ -164,6 +168,14 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	}
 	for (int e = tid; e < 64 * 64; e += kThreads)
 		*reinterpret_cast<__half*>(sm.W2c + tc::blk_off(e / 64, e % 64, 64)) = a.params[NEUS2B_RGB_W2 + e];
+	const bool moved = a.delta != nullptr;
+	if (tid == 0 && moved) {
+		const RigidMotion rm = load_rigid_motion(a.delta);
+#pragma unroll
+		for (int k = 0; k < 9; ++k) sm.motion[k] = rm.R[k];
+#pragma unroll
+		for (int k = 0; k < 3; ++k) sm.motion[9 + k] = rm.t[k];
+	}
 	const uint32_t mbar = sptr(&sm.mbar);
 	if (tid == 0) tc::mbar_init(mbar, 1);
 	if (warp == 0) tc::tmem_alloc(sptr(&sm.tmem_base), kTmemCols);
@@ -229,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			dir[1] = c[a.dir_offset + 1];
 			dir[2] = c[a.dir_offset + 2];
 		}
+		if (moved) move_sample(sm.motion, sm.motion + 9, a.first_frame_offset, x, dir);
 		// ---- gather: features of this thread's 4 levels -> Zs, Jacobian d enc / d x kept in registers.
 		// All 32 table loads of the thread are issued before the first is used: one trip to L2 per tile instead of one per level.
 		float J[4][6];
@@ -459,8 +472,10 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 				__align__(16) __half gs[8];  // rows 3..10 of the output gradient
 				*reinterpret_cast<uint4*>(gs) = *reinterpret_cast<const uint4*>(&sm.gst[s][0]);
 #pragma unroll
-				for (int e = 0; e < 3; ++e)
+				for (int e = 0; e < 3; ++e) {
 					sm.vbuf[s][e] = __half2float(__float2half_rn(v[3 + e])) + __half2float(gs[1 + e]) / a.batch_size + __half2float(gs[5 + e]);
+					sm.dxc[s][e] = __half2float(__float2half_rn(v[e]));
+				}
 			}
 			N2B_ISSUE_TAIL(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false),
 			               gemm<16>(WG_W2sT, mnmaj(sm.Hs, 64), mnmaj(sm.dY, 16), 8, !first));
@@ -505,6 +520,8 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			N2B_ISSUE_NOWAIT(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.E0, 16), 8, true));
 			// ---- B6: grid gradient (first + second order merged, one reduction per corner); runs while the tensor pipe
 			// finishes the tile's last weight-gradient GEMM
+			const bool want_dx = a.delta_sums != nullptr, do_grid = a.grad_grid != nullptr;
+			float dxp[3] = {0.f, 0.f, 0.f};  // this thread's levels' share of dL/dx (first-order backward of the encoding)
 			{
 				float dzv[8];
 				tmem_ld8(R1 + 8 * part, dzv);
@@ -515,6 +532,11 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 					if (l < a.lv.n_active) {
 						const float dz0 = __half2float(__float2half_rn(dzv[2 * j]));
 						const float dz1 = __half2float(__float2half_rn(dzv[2 * j + 1]));
+						if (want_dx) {
+#pragma unroll
+							for (int e = 0; e < 3; ++e) dxp[e] = __fmaf_rn(J[j][2 * e], dz0, __fmaf_rn(J[j][2 * e + 1], dz1, dxp[e]));
+						}
+						if (!do_grid) continue;  // the canonical model is frozen (a frame's first steps train the motion alone)
 						const float2 gef = __half22float2(ge[j]);
 						const LevelGeom g2 = level_geom(a.lv, l, x);
 						const float scale = a.lv.scale[l];
@@ -584,6 +606,43 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 					}
 				}
 			}
+			if (want_dx) {
+				// ---- gradient for the DeltaNetwork (nerf_network.h:589-612): dL/dx' = encoding dL/dx + xyz rows of both networks'
+				// input gradients; its twelve batch sums: sum dL/dx' and sum dL/dx' (x) (x + t) (common_operation.cuh:810-831)
+#pragma unroll
+				for (int e = 0; e < 3; ++e) sm.nrm[part][s][e] = dxp[e];
+				__syncthreads();
+				if (part == 0) {
+					float dzp[8];
+					tmem_ld8(R1 + 32, dzp);  // xyz columns of the SDF-net input gradient
+					tc::tmem_ld_wait();
+					float sums[12];
+#pragma unroll
+					for (int k = 0; k < 12; ++k) sums[k] = 0.f;
+					if (valid) {
+						const float* c = a.coords + (size_t)i * a.coord_stride;
+						float l3[3], vv[3];
+#pragma unroll
+						for (int e = 0; e < 3; ++e) {
+							l3[e] = (((sm.nrm[0][s][e] + sm.nrm[1][s][e]) + sm.nrm[2][s][e]) + sm.nrm[3][s][e]) + sm.dxc[s][e] +
+							        __half2float(__float2half_rn(dzp[e]));
+							vv[e] = c[e] + sm.motion[9 + e];
+						}
+#pragma unroll
+						for (int r = 0; r < 3; ++r) {
+							sums[r] = l3[r];
+#pragma unroll
+							for (int k = 0; k < 3; ++k) sums[3 + r * 3 + k] = l3[r] * vv[k];
+						}
+					}
+#pragma unroll
+					for (int k = 0; k < 12; ++k) {
+#pragma unroll
+						for (int o = 16; o > 0; o >>= 1) sums[k] += __shfl_xor_sync(0xffffffffu, sums[k], o);
+						if (lane == 0 && sums[k] != 0.f) atomicAdd(&sm.dsum[k], sums[k]);
+					}
+				}
+			}
 			pending = true;
 			first = false;
 		}
@@ -606,7 +665,8 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 
 	if constexpr (MODE == MODE_TRAIN) {
 		// ---- flush the weight gradients held in tensor memory (rows 0..63 of each accumulator)
-		if (ok && !first && s < 64) {
+		if (a.delta_sums && tid < 12 && sm.dsum[tid] != 0.f) atomicAdd(a.delta_sums + tid, sm.dsum[tid]);
+		if (ok && !first && s < 64 && a.grad_mlp) {
 			float v[16];
 			if (part == 0) {
 #pragma unroll
@@ -656,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		if (tid == 0) {
 			float t = 0.f;
 			for (int w = 0; w < kThreads / 32; ++w) t += sm.red[w];
-			if (t != 0.f) atomicAdd(a.grad_var, t);
+			if (t != 0.f && a.grad_var) atomicAdd(a.grad_var, t);
 		}
 	}
 	tc::fence_before_sync();

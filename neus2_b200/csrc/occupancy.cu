@@ -300,6 +300,15 @@ extern "C" int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint1
                                        uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp, uint8_t* d_bitfield,
                                        float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf, double* d_partial,
                                        neus2b_stream_t stream) {
+	return neus2b_occupancy_update_moved(desc, d_params, sdf_bias, n_cascades, n_uniform, n_nonuniform, rng_uniform, rng_nonuniform, ema_step, decay,
+	                                     d_grid, d_grid_tmp, d_bitfield, d_mean, d_pos, d_idx, d_sdf, d_partial, nullptr, stream);
+}
+
+extern "C" int neus2b_occupancy_update_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n_cascades,
+                                             uint32_t n_uniform, uint32_t n_nonuniform, neus2b_pcg32 rng_uniform,
+                                             neus2b_pcg32 rng_nonuniform, uint32_t ema_step, float decay, float* d_grid, float* d_grid_tmp,
+                                             uint8_t* d_bitfield, float* d_mean, float* d_pos, uint32_t* d_idx, uint16_t* d_sdf,
+                                             double* d_partial, const neus2b_motion* motion, neus2b_stream_t stream) {
 	if (!desc || !d_params || !d_grid || !d_grid_tmp || !d_bitfield || !d_mean || !d_pos || !d_idx || !d_sdf || !d_partial)
 		return NEUS2B_E_INVALID;
 	if (n_cascades == 0 || n_cascades > NEUS2B_CASCADES) return NEUS2B_E_INVALID;
@@ -321,7 +330,7 @@ extern "C" int neus2b_occupancy_update(const neus2b_grid_desc* desc, const uint1
 		N2B_CHECK_LAUNCH();
 	}
 	if (n) {
-		rc = neus2b_neus_sdf(desc, d_params, sdf_bias, n, d_pos, 3, d_sdf, stream);
+		rc = neus2b_neus_sdf_moved(desc, d_params, sdf_bias, n, d_pos, 3, motion, d_sdf, stream);
 		if (rc) return rc;
 		const __half* var_ptr = (const __half*)d_params + NEUS2B_GRID_OFF + (size_t)lv.offset[NEUS2B_MAX_LEVELS] * 2;
 		occ_splat_entry<<<div_up(n, 256), 256, 0, stream>>>(n, d_idx, (const __half*)d_sdf, var_ptr, d_grid_tmp);

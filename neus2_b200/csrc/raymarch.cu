@@ -11,6 +11,7 @@
 
 #include "common.cuh"
 #include "march.cuh"
+#include "delta.cuh"
 
 namespace n2b {
 
@@ -55,6 +56,18 @@ __global__ void __launch_bounds__(256) ray_setup_kernel(neus2b_dataset ds, neus2
 			const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
 #pragma unroll
 			for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+			if (cfg.use_global_movement) {  // :1370-1378: the ray is moved; its direction is not normalised again
+				float o2[3], q[3], dq[3];
+#pragma unroll
+				for (int e = 0; e < 3; ++e) o2[e] = r.o[e] - cfg.first_frame_offset[e];
+				rotate3(cfg.rotation, o2, q);
+				rotate3(cfg.rotation, dirn, dq);
+#pragma unroll
+				for (int e = 0; e < 3; ++e) {
+					r.o[e] = q[e] + cfg.transition[e];
+					r.d[e] = dirn[e] = dq[e];  // the later passes take this direction as it is
+				}
+			}
 			float tmin, tmax;
 			aabb_ray_intersect(cfg.aabb_min, cfg.aabb_max, r.o, dirn, tmin, tmax);
 			tmin = fmaxf(tmin, 0.0f);
@@ -82,7 +95,7 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_train_cfg cfg, 
 	for (uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); h < n_hit; h += warps) {
 		const uint32_t i = hit_list[h];
 		RayTmp r = tmp[i];
-		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+		const float inv = cfg.use_global_movement ? 1.0f : 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
 		float dirn[3];
 #pragma unroll
 		for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
@@ -215,7 +228,7 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
 			numsteps[kidx * 2 + 0] = r.numsteps;
 			numsteps[kidx * 2 + 1] = base;
 		}
-		const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
+		const float inv = cfg.use_global_movement ? 1.0f : 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
 		const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
 		// the mask record covers the first kMaskWords * 32 ray parameters; longer rays march again
 		if (masks && !long_ray)

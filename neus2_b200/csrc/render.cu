@@ -16,6 +16,7 @@
 // Compiled with -fmad=false like the training-side march (see march.cuh).
 #include "common.cuh"
 #include "march.cuh"
+#include "delta.cuh"
 
 namespace n2b {
 
@@ -81,6 +82,18 @@ __global__ void __launch_bounds__(256) render_setup_kernel(neus2b_render_cfg rc,
 		const float norm = sqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
 #pragma unroll
 		for (int e = 0; e < 3; ++e) r.d[e] = d[e] / norm;
+		if (rc.use_global_movement) {  // :2286-2296
+			float o2[3], q[3], dq[3];
+#pragma unroll
+			for (int e = 0; e < 3; ++e) o2[e] = r.o[e] - rc.first_frame_offset[e];
+			rotate3(rc.rotation, o2, q);
+			rotate3(rc.rotation, r.d, dq);
+#pragma unroll
+			for (int e = 0; e < 3; ++e) {
+				r.o[e] = q[e] + rc.transition[e];
+				r.d[e] = dq[e];
+			}
+		}
 		depth_buffer[idx] = 1e10f;
 		float tmin, tmax;
 		aabb_ray_intersect(rc.aabb_min, rc.aabb_max, r.o, r.d, tmin, tmax);
@@ -343,7 +356,11 @@ extern "C" int neus2b_render_frame(const neus2b_grid_desc* desc, const uint16_t*
 			                                                ws->d_scan_tmp, ws->d_occupied_bounds, ws->d_hit_list, ws->d_counters, ws->d_coords,
 			                                                ws->d_march_masks);
 			N2B_CHECK_LAUNCH();
-			const int rc = neus2b_neus_forward(desc, d_params, sdf_bias, ws->max_samples, ws->d_counters + 2, ws->d_coords, ws->d_out, stream_);
+			neus2b_motion motion{};
+			motion.d_delta = cfg->d_delta;
+			for (int e = 0; e < 3; ++e) motion.first_frame_offset[e] = cfg->first_frame_offset[e];
+			const int rc = neus2b_neus_forward_moved(desc, d_params, sdf_bias, ws->max_samples, ws->d_counters + 2, ws->d_coords,
+			                                         cfg->d_delta ? &motion : nullptr, ws->d_out, stream_);
 			if (rc != NEUS2B_OK) return rc;
 			render_composite_kernel<<<min(div_up(n_rays, 128), (uint32_t)kSMs * 16u), 128, 0, stream>>>(
 			    *cfg, (uint32_t)s0, ws->max_samples, (const RayTmp*)ws->d_ray_tmp, ws->d_scan_tmp, ws->d_hit_list, ws->d_counters, ws->d_coords,

@@ -100,11 +100,76 @@ def neus_train(d, params, coords, dL_dout, indeed_batch_size, grad_mlp, grad_gri
                                       u32(indeed_batch_size), L.ptr(grad_mlp), L.ptr(grad_grid), L.ptr(grad_var), L.cur_stream()))
 
 
-def neus_sdf(d, params, x, sdf_bias=-0.1):
+def neus_sdf(d, params, x, sdf_bias=-0.1, motion=None):
     out = _half((x.shape[0],), x.device)
-    L.check(L.lib().neus2b_neus_sdf(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]),
-                                    L.ptr(out), L.cur_stream()))
+    L.check(L.lib().neus2b_neus_sdf_moved(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(x.shape[0]), L.ptr(x), u32(x.shape[1]),
+                                          C.byref(motion) if motion is not None else None, L.ptr(out), L.cur_stream()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------ dynamic sequences
+DELTA_IDENTITY = (0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0)  # transition (4) | 6-D rotation (8)
+
+
+def motion(delta, sums=None, first_frame_offset=(0.0, 0.0, 0.0)):
+    """neus2b_motion over `delta` (fp16 CUDA tensor [12]) and, for training, the fp32 [12] tensor the backward's sums are added to."""
+    m = L.Motion()
+    m.d_delta = delta.data_ptr() if hasattr(delta, "data_ptr") else int(delta)
+    m.first_frame_offset[:] = list(first_frame_offset)
+    m.d_sums = (sums.data_ptr() if hasattr(sums, "data_ptr") else int(sums)) if sums is not None else None
+    m._keep = (delta, sums)
+    return m
+
+
+def neus_forward_moved(d, params, coords, mot, sdf_bias=-0.1, n_dev=None, out=None):
+    n = coords.shape[0]
+    if out is None:
+        out = _half((n, 16), coords.device)
+    L.check(L.lib().neus2b_neus_forward_moved(C.byref(d), L.ptr(params), C.c_float(sdf_bias), u32(n), L.ptr(n_dev), L.ptr(coords),
+                                              C.byref(mot) if mot is not None else None, L.ptr(out), L.cur_stream()))
+    return out
+
+
+def neus_train_moved(d, params, coords, mot, dL_dout, indeed_batch_size, grad_mlp, grad_grid, grad_var):
+    L.check(L.lib().neus2b_neus_train_moved(C.byref(d), L.ptr(params), u32(coords.shape[0]), L.ptr(coords),
+                                            C.byref(mot) if mot is not None else None, L.ptr(dL_dout), u32(indeed_batch_size),
+                                            L.ptr(grad_mlp), L.ptr(grad_grid), L.ptr(grad_var), L.cur_stream()))
+
+
+def delta_forward(delta, coords, first_frame_offset=(0.0, 0.0, 0.0)):
+    out = torch.empty_like(coords)
+    L.check(L.lib().neus2b_delta_forward(L.ptr(delta), (C.c_float * 3)(*first_frame_offset), u32(coords.shape[0]), L.ptr(coords), L.ptr(out),
+                                         L.cur_stream()))
+    return out
+
+
+def delta_backward(delta, coords, dL_dx, sums=None):
+    if sums is None:
+        sums = torch.zeros(12, dtype=torch.float32, device=coords.device)
+    L.check(L.lib().neus2b_delta_backward(L.ptr(delta), u32(coords.shape[0]), L.ptr(coords), L.ptr(dL_dx), L.ptr(sums), L.cur_stream()))
+    return sums
+
+
+def delta_gradient(delta, sums):
+    """The 12 parameters' gradients from the backward's sums (the sums are cleared)."""
+    g = torch.zeros(12, dtype=torch.float32, device=sums.device)
+    L.check(L.lib().neus2b_delta_optimizer_step(None, L.ptr(sums), None, None, None, L.ptr(delta), None, None, L.ptr(g), L.cur_stream()))
+    return g
+
+
+def delta_optimizer_step(cfg, sums, master, m, v, delta, delta_ema=None, ema_master=None, grad_out=None):
+    L.check(L.lib().neus2b_delta_optimizer_step(C.byref(cfg), L.ptr(sums), L.ptr(master), L.ptr(m), L.ptr(v), L.ptr(delta), L.ptr(delta_ema),
+                                                L.ptr(ema_master), L.ptr(grad_out), L.cur_stream()))
+
+
+def movement_accumulate(delta_bits, rotation, transition):
+    """Host: (rotation [9] row-major, transition [3]) with the frame's motion (12 fp16 bit patterns) folded in."""
+    import numpy as np
+    R = (C.c_float * 9)(*[float(v) for v in np.asarray(rotation, np.float32).reshape(9)])
+    t = (C.c_float * 3)(*[float(v) for v in np.asarray(transition, np.float32).reshape(3)])
+    d = (C.c_uint16 * 12)(*[int(v) for v in np.asarray(delta_bits).reshape(12)])
+    L.check(L.lib().neus2b_movement_accumulate(d, R, t))
+    return np.array(list(R), np.float32).reshape(3, 3), np.array(list(t), np.float32)
 
 
 class RayBatch:

@@ -522,6 +522,11 @@ void n2o_neus_sdf(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias
 
 void n2o_neus_backward(const n2o_grid_desc* d, const uint16_t* params, uint32_t n, const float* coords,
                        const uint16_t* dL_dout, uint32_t indeed_batch_size, double* grad) {
+	n2o_neus_backward_dx(d, params, n, coords, dL_dout, indeed_batch_size, grad, NULL);
+}
+
+void n2o_neus_backward_dx(const n2o_grid_desc* d, const uint16_t* params, uint32_t n, const float* coords,
+                          const uint16_t* dL_dout, uint32_t indeed_batch_size, double* grad, float* dL_dx) {
 	n2o_grid_levels lv;
 	n2o_grid_make_levels(d, &lv);
 	weights_t* w = load_weights(d, params);
@@ -579,6 +584,14 @@ void n2o_neus_backward(const n2o_grid_desc* d, const uint16_t* params, uint32_t 
 					atomic_add_d(&ggrid[2 * (size_t)cr.idx[k] + 1], (double)(cr.w[k] * dzs[3 + 2 * l + 1]));
 				}
 			}
+			/* gradient for the DeltaNetwork (nerf_network.h:589-612): encoding dL/dx (first order) + xyz rows of both input gradients */
+			if (dL_dx) {
+				for (int e = 0; e < 3; ++e) {
+					float a = 0.f;
+					for (uint32_t k = 0; k < W; ++k) a = fmaf(s.J[k][e], dzs[3 + k], a);
+					dL_dx[(size_t)i * 3 + e] = a + dzc[32 + e] + dzs[e];
+				}
+			}
 			/* variance gradient: sum of row 7 (nerf_network.h:452-460) */
 			loc[N2O_MLP_N] += (double)g[7];
 			/* v = dL/dnormal (nerf_network.h:465-491) */
@@ -607,6 +620,123 @@ void n2o_neus_backward(const n2o_grid_desc* d, const uint16_t* params, uint32_t 
 		free(loc);
 	}
 	free(w);
+}
+
+/* ------------------------------------------------------------------ DeltaNetwork (transform_network.h, common_operation.cuh) */
+static inline void normalize3(const float* a, float* b) {
+	const float n = sqrtf(a[0] * a[0] + a[1] * a[1] + a[2] * a[2]);
+	for (int e = 0; e < 3; ++e) b[e] = a[e] / n;
+}
+/* rotation_6d_to_matrix (common_operation.cuh:42-66): Gram-Schmidt on the two 3-vectors, columns b1, b2, b1 x b2 */
+void n2o_rotation_6d_to_matrix(const uint16_t* rot6, float* R) {
+	float a1[3], a2[3], b1[3], b2[3], u2[3];
+	for (int e = 0; e < 3; ++e) {
+		a1[e] = h2f(rot6[e]);
+		a2[e] = h2f(rot6[3 + e]);
+	}
+	normalize3(a1, b1);
+	const float dt = b1[0] * a2[0] + b1[1] * a2[1] + b1[2] * a2[2];
+	for (int e = 0; e < 3; ++e) u2[e] = a2[e] - dt * b1[e];
+	normalize3(u2, b2);
+	const float b3[3] = {b1[1] * b2[2] - b1[2] * b2[1], b1[2] * b2[0] - b1[0] * b2[2], b1[0] * b2[1] - b1[1] * b2[0]};
+	for (int r = 0; r < 3; ++r) {
+		R[r * 3 + 0] = b1[r];
+		R[r * 3 + 1] = b2[r];
+		R[r * 3 + 2] = b3[r];
+	}
+}
+static inline void matvec3(const float* R, const float* v, float* out) {
+	for (int r = 0; r < 3; ++r) out[r] = (R[r * 3] * v[0] + R[r * 3 + 1] * v[1]) + R[r * 3 + 2] * v[2];
+}
+
+void n2o_delta_forward(const uint16_t* delta, const float* off, uint32_t n, const float* coords_in, float* coords_out) {
+	float R[9];
+	n2o_rotation_6d_to_matrix(delta + 4, R);
+	const float t[3] = {h2f(delta[0]), h2f(delta[1]), h2f(delta[2])};
+#pragma omp parallel for schedule(static)
+	for (int64_t i = 0; i < (int64_t)n; ++i) {
+		const float* c = coords_in + (size_t)i * 7;
+		float* o = coords_out + (size_t)i * 7;
+		float p[3], q[3], dd[3], dr[3];
+		for (int e = 0; e < 3; ++e) p[e] = c[e] + (t[e] - off[e]); /* pos += transition - first_frame_offset (:443-445) */
+		matvec3(R, p, q);
+		for (int e = 0; e < 3; ++e) o[e] = q[e] + off[e];
+		o[3] = c[3];
+		for (int e = 0; e < 3; ++e) dd[e] = c[4 + e] * 2.0f - 1.0f;
+		matvec3(R, dd, dr);
+		for (int e = 0; e < 3; ++e) o[4 + e] = (dr[e] + 1.0f) * 0.5f;
+	}
+}
+
+/* d normalize(x) / d x applied to a gradient: (g - (g . b) b) / |x| with b = x / |x| (gradients_for_normalize, :68-94) */
+static inline void normalize_bwd(const double* x, const double* g, double* out) {
+	const double n = sqrt(x[0] * x[0] + x[1] * x[1] + x[2] * x[2]);
+	const double b[3] = {x[0] / n, x[1] / n, x[2] / n};
+	const double gb = g[0] * b[0] + g[1] * b[1] + g[2] * b[2];
+	for (int e = 0; e < 3; ++e) out[e] = (g[e] - gb * b[e]) / n;
+}
+/* gradient_rotation_matrix_to_6d (:96-158): backward of the Gram-Schmidt construction; G[r][c] = dL / dR(r, c) */
+static void rotation_6d_backward(const uint16_t* rot6, const double* G, double* g6) {
+	double a1[3], a2[3], b1[3], b2[3], u2[3];
+	for (int e = 0; e < 3; ++e) {
+		a1[e] = (double)h2f(rot6[e]);
+		a2[e] = (double)h2f(rot6[3 + e]);
+	}
+	const double n1 = sqrt(a1[0] * a1[0] + a1[1] * a1[1] + a1[2] * a1[2]);
+	for (int e = 0; e < 3; ++e) b1[e] = a1[e] / n1;
+	const double dt = b1[0] * a2[0] + b1[1] * a2[1] + b1[2] * a2[2];
+	for (int e = 0; e < 3; ++e) u2[e] = a2[e] - dt * b1[e];
+	const double n2 = sqrt(u2[0] * u2[0] + u2[1] * u2[1] + u2[2] * u2[2]);
+	for (int e = 0; e < 3; ++e) b2[e] = u2[e] / n2;
+	const double g1[3] = {G[0], G[3], G[6]}, g2[3] = {G[1], G[4], G[7]}, g3[3] = {G[2], G[5], G[8]};
+	/* b3 = b1 x b2: dL/db1 += b2 x g3, dL/db2 += g3 x b1 */
+	double db1[3] = {g1[0] + (b2[1] * g3[2] - b2[2] * g3[1]), g1[1] + (b2[2] * g3[0] - b2[0] * g3[2]), g1[2] + (b2[0] * g3[1] - b2[1] * g3[0])};
+	double db2[3] = {g2[0] + (g3[1] * b1[2] - g3[2] * b1[1]), g2[1] + (g3[2] * b1[0] - g3[0] * b1[2]), g2[2] + (g3[0] * b1[1] - g3[1] * b1[0])};
+	double du2[3], da2[3], da1[3];
+	normalize_bwd(u2, db2, du2);
+	const double du2b1 = du2[0] * b1[0] + du2[1] * b1[1] + du2[2] * b1[2];
+	for (int e = 0; e < 3; ++e) {
+		da2[e] = du2[e] - du2b1 * b1[e];          /* u2 = a2 - (b1 . a2) b1 */
+		db1[e] -= dt * du2[e] + du2b1 * a2[e];
+	}
+	normalize_bwd(a1, db1, da1);
+	for (int e = 0; e < 3; ++e) {
+		g6[e] = da1[e];
+		g6[3 + e] = da2[e];
+	}
+}
+
+void n2o_delta_backward(const uint16_t* delta, const float* off, uint32_t n, const float* coords_in, const float* dL_dx, double* grad) {
+	(void)off; /* the reference's backward leaves the offset out of the rotated vector (input + transition, :811) */
+	float R[9];
+	n2o_rotation_6d_to_matrix(delta + 4, R);
+	const float t[3] = {h2f(delta[0]), h2f(delta[1]), h2f(delta[2])};
+	double G[9] = {0}, L[3] = {0};
+	for (uint32_t i = 0; i < n; ++i) {
+		const float* c = coords_in + (size_t)i * 7;
+		const float* l = dL_dx + (size_t)i * 3;
+		const float v[3] = {c[0] + t[0], c[1] + t[1], c[2] + t[2]};
+		for (int r = 0; r < 3; ++r) {
+			L[r] += (double)l[r];
+			for (int k = 0; k < 3; ++k) G[r * 3 + k] += (double)(l[r] * v[k]); /* loss_vector (x) input_vector (:829-831) */
+		}
+	}
+	/* transition: R^-1 dL/dx' summed = R^T sum (:812-820); rotation: the 6-D backward is linear in G, so it is applied to the sum */
+	for (int e = 0; e < 3; ++e) grad[e] += (double)R[0 * 3 + e] * L[0] + (double)R[1 * 3 + e] * L[1] + (double)R[2 * 3 + e] * L[2];
+	double g6[6];
+	rotation_6d_backward(delta + 4, G, g6);
+	for (int e = 0; e < 6; ++e) grad[4 + e] += g6[e];
+}
+
+void n2o_accumulate_global_movement(const uint16_t* delta, float* acc_R, float* acc_t) {
+	float R[9], out[9], tv[3], tr[3];
+	n2o_rotation_6d_to_matrix(delta + 4, R);
+	for (int r = 0; r < 3; ++r)
+		for (int c = 0; c < 3; ++c) out[r * 3 + c] = (R[r * 3] * acc_R[c] + R[r * 3 + 1] * acc_R[3 + c]) + R[r * 3 + 2] * acc_R[6 + c];
+	for (int e = 0; e < 3; ++e) tv[e] = acc_t[e] + h2f(delta[e]); /* R (t_acc + t) (:583) */
+	matvec3(R, tv, tr);
+	for (int k = 0; k < 9; ++k) acc_R[k] = rh(out[k]);
+	for (int e = 0; e < 3; ++e) acc_t[e] = rh(tr[e]);
 }
 
 /* ------------------------------------------------------------------ PCG32 (published generator; float = 23 mantissa bits) */
@@ -815,6 +945,16 @@ static void ray_setup(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint32_t 
 	}
 	float inv = 1.0f / sqrtf(r->d[0] * r->d[0] + r->d[1] * r->d[1] + r->d[2] * r->d[2]);
 	for (int e = 0; e < 3; ++e) r->dirn[e] = r->d[e] * inv;
+	if (cfg->use_global_movement) { /* :1370-1378: the ray is moved, its direction is not normalised again */
+		float o2[3], q[3], dq[3];
+		for (int e = 0; e < 3; ++e) o2[e] = r->o[e] - cfg->first_frame_offset[e];
+		matvec3(cfg->rotation, o2, q);
+		matvec3(cfg->rotation, r->dirn, dq);
+		for (int e = 0; e < 3; ++e) {
+			r->o[e] = q[e] + cfg->transition[e];
+			r->dirn[e] = r->d[e] = dq[e]; /* (the ray handed on is the moved one) */
+		}
+	}
 	float tmin, tmax;
 	aabb_ray_intersect(cfg->aabb_min, cfg->aabb_max, r->o, r->dirn, &tmin, &tmax);
 	float cone_angle = cfg->cone_angle_constant;

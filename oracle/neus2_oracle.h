@@ -86,9 +86,29 @@ void n2o_neus_forward(const n2o_grid_desc* d, const uint16_t* params, float sdf_
 void n2o_neus_backward(const n2o_grid_desc* d, const uint16_t* params, uint32_t n, const float* coords,
                        const uint16_t* dL_dout /*[n][16]*/, uint32_t indeed_batch_size,
                        double* grad /*[model_n_params], accumulates; loss-scaled like dL_dout*/);
+/* The same, and the gradient that reaches the sample positions, dL_dx [n][3] (may be NULL): what NerfNetwork::backward_impl
+ * hands to the DeltaNetwork (nerf_network.h:589-612) = dL/dx of the encoding's first-order backward + the xyz rows of the
+ * colour-net and SDF-net input gradients.  (The second-order term's dL/dx is computed by the reference but never used.) */
+void n2o_neus_backward_dx(const n2o_grid_desc* d, const uint16_t* params, uint32_t n, const float* coords,
+                          const uint16_t* dL_dout, uint32_t indeed_batch_size, double* grad, float* dL_dx);
 /* NerfNetwork::sdf / density (nerf_network.h:643-726) */
 void n2o_neus_sdf(const n2o_grid_desc* d, const uint16_t* params, float sdf_bias, uint32_t n, const float* x,
                   uint32_t x_stride, uint16_t* sdf);
+
+/* --- DeltaNetwork: the learned rigid motion of the current frame (include/neural-graphics-primitives/transform_network.h:26-170,
+ * kernels common_operation.cuh:42-170, 419-474, 793-849).  delta = 12 fp16 parameters in the network's own order
+ * (set_params :183-205): transition [0..3] (xyz + one unused), 6-D rotation [4..11] (a1, a2 + two unused). --- */
+void n2o_rotation_6d_to_matrix(const uint16_t* rot6 /*fp16[6]*/, float* R /*[9] row-major*/);
+/* add_global_movement_with_rotation_6d: pos' = R (pos + t - off) + off, dir' = (R (2 dir - 1) + 1) / 2; coords [n][7], dt copied */
+void n2o_delta_forward(const uint16_t* delta, const float* first_frame_offset, uint32_t n, const float* coords_in, float* coords_out);
+/* add_loss_to_rotation_6d_each + the nine batch sums of DeltaNetwork::backward_impl: dL_dx [n][3] = gradient w.r.t. the moved
+ * position; grad [12] (+=): transition at [0..2], 6-D rotation at [4..9].  fp32 per sample, fp64 sums (the reference rounds
+ * every per-sample value to fp16 before it sums). */
+void n2o_delta_backward(const uint16_t* delta, const float* first_frame_offset, uint32_t n, const float* coords_in, const float* dL_dx,
+                        double* grad);
+/* accumulate_global_movement_rotation_6d_kernel (common_operation.cuh:555-589): R_acc <- R R_acc, t_acc <- R (t_acc + t); both
+ * arrays hold fp16-representable values (the reference keeps them in fp16 buffers) */
+void n2o_accumulate_global_movement(const uint16_t* delta, float* acc_rotation /*[9]*/, float* acc_transition /*[3]*/);
 
 /* --- ray march / loss (src/testbed_nerf.cu) --- */
 typedef struct {
@@ -116,6 +136,11 @@ typedef struct {
 	float loss_scale;        /* LOSS_SCALE = 128, include/neural-graphics-primitives/testbed.h:237 */
 	float mask_loss_weight, ek_loss_weight, cos_anneal_ratio;
 	uint32_t ray_index_offset, ray_count_scale; /* data-parallel ray sharding; 0 / 1 = single process */
+	/* accumulated global movement of the earlier frames of a dynamic sequence, applied to every ray before the march
+	 * (global_movement_with_rotation_6d, src/testbed_nerf.cu:183-203, call sites :1370-1378, :1550-1558, :2286-2296):
+	 * o = R (o - first_frame_offset) + t, dir = R dir (dir normalised before, not after).  R row-major. */
+	uint32_t use_global_movement;
+	float rotation[9], transition[3], first_frame_offset[3];
 } n2o_train_cfg;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene, canonical

@@ -47,7 +47,9 @@ class TrainCfg(C.Structure):
     _fields_ = [("aabb_min", C.c_float * 3), ("aabb_max", C.c_float * 3), ("cone_angle_constant", C.c_float),
                 ("snap_to_pixel_centers", C.c_uint32), ("random_bg_color", C.c_uint32), ("background_color", C.c_float * 3),
                 ("loss_scale", C.c_float), ("mask_loss_weight", C.c_float), ("ek_loss_weight", C.c_float),
-                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32)]
+                ("cos_anneal_ratio", C.c_float), ("ray_index_offset", C.c_uint32), ("ray_count_scale", C.c_uint32),
+                ("use_global_movement", C.c_uint32), ("rotation", C.c_float * 9), ("transition", C.c_float * 3),
+                ("first_frame_offset", C.c_float * 3)]
 
 
 class RenderCfg(C.Structure):
@@ -216,6 +218,45 @@ def neus_backward(d, params, coords, dL_dout, indeed_batch_size=None, grad=None)
     return grad
 
 
+def neus_backward_dx(d, params, coords, dL_dout, indeed_batch_size=None, grad=None):
+    """neus_backward plus dL/dx [n][3], the gradient handed to the DeltaNetwork."""
+    coords = _c(coords, np.float32)
+    n = coords.shape[0]
+    if grad is None:
+        grad = np.zeros(model_n_params(d), np.float64)
+    dx = np.zeros((n, 3), np.float32)
+    lib().n2o_neus_backward_dx(C.byref(d), _p(_c(params, np.uint16)), C.c_uint32(n), _p(coords), _p(_c(dL_dout, np.uint16)),
+                               C.c_uint32(n if indeed_batch_size is None else indeed_batch_size), _p(grad), _p(dx))
+    return grad, dx
+
+
+def rotation_6d_to_matrix(rot6_bits):
+    R = np.zeros(9, np.float32)
+    lib().n2o_rotation_6d_to_matrix(_p(_c(rot6_bits, np.uint16)), _p(R))
+    return R.reshape(3, 3)
+
+
+def delta_forward(delta_bits, coords, first_frame_offset=(0.0, 0.0, 0.0)):
+    coords = _c(coords, np.float32)
+    out = np.empty_like(coords)
+    lib().n2o_delta_forward(_p(_c(delta_bits, np.uint16)), (C.c_float * 3)(*first_frame_offset), C.c_uint32(coords.shape[0]), _p(coords), _p(out))
+    return out
+
+
+def delta_backward(delta_bits, coords, dL_dx, first_frame_offset=(0.0, 0.0, 0.0)):
+    coords, dL_dx = _c(coords, np.float32), _c(dL_dx, np.float32)
+    grad = np.zeros(12, np.float64)
+    lib().n2o_delta_backward(_p(_c(delta_bits, np.uint16)), (C.c_float * 3)(*first_frame_offset), C.c_uint32(coords.shape[0]), _p(coords),
+                             _p(dL_dx), _p(grad))
+    return grad
+
+
+def accumulate_global_movement(delta_bits, acc_rotation, acc_transition):
+    R, t = _c(acc_rotation, np.float32).copy().reshape(9), _c(acc_transition, np.float32).copy()
+    lib().n2o_accumulate_global_movement(_p(_c(delta_bits, np.uint16)), _p(R), _p(t))
+    return R.reshape(3, 3), t
+
+
 def neus_sdf(d, params, x, sdf_bias=-0.1):
     x = _c(x, np.float32)
     out = np.empty(x.shape[0], np.uint16)
@@ -259,8 +300,13 @@ def make_dataset(pixels, xforms, focal, principal):
 
 def train_cfg(ek_loss_weight=0.1, mask_loss_weight=0.0, random_bg_color=True, snap_to_pixel_centers=False,
               cos_anneal_ratio=1.0, loss_scale=128.0, background_color=(0.0, 0.0, 0.0), ray_index_offset=0,
-              ray_count_scale=1):
+              ray_count_scale=1, rotation=None, transition=None, first_frame_offset=(0.0, 0.0, 0.0)):
     c = TrainCfg()
+    if rotation is not None:
+        c.use_global_movement = 1
+        c.rotation[:] = [float(v) for v in np.asarray(rotation, np.float32).reshape(9)]
+        c.transition[:] = [float(v) for v in np.asarray(transition, np.float32).reshape(3)]
+        c.first_frame_offset[:] = list(first_frame_offset)
     c.aabb_min[:] = [0.0, 0.0, 0.0]
     c.aabb_max[:] = [1.0, 1.0, 1.0]
     c.cone_angle_constant = 0.0
