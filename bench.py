@@ -472,6 +472,51 @@ def run_kernel_only(args):
                                                                         "upper_half_p99_abs_sdf": float(err[seen].quantile(0.99))}}))
         tb.close()
         return
+    if args.kernel == "config3":
+        # BASELINE config 3 stand-in: a sequence of --frames frames of the config-1 sphere under a seeded per-frame rigid motion
+        # (rotation <= 5 deg, translation <= 0.02 per frame) and a sinusoidal radial bulge of amplitude 0.03, 24 views at 512 x 512
+        # per frame; 2 000 steps on the first frame, then --frame-steps steps per later frame (the first quarter of them on the
+        # learned rigid motion alone), warm-started from the previous frame.  Reports wall-clock per frame: image upload, frame
+        # switch and training (the frames are rendered ahead, which is data preparation).
+        import time
+        from neus2_b200.testbed import Testbed
+        n_frames, per_frame = args.frames, args.frame_steps
+        poses = S.sequence_poses(n_frames, seed=0)
+        tb = Testbed(batch_size=1 << 18, predict_global_movement=1, predict_global_movement_training_step=max(per_frame // 4, 1),
+                     finetune_global_movement=1, reset_density_grid_after_global_movement=0, after_learning_rate=1e-3, ek_loss_weight=0.01,
+                     base_training_step=100, valid_level_scale=0.02, base_valid_level_scale=0.2)
+
+        def views(f):
+            sc = S.render_sphere_views(24, 512, 512, device="cuda", seed=0, rotation=poses[f][0], translation=poses[f][1], radius=poses[f][2])
+            return [sc[k].cpu().numpy() for k in ("pixels", "xforms", "focal", "principal")]
+        t0 = time.perf_counter()
+        tb.load_training_data(*views(0))
+        tb.set_params(S.init_params(ng, seed=1337))
+        st = tb.train(args.first_frame_steps)
+        torch.cuda.synchronize()
+        first_s = time.perf_counter() - t0
+        per, losses = [], []
+        for f in range(1, n_frames):
+            data = views(f)  # (rendered outside the timed part)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            tb.next_frame(*data)
+            st = tb.train(per_frame)
+            torch.cuda.synchronize()
+            per.append(time.perf_counter() - t1)
+            losses.append(float(st.loss))
+        per_sorted = sorted(per)
+        frame, R_acc, t_acc, _ = tb.movement()
+        print(json.dumps({"kernel": "config3", "frames": n_frames, "views": 24, "resolution": 512, "first_frame_steps": args.first_frame_steps,
+                          "steps_per_later_frame": per_frame, "first_frame_s": first_s,
+                          "later_frame_ms": {"median": 1e3 * per_sorted[len(per) // 2], "mean": 1e3 * sum(per) / len(per),
+                                             "p90": 1e3 * per_sorted[int(0.9 * (len(per) - 1))], "max": 1e3 * per_sorted[-1]},
+                          "ms_per_step_in_later_frames": 1e3 * sum(per) / len(per) / per_frame,
+                          "final_loss": losses[-1], "max_loss": max(losses), "frame": frame,
+                          "accumulated_rotation_deg": float(np.degrees(np.arcsin(min(1.0, float(np.linalg.norm(R_acc - R_acc.T)) / (2.0 * 2.0 ** 0.5))))),
+                          "accumulated_translation": [float(v) for v in t_acc]}))
+        tb.close()
+        return
     if args.kernel == "render":
         # one frame of Testbed.render (1 sample per pixel) of the briefly trained config-1 scene, host image out
         import time
@@ -649,9 +694,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=1 << 18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render", "config2"], help="run one fused kernel alone (profiling)")
+    ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render", "config2", "config3"], help="run one fused kernel alone (profiling)")
     ap.add_argument("--kernel-n", type=int, default=1 << 17)
     ap.add_argument("--kernel-iters", type=int, default=3)
+    ap.add_argument("--frames", type=int, default=100, help="--kernel config3: frames of the sequence")
+    ap.add_argument("--frame-steps", type=int, default=100, help="--kernel config3: training steps per frame after the first")
+    ap.add_argument("--first-frame-steps", type=int, default=2000)
     ap.add_argument("--mesh-res", type=int, default=512)
     ap.add_argument("--no-mesh", action="store_true", help="skip the 512^3 mesh extraction record behind the timed steps")
     ap.add_argument("--render-res", type=int, nargs=2, default=[1600, 1200], help="width height of --kernel render (DTU images are 1600x1200)")

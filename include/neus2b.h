@@ -356,6 +356,17 @@ typedef struct {
 	uint32_t base_training_step;
 	uint32_t adam_flags;           /* NEUS2B_ADAM_* */
 	float loss_scale;              /* LOSS_SCALE (include/neural-graphics-primitives/testbed.h:237): 128 */
+	/* dynamic sequences: "hyperparams" of configs/nerf/base.json:70-82 (src/testbed.cu:2108-2122) and its "globalmove" optimizer
+	 * block (:84-110).  They matter from the second frame on (neus2b_testbed_next_frame). */
+	uint32_t predict_global_movement;                  /* learn a rigid motion per frame (DeltaNetwork); false */
+	uint32_t predict_global_movement_training_step;    /* steps of a frame that train the motion alone; 300 in the code, 100 shipped */
+	uint32_t finetune_global_movement;                 /* keep training the motion afterwards; true */
+	uint32_t reset_density_grid_after_global_movement; /* true in the code, false shipped */
+	float after_learning_rate;                         /* the canonical model's learning rate from the second frame on; 0 = unchanged */
+	float gm_learning_rate, gm_beta1, gm_beta2, gm_epsilon, gm_l2_reg, gm_ema_decay;
+	uint32_t gm_lr_decay_start, gm_lr_decay_interval;
+	float gm_lr_decay_base;
+	float first_frame_offset[3];                       /* Testbed::m_first_frame_offset (testbed.h:455): 0 */
 } neus2b_testbed_config;
 /* "top_resolution" -> per_level_scale when the config gives none (src/testbed.cu:2173-2177):
  * exp(log(top_resolution * aabb_scale / base_resolution) / (n_levels - 1)). */
@@ -426,6 +437,23 @@ int neus2b_testbed_train_wait_stats(neus2b_testbed* tb, neus2b_train_stats* h_st
  * samples drawn, then the wait for this step's statistics (h_stats may be NULL: nothing is waited for). */
 int neus2b_testbed_train_step(neus2b_testbed* tb, const float* h_next_xforms, const float* h_next_focal, const float* h_next_principal,
                               neus2b_train_stats* h_stats);
+/* Testbed::training_network_next_frame (src/testbed.cu:1991-2072) for a dynamic sequence: the next frame's images and cameras
+ * replace the current ones (same count and size; HOST arrays as in neus2b_testbed_load_training_data), the frame's learned
+ * motion is folded into the accumulated global movement that moves every ray from now on, the parameters are carried over
+ * as their fp16 values (the reference goes through a snapshot without optimizer state), both optimizers start afresh, the
+ * canonical learning rate becomes after_learning_rate, the step counter, the ray count and the ray generator's random stream
+ * restart, and the motion is reset to the identity.  The following steps train the motion alone for
+ * predict_global_movement_training_step steps (the canonical model frozen), then both.  The occupancy grid is rebuilt by the
+ * frame's first step. */
+int neus2b_testbed_next_frame(neus2b_testbed* tb, const uint32_t* h_pixels, const float* h_xforms, const float* h_focal,
+                              const float* h_principal);
+/* State of the sequence: frame index, accumulated global movement (rotation [9] row-major, transition [3]) and the current
+ * frame's motion parameters (12 floats, fp32 master; identity on the first frame).  Any pointer may be NULL. */
+int neus2b_testbed_get_movement(neus2b_testbed* tb, uint32_t* frame, float rotation[9], float transition[3], float delta[12]);
+/* Restores what neus2b_testbed_get_movement returned (snapshot["rotation"], ["transition"], ["local_rotation"],
+ * ["local_transition"] of the reference's snapshots, nerf_network.h:1169-1261). */
+int neus2b_testbed_set_movement(neus2b_testbed* tb, uint32_t frame, const float rotation[9], const float transition[3], const float delta[12]);
+
 /* Times the fused forward+backward kernel inside the step (the reference keeps a moving average of the whole step only,
  * m_training_ms, src/testbed.cu:2707-2721): arms CUDA-event pairs around that launch for the next max_steps steps on
  * the training stream (0 = off).  When h_ms_sum and h_n are given, first returns the sum of the durations recorded

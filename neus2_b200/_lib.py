@@ -87,7 +87,12 @@ class TestbedConfig(C.Structure):
                 ("progressive_start_levels", C.c_uint32), ("progressive_levels_per_increment", C.c_uint32),
                 ("progressive_steps_per_increment", C.c_uint32), ("world_size", C.c_uint32), ("rank", C.c_uint32),
                 ("valid_level_scale", C.c_float), ("base_valid_level_scale", C.c_float), ("base_training_step", C.c_uint32),
-                ("adam_flags", C.c_uint32), ("loss_scale", C.c_float)]
+                ("adam_flags", C.c_uint32), ("loss_scale", C.c_float),
+                ("predict_global_movement", C.c_uint32), ("predict_global_movement_training_step", C.c_uint32),
+                ("finetune_global_movement", C.c_uint32), ("reset_density_grid_after_global_movement", C.c_uint32),
+                ("after_learning_rate", C.c_float), ("gm_learning_rate", C.c_float), ("gm_beta1", C.c_float), ("gm_beta2", C.c_float),
+                ("gm_epsilon", C.c_float), ("gm_l2_reg", C.c_float), ("gm_ema_decay", C.c_float), ("gm_lr_decay_start", C.c_uint32),
+                ("gm_lr_decay_interval", C.c_uint32), ("gm_lr_decay_base", C.c_float), ("first_frame_offset", C.c_float * 3)]
 
 
 class TrainingState(C.Structure):
@@ -125,7 +130,7 @@ EXPORTS = [
     "neus2b_testbed_train_optimizer_step", "neus2b_testbed_sdf_grid", "neus2b_testbed_profile", "neus2b_marching_cubes_scratch_bytes", "neus2b_marching_cubes", "neus2b_marching_cubes_slab", "neus2b_marching_cubes_slab_global",
     "neus2b_render_frame", "neus2b_render_accumulate", "neus2b_render_tonemap", "neus2b_ld_random_pixel_offset", "neus2b_testbed_render", "neus2b_testbed_render_stats",
     "neus2b_mesh_1ring", "neus2b_mesh_vertex_colors", "neus2b_save_mesh", "neus2b_occupancy_mean_and_bitfield",
-    "neus2b_testbed_get_training_state", "neus2b_testbed_set_training_state", "neus2b_testbed_get_array", "neus2b_testbed_set_array",
+    "neus2b_testbed_next_frame", "neus2b_testbed_get_movement", "neus2b_testbed_set_movement", "neus2b_testbed_get_training_state", "neus2b_testbed_set_training_state", "neus2b_testbed_get_array", "neus2b_testbed_set_array",
 ]
 
 

@@ -88,4 +88,32 @@ def testbed_config_from_json(cfg, aabb_scale=1, base=None):
     out.anneal_end = int(hp.get("anneal_end", 0))
     if "batch_size" in hp:
         out.batch_size = int(hp["batch_size"])
+    # dynamic sequences (src/testbed.cu:2108-2122; the frame counts are the caller's loop: dynamic_schedule below)
+    out.predict_global_movement = int(bool(hp.get("predict_global_movement", False)))
+    out.predict_global_movement_training_step = int(hp.get("predict_global_movement_training_step", 300)) if out.predict_global_movement else 0
+    out.finetune_global_movement = int(bool(hp.get("finetune_global_movement", True)))
+    out.reset_density_grid_after_global_movement = int(bool(hp.get("reset_density_grid_after_global_movement", True)))
+    out.after_learning_rate = float(adam.get("after_learning_rate", 0.0))
+    gm = cfg.get("globalmove", {}).get("optimizer", opt)  # src/testbed.cu:2311-2312: the main optimizer's block when absent
+    g_ema, g_decay, g_adam = _find(gm, "Ema"), _find(gm, "ExponentialDecay"), _find(gm, "Adam")
+    if g_adam is not None:
+        out.gm_learning_rate = float(g_adam.get("learning_rate", out.gm_learning_rate))
+        out.gm_beta1 = float(g_adam.get("beta1", out.gm_beta1))
+        out.gm_beta2 = float(g_adam.get("beta2", out.gm_beta2))
+        out.gm_epsilon = float(g_adam.get("epsilon", out.gm_epsilon))
+        out.gm_l2_reg = float(g_adam.get("l2_reg", out.gm_l2_reg))
+    out.gm_ema_decay = float(g_ema["decay"]) if g_ema is not None else 0.0
+    if g_decay is not None:
+        out.gm_lr_decay_start = int(g_decay.get("decay_start", out.gm_lr_decay_start))
+        out.gm_lr_decay_interval = int(g_decay.get("decay_interval", out.gm_lr_decay_interval))
+        out.gm_lr_decay_base = float(g_decay.get("decay_base", out.gm_lr_decay_base))
+    else:
+        out.gm_lr_decay_interval = 0
     return out
+
+
+def dynamic_schedule(cfg):
+    """(first_frame_max_training_step, next_frame_max_training_step) of a parsed configuration: how long Testbed::frame trains
+    the first and every later frame before it switches (src/testbed.cu:1739-1746, 2108-2109)."""
+    hp = cfg.get("hyperparams", {})
+    return int(hp.get("first_frame_max_training_step", 2000)), int(hp.get("next_frame_max_training_step", 1000))

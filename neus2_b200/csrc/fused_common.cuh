@@ -80,8 +80,13 @@ __device__ __forceinline__ uint32_t geom_index(const LevelGeom& g, uint32_t k) {
 	if (g.hashed) {
 		idx = (g.hx[bx] ^ g.hy[by] ^ g.hz[bz]) & g.mask_or_size;
 	} else {
-		idx = g.hx[bx] + g.hy[by] + g.hz[bz];  // < 2 * size: a corner on the far cube face wraps once (== idx % size)
-		if (idx >= g.mask_or_size) idx -= g.mask_or_size;
+		// positions inside the unit cube give < 2 * size: a corner on the far cube face wraps once.  Samples a learned motion
+		// has carried outside the cube can give anything: then the index is reduced like the general rule says (% size)
+		idx = g.hx[bx] + g.hy[by] + g.hz[bz];
+		if (idx >= g.mask_or_size) {
+			idx -= g.mask_or_size;
+			if (idx >= g.mask_or_size) idx %= g.mask_or_size;
+		}
 	}
 	return g.offset + idx;
 }

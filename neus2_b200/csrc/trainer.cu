@@ -75,6 +75,19 @@ __global__ void master_to_half_kernel(uint64_t n, const float* __restrict__ mast
 	}
 }
 
+// Trainer::deserialize of a snapshot without optimizer state: the stored fp16 parameters become the fp32 master weights and
+// the inference (EMA) copies
+__global__ void half_to_master_kernel(uint64_t n, const __half* __restrict__ p, float* __restrict__ master, float* __restrict__ ema,
+                                      __half* __restrict__ pe) {
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+		const __half h = p[i];
+		const float w = __half2float(h);
+		master[i] = w;
+		ema[i] = w;
+		pe[i] = h;
+	}
+}
+
 // generate_grid_samples_nerf_uniform (src/testbed_nerf.cu:586-599): lattice positions x / res, unit aabb
 __global__ void sdf_grid_positions_kernel(uint32_t rx, uint32_t ry, uint64_t first, uint32_t n, float ix, float iy, float iz,
                                           float* __restrict__ pos) {
@@ -136,6 +149,14 @@ struct neus2b_testbed {
 	uint32_t render_pixels = 0;
 	neus2b_render_workspace render_ws{};
 	float *render_frame = nullptr, *render_depth = nullptr, *render_acc = nullptr, *render_out = nullptr;
+	// dynamic sequences (frames after the first): the frame's learned motion and the accumulated movement of the earlier frames
+	uint32_t frame = 0;
+	bool train_canonical = true, train_delta = false;
+	uint32_t canonical_step = 0;  // m_canonical_training_step (src/testbed_nerf.cu:3506-3522)
+	uint32_t adam_step = 0, delta_adam_step = 0;  // steps taken by the frame's optimizers (both start afresh with every frame)
+	float acc_rotation[9] = {1.f, 0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f, 1.f}, acc_transition[3] = {0.f, 0.f, 0.f};
+	__half *delta = nullptr, *delta_ema = nullptr;
+	float *delta_master = nullptr, *delta_m = nullptr, *delta_v = nullptr, *delta_ema_master = nullptr, *delta_sums = nullptr;
 	bool step_pending = false;  // between a step's backward pass and its optimizer pass
 	cudaEvent_t stats_event = nullptr;  // behind the last copy of the step statistics to the host
 	uint32_t stats_step = 0;
@@ -192,6 +213,21 @@ extern "C" void neus2b_testbed_default_config(neus2b_testbed_config* c) {
 	c->world_size = 1;
 	c->rank = 0;
 	c->loss_scale = 128.f;
+	c->predict_global_movement = 0;
+	c->predict_global_movement_training_step = 300;  // src/testbed.cu:2120
+	c->finetune_global_movement = 1;
+	c->reset_density_grid_after_global_movement = 1;
+	c->after_learning_rate = 0.f;
+	// "globalmove" optimizer of configs/nerf/base.json:84-110
+	c->gm_learning_rate = 5e-3f;
+	c->gm_beta1 = 0.9f;
+	c->gm_beta2 = 0.99f;
+	c->gm_epsilon = 1e-10f;
+	c->gm_l2_reg = 1e-10f;
+	c->gm_ema_decay = 0.95f;
+	c->gm_lr_decay_start = 6000;
+	c->gm_lr_decay_interval = 25;
+	c->gm_lr_decay_base = 0.99f;
 }
 
 extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
@@ -208,6 +244,28 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	if (tb->stats_event) cudaEventDestroy(tb->stats_event);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
+}
+
+// DeltaNetwork::initialize_params (transform_network.h:207-246): no translation, the unit 6-D rotation (1 0 0 | 0 1 0), and a
+// fresh optimizer for it.
+static int write_delta(neus2b_testbed* tb, const float h[12]) {
+	float buf[12 * 5] = {};
+	uint16_t hb[16] = {};
+	for (int k = 0; k < 12; ++k) {
+		buf[k] = buf[36 + k] = h[k];
+		const __half v = __float2half_rn(h[k]);
+		memcpy(&hb[k], &v, 2);
+	}
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->delta_master, buf, sizeof(buf), cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->delta, hb, sizeof(hb), cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->delta_ema, hb, sizeof(hb), cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));  // the sources are on this thread's stack
+	tb->delta_adam_step = 0;
+	return NEUS2B_OK;
+}
+static int reset_delta(neus2b_testbed* tb) {
+	const float ident[12] = {0.f, 0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f};
+	return write_delta(tb, ident);
 }
 
 extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_testbed** out) {
@@ -278,6 +336,13 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	TB_ALLOC(tb->loss, (size_t)tb->max_rays);
 	TB_ALLOC(tb->ek_loss, (size_t)tb->max_rays);
 	TB_ALLOC(tb->state, (size_t)1);
+	TB_ALLOC(tb->delta, (size_t)16);
+	TB_ALLOC(tb->delta_ema, (size_t)16);
+	TB_ALLOC(tb->delta_master, (size_t)12 * 5);  // master, m, v, ema master, sums
+	tb->delta_m = tb->delta_master + 12;
+	tb->delta_v = tb->delta_master + 24;
+	tb->delta_ema_master = tb->delta_master + 36;
+	tb->delta_sums = tb->delta_master + 48;
 	tb->ws.d_n_rays_total = &tb->state->n_rays_total;
 	{
 		const int erc = tc_error_device_ptr(&tb->d_device_error);
@@ -299,6 +364,11 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	if (e != cudaSuccess) {
 		neus2b_testbed_destroy(tb);
 		return (int)e;
+	}
+	rc = reset_delta(tb);
+	if (rc) {
+		neus2b_testbed_destroy(tb);
+		return rc;
 	}
 	*out = tb;
 	return NEUS2B_OK;
@@ -422,10 +492,25 @@ static int device_error_status() {
 	return flags ? NEUS2B_E_DEVICE : NEUS2B_OK;
 }
 
+// The mask's clock: the training step, and on later frames of a dynamic sequence the steps behind the phase that trains the
+// motion alone (set_training_step(m_training_step - m_predict_global_movement_training_step), src/testbed.cu:2642-2647).
+static uint32_t predict_steps(const neus2b_testbed* tb) {
+	return tb->cfg.predict_global_movement ? tb->cfg.predict_global_movement_training_step : 0u;
+}
 static neus2b_grid_desc active_desc(const neus2b_testbed* tb) {
 	neus2b_grid_desc d = tb->cfg.grid;
-	d.n_active_levels = neus2b_testbed_config_active_levels(&tb->cfg, tb->training_step);
+	uint32_t step = tb->training_step;
+	if (tb->frame >= 1) step = step > predict_steps(tb) ? step - predict_steps(tb) : 0u;
+	d.n_active_levels = neus2b_testbed_config_active_levels(&tb->cfg, step);
 	return d;
+}
+// The motion the networks apply to the samples (m_use_delta: a later frame whose motion is being trained, src/testbed.cu:2694-2700).
+static const neus2b_motion* step_motion(const neus2b_testbed* tb, neus2b_motion* m, bool with_sums) {
+	if (tb->frame == 0 || !tb->train_delta) return nullptr;
+	m->d_delta = (const uint16_t*)tb->delta;
+	for (int e = 0; e < 3; ++e) m->first_frame_offset[e] = tb->cfg.first_frame_offset[e];
+	m->d_sums = with_sums ? tb->delta_sums : nullptr;
+	return m;
 }
 
 // training_prep_nerf (src/testbed_nerf.cu:3989-4003), called every clamp(step/16, 1, 16) steps (src/testbed.cu:2659)
@@ -444,9 +529,15 @@ static int training_prep(neus2b_testbed* tb) {
 	const neus2b_pcg32 rn{tb->density_rng.state, tb->density_rng.inc};
 	tb->density_rng.advance(1ull << 32);
 	const neus2b_grid_desc d = active_desc(tb);
-	int rc = neus2b_occupancy_update(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, nc, n_uniform, n_nonuniform, ru, rn, tb->ema_step,
-	                                 tb->cfg.density_grid_decay, tb->density_grid, tb->density_tmp, tb->bitfield, tb->density_mean,
-	                                 tb->occ_pos, tb->occ_idx, (uint16_t*)tb->occ_sdf, tb->occ_partial, tb->stream);
+	if (tb->training_step == 0) {  // a frame's first update starts from an empty grid (src/testbed_nerf.cu:3308-3325)
+		tb->ema_step = 0;
+		N2B_CHECK_CUDA(cudaMemsetAsync(tb->density_grid, 0, sizeof(float) * (size_t)cells * nc, tb->stream));
+	}
+	neus2b_motion mo{};
+	int rc = neus2b_occupancy_update_moved(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, nc, n_uniform, n_nonuniform, ru, rn, tb->ema_step,
+	                                       tb->cfg.density_grid_decay, tb->density_grid, tb->density_tmp, tb->bitfield, tb->density_mean,
+	                                       tb->occ_pos, tb->occ_idx, (uint16_t*)tb->occ_sdf, tb->occ_partial, step_motion(tb, &mo, false),
+	                                       tb->stream);
 	++tb->ema_step;
 	tb->occ_bounds_stale = true;
 	return rc;
@@ -468,7 +559,21 @@ static neus2b_train_cfg make_train_cfg(const neus2b_testbed* tb) {
 	c.ray_index_offset = tb->cfg.rank * tb->max_rays;
 	c.ray_count_scale = tb->cfg.world_size;
 	c.cos_anneal_ratio = tb->cfg.anneal_end == 0 ? 1.0f : fminf(1.0f, (float)tb->training_step / (float)tb->cfg.anneal_end);
+	// rays go through the accumulated movement of the earlier frames (m_predict_global_movement, src/testbed_nerf.cu:3830-3832)
+	if (tb->cfg.predict_global_movement) {
+		c.use_global_movement = 1;
+		memcpy(c.rotation, tb->acc_rotation, sizeof(c.rotation));
+		memcpy(c.transition, tb->acc_transition, sizeof(c.transition));
+		memcpy(c.first_frame_offset, tb->cfg.first_frame_offset, sizeof(c.first_frame_offset));
+	}
 	return c;
+}
+
+// m_canonical_training_step after a step (src/testbed_nerf.cu:3506-3522): the step count, or on later frames the steps behind
+// the motion-only phase, during which it stays where the frame switch put it (0: the occupancy grid is updated every step).
+static uint32_t next_canonical_step(const neus2b_testbed* tb, uint32_t training_step) {
+	if (!tb->cfg.predict_global_movement || tb->frame == 0) return training_step;
+	return training_step < predict_steps(tb) ? 0u : training_step - predict_steps(tb);
 }
 
 static uint32_t occupancy_skip(uint32_t step) { return step / 16u < 1u ? 1u : (step / 16u > 16u ? 16u : step / 16u); }
@@ -494,7 +599,17 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	int rc;
-	if (tb->training_step % occupancy_skip(tb->training_step) == 0) {
+	// a later frame of a dynamic sequence: the canonical model joins once the motion-only phase is over (src/testbed.cu:2649-2657)
+	if (tb->frame >= 1 && tb->training_step == predict_steps(tb)) {
+		tb->train_canonical = true;
+		if (!tb->cfg.finetune_global_movement) tb->train_delta = false;
+		if (tb->cfg.reset_density_grid_after_global_movement && predict_steps(tb) > 0) {
+			N2B_CHECK_CUDA(cudaMemsetAsync(tb->density_grid, 0,
+			                               sizeof(float) * (size_t)NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * NEUS2B_GRIDSIZE * tb->cfg.n_cascades, tb->stream));
+			tb->ema_step = 0;
+		}
+	}
+	if (tb->canonical_step % occupancy_skip(tb->canonical_step) == 0) {
 		if (tb->pregenerated) return NEUS2B_E_INVALID;  // (pregenerate refuses steps that start with an occupancy update)
 		rc = training_prep(tb);
 		if (rc) return rc;
@@ -509,16 +624,22 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 		rc = generate_step_samples(tb, tc, rng);
 		if (rc) return rc;
 	}
-	rc = neus2b_neus_forward(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, tb->max_samples, tb->ws.d_counters + 4, tb->ws.d_coords,
-	                         (uint16_t*)tb->mlp_out, tb->stream);
+	neus2b_motion mo{};
+	const neus2b_motion* motion = step_motion(tb, &mo, true);
+	rc = neus2b_neus_forward_moved(&d, (const uint16_t*)tb->params, tb->cfg.sdf_bias, tb->max_samples, tb->ws.d_counters + 4, tb->ws.d_coords,
+	                               motion, (uint16_t*)tb->mlp_out, tb->stream);
 	if (rc) return rc;
 	rc = neus2b_compute_loss(&tb->ds, &tc, tb->max_rays, d_n_rays, 0, rng, tb->target, (const uint16_t*)tb->mlp_out, &tb->ws,
 	                         tb->coords_compacted, (uint16_t*)tb->dloss, tb->loss, tb->ek_loss, 1, tb->stream);
 	if (rc) return rc;
 	const bool timed = tb->prof_on && tb->prof_used + 2 <= tb->prof_events.size();
 	if (timed) cudaEventRecord(tb->prof_events[tb->prof_used], tb->stream);
-	rc = neus2b_neus_train(&d, (const uint16_t*)tb->params, tb->target, tb->coords_compacted, (const uint16_t*)tb->dloss,
-	                       tb->target * tb->cfg.world_size, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->stream);
+	// (the canonical gradients are not formed while the canonical model is frozen: m_train_canonical, nerf_network.h:446)
+	const bool canon = tb->train_canonical;
+	if (canon || motion)
+		rc = neus2b_neus_train_moved(&d, (const uint16_t*)tb->params, tb->target, tb->coords_compacted, motion, (const uint16_t*)tb->dloss,
+		                             tb->target * tb->cfg.world_size, canon ? tb->grad_mlp : nullptr, canon ? (uint16_t*)tb->grad_grid : nullptr,
+		                             canon ? tb->grad_var : nullptr, tb->stream);
 	if (rc) return rc;
 	if (timed) {
 		cudaEventRecord(tb->prof_events[tb->prof_used + 1], tb->stream);
@@ -537,8 +658,9 @@ extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
 	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
 	if (tb->pregenerated) return NEUS2B_OK;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
-	const uint32_t next = tb->training_step + (tb->step_pending ? 1u : 0u);
+	const uint32_t next = next_canonical_step(tb, tb->training_step + (tb->step_pending ? 1u : 0u));
 	if (next % occupancy_skip(next) == 0) return 1;
+	if (tb->frame >= 1 && tb->training_step + (tb->step_pending ? 1u : 0u) == predict_steps(tb)) return 1;  // the phase change may clear the grid
 	if (tb->step_pending && !tb->tuned) {
 		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
 		N2B_CHECK_LAUNCH();
@@ -580,8 +702,9 @@ static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	const neus2b_testbed_config& c = tb->cfg;
 	neus2b_adam_cfg ac{};
-	ac.learning_rate = c.learning_rate;
-	const uint32_t step = tb->training_step + 1;
+	// from the second frame on the canonical model trains at "after_learning_rate" (src/testbed.cu:2684-2692)
+	ac.learning_rate = (tb->frame >= 1 && c.after_learning_rate > 0.f) ? c.after_learning_rate : c.learning_rate;
+	const uint32_t step = tb->adam_step + 1;  // steps of this frame's optimizer (a new one per frame, src/testbed.cu:2031-2033)
 	if (c.lr_decay_interval && step >= c.lr_decay_start)  // ExponentialDecay (configs/nerf/dtu.json:8-12)
 		ac.learning_rate *= powf(c.lr_decay_base, (float)((step - c.lr_decay_start) / c.lr_decay_interval + 1));
 	ac.beta1 = c.beta1;
@@ -594,9 +717,33 @@ static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 	ac.n_matrix = NEUS2B_MLP_N;
 	ac.flags = c.adam_flags;
 	ac.d_nonfinite = &tb->state->nonfinite;
-	int rc = neus2b_adam_step(&ac, tb->n_params, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->master, tb->adam_m, tb->adam_v,
-	                          (uint16_t*)tb->params, (uint16_t*)tb->params_ema, tb->ema_master, tb->stream);
-	if (rc) return rc;
+	int rc = NEUS2B_OK;
+	if (tb->train_canonical) {  // src/testbed_nerf.cu:3497-3499
+		rc = neus2b_adam_step(&ac, tb->n_params, tb->grad_mlp, (uint16_t*)tb->grad_grid, tb->grad_var, tb->master, tb->adam_m, tb->adam_v,
+		                      (uint16_t*)tb->params, (uint16_t*)tb->params_ema, tb->ema_master, tb->stream);
+		if (rc) return rc;
+		++tb->adam_step;
+	}
+	if (tb->frame >= 1 && tb->train_delta) {  // m_global_move.trainer->optimizer_step (:3500-3502)
+		neus2b_adam_cfg dc{};
+		const uint32_t dstep = tb->delta_adam_step + 1;
+		dc.learning_rate = c.gm_learning_rate;
+		if (c.gm_lr_decay_interval && dstep >= c.gm_lr_decay_start)
+			dc.learning_rate *= powf(c.gm_lr_decay_base, (float)((dstep - c.gm_lr_decay_start) / c.gm_lr_decay_interval + 1));
+		dc.beta1 = c.gm_beta1;
+		dc.beta2 = c.gm_beta2;
+		dc.epsilon = c.gm_epsilon;
+		dc.l2_reg = c.gm_l2_reg;
+		dc.ema_decay = c.gm_ema_decay;
+		dc.loss_scale = c.loss_scale;
+		dc.step = dstep;
+		dc.flags = c.adam_flags;
+		dc.d_nonfinite = &tb->state->nonfinite;
+		rc = neus2b_delta_optimizer_step(&dc, tb->delta_sums, tb->delta_master, tb->delta_m, tb->delta_v, (uint16_t*)tb->delta,
+		                                 (uint16_t*)tb->delta_ema, tb->delta_ema_master, nullptr, tb->stream);
+		if (rc) return rc;
+		++tb->delta_adam_step;
+	}
 	if (!tb->tuned) {
 		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
 		N2B_CHECK_LAUNCH();
@@ -604,6 +751,7 @@ static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 	tb->tuned = false;
 	tb->step_pending = false;
 	++tb->training_step;
+	tb->canonical_step = next_canonical_step(tb, tb->training_step);
 	if (want_stats) {
 		loss_reduce_kernel<<<1, 1024, 0, tb->stream>>>(tb->state, tb->loss, tb->ek_loss, tb->target);
 		N2B_CHECK_LAUNCH();
@@ -683,8 +831,11 @@ extern "C" int neus2b_testbed_sdf_grid(neus2b_testbed* tb, const uint32_t res[3]
 		const uint32_t n = (uint32_t)((total - off) < chunk ? (total - off) : chunk);
 		sdf_grid_positions_kernel<<<div_up(n, 256), 256, 0, tb->stream>>>(res[0], res[1], first + off, n, ix, iy, iz, tb->occ_pos);
 		N2B_CHECK_LAUNCH();
-		int rc = neus2b_neus_sdf(&d, (const uint16_t*)(use_ema ? tb->params_ema : tb->params), tb->cfg.sdf_bias, n, tb->occ_pos, 3,
-		                         (uint16_t*)tb->occ_sdf, tb->stream);
+		neus2b_motion mo{};
+		const neus2b_motion* motion = step_motion(tb, &mo, false);
+		if (motion && use_ema) mo.d_delta = (const uint16_t*)tb->delta_ema;
+		int rc = neus2b_neus_sdf_moved(&d, (const uint16_t*)(use_ema ? tb->params_ema : tb->params), tb->cfg.sdf_bias, n, tb->occ_pos, 3,
+		                               motion, (uint16_t*)tb->occ_sdf, tb->stream);
 		if (rc) return rc;
 		half_to_float_kernel<<<div_up(n, 256), 256, 0, tb->stream>>>(n, tb->occ_sdf, d_out + off);
 		N2B_CHECK_LAUNCH();
@@ -778,6 +929,13 @@ extern "C" int neus2b_testbed_render(neus2b_testbed* tb, const neus2b_render_req
 	c.min_transmittance = req->min_transmittance;
 	c.linear_colors = 0;
 	c.max_steps = 0;
+	if (tb->cfg.predict_global_movement) {  // src/testbed_nerf.cu:2719-2721
+		c.use_global_movement = 1;
+		memcpy(c.rotation, tb->acc_rotation, sizeof(c.rotation));
+		memcpy(c.transition, tb->acc_transition, sizeof(c.transition));
+		memcpy(c.first_frame_offset, tb->cfg.first_frame_offset, sizeof(c.first_frame_offset));
+	}
+	if (tb->frame >= 1 && tb->train_delta) c.d_delta = (const uint16_t*)(req->use_ema ? tb->delta_ema : tb->delta);
 	neus2b_grid_desc d = tb->cfg.grid;  // every level, like the SDF lattice
 	const uint16_t* params = (const uint16_t*)(req->use_ema ? tb->params_ema : tb->params);
 	for (cudaEvent_t& e : tb->render_ev)
@@ -813,6 +971,88 @@ extern "C" int neus2b_testbed_render_stats(const neus2b_testbed* tb, uint64_t* n
 	return NEUS2B_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ dynamic sequences
+
+extern "C" int neus2b_testbed_next_frame(neus2b_testbed* tb, const uint32_t* h_pixels, const float* h_xforms, const float* h_focal,
+                                         const float* h_principal) {
+	if (!tb || !tb->ds.n_images || !h_pixels || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
+	if (tb->step_pending) return NEUS2B_E_INVALID;  // between the halves of a step
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	// NerfNetwork::accumulate_global_movement (src/testbed.cu:2044) with the motion as trained (its fp16 parameters)
+	if (tb->frame >= 1 && tb->cfg.predict_global_movement) {
+		uint16_t hb[12];
+		N2B_CHECK_CUDA(cudaMemcpy(hb, tb->delta, sizeof(hb), cudaMemcpyDeviceToHost));
+		int rc = neus2b_movement_accumulate(hb, tb->acc_rotation, tb->acc_transition);
+		if (rc) return rc;
+	}
+	// load_nerf(frame): the new images and cameras
+	const size_t npx = (size_t)tb->ds.n_images * tb->ds.width * tb->ds.height;
+	N2B_CHECK_CUDA(cudaMemcpyAsync((void*)tb->ds.d_pixels, h_pixels, npx * 4, cudaMemcpyHostToDevice, tb->stream));
+	int rc = neus2b_testbed_update_cameras(tb, h_xforms, h_focal, h_principal);
+	if (rc) return rc;
+	// save_snapshot_incremental(no optimizer state) + load_snapshot_incremental (src/testbed.cu:2052-2053, 3169-3256): the fp16
+	// parameters become every copy of the weights, Adam starts from zero moments, the EMA from the weights
+	half_to_master_kernel<<<kSMs * 4, 256, 0, tb->stream>>>(tb->n_params, tb->params, tb->master, tb->ema_master, tb->params_ema);
+	N2B_CHECK_LAUNCH();
+	N2B_CHECK_CUDA(cudaMemsetAsync(tb->adam_m, 0, sizeof(float) * tb->n_params, tb->stream));
+	N2B_CHECK_CUDA(cudaMemsetAsync(tb->adam_v, 0, sizeof(float) * tb->n_params, tb->stream));
+	N2B_CHECK_CUDA(cudaMemsetAsync(tb->grad_grid, 0, sizeof(__half) * tb->n_grid, tb->stream));
+	N2B_CHECK_CUDA(cudaMemsetAsync(tb->grad_mlp, 0, sizeof(float) * (NEUS2B_MLP_N + 4), tb->stream));
+	rc = reset_delta(tb);  // a new DeltaNetwork trainer: identity motion, fresh optimizer (src/testbed.cu:2559-2568)
+	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaMemsetAsync(tb->delta_sums, 0, sizeof(float) * 12, tb->stream));
+	++tb->frame;
+	tb->training_step = 0;
+	tb->canonical_step = 0;
+	tb->adam_step = 0;
+	tb->train_canonical = false;  // src/testbed.cu:2065-2068
+	tb->train_delta = tb->cfg.predict_global_movement != 0;
+	tb->pregenerated = tb->tuned = false;
+	// reset_network_incremental (src/testbed.cu:2341-2352): the ray generator's stream and the ray count restart
+	neus2b_pcg32 r;
+	neus2b_pcg32_seed(&r, tb->cfg.seed);
+	tb->rng = Pcg32{r.state, r.inc};
+	TrainState st{};
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->h_state, tb->state, sizeof(TrainState), cudaMemcpyDeviceToHost, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	st = *tb->h_state;
+	st.rays_per_batch = 1u << 12;
+	st.measured_pre = 0;
+	*tb->h_state = st;
+	N2B_CHECK_CUDA(cudaMemcpyAsync(tb->state, tb->h_state, sizeof(TrainState), cudaMemcpyHostToDevice, tb->stream));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_get_movement(neus2b_testbed* tb, uint32_t* frame, float rotation[9], float transition[3], float delta[12]) {
+	if (!tb) return NEUS2B_E_INVALID;
+	if (frame) *frame = tb->frame;
+	if (rotation) memcpy(rotation, tb->acc_rotation, sizeof(tb->acc_rotation));
+	if (transition) memcpy(transition, tb->acc_transition, sizeof(tb->acc_transition));
+	if (delta) {
+		N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+		N2B_CHECK_CUDA(cudaMemcpyAsync(delta, tb->delta_master, sizeof(float) * 12, cudaMemcpyDeviceToHost, tb->stream));
+		N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	}
+	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_set_movement(neus2b_testbed* tb, uint32_t frame, const float rotation[9], const float transition[3],
+                                           const float delta[12]) {
+	if (!tb || !rotation || !transition) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
+	tb->frame = frame;
+	memcpy(tb->acc_rotation, rotation, sizeof(tb->acc_rotation));
+	memcpy(tb->acc_transition, transition, sizeof(tb->acc_transition));
+	tb->train_delta = frame >= 1 && tb->cfg.predict_global_movement;
+	tb->train_canonical = frame == 0 || tb->training_step >= predict_steps(tb);
+	tb->canonical_step = next_canonical_step(tb, tb->training_step);
+	tb->pregenerated = false;
+	return delta ? write_delta(tb, delta) : NEUS2B_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ snapshot state
 
 extern "C" int neus2b_testbed_get_training_state(neus2b_testbed* tb, neus2b_training_state* out) {
@@ -838,6 +1078,11 @@ extern "C" int neus2b_testbed_set_training_state(neus2b_testbed* tb, const neus2
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	tb->training_step = in->training_step;
+	tb->canonical_step = next_canonical_step(tb, tb->training_step);
+	tb->train_canonical = tb->frame == 0 || tb->training_step >= predict_steps(tb);
+	if (tb->frame >= 1) tb->train_delta = tb->cfg.predict_global_movement && (tb->cfg.finetune_global_movement || tb->training_step < predict_steps(tb));
+	if (tb->frame == 0) tb->adam_step = in->training_step;  // the first frame's optimizer has taken every step
+	else tb->adam_step = tb->training_step > predict_steps(tb) ? tb->training_step - predict_steps(tb) : 0u;
 	tb->pregenerated = tb->tuned = false;
 	tb->ema_step = in->density_grid_ema_step;
 	tb->rng = Pcg32{in->rng.state, in->rng.inc};

@@ -90,6 +90,23 @@ def _image_path(base, file_path):
     return p
 
 
+def list_frame_jsons(data_path):
+    """The per-frame transforms files of a data path (Testbed::load_nerf, src/testbed_nerf.cu:2957-2989): a directory gives every
+    *.json in it whose name does not contain "downsample", sorted by base name, one file per frame of a dynamic sequence; a
+    single .json is a one-frame sequence."""
+    data_path = os.fspath(data_path)
+    if os.path.isdir(data_path):
+        names = [n for n in os.listdir(data_path)
+                 if n.lower().endswith(".json") and "downsample" not in os.path.splitext(n)[0] and os.path.isfile(os.path.join(data_path, n))]
+        names.sort(key=lambda n: os.path.splitext(n)[0])
+        if not names:
+            raise ValueError("NeRF data path contains no json files.")
+        return [os.path.join(data_path, n) for n in names]
+    if data_path.lower().endswith(".json"):
+        return [data_path]
+    raise ValueError("NeRF data path must either be a json file or a directory containing json files.")
+
+
 def load_nerf_dataset(json_paths):
     """json_paths: one transforms file or a list of them.  Returns a dict with pixels [n][h][w] uint32, xforms [n][12] (3x4
     column major), focal [n][2], principal [n][2], and the dataset's scale / offset / aabb_scale / from_na / from_mitsuba /

@@ -86,6 +86,15 @@ def save_snapshot(tb, path, include_optimizer_state=False):
                    "ek_loss": float(st.ek_loss), "rng": [int(st.rng.state), int(st.rng.inc)],
                    "density_rng": [int(st.density_rng.state), int(st.density_rng.inc)]},
     }
+    # dynamic sequences (NerfNetwork::save_global_movement / save_local_movement, nerf_network.h:1169-1196, 1231-1235): the
+    # accumulated movement (9 + 3 fp16 values) and the current frame's motion parameters (8 + 4 fp16 values)
+    frame, R_acc, t_acc, delta = tb.movement()
+    snap["rotation"] = R_acc.astype(np.float16).tobytes()
+    snap["transition"] = t_acc.astype(np.float16).tobytes()
+    snap["local_rotation"] = delta[4:12].astype(np.float16).tobytes()
+    snap["local_transition"] = delta[0:4].astype(np.float16).tobytes()
+    snap["neus2b"]["frame"] = int(frame)
+    snap["neus2b"]["local_movement_fp32"] = delta.astype(np.float32).tobytes()
     if include_optimizer_state:
         snap["optimizer"] = {"otype": "Ema", "ema_master_binary": get_array(tb, "ema_master").tobytes(),
                              "nested": {"otype": "Adam", "current_step": int(st.training_step),
@@ -133,6 +142,14 @@ def load_snapshot(tb, path):
         set_array(tb, "density_grid", grid)
     elif grid.size != 0:  # size 0: a model that was never trained
         raise ValueError("Incompatible number of grid cascades.")
+    if "rotation" in snap:  # load_global_movement / load_local_movement (nerf_network.h:1198-1261)
+        R_acc = np.frombuffer(snap["rotation"], np.float16).astype(np.float32)
+        t_acc = np.frombuffer(snap["transition"], np.float16).astype(np.float32)
+        if "local_movement_fp32" in extra:
+            delta = np.frombuffer(extra["local_movement_fp32"], np.float32)
+        else:
+            delta = np.concatenate([np.frombuffer(snap["local_transition"], np.float16), np.frombuffer(snap["local_rotation"], np.float16)]).astype(np.float32)
+        tb.set_movement(int(extra.get("frame", 0)), R_acc, t_acc, delta)
     st = get_training_state(tb)
     st.training_step = int(snap["training_step"])
     st.loss = float(snap["loss"])

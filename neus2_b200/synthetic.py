@@ -61,8 +61,30 @@ def _linear_to_srgb(x):
     return torch.where(x < 0.0031308, 12.92 * x, 1.055 * x.clamp_min(1e-8) ** (1 / 2.4) - 0.055)
 
 
-def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=0.3, seed=0, device="cpu", cam_radius=2.5):
-    """Returns dict(pixels int32 [n][H][W] (RGBA8, R low byte), xforms [n][12], focal [n][2], principal [n][2])."""
+def sequence_poses(n_frames, seed=0, max_rot_deg=5.0, max_shift=0.02, bulge=0.03, bulge_period=25.0, radius=0.3):
+    """Per-frame pose of the moving sphere of the dynamic stand-in sequence: a seeded random walk of rigid motions (each step a
+    rotation of at most `max_rot_deg` about a random axis and a translation of at most `max_shift`) and a sinusoidal radial
+    bulge.  Returns [(rotation [3][3], translation [3], radius)] with the identity first."""
+    rng = np.random.default_rng(seed)
+    R, t, out = np.eye(3), np.zeros(3), []
+    for f in range(n_frames):
+        out.append((R.astype(np.float32), t.astype(np.float32), float(radius + bulge * math.sin(2.0 * math.pi * f / bulge_period))))
+        axis = rng.normal(size=3)
+        axis /= np.linalg.norm(axis)
+        ang = math.radians(max_rot_deg) * rng.uniform(0.3, 1.0)
+        K = np.array([[0, -axis[2], axis[1]], [axis[2], 0, -axis[0]], [-axis[1], axis[0], 0]])
+        step = np.eye(3) + math.sin(ang) * K + (1 - math.cos(ang)) * (K @ K)
+        R = step @ R
+        shift = rng.normal(size=3)
+        t = t + max_shift * rng.uniform(0.3, 1.0) * shift / np.linalg.norm(shift)
+    return out
+
+
+def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=0.3, seed=0, device="cpu", cam_radius=2.5,
+                        rotation=None, translation=None):
+    """Returns dict(pixels int32 [n][H][W] (RGBA8, R low byte), xforms [n][12], focal [n][2], principal [n][2]).
+    `rotation` [3][3] / `translation` [3] move the object rigidly about the cube's centre (its albedo moves with it); the
+    cameras and the light stay."""
     xforms = torch.from_numpy(fibonacci_cameras(n_views, cam_radius)).to(device)
     focal_px = 0.5 * width / math.tan(0.5 * math.radians(fov_deg))
     focal = torch.full((n_views, 2), focal_px, dtype=torch.float32, device=device)
@@ -71,7 +93,10 @@ def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=
     u = ((xs.float() + 0.5) / width).reshape(-1)
     v = ((ys.float() + 0.5) / height).reshape(-1)
     dl = torch.stack([(u - 0.5) * width / focal_px, (v - 0.5) * height / focal_px, torch.ones_like(u)], 1)
-    center = torch.tensor([0.5, 0.5, 0.5], device=device)
+    cube_center = torch.tensor([0.5, 0.5, 0.5], device=device)
+    Robj = torch.eye(3, device=device) if rotation is None else torch.as_tensor(np.asarray(rotation, np.float32), device=device)
+    tobj = torch.zeros(3, device=device) if translation is None else torch.as_tensor(np.asarray(translation, np.float32), device=device)
+    center = cube_center + tobj
     light = torch.tensor([0.4, -0.5, 0.77], device=device)
     light = light / light.norm()
     pixels = torch.zeros((n_views, height, width), dtype=torch.int32, device=device)
@@ -88,7 +113,8 @@ def render_sphere_views(n_views=64, width=512, height=512, fov_deg=40.0, radius=
         t = -b - torch.sqrt(disc.clamp_min(0))
         p = o + t[:, None] * d
         nrm = (p - center) / radius
-        albedo = 0.15 + 0.8 * _value_noise(p.clamp(0, 1), seed)
+        q = (p - center) @ Robj + cube_center  # the point in the object's own frame: R^T (p - c - t) + c
+        albedo = 0.15 + 0.8 * _value_noise(q.clamp(0, 1), seed)
         shade = 0.3 + 0.7 * (nrm @ light).clamp_min(0)
         col = _linear_to_srgb((albedo * shade[:, None]).clamp(0, 1))
         rgb8 = (col * 255.0 + 0.5).clamp(0, 255).to(torch.int64)

@@ -17,6 +17,8 @@ class Testbed:
         for k, v in overrides.items():
             if k in ("n_levels", "log2_hashmap_size", "base_resolution", "per_level_scale", "n_active_levels"):
                 setattr(cfg.grid, k, v)
+            elif k == "first_frame_offset":
+                cfg.first_frame_offset[:] = [float(x) for x in v]
             else:
                 if not hasattr(cfg, k):
                     raise AttributeError(k)
@@ -44,7 +46,11 @@ class Testbed:
         """A testbed configured by one of the reference's network configuration files (configs/nerf/*.json) or the parsed
         dict: what ``Testbed.reload_network_from_file`` (src/python_api.cu:339, src/testbed.cu:2093-2339) sets up."""
         from . import config
-        return cls(config=config.testbed_config_from_json(network_config, aabb_scale=aabb_scale), **overrides)
+        if not isinstance(network_config, dict):
+            network_config = config.load_json_with_comments(network_config)
+        tb = cls(config=config.testbed_config_from_json(network_config, aabb_scale=aabb_scale), **overrides)
+        tb.first_frame_max_training_step, tb.next_frame_max_training_step = config.dynamic_schedule(network_config)
+        return tb
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
@@ -67,9 +73,19 @@ class Testbed:
                                                           *[a.ctypes.data_as(C.c_void_p) for a in self._cams]))
 
     def load_training_data_from_json(self, json_paths):
-        """``Testbed.load_training_data(path)`` for a transforms file of a static scene (src/testbed.cu:155, src/nerf_loader.cu:197):
-        images and cameras through ``neus2_b200.loader``.  Returns the loaded dataset description."""
+        """``Testbed.load_training_data(path)`` (src/testbed.cu:155, src/testbed_nerf.cu:2957-2996, src/nerf_loader.cu:197): a
+        transforms file, a list of them (one scene), or a directory with one transforms file per frame of a dynamic sequence
+        (sorted by name; the first is loaded, ``training_network_next_frame`` moves on).  Images and cameras come through
+        ``neus2_b200.loader``.  Returns the loaded dataset description."""
         from . import loader
+        import os
+        if isinstance(json_paths, (str, os.PathLike)) and os.path.isdir(json_paths):
+            self.all_json_paths = loader.list_frame_jsons(json_paths)
+            json_paths = self.all_json_paths[0]
+        else:
+            self.all_json_paths = [json_paths]
+        self.all_training_time_frame = len(self.all_json_paths)
+        self.current_training_time_frame = 0
         ds = loader.load_nerf_dataset(json_paths)
         if ds["aabb_scale"] != 1 << (int(self.config.n_cascades) - 1):
             raise ValueError(f"the dataset's aabb_scale {ds['aabb_scale']} needs n_cascades = {int(ds['aabb_scale']).bit_length()}")
@@ -82,6 +98,30 @@ class Testbed:
         from . import loader
         ds = getattr(self, "dataset", None) or dict(scale=loader.NERF_SCALE, offset=[0.5, 0.5, 0.5], from_na=False, from_mitsuba=False)
         self.camera_matrix = loader.nerf_matrix_to_ngp(nerf_matrix, ds["scale"], ds["offset"], ds["from_na"], ds["from_mitsuba"])
+
+    # --- dynamic sequences
+    def next_frame(self, pixels, xforms, focal, principal):
+        """``Testbed::training_network_next_frame`` (src/testbed.cu:1991-2072): the next frame's images and cameras (same count and
+        size), the learned motion folded into the accumulated one, fresh optimizers, the motion-only phase ahead."""
+        pixels = np.ascontiguousarray(pixels).view(np.uint32)
+        self._cams = [np.ascontiguousarray(a, dtype=np.float32) for a in (xforms, focal, principal)]
+        L.check(L.lib().neus2b_testbed_next_frame(self._h, pixels.ctypes.data_as(C.c_void_p), *[a.ctypes.data_as(C.c_void_p) for a in self._cams]))
+        self.stats.training_step = 0
+
+    def movement(self):
+        """(frame index, accumulated rotation [3][3], accumulated transition [3], the frame's motion parameters [12])."""
+        frame = C.c_uint32(0)
+        R, t, d = np.zeros(9, np.float32), np.zeros(3, np.float32), np.zeros(12, np.float32)
+        L.check(L.lib().neus2b_testbed_get_movement(self._h, C.byref(frame), R.ctypes.data_as(C.c_void_p), t.ctypes.data_as(C.c_void_p),
+                                                    d.ctypes.data_as(C.c_void_p)))
+        return int(frame.value), R.reshape(3, 3), t, d
+
+    def set_movement(self, frame, rotation, transition, delta=None):
+        R = np.ascontiguousarray(rotation, dtype=np.float32).reshape(9)
+        t = np.ascontiguousarray(transition, dtype=np.float32).reshape(3)
+        d = np.ascontiguousarray(delta, dtype=np.float32).reshape(12) if delta is not None else None
+        L.check(L.lib().neus2b_testbed_set_movement(self._h, C.c_uint32(int(frame)), R.ctypes.data_as(C.c_void_p), t.ctypes.data_as(C.c_void_p),
+                                                    d.ctypes.data_as(C.c_void_p) if d is not None else None))
 
     def update_cameras(self, xforms=None, focal=None, principal=None):
         cams = [np.ascontiguousarray(a, dtype=np.float32) if a is not None else b
@@ -109,9 +149,32 @@ class Testbed:
         return self.stats
 
     def frame(self):
-        """One training step, like ``Testbed::frame`` with ``shall_train`` set (src/testbed.cu:1712)."""
+        """One training step, like ``Testbed::frame`` with ``shall_train`` set (src/testbed.cu:1712).  On a dynamic sequence the
+        frame is switched first when the current one has had its steps (src/testbed.cu:1739-1746)."""
         if self.shall_train:
+            n_frames = getattr(self, "all_training_time_frame", 1)
+            if n_frames > 1:
+                cur = getattr(self, "current_training_time_frame", 0)
+                limit = self.first_frame_max_training_step if cur == 0 else self.next_frame_max_training_step
+                if self.stats.training_step >= limit:
+                    self.training_network_next_frame()
             self.train(1)
+        return True
+
+    first_frame_max_training_step = 2000  # hyperparams of the network configuration (src/testbed.cu:2108-2109)
+    next_frame_max_training_step = 1000
+
+    def training_network_next_frame(self):
+        """``Testbed::training_network_next_frame`` (src/testbed.cu:1991-2072) for a sequence loaded from a directory of per-frame
+        transforms files: loads the next frame's images and cameras and switches to it.  False on the last frame."""
+        from . import loader
+        cur = getattr(self, "current_training_time_frame", 0)
+        if cur >= getattr(self, "all_training_time_frame", 1) - 1:
+            return False
+        ds = loader.load_nerf_dataset(self.all_json_paths[cur + 1])
+        self.dataset = ds
+        self.next_frame(ds["pixels"], ds["xforms"], ds["focal"], ds["principal"])
+        self.current_training_time_frame = cur + 1
         return True
 
     def train_backward(self):

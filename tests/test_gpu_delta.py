@@ -103,6 +103,25 @@ def test_fused_kernels_with_motion_match_oracle(gpu, oracle, n, L_, n_active):
         ops.neus_train_moved(ld, half(params), dev_coords, None, half(dl_bits), n, None, None, None)
 
 
+def test_samples_moved_outside_the_unit_cube(gpu, oracle):
+    """A motion can carry samples out of the cube the grid was built for: dense levels then wrap by the general rule (index
+    modulo the level's size) instead of the single wrap that positions inside the cube need."""
+    L, ops = gpu
+    O = oracle
+    d, params, coords, rng = model(O, seed=5, n=20000)
+    big = DELTA.copy()
+    big[:3] = [0.35, -0.3, 0.25]
+    bits = O.f16_bits(big)
+    moved = O.delta_forward(bits, coords)
+    outside = ((moved[:, :3] < 0) | (moved[:, :3] > 1)).any(1)
+    assert 0.3 < outside.mean() < 0.95
+    ref = O.bits_f32(O.neus_forward(d, params, moved))
+    out = ops.neus_forward_moved(to_lib_desc(L, d), half(params), torch.from_numpy(coords).cuda(), ops.motion(half(bits))).float().cpu().numpy()
+    torch.cuda.synchronize()
+    check_fp16("delta_outside_sdf", out[:, 3], ref[:, 3], min_frac=0.9999, min_cos=0.99999)
+    check_fp16("delta_outside_rgb", out[:, 0:3], ref[:, 0:3], min_frac=0.9999, min_cos=0.99999)
+
+
 def test_motion_optimizer_step(gpu, oracle):
     L, ops = gpu
     bits = oracle.f16_bits(DELTA)

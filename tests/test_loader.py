@@ -118,3 +118,21 @@ def test_errors(tmp_path):
     path.write_text(json.dumps(raw))
     with pytest.raises(ValueError, match="No training images"):
         loader.load_nerf_dataset(path)
+
+
+def test_directory_of_per_frame_files_is_a_sequence(tmp_path):
+    """A data path that is a directory holds one transforms file per frame of a dynamic sequence: every .json whose name does
+    not contain "downsample", sorted by base name (src/testbed_nerf.cu:2957-2989)."""
+    from neus2_b200 import loader
+    for name in ("frame_010.json", "frame_002.json", "frame_002_downsample.json", "notes.txt", "frame_001.JSON"):
+        (tmp_path / name).write_text("{}")
+    (tmp_path / "sub.json").mkdir()
+    got = [p.split("/")[-1] for p in loader.list_frame_jsons(tmp_path)]
+    assert got == ["frame_001.JSON", "frame_002.json", "frame_010.json"]
+    assert loader.list_frame_jsons(tmp_path / "frame_010.json") == [str(tmp_path / "frame_010.json")]
+    with pytest.raises(ValueError):
+        loader.list_frame_jsons(tmp_path / "notes.txt")
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(ValueError):
+        loader.list_frame_jsons(empty)
