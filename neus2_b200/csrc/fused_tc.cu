@@ -42,7 +42,7 @@ constexpr int T48 = 128 * 48 * 2, T64 = 128 * 64 * 2, T16 = 128 * 16 * 2;
 
 static __device__ uint32_t g_tc_error;  // bit 0: a bounded completion wait ran out
 
-template <int MODE>
+template <int MODE, bool DYN>
 struct Smem {
 	alignas(128) unsigned char W1s[64 * 48 * 2];
 	unsigned char W2s[16 * 64 * 2];
@@ -60,7 +60,10 @@ struct Smem {
 	__half gst[MODE == MODE_TRAIN ? 128 : 1][8];      // rows 3..10 of a sample's output gradient, from part 0 to part 1
 	float nrm[kParts][128][3];
 	float vbuf[128][4];
-	float dxc[MODE == MODE_TRAIN ? 128 : 1][3];  // xyz rows of the colour-net input gradient (for the DeltaNetwork's dL/dx)
+	// xyz rows of the colour-net input gradient (for the DeltaNetwork's dL/dx).  Only in the dynamic instantiation: with it the
+	// static training kernel's shared memory (plus the 1 KB the system reserves per CTA) would cross 132 KB, the carve-out
+	// would move up a step and the L1 that the table gathers live on would shrink from 124 to 92 KB.
+	float dxc[(MODE == MODE_TRAIN && DYN) ? 128 : 1][3];
 	float motion[12];                            // the frame's rigid motion: R row-major, t
 	float dsum[12];                              // this CTA's share of the DeltaNetwork's backward sums
 	float red[kThreads / 32];
@@ -145,17 +148,21 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 	for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int MODE>
+// DYN compiles the dynamic-sequence parts in (the frame's rigid motion applied to the samples, the motion's backward sums,
+// gradient outputs that may be absent while the canonical model is frozen).  Static scenes run the DYN = false
+// instantiation: keeping the encoding's Jacobian alive up to the scatter for a flag that is never set costs the static
+// kernel 9 % (0.275 -> 0.300 ms at 2^18 samples).
+template <int MODE, bool DYN>
 __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) {
 	extern __shared__ __align__(128) unsigned char smem_raw[];
-	Smem<MODE>& sm = *reinterpret_cast<Smem<MODE>*>(smem_raw);
+	Smem<MODE, DYN>& sm = *reinterpret_cast<Smem<MODE, DYN>*>(smem_raw);
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int s = tid & 127, part = tid >> 7;
 	const __half* grid = a.params + NEUS2B_GRID_OFF;
 	constexpr uint32_t kTmemCols = MODE == MODE_TRAIN ? 512u : 128u;
 
 	// ---- one-time set-up: zero the tiles (padding columns stay zero), stage the weights, allocate tensor memory
-	for (int e = tid; e < (int)(sizeof(Smem<MODE>) / 16); e += kThreads) reinterpret_cast<uint4*>(smem_raw)[e] = make_uint4(0, 0, 0, 0);
+	for (int e = tid; e < (int)(sizeof(Smem<MODE, DYN>) / 16); e += kThreads) reinterpret_cast<uint4*>(smem_raw)[e] = make_uint4(0, 0, 0, 0);
 	__syncthreads();
 	for (int e = tid; e < 64 * 48; e += kThreads) {
 		const int r = e / 48, k = e % 48;
@@ -168,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	}
 	for (int e = tid; e < 64 * 64; e += kThreads)
 		*reinterpret_cast<__half*>(sm.W2c + tc::blk_off(e / 64, e % 64, 64)) = a.params[NEUS2B_RGB_W2 + e];
-	const bool moved = a.delta != nullptr;
+	const bool moved = DYN && a.delta != nullptr;
 	if (tid == 0 && moved) {
 		const RigidMotion rm = load_rigid_motion(a.delta);
 #pragma unroll
@@ -474,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 #pragma unroll
 				for (int e = 0; e < 3; ++e) {
 					sm.vbuf[s][e] = __half2float(__float2half_rn(v[3 + e])) + __half2float(gs[1 + e]) / a.batch_size + __half2float(gs[5 + e]);
-					sm.dxc[s][e] = __half2float(__float2half_rn(v[e]));
+					if (DYN) sm.dxc[s][e] = __half2float(__float2half_rn(v[e]));
 				}
 			}
 			N2B_ISSUE_TAIL(gemm<64>(tm, kmaj(sm.dY, 16), mnmaj(sm.W2s, 64), 1, false),
@@ -520,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 			N2B_ISSUE_NOWAIT(gemm<16>(WG_W2sT, mnmaj(sm.X3, 64), mnmaj(sm.E0, 16), 8, true));
 			// ---- B6: grid gradient (first + second order merged, one reduction per corner); runs while the tensor pipe
 			// finishes the tile's last weight-gradient GEMM
-			const bool want_dx = a.delta_sums != nullptr, do_grid = a.grad_grid != nullptr;
+			const bool want_dx = DYN && a.delta_sums != nullptr, do_grid = !DYN || a.grad_grid != nullptr;
 			float dxp[3] = {0.f, 0.f, 0.f};  // this thread's levels' share of dL/dx (first-order backward of the encoding)
 			{
 				float dzv[8];
@@ -665,8 +672,8 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 
 	if constexpr (MODE == MODE_TRAIN) {
 		// ---- flush the weight gradients held in tensor memory (rows 0..63 of each accumulator)
-		if (a.delta_sums && tid < 12 && sm.dsum[tid] != 0.f) atomicAdd(a.delta_sums + tid, sm.dsum[tid]);
-		if (ok && !first && s < 64 && a.grad_mlp) {
+		if (DYN && a.delta_sums && tid < 12 && sm.dsum[tid] != 0.f) atomicAdd(a.delta_sums + tid, sm.dsum[tid]);
+		if (ok && !first && s < 64 && (!DYN || a.grad_mlp)) {
 			float v[16];
 			if (part == 0) {
 #pragma unroll
@@ -716,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 		if (tid == 0) {
 			float t = 0.f;
 			for (int w = 0; w < kThreads / 32; ++w) t += sm.red[w];
-			if (t != 0.f && a.grad_var) atomicAdd(a.grad_var, t);
+			if (t != 0.f && (!DYN || a.grad_var)) atomicAdd(a.grad_var, t);
 		}
 	}
 	tc::fence_before_sync();
@@ -724,23 +731,28 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
 }
 
-template <int MODE>
+template <int MODE, bool DYN>
 static int launch(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) {
-	const size_t smem = sizeof(Smem<MODE>) + 128;
-	N2B_CHECK_CUDA(cudaFuncSetAttribute(neus_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	const size_t smem = sizeof(Smem<MODE, DYN>) + 128;
+	N2B_CHECK_CUDA(cudaFuncSetAttribute(neus_tc_kernel<MODE, DYN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	uint32_t ctas = (n_upper + 127u) / 128u;
 	const uint32_t per_sm = 1u;
 	if (ctas > kSMs * per_sm) ctas = kSMs * per_sm;
 	if (ctas == 0) return NEUS2B_OK;
-	neus_tc_kernel<MODE><<<ctas, kThreads, smem, stream>>>(a);
+	neus_tc_kernel<MODE, DYN><<<ctas, kThreads, smem, stream>>>(a);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;
 }
 
 }  // namespace tcf
 
-int launch_neus_tc_forward(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) { return tcf::launch<MODE_FWD>(a, n_upper, stream); }
-int launch_neus_tc_train(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) { return tcf::launch<MODE_TRAIN>(a, n_upper, stream); }
+int launch_neus_tc_forward(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) {
+	return a.delta ? tcf::launch<MODE_FWD, true>(a, n_upper, stream) : tcf::launch<MODE_FWD, false>(a, n_upper, stream);
+}
+int launch_neus_tc_train(const NeusArgs& a, uint32_t n_upper, cudaStream_t stream) {
+	const bool dynamic = a.delta || a.delta_sums || !a.grad_grid || !a.grad_mlp || !a.grad_var;
+	return dynamic ? tcf::launch<MODE_TRAIN, true>(a, n_upper, stream) : tcf::launch<MODE_TRAIN, false>(a, n_upper, stream);
+}
 int read_tc_error(uint32_t* h_flags) {
 	uint32_t v = 0;
 	cudaError_t e = cudaMemcpyFromSymbol(&v, tcf::g_tc_error, sizeof(v));

@@ -90,10 +90,16 @@ static inline void level_corners(const n2o_grid_levels* lv, uint32_t l, const fl
 		uint32_t idx;
 		if (lv->hashed[l]) {
 			idx = (cc[0] * 1u) ^ (cc[1] * 2654435761u) ^ (cc[2] * 805459861u);
+			idx %= n;
 		} else {
-			idx = cc[0] + cc[1] * res + cc[2] * res * res;
+			/* dense level: the lattice index modulo the level's size, over the integers (cells outside the lattice have
+			 * negative or large coordinates; inside the unit cube this is the plain index, or one wrap on the far face) */
+			int64_t v = (int64_t)(int32_t)cc[0] + (int64_t)(int32_t)cc[1] * (int64_t)res + (int64_t)(int32_t)cc[2] * (int64_t)res * (int64_t)res;
+			v %= (int64_t)n;
+			if (v < 0) v += (int64_t)n;
+			idx = (uint32_t)v;
 		}
-		c->idx[k] = lv->offset[l] + idx % n;
+		c->idx[k] = lv->offset[l] + idx;
 		c->w[k] = wd[0] * wd[1] * wd[2];
 		c->dw[k][0] = ((k & 1u) ? scale : -scale) * wd[1] * wd[2];
 		c->dw[k][1] = ((k & 2u) ? scale : -scale) * wd[0] * wd[2];
