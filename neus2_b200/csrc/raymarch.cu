@@ -51,11 +51,9 @@ __global__ void __launch_bounds__(256) ray_setup_kernel(neus2b_dataset ds, neus2
 #pragma unroll
 			for (int e = 0; e < 3; ++e) {
 				r.o[e] = X[9 + e];
-				r.d[e] = X[0 + e] * dl[0] + X[3 + e] * dl[1] + X[6 + e] * dl[2];
+				r.d[e] = sum3_eigen(X[0 + e] * dl[0], X[3 + e] * dl[1], X[6 + e] * dl[2]);
 			}
-			const float inv = 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
-#pragma unroll
-			for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+			normalize3_eigen(r.d, dirn);
 			if (cfg.use_global_movement) {  // :1370-1378: the ray is moved; its direction is not normalised again
 				float o2[3], q[3], dq[3];
 #pragma unroll
@@ -95,10 +93,13 @@ __global__ void __launch_bounds__(128) count_steps_kernel(neus2b_train_cfg cfg, 
 	for (uint32_t h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); h < n_hit; h += warps) {
 		const uint32_t i = hit_list[h];
 		RayTmp r = tmp[i];
-		const float inv = cfg.use_global_movement ? 1.0f : 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
 		float dirn[3];
+		if (cfg.use_global_movement) {
 #pragma unroll
-		for (int e = 0; e < 3; ++e) dirn[e] = r.d[e] * inv;
+			for (int e = 0; e < 3; ++e) dirn[e] = r.d[e];
+		} else {
+			normalize3_eigen(r.d, dirn);
+		}
 		float t_lo, t_hi;
 		(void)cull_ray(box, r.o, dirn, t_lo, t_hi);
 		uint32_t n_chunks = 0;
@@ -228,8 +229,13 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
 			numsteps[kidx * 2 + 0] = r.numsteps;
 			numsteps[kidx * 2 + 1] = base;
 		}
-		const float inv = cfg.use_global_movement ? 1.0f : 1.0f / sqrtf(r.d[0] * r.d[0] + r.d[1] * r.d[1] + r.d[2] * r.d[2]);
-		const float dirn[3] = {r.d[0] * inv, r.d[1] * inv, r.d[2] * inv};
+		float dirn[3];
+		if (cfg.use_global_movement) {
+#pragma unroll
+			for (int e = 0; e < 3; ++e) dirn[e] = r.d[e];
+		} else {
+			normalize3_eigen(r.d, dirn);
+		}
 		// the mask record covers the first kMaskWords * 32 ray parameters; longer rays march again
 		if (masks && !long_ray)
 			emit_from_masks(cfg, r.o, dirn, r.startt, masks + (size_t)i * kMaskWords, r.numsteps, coords + (size_t)base * 7, lane);
@@ -279,9 +285,7 @@ __device__ __forceinline__ void bent_dir_from_lane0(uint32_t wx, uint32_t wy, fl
 	wy = __shfl_sync(kFull, wy, 0);
 	const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&wx)), b = __half22float2(*reinterpret_cast<const __half2*>(&wy));
 	const float dd[3] = {a.x * 2.f - 1.f, a.y * 2.f - 1.f, b.x * 2.f - 1.f};
-	const float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
-#pragma unroll
-	for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+	normalize3_eigen(dd, dir);
 }
 
 // Pass A (:1563-1617): composite along the ray until transmittance drops below 1e-4; count the surviving samples.
@@ -449,7 +453,7 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 			gws = (mask_gt - sg) * ws * cfg.mask_loss_weight;
 		}
 		const float n_rays_f = (float)n_rays * (float)(cfg.ray_count_scale ? cfg.ray_count_scale : 1u);
-		if (lane == 0 && loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
+		if (lane == 0 && loss_out) loss_out[i] = sum3_eigen(lgl[0], lgl[1], lgl[2]) / 3.0f / n_rays_f;  // lg.loss.mean() (:1715)
 		const float loss_scale = cfg.loss_scale / n_rays_f;
 		float dir[3];
 		bent_dir_from_lane0(q1.x, q1.y, dir);
@@ -492,13 +496,14 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 				float g[16];
 #pragma unroll
 				for (int k = 0; k < 16; ++k) g[k] = 0.f;
-				float dla = gws * (1.0f - ws);
+				float dterm[3];
 #pragma unroll
 				for (int e = 0; e < 3; ++e) {
 					const float suffix = rgb_ray[e] - rgb2[e];
 					g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
-					dla += lgg[e] * (Ta * s.rgb[e] - suffix);
+					dterm[e] = lgg[e] * (Ta * s.rgb[e] - suffix);
 				}
+				float dla = sum3_eigen(dterm[0], dterm[1], dterm[2]) + gws * (1.0f - ws);  // gradient.dot(T rgb - suffix) + mask term (:1829-1831)
 				dla = (float)((double)dla / ((double)(1.0f - s.alpha) + 1e-5));  // "/ (1.0f - alpha + 1e-5)": fp64 divide (:1829-1832)
 				float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
 				if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {

@@ -27,7 +27,7 @@ def build(verbose=False):
     if ref is None or flags is None:
         return None
     src = os.path.join(HERE, "ref_kernels", "ref_nerf_kernels.cu")
-    deps = [src, os.path.join(ref, "src", "testbed_nerf.cu")] + [os.path.join(d, f) for d, _, fs in os.walk(os.path.join(ROOT, "include")) for f in fs]
+    deps = [src, os.path.abspath(__file__), os.path.join(ref, "src", "testbed_nerf.cu")] + [os.path.join(d, f) for d, _, fs in os.walk(os.path.join(ROOT, "include")) for f in fs]
     if os.path.exists(OUT) and os.path.getmtime(OUT) > max(os.path.getmtime(p) for p in deps):
         return OUT
     os.makedirs(os.path.dirname(OUT), exist_ok=True)

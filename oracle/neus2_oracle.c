@@ -923,6 +923,21 @@ static inline void random_image_pos(n2o_pcg32* rng, const n2o_dataset* ds, int s
 	}
 }
 
+/* The reference writes these with Eigen expressions: a reduction over three terms is evaluated as a0 + (a1 + a2) (the
+ * unrolled redux splits the range in halves, Eigen/src/Core/Redux.h), and normalized() divides every component by the root of
+ * the squared norm (Eigen/src/Core/Dot.h) instead of multiplying by a reciprocal.  Checked against the reference's kernels
+ * running on a GPU: with these the rays and sample positions agree bit for bit. */
+static inline float sum3_eigen(float a, float b, float c) { return a + (b + c); }
+static inline void normalize3_eigen(const float* v, float* out) {
+	const float z = sum3_eigen(v[0] * v[0], v[1] * v[1], v[2] * v[2]);
+	if (z > 0.0f) {
+		const float n = sqrtf(z);
+		for (int e = 0; e < 3; ++e) out[e] = v[e] / n;
+	} else {
+		for (int e = 0; e < 3; ++e) out[e] = v[e];
+	}
+}
+
 typedef struct {
 	uint32_t keep, numsteps;
 	float o[3], d[3], dirn[3], startt;
@@ -947,10 +962,9 @@ static void ray_setup(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint32_t 
 	float dl[3] = {(xy[0] - pp[0]) * (float)ds->width / fl[0], (xy[1] - pp[1]) * (float)ds->height / fl[1], 1.0f};
 	for (int e = 0; e < 3; ++e) {
 		r->o[e] = X[9 + e];
-		r->d[e] = X[0 + e] * dl[0] + X[3 + e] * dl[1] + X[6 + e] * dl[2];
+		r->d[e] = sum3_eigen(X[0 + e] * dl[0], X[3 + e] * dl[1], X[6 + e] * dl[2]);
 	}
-	float inv = 1.0f / sqrtf(r->d[0] * r->d[0] + r->d[1] * r->d[1] + r->d[2] * r->d[2]);
-	for (int e = 0; e < 3; ++e) r->dirn[e] = r->d[e] * inv;
+	normalize3_eigen(r->d, r->dirn);
 	if (cfg->use_global_movement) { /* :1370-1378: the ray is moved, its direction is not normalised again */
 		float o2[3], q[3], dq[3];
 		for (int e = 0; e < 3; ++e) o2[e] = r->o[e] - cfg->first_frame_offset[e];
@@ -1090,16 +1104,15 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 	for (int64_t i = 0; i < (int64_t)n_rays_kept; ++i) {
 		uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
 		const float* rd = rays + (size_t)i * 6 + 3;
-		float inv = 1.0f / sqrtf(rd[0] * rd[0] + rd[1] * rd[1] + rd[2] * rd[2]);
-		float dir[3] = {rd[0] * inv, rd[1] * inv, rd[2] * inv};
+		float dir[3];
+		normalize3_eigen(rd, dir);
 		comp_t c = {{0, 0, 0}, 1.f, 0.f, 0};
 		for (; c.n < ns; ++c.n) {
 			if (c.T < 1e-4f) break;
 			const uint16_t* o = mlp_out + (size_t)(base + c.n) * 16;
 			if (c.n == 0) { /* BENT_DIR (:1574-1579) */
 				float dd[3] = {h2f(o[8]) * 2.f - 1.f, h2f(o[9]) * 2.f - 1.f, h2f(o[10]) * 2.f - 1.f};
-				float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
-				for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+				normalize3_eigen(dd, dir);
 			}
 			neus_sample_t s;
 			neus_sample(o, coords + (size_t)(base + c.n) * 7, dir, anneal, &s);
@@ -1164,17 +1177,16 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 		else if ((double)ws <= 1e-4) { ws = (float)1e-4; gws = 0.f; }
 		else { float sg = 1.0f / (1.0f + expf(-ws)); gws = (mask_gt - sg) * ws * cfg->mask_loss_weight; }
 		const float n_rays_f = (float)n_rays * (float)(cfg->ray_count_scale ? cfg->ray_count_scale : 1u);
-		if (loss_out) loss_out[i] = (lgl[0] + lgl[1] + lgl[2]) / 3.0f / n_rays_f;
+		if (loss_out) loss_out[i] = sum3_eigen(lgl[0], lgl[1], lgl[2]) / 3.0f / n_rays_f; /* lg.loss.mean() (:1715) */
 		const float loss_scale = cfg->loss_scale / n_rays_f;
 		/* pass B (:1761-1952) */
 		const float* rd = rays + (size_t)i * 6 + 3;
-		float inv = 1.0f / sqrtf(rd[0] * rd[0] + rd[1] * rd[1] + rd[2] * rd[2]);
-		float dir[3] = {rd[0] * inv, rd[1] * inv, rd[2] * inv};
+		float dir[3];
+		normalize3_eigen(rd, dir);
 		{
 			const uint16_t* o = mlp_out + (size_t)base * 16;
 			float dd[3] = {h2f(o[8]) * 2.f - 1.f, h2f(o[9]) * 2.f - 1.f, h2f(o[10]) * 2.f - 1.f};
-			float iv = 1.0f / sqrtf(dd[0] * dd[0] + dd[1] * dd[1] + dd[2] * dd[2]);
-			for (int e = 0; e < 3; ++e) dir[e] = dd[e] * iv;
+			normalize3_eigen(dd, dir);
 		}
 		float rgb2[3] = {0, 0, 0}, T = 1.f, ek = 0.f;
 		for (uint32_t j = 0; j < cn; ++j) {
@@ -1188,12 +1200,13 @@ uint32_t n2o_compute_loss(const n2o_dataset* ds, const n2o_train_cfg* cfg, uint3
 			T *= (1.f - s.alpha);
 			float g[16];
 			memset(g, 0, sizeof(g));
-			float dla = gws * (1.0f - ws);
+			float dterm[3];
 			for (int e = 0; e < 3; ++e) {
 				float suffix = rgb_ray[e] - rgb2[e];
 				g[e] = loss_scale * (w * lgg[e] * (s.rgb[e] * (1.0f - s.rgb[e])));
-				dla += lgg[e] * (T * s.rgb[e] - suffix);
+				dterm[e] = lgg[e] * (T * s.rgb[e] - suffix);
 			}
+			float dla = sum3_eigen(dterm[0], dterm[1], dterm[2]) + gws * (1.0f - ws); /* gradient.dot(T rgb - suffix) + mask term (:1829-1831) */
 			dla = (float)((double)dla / ((double)(1.0f - s.alpha) + 1e-5)); /* "/ (1.0f - alpha + 1e-5)": fp64 divide (:1829-1832) */
 			float da_dE = 0, dE_dsdf = 0, dE_ds = 0, da_dP = 0, dP_ds = 0, dP_dic = 0, dE_dic = 0;
 			if (!(s.p_div_c <= 0.0f || s.p_div_c >= 1.0f)) {

@@ -1,0 +1,250 @@
+"""The reference's own CUDA kernels of the training step, executed on the GPU next to this repository's kernels on the same
+inputs.  oracle/_ref/libref_nerf_kernels.so (built by oracle/build_ref_kernels.py where a reference checkout is present)
+includes the reference's src/testbed_nerf.cu in place and exposes launchers for
+generate_training_samples_nerf_with_global_movement, compute_loss_kernel_train_nerf_with_global_movement and the occupancy-grid
+kernels.  This pins the restatements (the CPU oracle and the CUDA path, which the other tests compare with each other) against
+the reference's code itself.  The reference hands out sample ranges by atomicAdd, in arrival order; this repository in ray
+order: results are compared per ray."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from test_gpu_raymarch import ball_bitfield, bits, half, scene, sphere_model
+from util import check_fp16, record
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_nerf_kernels.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_LIB):
+        pytest.skip("oracle/_ref/libref_nerf_kernels.so was not built: no reference checkout at build time")
+    lib = C.CDLL(REF_LIB)
+    assert lib.ref_sizeof_nerf_coordinate() == 28 and lib.ref_sizeof_ray() == 24 and lib.ref_nerf_gridsize() == 128
+    return lib
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from neus2_b200 import _lib as L
+    from neus2_b200 import ops
+    L.lib()
+    return L, ops
+
+
+def p(t):
+    return C.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def fptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class RefScene:
+    """The arguments every launcher takes for the dataset: device pixels, host cameras."""
+
+    def __init__(self, n_views=8, res=96):
+        from neus2_b200 import synthetic as S
+        sc = S.render_sphere_views(n_views, res, res, device="cpu", seed=3)
+        self.n, self.w, self.h = n_views, res, res
+        self.pixels = sc["pixels"].cuda().contiguous()
+        self.xforms = np.ascontiguousarray(sc["xforms"].numpy(), np.float32)
+        self.focal = np.ascontiguousarray(sc["focal"].numpy(), np.float32)
+        self.principal = np.ascontiguousarray(sc["principal"].numpy(), np.float32)
+
+    def args(self):
+        return (C.c_uint32(self.n), C.c_uint32(self.w), C.c_uint32(self.h), p(self.pixels), fptr(self.xforms), fptr(self.focal), fptr(self.principal))
+
+
+def ref_generate(ref, rs, n_rays, n_rays_total, rng, max_samples, bitfield, snap, movement=None):
+    dev = "cuda"
+    out = dict(ray_counter=torch.zeros(1, dtype=torch.int32, device=dev), numsteps_counter=torch.zeros(1, dtype=torch.int32, device=dev),
+               ray_indices=torch.zeros(n_rays, dtype=torch.int32, device=dev), rays=torch.zeros((n_rays, 6), dtype=torch.float32, device=dev),
+               numsteps=torch.zeros((n_rays, 2), dtype=torch.int32, device=dev), coords=torch.zeros((max_samples, 7), dtype=torch.float32, device=dev))
+    rot, tr, off = movement if movement else (None, None, np.zeros(3, np.float32))
+    rc = ref.ref_generate_training_samples(C.c_uint32(n_rays), C.c_uint32(n_rays_total), C.c_uint64(rng.state), C.c_uint64(rng.inc), C.c_uint32(max_samples),
+                                           *rs.args(), p(bitfield), C.c_int(int(snap)), C.c_float(0.0), C.c_uint32(0), p(rot), p(tr), fptr(off),
+                                           p(out["ray_counter"]), p(out["numsteps_counter"]), p(out["ray_indices"]), p(out["rays"]), p(out["numsteps"]),
+                                           p(out["coords"]))
+    assert rc == 0
+    return out
+
+
+def per_ray(ray_indices, numsteps, n_kept):
+    """{global ray index: (count, base)} from slot-ordered arrays."""
+    idx = ray_indices.cpu().numpy().view(np.uint32)[:n_kept]
+    ns = numsteps.cpu().numpy().view(np.uint32)[:n_kept]
+    return idx, ns
+
+
+@pytest.mark.parametrize("n_rays,snap", [(8192, False), (4096, True)])
+def test_sample_generation_equals_the_reference_kernel(ref, gpu, oracle, n_rays, snap):
+    L, ops = gpu
+    rs = RefScene()
+    _, gds = scene(oracle, ops)
+    _, bf, _ = ball_bitfield(oracle)
+    bf_gpu = torch.from_numpy(bf).cuda()
+    max_samples = 1 << 20
+    r = ref_generate(ref, rs, n_rays, 12345, L.pcg32(1337), max_samples, bf_gpu, snap)
+    batch = ops.RayBatch(n_rays, max_samples)
+    ops.generate_samples(gds, L.train_cfg(snap_to_pixel_centers=snap), n_rays, 12345, L.pcg32(1337), bf_gpu, batch)
+    torch.cuda.synchronize()
+    cnt = batch.counters.cpu().numpy().view(np.uint32)
+    k = int(r["ray_counter"].item())
+    assert k > 0 and cnt[0] == k, "number of rays that take samples"
+    assert int(r["numsteps_counter"].item()) == cnt[1], "number of samples"
+    ridx, rns = per_ray(r["ray_indices"], r["numsteps"], k)
+    midx, mns = per_ray(batch.ray_indices, batch.numsteps, k)
+    order = np.argsort(ridx, kind="stable")  # reference slots in ray order
+    assert np.array_equal(ridx[order], midx), "the same rays are kept"
+    assert np.array_equal(rns[order, 0], mns[:, 0]), "every ray takes the same number of samples"
+    rrays, mrays = r["rays"].cpu().numpy()[:k][order], batch.rays.cpu().numpy()[:k]
+    assert np.array_equal(rrays.view(np.uint32), mrays.view(np.uint32)), "ray origins and directions bit for bit"
+    rc, mc = r["coords"].cpu().numpy(), batch.coords.cpu().numpy()
+    gather = np.concatenate([np.arange(b, b + n) for n, b in rns[order]])
+    assert np.array_equal(rc[gather].view(np.uint32), mc[:len(gather)].view(np.uint32)), "sample coordinates bit for bit"
+    record("ref_kernel_generate_%d" % n_rays, rays=k, samples=int(cnt[1]))
+
+
+def test_sample_generation_with_accumulated_movement_equals_the_reference_kernel(ref, gpu, oracle):
+    """Later frames of a dynamic sequence: every ray is moved by the accumulated rotation and translation first."""
+    L, ops = gpu
+    rs = RefScene()
+    _, gds = scene(oracle, ops)
+    _, bf, _ = ball_bitfield(oracle)
+    bf_gpu = torch.from_numpy(bf).cuda()
+    ang = 0.07
+    R = np.array([[np.cos(ang), -np.sin(ang), 0], [np.sin(ang), np.cos(ang), 0], [0, 0, 1]], np.float32)
+    R16, t16 = R.astype(np.float16), np.array([0.02, -0.015, 0.01, 0.0], np.float16)
+    off = np.array([0.5, 0.5, 0.5], np.float32)
+    rot = torch.from_numpy(np.concatenate([R16.reshape(-1), np.zeros(3, np.float16)])).cuda()  # 12 slots, row major
+    tr = torch.from_numpy(t16).cuda()
+    n_rays, max_samples = 4096, 1 << 20
+    r = ref_generate(ref, rs, n_rays, 999, L.pcg32(7), max_samples, bf_gpu, False, movement=(rot, tr, off))
+    cfg = L.train_cfg(rotation=R16.astype(np.float32).reshape(-1), transition=t16[:3].astype(np.float32), first_frame_offset=off)
+    batch = ops.RayBatch(n_rays, max_samples)
+    ops.generate_samples(gds, cfg, n_rays, 999, L.pcg32(7), bf_gpu, batch)
+    torch.cuda.synchronize()
+    cnt = batch.counters.cpu().numpy().view(np.uint32)
+    k = int(r["ray_counter"].item())
+    assert k > 0 and cnt[0] == k and int(r["numsteps_counter"].item()) == cnt[1]
+    ridx, rns = per_ray(r["ray_indices"], r["numsteps"], k)
+    midx, mns = per_ray(batch.ray_indices, batch.numsteps, k)
+    order = np.argsort(ridx, kind="stable")
+    assert np.array_equal(ridx[order], midx) and np.array_equal(rns[order, 0], mns[:, 0])
+    gather = np.concatenate([np.arange(b, b + n) for n, b in rns[order]])
+    rc, mc = r["coords"].cpu().numpy()[gather], batch.coords.cpu().numpy()[:len(gather)]
+    assert np.array_equal(rc.view(np.uint32), mc.view(np.uint32)), "sample coordinates bit for bit"
+
+
+@pytest.mark.parametrize("n_rays,target,variance,ek,mask_w", [(8192, 1 << 20, 0.5, 0.1, 0.0), (4096, 1 << 20, 0.3, 0.01, 0.1)])
+def test_loss_and_compaction_equal_the_reference_kernel(ref, gpu, oracle, n_rays, target, variance, ek, mask_w):
+    L, ops = gpu
+    O = oracle
+    rs = RefScene()
+    _, gds = scene(O, ops)
+    _, bf, _ = ball_bitfield(O)
+    bf_gpu = torch.from_numpy(bf).cuda()
+    d, params = sphere_model(O, variance)
+    ld = L.GridDesc(d.n_levels, d.log2_hashmap_size, d.base_resolution, d.per_level_scale, d.n_active_levels)
+    P = half(params)
+    max_samples = 1 << 20
+    rng = L.pcg32(99)
+    # reference side: its generator, this repository's network on its samples, its loss kernel
+    r = ref_generate(ref, rs, n_rays, 777, rng, max_samples, bf_gpu, False)
+    k = int(r["ray_counter"].item())
+    n_samples = int(r["numsteps_counter"].item())
+    ridx, rns_before = per_ray(r["ray_indices"], r["numsteps"], k)
+    r_out = ops.neus_forward(ld, P, r["coords"][:n_samples].contiguous())
+    r_net = torch.zeros((max_samples, 16), dtype=torch.float16, device="cuda")
+    r_net[:n_samples] = r_out
+    variance_param = float(P[12288 + O.grid_n_params(d)].item())
+    dev = "cuda"
+    rl = dict(counter=torch.zeros(1, dtype=torch.int32, device=dev), coords=torch.zeros((target, 7), dtype=torch.float32, device=dev),
+              dloss=torch.zeros((target, 16), dtype=torch.float16, device=dev), loss=torch.zeros(n_rays, device=dev), ek=torch.zeros(n_rays, device=dev),
+              mask=torch.zeros(n_rays, device=dev))
+    bg = np.zeros(3, np.float32)
+    rc = ref.ref_compute_loss(C.c_uint32(n_rays), C.c_uint32(777), C.c_uint64(rng.state), C.c_uint64(rng.inc), C.c_uint32(target), *rs.args(),
+                              p(r["ray_counter"]), p(r_net), p(r["ray_indices"]), p(r["rays"]), p(r["numsteps"]), p(r["coords"]), C.c_int(1), fptr(bg),
+                              C.c_int(0), C.c_float(variance_param), C.c_uint32(0), p(None), p(None), fptr(np.zeros(3, np.float32)), C.c_float(mask_w),
+                              C.c_float(ek), C.c_float(1.0), p(rl["counter"]), p(rl["coords"]), p(rl["dloss"]), p(rl["loss"]), p(rl["ek"]), p(rl["mask"]))
+    assert rc == 0
+    # this repository's side
+    cfg = L.train_cfg(ek_loss_weight=ek, mask_loss_weight=mask_w)
+    batch = ops.RayBatch(n_rays, max_samples)
+    ops.generate_samples(gds, cfg, n_rays, 777, rng, bf_gpu, batch)
+    mlp_out = ops.neus_forward(ld, P, batch.coords, n_dev=batch.counters[4:5])
+    coords_out = torch.zeros((target, 7), dtype=torch.float32, device=dev)
+    dloss = torch.zeros((target, 16), dtype=torch.float16, device=dev)
+    loss, ekl = torch.zeros(n_rays, device=dev), torch.zeros(n_rays, device=dev)
+    ops.compute_loss(gds, cfg, n_rays, 777, rng, target, mlp_out, batch, coords_out, dloss, loss, ekl, rollover=False)
+    torch.cuda.synchronize()
+    cnt = batch.counters.cpu().numpy().view(np.uint32)
+    assert cnt[0] == k
+    order = np.argsort(ridx, kind="stable")
+    _, rns = per_ray(r["ray_indices"], r["numsteps"], k)  # rewritten by the loss kernel: compacted {count, base}
+    _, mns = per_ray(batch.ray_indices, batch.numsteps, k)
+    assert int(rl["counter"].item()) == cnt[2], "compacted sample count"
+    assert np.array_equal(rns[order, 0], mns[:, 0]), "samples every ray keeps"
+    total = int(cnt[2])
+    assert 0 < total <= target, "the case must fit the target batch (the reference drops whole rays in arrival order beyond it)"
+    gather = np.concatenate([np.arange(b, b + n) for n, b in rns[order]]).astype(np.int64)
+    assert np.array_equal(rl["coords"].cpu().numpy()[gather].view(np.uint32), coords_out.cpu().numpy()[:total].view(np.uint32)), "compacted coordinates"
+    got, want = dloss.float().cpu().numpy()[:total], rl["dloss"].float().cpu().numpy()[gather]
+    for name, sl in [("rgb", slice(0, 3)), ("sdf", slice(3, 4)), ("eik", slice(4, 7)), ("var", slice(7, 8)), ("cos", slice(8, 11))]:
+        check_fp16("ref_kernel_dloss_%s_%d" % (name, n_rays), got[:, sl], want[:, sl], rel=2e-3, min_frac=0.998, min_cos=0.9999)
+    assert np.allclose(loss.cpu().numpy()[:k], rl["loss"].cpu().numpy()[:k][order], rtol=2e-3, atol=1e-9)
+    assert np.allclose(ekl.cpu().numpy()[:k], rl["ek"].cpu().numpy()[:k][order], rtol=2e-3, atol=1e-9)
+    record("ref_kernel_loss_%d" % n_rays, rays=k, compacted=total)
+
+
+def test_occupancy_update_equals_the_reference_kernels(ref, gpu, oracle):
+    L, ops = gpu
+    O = oracle
+    d, params = sphere_model(O, 0.3)
+    ld = L.GridDesc(d.n_levels, d.log2_hashmap_size, d.base_resolution, d.per_level_scale, d.n_active_levels)
+    P = half(params)
+    cells = 128 ** 3
+    n = cells // 4
+    occ = ops.OccupancyGrid(1)
+    rgrid = torch.zeros(cells, dtype=torch.float32, device="cuda")
+    rtmp = torch.zeros_like(rgrid)
+    rbits = torch.zeros(cells, dtype=torch.uint8, device="cuda")
+    rmean = torch.zeros(32, dtype=torch.float32, device="cuda")
+    rpos = torch.zeros((2 * n, 3), dtype=torch.float32, device="cuda")
+    ridx = torch.zeros(2 * n, dtype=torch.int32, device="cuda")
+    variance = P[12288 + O.grid_n_params(d):].contiguous()
+    rng = L.pcg32(4242)
+    for step in range(3):
+        rng2 = L.pcg32_advance(rng, 1 << 32)  # the reference advances its generator by the default stride between the two draws
+        so, io = C.c_uint64(0), C.c_uint64(0)
+        assert ref.ref_density_grid_samples(C.c_uint32(n), C.c_uint32(n), C.c_uint64(rng.state), C.c_uint64(rng.inc), C.c_uint32(step), C.c_uint32(1), p(rgrid),
+                                            p(rpos), p(ridx), C.byref(so), C.byref(io)) == 0
+        occ.update(ld, P, n, n, rng, rng2, decay=0.95)
+        torch.cuda.synchronize()
+        assert np.array_equal(occ.idx.cpu().numpy()[:2 * n], ridx.cpu().numpy()), "grid cells drawn"
+        assert np.array_equal(occ.pos.cpu().numpy()[:2 * n].view(np.uint32), rpos.cpu().numpy().view(np.uint32)), "positions bit for bit"
+        sdf = occ.sdf[:2 * n].clone()  # the SDF values this repository's network gave at those positions
+        assert ref.ref_density_grid_update(C.c_uint32(2 * n), p(ridx), p(sdf), p(variance), C.c_float(0.95), C.c_uint32(step), C.c_uint32(1), p(rgrid), p(rtmp),
+                                           p(rbits), p(rmean)) == 0
+        torch.cuda.synchronize()
+        got, want = occ.grid.cpu().numpy(), rgrid.cpu().numpy()
+        close = np.isclose(got, want, rtol=2e-3, atol=1e-6).mean()
+        record("ref_kernel_occupancy_step%d" % step, close=float(close), exact=float((got == want).mean()))
+        assert close > 0.9999
+        assert abs(occ.mean.item() - rmean[0].item()) <= 1e-3 * abs(rmean[0].item()) + 1e-9
+        # thresholding and pooling are integer work: on the same grid (decay 1, no samples: the grid stays as it is) the bits
+        # and their mip levels must be equal
+        rgrid.copy_(occ.grid)
+        assert ref.ref_density_grid_update(C.c_uint32(0), p(ridx), p(sdf), p(variance), C.c_float(1.0), C.c_uint32(step + 1), C.c_uint32(1), p(rgrid), p(rtmp),
+                                           p(rbits), p(rmean)) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(rgrid.cpu().numpy(), occ.grid.cpu().numpy())
+        assert np.array_equal(occ.bitfield.cpu().numpy(), rbits.cpu().numpy()), "occupancy bits and their mip levels"
+        rng = L.pcg32_advance(rng2, 1 << 32)
+        assert (rng.state, rng.inc) == (so.value, io.value), "generator state after the two draws"
