@@ -98,17 +98,15 @@ __device__ __forceinline__ uint32_t corner_index(const GridLevels& lv, uint32_t 
 		idx = cx ^ (cy * 2654435761u) ^ (cz * 805459861u);
 		idx &= lv.size[l] - 1u;  // hashed levels have a power-of-two size
 	} else {
-		// dense level: the lattice index modulo the level's size, over the integers.  Inside the unit cube that is the plain
-		// index, or one wrap for a corner on the far face; cells outside the lattice (negative or large coordinates, from a
-		// learned motion or a caller's query box) take the slow general form
-		const uint32_t res = lv.res[l], size = lv.size[l];
-		if (max(cx, max(cy, cz)) <= res) {
-			idx = cx + cy * res + cz * res * res;
-			idx -= idx >= size ? size : 0u;
-		} else {
-			const long long v = ((long long)(int32_t)cx + (long long)(int32_t)cy * res + (long long)(int32_t)cz * res * res) % (long long)size;
-			idx = (uint32_t)(v < 0 ? v + size : v);
-		}
+		// dense level: the cell is clamped to the lattice (no change inside the unit cube; samples outside it read the edge
+		// cells), a corner on the far cube face wraps once
+		const int res = (int)lv.res[l];
+		const uint32_t size = lv.size[l];
+		const uint32_t bx = k & 1u, by = (k >> 1) & 1u, bz = (k >> 2) & 1u;
+		const uint32_t x0 = (uint32_t)min(max((int)c.c0[0], 0), res - 1) + bx, y0 = (uint32_t)min(max((int)c.c0[1], 0), res - 1) + by,
+		               z0 = (uint32_t)min(max((int)c.c0[2], 0), res - 1) + bz;
+		idx = x0 + y0 * (uint32_t)res + z0 * (uint32_t)(res * res);
+		idx -= idx >= size ? size : 0u;
 	}
 	return lv.offset[l] + idx;
 }

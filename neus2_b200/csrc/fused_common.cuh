@@ -42,16 +42,6 @@ struct LevelGeom {
 	bool hashed;
 };
 
-// The rare part of level_geom for a dense level: one axis of a cell outside the lattice, both corners, reduced modulo the
-// level's size over the integers.  Kept out of line (and free of pointers, so that the caller's arrays stay in registers):
-// inlined, its 64-bit divisions sit in the middle of the gather's unrolled loads and cost the fused kernels 5-8 % on samples
-// that never take it.
-static __device__ __noinline__ uint2 reduce_outside_axis(uint32_t c0, uint32_t stride, uint32_t size_u) {
-	const long long size = size_u;
-	const long long v0 = ((long long)(int32_t)c0 * stride) % size, v1 = (((long long)(int32_t)c0 + 1) * stride) % size;
-	return make_uint2((uint32_t)(v0 < 0 ? v0 + size : v0), (uint32_t)(v1 < 0 ? v1 + size : v1));
-}
-
 __device__ __forceinline__ LevelGeom level_geom(const GridLevels& lv, uint32_t l, const float* x) {
 	LevelGeom g;
 	const Cell c = level_cell(lv, l, x);
@@ -72,23 +62,20 @@ __device__ __forceinline__ LevelGeom level_geom(const GridLevels& lv, uint32_t l
 		g.hz[1] = (c.c0[2] + 1u) * 805459861u;
 		g.mask_or_size = lv.size[l] - 1u;
 	} else {
-		const uint32_t res = lv.res[l];
-		g.hx[0] = c.c0[0];
-		g.hx[1] = c.c0[0] + 1u;
-		g.hy[0] = c.c0[1] * res;
-		g.hy[1] = g.hy[0] + res;
-		g.hz[0] = c.c0[2] * res * res;
-		g.hz[1] = g.hz[0] + res * res;
+		// A dense level's cell is clamped to the lattice: inside the unit cube that changes nothing (the far face is cell
+		// res - 1 with its upper corner at res, which wraps once below); a sample that a learned motion, or a caller's query
+		// box, has put outside the cube reads the edge cells instead of whatever index arithmetic on a negative or large
+		// coordinate would land on.  Branch-free on purpose: a rare branch here costs the fused kernels 4-8 %.
+		const int res = (int)lv.res[l];
+		const uint32_t cx = (uint32_t)min(max((int)c.c0[0], 0), res - 1), cy = (uint32_t)min(max((int)c.c0[1], 0), res - 1),
+		               cz = (uint32_t)min(max((int)c.c0[2], 0), res - 1);
+		g.hx[0] = cx;
+		g.hx[1] = cx + 1u;
+		g.hy[0] = cy * (uint32_t)res;
+		g.hy[1] = g.hy[0] + (uint32_t)res;
+		g.hz[0] = cz * (uint32_t)(res * res);
+		g.hz[1] = g.hz[0] + (uint32_t)(res * res);
 		g.mask_or_size = lv.size[l];
-		// A cell inside the lattice gives a sum below 2 * size (a corner on the far cube face wraps once).  A sample that a
-		// learned motion, or a caller's query box, has put outside the unit cube can give anything; the general rule is the
-		// lattice index modulo the level's size, over the integers.  The three terms are reduced here, once per level and only
-		// for such samples, so that the per-corner combination stays two compare-and-subtract steps.
-		if (max(c.c0[0], max(c.c0[1], c.c0[2])) >= res) {
-			const uint2 vx = reduce_outside_axis(c.c0[0], 1u, g.mask_or_size), vy = reduce_outside_axis(c.c0[1], res, g.mask_or_size),
-			            vz = reduce_outside_axis(c.c0[2], res * res, g.mask_or_size);
-			g.hx[0] = vx.x, g.hx[1] = vx.y, g.hy[0] = vy.x, g.hy[1] = vy.y, g.hz[0] = vz.x, g.hz[1] = vz.y;
-		}
 	}
 	return g;
 }
@@ -99,8 +86,7 @@ __device__ __forceinline__ uint32_t geom_index(const LevelGeom& g, uint32_t k) {
 	if (g.hashed) {
 		idx = (g.hx[bx] ^ g.hy[by] ^ g.hz[bz]) & g.mask_or_size;
 	} else {
-		idx = g.hx[bx] + g.hy[by] + g.hz[bz];  // < 3 * size (level_geom)
-		idx -= idx >= g.mask_or_size ? g.mask_or_size : 0u;
+		idx = g.hx[bx] + g.hy[by] + g.hz[bz];  // < 2 * size: a corner on the far cube face wraps once
 		idx -= idx >= g.mask_or_size ? g.mask_or_size : 0u;
 	}
 	return g.offset + idx;

@@ -92,12 +92,16 @@ static inline void level_corners(const n2o_grid_levels* lv, uint32_t l, const fl
 			idx = (cc[0] * 1u) ^ (cc[1] * 2654435761u) ^ (cc[2] * 805459861u);
 			idx %= n;
 		} else {
-			/* dense level: the lattice index modulo the level's size, over the integers (cells outside the lattice have
-			 * negative or large coordinates; inside the unit cube this is the plain index, or one wrap on the far face) */
-			int64_t v = (int64_t)(int32_t)cc[0] + (int64_t)(int32_t)cc[1] * (int64_t)res + (int64_t)(int32_t)cc[2] * (int64_t)res * (int64_t)res;
-			v %= (int64_t)n;
-			if (v < 0) v += (int64_t)n;
-			idx = (uint32_t)v;
+			/* dense level: the cell is clamped to the lattice (no change inside the unit cube, where the far face is cell
+			 * res - 1 with its upper corner at res; samples outside the cube read the edge cells), then the plain lattice
+			 * index, which wraps once for a corner on the far face (assumption A1) */
+			int32_t cl[3];
+			for (int d = 0; d < 3; ++d) {
+				int32_t v = (int32_t)c0[d];
+				cl[d] = v < 0 ? 0 : (v > (int32_t)res - 1 ? (int32_t)res - 1 : v);
+			}
+			idx = ((uint32_t)cl[0] + (k & 1u)) + ((uint32_t)cl[1] + ((k >> 1) & 1u)) * res + ((uint32_t)cl[2] + ((k >> 2) & 1u)) * res * res;
+			idx %= n;
 		}
 		c->idx[k] = lv->offset[l] + idx;
 		c->w[k] = wd[0] * wd[1] * wd[2];

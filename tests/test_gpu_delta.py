@@ -104,8 +104,8 @@ def test_fused_kernels_with_motion_match_oracle(gpu, oracle, n, L_, n_active):
 
 
 def test_samples_moved_outside_the_unit_cube(gpu, oracle):
-    """A motion can carry samples out of the cube the grid was built for: dense levels then wrap by the general rule (index
-    modulo the level's size) instead of the single wrap that positions inside the cube need."""
+    """A motion can carry samples out of the cube the grid was built for: dense levels clamp the cell to the lattice (such
+    samples read the edge cells), hashed levels hash whatever coordinate comes; nothing reads outside the tables."""
     L, ops = gpu
     O = oracle
     d, params, coords, rng = model(O, seed=5, n=20000)
