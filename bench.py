@@ -132,7 +132,10 @@ def run_ours(args):
     L.lib()
 
     scene = make_scene("cuda")
-    tb = Testbed(batch_size=BATCH, world_size=world, rank=rank, **({"learning_rate": args.lr} if args.lr else {}))
+    kw = {"learning_rate": args.lr} if args.lr else {}
+    if args.forward_windows is not None:
+        kw["forward_windows"] = [int(v) for v in args.forward_windows.split(",") if v]
+    tb = Testbed(batch_size=BATCH, world_size=world, rank=rank, **kw)
     px = scene["pixels"].cpu().numpy()
     cams = [scene[k].cpu().numpy() for k in ("xforms", "focal", "principal")]
     tb.load_training_data(px, *cams)
@@ -218,7 +221,7 @@ def run_ours(args):
             "gpu_launches": launches, "clocks": clocks,
             "train_state": {"timed_steps": [step_first, int(st.training_step)], "training_step": int(st.training_step),
                             "rays_per_batch": int(st.rays_per_batch),
-                            "samples_before_compaction": int(st.measured_batch_size_before_compaction),
+                            "samples_before_compaction": int(st.measured_batch_size_before_compaction), "samples_evaluated": int(st.n_samples_evaluated),
                             "samples_after_compaction": int(st.measured_batch_size), "loss": float(st.loss),
                             "ek_loss": float(st.ek_loss), "overflow": int(st.overflow)}}
 
@@ -692,6 +695,7 @@ def main():
     ap.add_argument("--pretrain", type=int, default=500)
     ap.add_argument("--lr", type=float, default=0.0, help="override the Adam learning rate of BASELINE config 1 (1e-2), e.g. to time late training states")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--forward-windows", default=None, help="cumulative window ends of the step's network pass, e.g. 16,64 ('' = every sample like the reference; default: the library's)")
     ap.add_argument("--cpu-sample", type=int, default=1 << 18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None, choices=["train", "forward", "adam", "mesh", "render", "config2", "config3"], help="run one fused kernel alone (profiling)")

@@ -158,6 +158,11 @@ struct neus2b_motion {
 int neus2b_neus_forward_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
                               const uint32_t* d_n, const float* d_coords, const neus2b_motion* motion, uint16_t* d_out,
                               neus2b_stream_t stream);
+/* The same pass on a list of samples: entry i reads row d_index[i] of d_coords and writes row d_index[i] of d_out (d_index NULL:
+ * row i; a list needs the tcgen05 path).  n, d_n: capacity and device-side length of the list. */
+int neus2b_neus_forward_indexed(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
+                                const uint32_t* d_n, const uint32_t* d_index, const float* d_coords, const neus2b_motion* motion,
+                                uint16_t* d_out, neus2b_stream_t stream);
 int neus2b_neus_train_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, uint32_t n, const float* d_coords,
                             const neus2b_motion* motion, const uint16_t* d_dL_dout, uint32_t indeed_batch_size, float* d_grad_mlp,
                             uint16_t* d_grad_grid, float* d_grad_variance, neus2b_stream_t stream);
@@ -223,13 +228,16 @@ typedef struct {
 	float* d_rays;           /* [max_rays][6] origin, unnormalised direction */
 	uint32_t* d_numsteps;    /* [max_rays][2] {n, base} */
 	float* d_coords;         /* [max_samples][7] */
-	uint32_t* d_counters;    /* [8]: 0 kept rays, 1 samples, 2 compacted samples (unclipped), 3 overflow flag */
+	uint32_t* d_counters;    /* [8]: 0 kept rays, 1 samples, 2 compacted samples (unclipped), 3 overflow flag,
+	                            5 samples the windowed network pass evaluated */
 	uint64_t* d_scan_tmp;    /* [max_rays + 1024]: keys, the total behind them and 1023 entries of scan scratch */
 	float* d_ray_tmp;        /* [max_rays][8] */
 	const uint32_t* d_n_rays_total; /* optional: overrides the n_rays_total argument with a device value */
 	uint32_t* d_march_masks;        /* optional [max_rays][64]: lets the second march pass skip the occupancy lookups */
 	const int32_t* d_occupied_bounds; /* optional int32[6] from neus2b_occupancy_bounds: rays that miss the box of occupied
 	                                     cells are not marched (they cannot take a sample; the result is unchanged) */
+	uint32_t* d_window_list;          /* optional [max_samples]: sample rows of the current window (neus2b_forward_compute_loss) */
+	uint32_t* d_window_lens;          /* optional [8]: the length of each window's list */
 } neus2b_ray_workspace;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is
@@ -262,6 +270,21 @@ int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, u
                         uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, const uint16_t* d_mlp_out,
                         neus2b_ray_workspace* ws, float* d_coords_out, uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss,
                         int rollover, neus2b_stream_t stream);
+
+/* The network pass over the step's samples (src/testbed_nerf.cu:3840) and the loss pass (:3845-3916) in one call that evaluates
+ * the network only on samples whose output is used.  Rays are evaluated in windows of consecutive samples: the first
+ * window_ends[0] samples of every ray, then [window_ends[0], window_ends[1]) of the rays that are still transparent, ...,
+ * finally the rest of the rays that remain (window_ends: host array, increasing, at most NEUS2B_MAX_FORWARD_WINDOWS entries;
+ * n_windows == 0: every sample, then the loss pass, in the reference's order).  Same per-ray records, compacted batch and loss
+ * gradient as neus2b_neus_forward on all samples followed by neus2b_compute_loss; rows of d_mlp_out [max_samples][16] behind a
+ * ray's last evaluated sample keep what they held.  Needs ws->d_window_list and ws->d_window_lens when n_windows > 0 and the
+ * tcgen05 path.  motion: NULL for a static scene. */
+#define NEUS2B_MAX_FORWARD_WINDOWS 6
+int neus2b_forward_compute_loss(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, const neus2b_motion* motion,
+                                const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                                uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, neus2b_ray_workspace* ws,
+                                const uint32_t* window_ends, uint32_t n_windows, uint16_t* d_mlp_out, float* d_coords_out,
+                                uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss, int rollover, neus2b_stream_t stream);
 
 /* Occupancy grid (src/testbed_nerf.cu:630-785, 3287-3391). One call = update_density_grid_nerf's inner step for
  * n_uniform + n_nonuniform samples followed by update_density_grid_mean_and_bitfield.
@@ -367,6 +390,11 @@ typedef struct {
 	uint32_t gm_lr_decay_start, gm_lr_decay_interval;
 	float gm_lr_decay_base;
 	float first_frame_offset[3];                       /* Testbed::m_first_frame_offset (testbed.h:455): 0 */
+	/* no counterpart in the reference: the step's network pass over the generated samples runs in windows of consecutive
+	 * samples per ray and skips what lies behind the point where a ray turns opaque (neus2b_forward_compute_loss; same
+	 * compacted batch and loss).  Cumulative window ends; n_forward_windows = 0 evaluates every sample like the reference. */
+	uint32_t n_forward_windows;
+	uint32_t forward_window_ends[6];
 } neus2b_testbed_config;
 /* "top_resolution" -> per_level_scale when the config gives none (src/testbed.cu:2173-2177):
  * exp(log(top_resolution * aabb_scale / base_resolution) / (n_levels - 1)). */
@@ -384,6 +412,8 @@ typedef struct {
 	float loss, ek_loss;                           /* Testbed.loss / ek_loss (python_api.cu:447-449) */
 	uint32_t nonfinite_gradients;                  /* gradient entries the optimizer refused so far (NaN / infinite), cumulative */
 	uint32_t device_error;                         /* sticky device error bits at the end of the step (neus2b_device_error_flags) */
+	uint32_t n_samples_evaluated;                  /* samples the step's network pass evaluated (== ..._before_compaction without
+	                                                  forward windows) */
 } neus2b_train_stats;
 
 typedef struct neus2b_testbed neus2b_testbed;

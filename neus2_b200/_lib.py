@@ -42,7 +42,8 @@ class Motion(C.Structure):
 class RayWorkspace(C.Structure):
     _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_indices", C.c_void_p), ("d_rays", C.c_void_p),
                 ("d_numsteps", C.c_void_p), ("d_coords", C.c_void_p), ("d_counters", C.c_void_p), ("d_scan_tmp", C.c_void_p),
-                ("d_ray_tmp", C.c_void_p), ("d_n_rays_total", C.c_void_p), ("d_march_masks", C.c_void_p), ("d_occupied_bounds", C.c_void_p)]
+                ("d_ray_tmp", C.c_void_p), ("d_n_rays_total", C.c_void_p), ("d_march_masks", C.c_void_p), ("d_occupied_bounds", C.c_void_p),
+                ("d_window_list", C.c_void_p), ("d_window_lens", C.c_void_p)]
 
 
 class RenderCfg(C.Structure):
@@ -92,7 +93,8 @@ class TestbedConfig(C.Structure):
                 ("finetune_global_movement", C.c_uint32), ("reset_density_grid_after_global_movement", C.c_uint32),
                 ("after_learning_rate", C.c_float), ("gm_learning_rate", C.c_float), ("gm_beta1", C.c_float), ("gm_beta2", C.c_float),
                 ("gm_epsilon", C.c_float), ("gm_l2_reg", C.c_float), ("gm_ema_decay", C.c_float), ("gm_lr_decay_start", C.c_uint32),
-                ("gm_lr_decay_interval", C.c_uint32), ("gm_lr_decay_base", C.c_float), ("first_frame_offset", C.c_float * 3)]
+                ("gm_lr_decay_interval", C.c_uint32), ("gm_lr_decay_base", C.c_float), ("first_frame_offset", C.c_float * 3),
+                ("n_forward_windows", C.c_uint32), ("forward_window_ends", C.c_uint32 * 6)]
 
 
 class TrainingState(C.Structure):
@@ -105,7 +107,7 @@ class TrainStats(C.Structure):
     _fields_ = [("training_step", C.c_uint32), ("rays_per_batch", C.c_uint32), ("n_rays_kept", C.c_uint32),
                 ("measured_batch_size_before_compaction", C.c_uint32), ("measured_batch_size", C.c_uint32),
                 ("overflow", C.c_uint32), ("loss", C.c_float), ("ek_loss", C.c_float), ("nonfinite_gradients", C.c_uint32),
-                ("device_error", C.c_uint32)]
+                ("device_error", C.c_uint32), ("n_samples_evaluated", C.c_uint32)]
 
 
 class Neus2bError(RuntimeError):

@@ -596,7 +596,15 @@ extern "C" int neus2b_neus_forward(const neus2b_grid_desc* desc, const uint16_t*
 extern "C" int neus2b_neus_forward_moved(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
                                          const uint32_t* d_n, const float* d_coords, const neus2b_motion* motion, uint16_t* d_out,
                                          neus2b_stream_t stream) {
+	return neus2b_neus_forward_indexed(desc, d_params, sdf_bias, n, d_n, nullptr, d_coords, motion, d_out, stream);
+}
+
+extern "C" int neus2b_neus_forward_indexed(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, uint32_t n,
+                                           const uint32_t* d_n, const uint32_t* d_index, const float* d_coords, const neus2b_motion* motion,
+                                           uint16_t* d_out, neus2b_stream_t stream) {
 	NeusArgs a = {};
+	a.index = d_index;
+	if (d_index && g_mma_path != NEUS2B_MMA_TCGEN05) return NEUS2B_E_UNSUPPORTED;
 	int rc = fill_common(a, desc, d_params);
 	if (rc) return rc;
 	if (!d_coords || !d_out || ((uintptr_t)d_out & 15u)) return NEUS2B_E_INVALID;

@@ -28,6 +28,8 @@ struct NeusArgs {
 	const __half* delta;
 	float first_frame_offset[3];
 	float* delta_sums;
+	// forward pass on a list of samples: entry i of the pass reads coords row index[i] and writes out row index[i] (nullptr: i)
+	const uint32_t* index;
 };
 
 // original column of the SDF-net input for internal column k

@@ -161,6 +161,11 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	const __half* grid = a.params + NEUS2B_GRID_OFF;
 	constexpr uint32_t kTmemCols = MODE == MODE_TRAIN ? 512u : 128u;
 
+	// A CTA without a tile leaves before the set-up (a windowed forward pass runs on short lists: most of the 148 CTAs of
+	// such a launch have nothing to do, and the set-up is the larger part of what a short launch costs).  The whole CTA
+	// takes the same branch: no barrier, no tensor memory yet.
+	if ((size_t)blockIdx.x * 128u >= (size_t)(a.d_n ? min(*a.d_n, a.n) : a.n)) return;
+
 	// ---- one-time set-up: zero the tiles (padding columns stay zero), stage the weights, allocate tensor memory
 	for (int e = tid; e < (int)(sizeof(Smem<MODE, DYN>) / 16); e += kThreads) reinterpret_cast<uint4*>(smem_raw)[e] = make_uint4(0, 0, 0, 0);
 	__syncthreads();
@@ -238,9 +243,12 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 	for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
 		const uint32_t i = tile * 128u + (uint32_t)s;
 		const bool valid = i < n;
+		// (the forward pass can run on a list of samples: row of the coordinate and output arrays this entry stands for)
+		uint32_t row = i;
+		if (MODE == MODE_FWD && valid && a.index) row = __ldg(a.index + i);
 		float x[3] = {0.5f, 0.5f, 0.5f}, dir[3] = {0.5f, 0.5f, 0.5f};
 		if (valid) {
-			const float* c = a.coords + (size_t)i * a.coord_stride;
+			const float* c = a.coords + (size_t)row * a.coord_stride;
 			x[0] = c[0];
 			x[1] = c[1];
 			x[2] = c[2];
@@ -429,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) neus_tc_kernel(const NeusArgs a) 
 						o[8 + e] = __float2half_rn(dir[e]);
 					}
 					o[7] = variance;
-					uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)i * 16);
+					uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)row * 16);
 					dst[0] = reinterpret_cast<const uint4*>(o)[0];
 					dst[1] = reinterpret_cast<const uint4*>(o)[1];
 				}

@@ -247,7 +247,8 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
 // ------------------------------------------------------------------------------------------------ loss
 struct CompTmp {  // 8 floats per kept ray
 	float rgb[3], T, weight_sum;
-	uint32_t n, full, pad;
+	uint32_t n, full;
+	uint32_t state;  // windowed evaluation: bit 0 = the ray is finished (terminated or all samples seen), bits 1.. = samples seen
 };
 
 constexpr uint32_t kFull = 0xffffffffu;
@@ -290,10 +291,18 @@ __device__ __forceinline__ void bent_dir_from_lane0(uint32_t wx, uint32_t wy, fl
 
 // Pass A (:1563-1617): composite along the ray until transmittance drops below 1e-4; count the surviving samples.
 // One warp per kept ray, 32 samples per iteration.
+//
+// Windowed form: a call composites samples [lo, min(ns, hi)) of every ray that is not finished yet, picking the ray's state
+// up from tmp (lo > 0) and leaving it there.  A ray that goes on appends the rows of its next window, samples
+// [hi, min(ns, next_hi)), to list (a range reserved with one atomicAdd on *list_len: the order of the list does not matter,
+// every row is evaluated on its own) and adds their number to *evaluated.  lo = 0, hi = all, list = nullptr: the whole ray
+// in one call, as the reference does.
 __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, const uint32_t* __restrict__ counters,
                                                         const __half* __restrict__ mlp_out, const uint32_t* __restrict__ numsteps,
                                                         const float* __restrict__ coords, CompTmp* __restrict__ tmp,
-                                                        uint64_t* __restrict__ scan_in, uint32_t n_rays_max) {
+                                                        uint64_t* __restrict__ scan_in, uint32_t n_rays_max, uint32_t lo, uint32_t hi,
+                                                        uint32_t next_hi, uint32_t* __restrict__ list, uint32_t* __restrict__ list_len,
+                                                        uint32_t* __restrict__ evaluated) {
 	const int lane = threadIdx.x & 31;
 	if (blockIdx.x == 0 && threadIdx.x == 0) scan_in[n_rays_max + 512] = 0ull;  // the scan's ticket counter (see scan_kernel)
 	const uint32_t n_kept = counters[0];
@@ -302,24 +311,37 @@ __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, co
 		const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
 		float T = 1.f, rgb[3] = {0.f, 0.f, 0.f}, ws = 0.f;
 		uint32_t n = 0;
-		bool done = false;
+		if (lo > 0) {
+			const CompTmp c = tmp[i];
+			if (c.state & 1u) continue;  // finished in an earlier window: its record stands
+			T = c.T, rgb[0] = c.rgb[0], rgb[1] = c.rgb[1], rgb[2] = c.rgb[2], ws = c.weight_sum, n = c.n;
+		}
+		const uint32_t lim = min(ns, hi);
+		bool done = false, terminated = false;
 		// the next 32 samples are in flight while the current 32 are composited (a long ray is a serial chain of chunks)
 		uint4 q0 = make_uint4(0u, 0u, 0u, 0u), q1 = q0;
 		float qdt = 0.f;
-		if ((uint32_t)lane < ns) {
-			const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + lane) * 16);
+		if (lo + (uint32_t)lane < lim) {
+			const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + lo + lane) * 16);
 			q0 = __ldg(p);
 			q1 = __ldg(p + 1);
-			qdt = coords[(size_t)(base + lane) * 7 + 3];
+			qdt = coords[(size_t)(base + lo + lane) * 7 + 3];
 		}
 		float dir[3];
-		bent_dir_from_lane0(q1.x, q1.y, dir);  // kept rays have at least one sample
-		for (uint32_t j0 = 0; j0 < ns && !done; j0 += 32) {
+		{  // BENT_DIR: the direction the network saw at the ray's first sample (kept rays have at least one sample)
+			uint32_t wx = q1.x, wy = q1.y;
+			if (lo > 0 && lane == 0) {
+				const uint4 f = __ldg(reinterpret_cast<const uint4*>(mlp_out + (size_t)base * 16) + 1);
+				wx = f.x, wy = f.y;
+			}
+			bent_dir_from_lane0(wx, wy, dir);
+		}
+		for (uint32_t j0 = lo; j0 < lim && !done; j0 += 32) {
 			const uint32_t j = j0 + lane;
-			const bool valid = j < ns;
+			const bool valid = j < lim;
 			const uint4 c0 = q0, c1 = q1;
 			const float cdt = qdt;
-			if (j + 32u < ns) {
+			if (j + 32u < lim) {
 				const uint4* p = reinterpret_cast<const uint4*>(mlp_out + (size_t)(base + j + 32u) * 16);
 				q0 = __ldg(p);
 				q1 = __ldg(p + 1);
@@ -337,14 +359,26 @@ __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, co
 			const float om = 1.f - s.alpha;
 			const float Tb = serial_transmittance(T, om, lane);
 			const bool active = valid && !(Tb < 1e-4f);
-			const uint32_t cnt = __popc(__ballot_sync(kFull, active));
+			const uint32_t cnt = __popc(__ballot_sync(kFull, active)), n_valid = __popc(__ballot_sync(kFull, valid));
 			const float w = active ? s.alpha * Tb : 0.f;
 #pragma unroll
 			for (int e = 0; e < 3; ++e) rgb[e] += warp_sum(w * s.rgb[e]);
 			ws += warp_sum(w);
 			if (cnt) T = __shfl_sync(kFull, Tb * om, cnt - 1);
 			n += cnt;
-			done = cnt < 32;
+			terminated = cnt < n_valid;  // a sample inside the window found the ray opaque
+			done = terminated || n_valid < 32u;
+		}
+		const bool finished = terminated || lim == ns;
+		if (list && !finished) {  // the rows of this ray's next window
+			const uint32_t cnt = min(ns, next_hi) - lim;
+			uint32_t off = 0;
+			if (lane == 0) {
+				off = atomicAdd(list_len, cnt);
+				atomicAdd(evaluated, cnt);
+			}
+			off = __shfl_sync(kFull, off, 0);
+			for (uint32_t k = lane; k < cnt; k += 32) list[off + k] = base + lim + k;
 		}
 		if (lane == 0) {
 			CompTmp c;
@@ -355,10 +389,31 @@ __global__ void __launch_bounds__(128) composite_kernel(neus2b_train_cfg cfg, co
 			c.weight_sum = ws;
 			c.n = n;
 			c.full = n == ns;
-			c.pad = 0;
+			c.state = (lim << 1) | (finished ? 1u : 0u);
 			tmp[i] = c;
 			scan_in[i] = (uint64_t)n;
 		}
+	}
+}
+
+// The first window's list: samples [0, min(ns, hi)) of every kept ray (later windows' lists come from composite_kernel).
+// One warp per ray; lens[0] (the list's length) and *evaluated are zero before the launch.
+__global__ void __launch_bounds__(128) window_first_kernel(const uint32_t* __restrict__ counters, const uint32_t* __restrict__ numsteps, uint32_t hi,
+                                                           uint32_t* __restrict__ list, uint32_t* __restrict__ list_len,
+                                                           uint32_t* __restrict__ evaluated) {
+	const int lane = threadIdx.x & 31;
+	const uint32_t n_kept = counters[0];
+	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_kept; i += warps) {
+		const uint32_t ns = numsteps[i * 2], base = numsteps[i * 2 + 1];
+		const uint32_t cnt = min(ns, hi);
+		uint32_t off = 0;
+		if (lane == 0) {
+			off = atomicAdd(list_len, cnt);
+			atomicAdd(evaluated, cnt);
+		}
+		off = __shfl_sync(kFull, off, 0);
+		for (uint32_t k = lane; k < cnt; k += 32) list[off + k] = base + k;
 	}
 }
 
@@ -627,6 +682,10 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	return NEUS2B_OK;
 }
 
+static int loss_after_composite(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays, uint32_t n_rays_total,
+                                Pcg32 r, uint32_t max_compacted, const uint16_t* d_mlp_out, neus2b_ray_workspace* ws, float* d_coords_out,
+                                uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss, int rollover, cudaStream_t stream);
+
 extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
                                    uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, const uint16_t* d_mlp_out,
                                    neus2b_ray_workspace* ws, float* d_coords_out, uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss,
@@ -638,8 +697,17 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 	Pcg32 r{rng.state, rng.inc};
 	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);  // 4 warps per CTA, one warp per ray, grid-stride
 	composite_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, ws->d_counters, (const __half*)d_mlp_out, ws->d_numsteps, ws->d_coords,
-	                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, n_rays);
+	                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, n_rays, 0u, 0xffffffffu, 0xffffffffu, nullptr, nullptr, nullptr);
 	N2B_CHECK_LAUNCH();
+	return loss_after_composite(ds, cfg, n_rays, d_n_rays, n_rays_total, r, max_compacted, d_mlp_out, ws, d_coords_out, d_dloss_dout, d_loss, d_ek_loss,
+	                            rollover, stream);
+}
+
+// Compaction offsets, loss pass and roll-over on the per-ray records the compositing pass left behind.
+static int loss_after_composite(const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays, uint32_t n_rays_total,
+                                Pcg32 r, uint32_t max_compacted, const uint16_t* d_mlp_out, neus2b_ray_workspace* ws, float* d_coords_out,
+                                uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss, int rollover, cudaStream_t stream) {
+	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, ws->d_counters, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
 	loss_kernel<<<ray_ctas, 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted,
@@ -654,6 +722,59 @@ extern "C" int neus2b_compute_loss(const neus2b_dataset* ds, const neus2b_train_
 		N2B_CHECK_LAUNCH();
 	}
 	return NEUS2B_OK;
+}
+
+// The network pass over the samples and the loss pass as one call that evaluates the network only where its output is
+// used.  The reference evaluates every sample the generator drew and then keeps, per ray, the samples in front of the point
+// where the ray turns opaque (transmittance below 1e-4): half to five sixths of the evaluations are thrown away.  Here the
+// rays are evaluated in windows of consecutive samples: the first window_ends[0] samples of every ray, then samples
+// [window_ends[0], window_ends[1]) of the rays that are still transparent, ..., finally the rest of those that remain.
+// Between windows the compositing pass continues each ray's record and appends the rows of the ray's next window to the
+// list that the fused forward kernel works through next: two launches per window.
+// Everything stays on the stream: no host round trip.  The per-ray records, the compacted batch and the loss gradient are
+// those of the full pass (every kept sample is evaluated by the same per-sample arithmetic); rows of d_mlp_out behind a
+// ray's last evaluated sample keep whatever they held.
+extern "C" int neus2b_forward_compute_loss(const neus2b_grid_desc* desc, const uint16_t* d_params, float sdf_bias, const neus2b_motion* motion,
+                                           const neus2b_dataset* ds, const neus2b_train_cfg* cfg, uint32_t n_rays, const uint32_t* d_n_rays,
+                                           uint32_t n_rays_total, neus2b_pcg32 rng, uint32_t max_compacted, neus2b_ray_workspace* ws,
+                                           const uint32_t* window_ends, uint32_t n_windows, uint16_t* d_mlp_out, float* d_coords_out,
+                                           uint16_t* d_dloss_dout, float* d_loss, float* d_ek_loss, int rollover, neus2b_stream_t stream) {
+	if (!desc || !d_params || !ds || !cfg || !d_mlp_out || !d_coords_out || !d_dloss_dout || check_ws(ws)) return NEUS2B_E_INVALID;
+	if (n_rays == 0 || n_rays > ws->max_rays || max_compacted == 0) return NEUS2B_E_INVALID;
+	if (n_rays > kScanMaxKeys) return NEUS2B_E_TOO_LARGE;
+	if (((uintptr_t)d_mlp_out | (uintptr_t)d_dloss_dout) & 15u) return NEUS2B_E_INVALID;
+	if (n_windows > NEUS2B_MAX_FORWARD_WINDOWS || (n_windows && !window_ends)) return NEUS2B_E_INVALID;
+	for (uint32_t w = 0; w < n_windows; ++w)
+		if (window_ends[w] == 0 || (w && window_ends[w] <= window_ends[w - 1])) return NEUS2B_E_INVALID;
+	if (n_windows == 0) {  // the reference's order: everything, then the loss pass
+		int rc = neus2b_neus_forward_moved(desc, d_params, sdf_bias, ws->max_samples, ws->d_counters + 4, ws->d_coords, motion, d_mlp_out, stream);
+		if (rc) return rc;
+		return neus2b_compute_loss(ds, cfg, n_rays, d_n_rays, n_rays_total, rng, max_compacted, d_mlp_out, ws, d_coords_out, d_dloss_dout, d_loss,
+		                           d_ek_loss, rollover, stream);
+	}
+	if (!ws->d_window_list || !ws->d_window_lens) return NEUS2B_E_INVALID;
+	Pcg32 r{rng.state, rng.inc};
+	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);
+	uint32_t* lens = ws->d_window_lens;        // one list length per window
+	uint32_t* evaluated = ws->d_counters + 5;  // (cleared by the generator with the other counters)
+	N2B_CHECK_CUDA(cudaMemsetAsync(lens, 0, sizeof(uint32_t) * (NEUS2B_MAX_FORWARD_WINDOWS + 2), stream));
+	window_first_kernel<<<ray_ctas, 128, 0, stream>>>(ws->d_counters, ws->d_numsteps, window_ends[0], ws->d_window_list, lens, evaluated);
+	N2B_CHECK_LAUNCH();
+	uint32_t lo = 0;
+	for (uint32_t w = 0; w <= n_windows; ++w) {
+		const uint32_t hi = w < n_windows ? window_ends[w] : 0xffffffffu;
+		const uint32_t next_hi = w + 1 < n_windows ? window_ends[w + 1] : 0xffffffffu;
+		int rc = neus2b_neus_forward_indexed(desc, d_params, sdf_bias, ws->max_samples, lens + w, ws->d_window_list, ws->d_coords, motion, d_mlp_out, stream);
+		if (rc) return rc;
+		const bool more = w < n_windows;
+		composite_kernel<<<ray_ctas, 128, 0, stream>>>(*cfg, ws->d_counters, (const __half*)d_mlp_out, ws->d_numsteps, ws->d_coords,
+		                                               (CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, n_rays, lo, hi, next_hi,
+		                                               more ? ws->d_window_list : nullptr, more ? lens + w + 1 : nullptr, more ? evaluated : nullptr);
+		N2B_CHECK_LAUNCH();
+		lo = hi;
+	}
+	return loss_after_composite(ds, cfg, n_rays, d_n_rays, n_rays_total, r, max_compacted, d_mlp_out, ws, d_coords_out, d_dloss_dout, d_loss, d_ek_loss,
+	                            rollover, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

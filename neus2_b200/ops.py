@@ -186,9 +186,11 @@ class RayBatch:
         self.scan_tmp = torch.zeros(max_rays + 1024, dtype=torch.int64, device=device)
         self.ray_tmp = torch.zeros((max_rays, 8), dtype=f32, device=device)
         self.march_masks = torch.zeros((max_rays, 64), dtype=i32, device=device) if march_masks else None
+        self.window_list = torch.zeros(max_samples, dtype=i32, device=device)
+        self.window_lens = torch.zeros(8, dtype=i32, device=device)
         self.ws = L.RayWorkspace(max_rays, max_samples, L.ptr(self.ray_indices), L.ptr(self.rays), L.ptr(self.numsteps),
                                  L.ptr(self.coords), L.ptr(self.counters), L.ptr(self.scan_tmp), L.ptr(self.ray_tmp), None,
-                                 L.ptr(self.march_masks), L.ptr(occupied_bounds))
+                                 L.ptr(self.march_masks), L.ptr(occupied_bounds), L.ptr(self.window_list), L.ptr(self.window_lens))
         self.occupied_bounds = occupied_bounds
 
 
@@ -218,6 +220,17 @@ def compute_loss(ds, cfg, n_rays, n_rays_total, rng, max_compacted, mlp_out, bat
     L.check(L.lib().neus2b_compute_loss(C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total), rng,
                                         u32(max_compacted), L.ptr(mlp_out), C.byref(batch.ws), L.ptr(coords_out), L.ptr(dloss),
                                         L.ptr(loss), L.ptr(ek_loss), C.c_int(int(rollover)), L.cur_stream()))
+
+
+def forward_compute_loss(desc, params, ds, cfg, n_rays, n_rays_total, rng, max_compacted, batch, mlp_out, coords_out, dloss, loss=None,
+                         ek_loss=None, window_ends=(32, 96), rollover=True, sdf_bias=-0.1, motion=None, n_rays_dev=None):
+    """neus2b_forward_compute_loss: the network pass over the batch's samples in windows per ray plus the loss pass.  window_ends ():
+    every sample, like neus_forward followed by compute_loss."""
+    ends = (C.c_uint32 * max(1, len(window_ends)))(*window_ends)
+    L.check(L.lib().neus2b_forward_compute_loss(C.byref(desc), L.ptr(params), C.c_float(sdf_bias), C.byref(motion) if motion is not None else None,
+                                                C.byref(ds), C.byref(cfg), u32(n_rays), L.ptr(n_rays_dev), u32(n_rays_total), rng, u32(max_compacted),
+                                                C.byref(batch.ws), ends, u32(len(window_ends)), L.ptr(mlp_out), L.ptr(coords_out), L.ptr(dloss),
+                                                L.ptr(loss), L.ptr(ek_loss), C.c_int(int(rollover)), L.cur_stream()))
 
 
 class OccupancyGrid:

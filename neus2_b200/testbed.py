@@ -19,6 +19,10 @@ class Testbed:
                 setattr(cfg.grid, k, v)
             elif k == "first_frame_offset":
                 cfg.first_frame_offset[:] = [float(x) for x in v]
+            elif k == "forward_windows":  # cumulative window ends of the step's network pass; () = every sample, like the reference
+                cfg.n_forward_windows = len(v)
+                for i, e in enumerate(v):
+                    cfg.forward_window_ends[i] = int(e)
             else:
                 if not hasattr(cfg, k):
                     raise AttributeError(k)
