@@ -123,7 +123,7 @@ EXPORTS = [
     "neus2b_mlp_forward", "neus2b_mlp_forward_tcgen05", "neus2b_mlp_backward", "neus2b_mlp_backward_backward_input", "neus2b_sh4_forward",
     "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_set_device_error_flags",
     "neus2b_per_level_scale_from_top_resolution", "neus2b_testbed_config_active_levels", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf",
-    "neus2b_neus_forward_moved", "neus2b_neus_train_moved", "neus2b_neus_sdf_moved", "neus2b_delta_forward", "neus2b_delta_backward",
+    "neus2b_neus_forward_moved", "neus2b_neus_forward_indexed", "neus2b_forward_compute_loss", "neus2b_neus_train_moved", "neus2b_neus_sdf_moved", "neus2b_delta_forward", "neus2b_delta_backward",
     "neus2b_delta_optimizer_step", "neus2b_movement_accumulate", "neus2b_occupancy_update_moved", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_occupancy_bounds", "neus2b_adam_step", "neus2b_adam_step_packed",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
