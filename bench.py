@@ -281,9 +281,9 @@ def mesh_record(tb, rank, world, res):
 # in profiles/neus_tc_kernel_train_2p18_samples.txt (constants copied from that capture, not measured by this run):
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum: the hash table and its gradient table stay in L2, what
 # reaches HBM is their first touch plus the sample streams), L2 sectors requested by the SMs, tensor-pipe activity.
-TRAIN_KERNEL_DRAM_BYTES = 59969536 + 534016
-TRAIN_KERNEL_L2_SECTORS = 30405708
-TRAIN_KERNEL_TENSOR_PIPE_PCT = 4.6
+TRAIN_KERNEL_DRAM_BYTES = 59966464 + 516096
+TRAIN_KERNEL_L2_SECTORS = 26909409
+TRAIN_KERNEL_TENSOR_PIPE_PCT = 5.4
 
 
 def roofline_train_kernel(tb, ptrs, st, ng, ms_in_step, launches_in_step):
