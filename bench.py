@@ -225,6 +225,14 @@ def run_ours(args):
                             "samples_after_compaction": int(st.measured_batch_size), "loss": float(st.loss),
                             "ek_loss": float(st.ek_loss), "overflow": int(st.overflow)}}
 
+    # ---- where the gradient exchange sits in a step (several GPUs): CUDA events over 20 more training steps, outside `value`
+    if world > 1:
+        ex = dp.probe_exchange(20)
+        t = torch.tensor([ex["allreduce_ms"], ex["generation_in_front_ms"], ex["exposed_wait_ms"]], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        line["exchange"] = dict(zip(("allreduce_ms", "generation_in_front_ms", "exposed_wait_ms"), [round(v, 4) for v in t.tolist()]),
+                                note="max over ranks of per-rank medians; 25 MB fp16 grid gradient + 48 KB fp32 MLP/variance gradient per step")
+
     # ---- mesh extraction at 512^3, sharded by z-slab over the ranks (SDF lattice with the EMA weights, marching cubes with
     # global numbering, counters all-gathered, slices gathered into rank 0): not part of `value`
     if not args.no_mesh:

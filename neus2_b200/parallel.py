@@ -168,3 +168,38 @@ class DataParallelTrainer:
             for w in works:
                 w.wait()
         return self.tb.optimizer_step(read_stats=read_stats)
+
+    def probe_exchange(self, steps=20):
+        """Where the gradient exchange sits in a step, by CUDA events on the training stream over `steps` real training steps:
+        the all-reduce alone (a step without overlap), the sample generation that is placed in front of the wait, and the wait
+        that is left (how long the training stream still stands at the collectives after the generation).  Milliseconds per
+        step, maxima over the ranks are the caller's business."""
+        assert self.world > 1
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        alone, gen, exposed = [], [], []
+        for k in range(steps):
+            self.tb.train_backward()
+            e0, e1, e2 = ev(), ev(), ev()
+            with torch.cuda.stream(self.stream):
+                e0.record()
+                if k % 2 == 0:  # exchange with nothing in front of the wait
+                    for t in self.grads:
+                        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+                    e1.record()
+                else:
+                    works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
+                    self.tb.train_pregenerate()
+                    e1.record()
+                    for w in works:
+                        w.wait()
+                    e2.record()
+            self.tb.optimizer_step(read_stats=False)
+            torch.cuda.synchronize()
+            if k % 2 == 0:
+                alone.append(e0.elapsed_time(e1))
+            else:
+                gen.append(e0.elapsed_time(e1))
+                exposed.append(e1.elapsed_time(e2))
+        med = lambda v: float(sorted(v)[len(v) // 2]) if v else 0.0
+        return {"allreduce_ms": med(alone), "generation_in_front_ms": med(gen), "exposed_wait_ms": med(exposed)}
+
