@@ -77,11 +77,9 @@ __global__ void __launch_bounds__(256) render_setup_kernel(neus2b_render_cfg rc,
 #pragma unroll
 		for (int e = 0; e < 3; ++e) {
 			r.o[e] = rc.camera[9 + e];
-			d[e] = rc.camera[0 + e] * dl[0] + rc.camera[3 + e] * dl[1] + rc.camera[6 + e] * dl[2];
+			d[e] = sum3_eigen(rc.camera[0 + e] * dl[0], rc.camera[3 + e] * dl[1], rc.camera[6 + e] * dl[2]);
 		}
-		const float norm = sqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
-#pragma unroll
-		for (int e = 0; e < 3; ++e) r.d[e] = d[e] / norm;
+		normalize3_eigen(d, r.d);
 		if (rc.use_global_movement) {  // :2286-2296
 			float o2[3], q[3], dq[3];
 #pragma unroll

@@ -1294,10 +1294,9 @@ static void render_init_ray(const n2o_render_cfg* rc, uint32_t x, uint32_t y, re
 	float d[3];
 	for (int e = 0; e < 3; ++e) {
 		r->o[e] = rc->camera[9 + e];
-		d[e] = rc->camera[0 + e] * dl[0] + rc->camera[3 + e] * dl[1] + rc->camera[6 + e] * dl[2];
+		d[e] = sum3_eigen(rc->camera[0 + e] * dl[0], rc->camera[3 + e] * dl[1], rc->camera[6 + e] * dl[2]);
 	}
-	const float norm = sqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
-	for (int e = 0; e < 3; ++e) r->d[e] = d[e] / norm;
+	normalize3_eigen(d, r->d);
 	float tmin, tmax;
 	aabb_ray_intersect(rc->aabb_min, rc->aabb_max, r->o, r->d, &tmin, &tmax);
 	float t = fmaxf(tmin, 0.2f) + 1e-6f; /* NERF_RENDERING_NEAR_DISTANCE */

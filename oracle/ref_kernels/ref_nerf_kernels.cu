@@ -7,6 +7,8 @@
  *   compute_loss_kernel_train_nerf_with_global_movement    (src/testbed_nerf.cu:1465)
  *   generate_grid_samples_nerf_nonuniform, splat_grid_samples_nerf_max_nearest_neighbor, ema_grid_samples_nerf,
  *   grid_to_bitfield, bitfield_max_pool                    (src/testbed_nerf.cu:630-785, launched as in :3287-3391)
+ *   Testbed::NerfTracer::init_rays_from_camera / trace + shade_kernel_nerf (src/testbed_nerf.cu:2398-2660, driven as in
+ *   Testbed::render_nerf, :2671-2800), with the reference's NerfNetwork<__half> over this repository's layered kernels
  * The launch arguments mirror Testbed::train_nerf_step (:3797-3906) and update_density_grid_nerf (:3327-3391) for a
  * static scene with the default switches.  The reference's tiny-cuda-nn fork is not vendored: the headers under
  * include/tiny-cuda-nn of this repository stand in for it, so pcg32, morton3D_invert, logistic and reduce_sum come from
@@ -185,6 +187,55 @@ int ref_density_grid_update(uint32_t n_samples, const uint32_t* d_indices, uint1
 		for (uint32_t level = 1; level < NERF_CASCADES(); ++level)
 			linear_kernel(bitfield_max_pool, 0, stream, cells / 64, d_bitfield + (size_t)grid_mip_offset(level - 1) / 8, d_bitfield + (size_t)grid_mip_offset(level) / 8);
 		CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+	});
+}
+
+/* One frame through the reference's inference path: NerfTracer::init_rays_from_camera, NerfTracer::trace (rounds of marching,
+ * network queries and compositing with compaction of the live rays) and shade_kernel_nerf, Shade mode, pinhole camera.
+ * d_params: the fp16 parameter block [SDF MLP | colour MLP | grid | variance]; grid geometry as in the arguments.
+ * Outputs: d_frame [h][w][4], d_depth [h][w]. */
+int ref_render_frame(uint32_t n_levels, uint32_t log2_hashmap_size, uint32_t base_resolution, float per_level_scale, float sdf_bias, uint16_t* d_params,
+                     uint32_t width, uint32_t height, const float* focal_length, const float* camera, const float* screen_center, uint32_t spp,
+                     int snap_to_pixel_centers, uint8_t* d_bitfield, float min_transmittance, float cone_angle_constant, float* d_frame, float* d_depth,
+                     uint32_t* n_hit_out) {
+	return guarded([&] {
+		const json pos_encoding = {{"otype", "HashGrid"},          {"n_levels", n_levels},
+		                           {"n_features_per_level", 2},   {"log2_hashmap_size", log2_hashmap_size},
+		                           {"base_resolution", base_resolution}, {"per_level_scale", per_level_scale}};
+		const json dir_encoding = {{"otype", "Composite"},
+		                           {"nested", {{{"n_dims_to_encode", 3}, {"otype", "SphericalHarmonics"}, {"degree", 4}}, {{"otype", "Identity"}, {"n_bins", 4}, {"degree", 4}}}}};
+		const json density_network = {{"otype", "FullyFusedMLP"}, {"activation", "ReLU"}, {"output_activation", "None"}, {"n_neurons", 64}, {"n_hidden_layers", 1},
+		                              {"sdf_bias", sdf_bias}};
+		const json rgb_network = {{"otype", "FullyFusedMLP"}, {"activation", "ReLU"}, {"output_activation", "None"}, {"n_neurons", 64}, {"n_hidden_layers", 2}};
+		NerfNetwork<network_precision_t> network(3u, 3u, 0u, 4u, pos_encoding, dir_encoding, density_network, rgb_network);
+		GPUMemory<network_precision_t> gradients(network.n_params());
+		network.set_params((network_precision_t*)d_params, (network_precision_t*)d_params, (network_precision_t*)d_params, gradients.data());
+		network.m_training_step = 0;
+		network.set_anneal_end(0);  // as the testbed does after it has built the network (src/testbed.cu:2220); the member has no initialiser
+		network.m_use_delta = false;
+		network.m_train_delta = false;
+		cudaStream_t stream;
+		CUDA_CHECK_THROW(cudaStreamCreate(&stream));
+		{
+			Testbed::NerfTracer tracer;
+			const BoundingBox aabb{Vector3f::Zero(), Vector3f::Ones()};
+			Matrix<float, 3, 4> cam;
+			std::memcpy(cam.data(), camera, 12 * sizeof(float));
+			const Vector2i resolution((int)width, (int)height);
+			const Vector2f focal(focal_length[0], focal_length[1]);
+			CUDA_CHECK_THROW(cudaMemsetAsync(d_frame, 0, (size_t)width * height * 4 * sizeof(float), stream));
+			tracer.init_rays_from_camera(spp, network.padded_output_width(), network.n_extra_dims(), resolution, focal, cam, cam, Vector4f::Zero(),
+			                             Vector2f(screen_center[0], screen_center[1]), Vector3f(0.f, 0.f, 1.f), snap_to_pixel_centers != 0, aabb, 1.0f, 0.0f,
+			                             CameraDistortion{}, nullptr, Vector2i::Zero(), nullptr, Vector2i::Zero(), (Array4f*)d_frame, d_depth, d_bitfield, -1,
+			                             cone_angle_constant, ERenderMode::Shade, stream, nullptr, nullptr, Vector3f::Zero());
+			const uint32_t n_hit = tracer.trace(network, aabb, aabb, 0, nullptr, focal, cone_angle_constant, d_bitfield, ERenderMode::Shade, cam, 1.0f, 0, -1,
+			                                    ENerfActivation::Logistic, ENerfActivation::Exponential, -1, min_transmittance, 0.0f, 0, nullptr, stream);
+			RaysNerfSoa& rays_hit = tracer.rays_hit();
+			linear_kernel(shade_kernel_nerf, 0, stream, n_hit, rays_hit.rgba, rays_hit.depth, rays_hit.payload, ERenderMode::Shade, false, (Array4f*)d_frame, d_depth);
+			CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+			if (n_hit_out) *n_hit_out = n_hit;
+		}
+		CUDA_CHECK_THROW(cudaStreamDestroy(stream));
 	});
 }
 
