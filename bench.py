@@ -685,14 +685,42 @@ def run_reference(args):
     value = BATCH * args.steps / dt
     sample = ("%d compacted samples per step (+2x pre-compaction forward) scaled to the 2^18-sample step, "
               "plus Adam over all 12.6 M parameters every step" % n)
-    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                      "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-                      "scaling": "weak", "vs_baseline": None, "dtype": "fp16 storage, fp32 math (CPU)", "data": "synthetic",
-                      "config": workload_config(world),
-                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
-                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                      "note": "the reference's own CUDA build needs the un-vendored tiny-cuda-nn fork (empty submodule) and it has "
-                              "no CPU path: this arm times the CPU oracle port"}), flush=True)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp16 storage, fp32 math (CPU)", "data": "synthetic",
+            "config": workload_config(world),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference's own CUDA build needs the un-vendored tiny-cuda-nn fork (empty submodule) and it has "
+                    "no CPU path: this arm times the CPU oracle port"}
+    loop = reference_loop_on_gpu()
+    if loop is not None:
+        line["reference_loop_on_gpu"] = loop
+    print(json.dumps(line), flush=True)
+
+
+def reference_loop_on_gpu():
+    """Beside the CPU figure: the reference's own headless training loop (its unmodified sources compiled over this repository's
+    tiny-cuda-nn headers, oracle/_ref/libref_testbed.so) on the same workload on this GPU: the reference's host code, ray-march, loss
+    and occupancy kernels and its NerfNetwork / Trainer objects, with this repository's layered kernels under them.  It is not the
+    reference's tiny-cuda-nn build, which cannot be produced.  Runs as a child process; None when there is no GPU or no such library."""
+    import subprocess
+    import torch
+    here = os.path.dirname(os.path.abspath(__file__))
+    if not torch.cuda.is_available() or not os.path.exists(os.path.join(here, "oracle", "_ref", "libref_testbed.so")):
+        return None
+    try:
+        r = subprocess.run([sys.executable, os.path.join(here, "oracle", "run_ref_testbed.py"), "--views", "64", "--res", "512", "--batch", str(BATCH),
+                            "--warmup", "520", "--steps", "200"], capture_output=True, text=True, timeout=600, cwd=here)
+        out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    except Exception as e:  # the measurement is an extra: never fail the arm over it
+        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+    if "ms_per_step" in out:
+        out["value"] = BATCH / (out["ms_per_step"] * 1e-3)
+        out["unit"] = UNIT
+        out["what"] = ("the reference's unmodified headless Testbed loop over this repository's tiny-cuda-nn headers (layered kernels), "
+                       "steps 520-720 of config 1, wall clock around 200 frame() calls")
+    return out
 
 
 def main():
