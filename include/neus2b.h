@@ -189,7 +189,7 @@ int neus2b_neus_sdf(const neus2b_grid_desc* desc, const uint16_t* d_params, floa
 typedef struct {
 	uint64_t state, inc;
 } neus2b_pcg32; /* tcnn::default_rng_t */
-void neus2b_pcg32_seed(neus2b_pcg32* rng, uint64_t seed);
+void neus2b_pcg32_seed(neus2b_pcg32* rng, uint64_t seed); /* default_rng_t{seed}: stream selector 1, as the constructor defaults */
 void neus2b_pcg32_advance(neus2b_pcg32* rng, uint64_t delta);
 
 typedef struct {
@@ -238,6 +238,10 @@ typedef struct {
 	                                     cells are not marched (they cannot take a sample; the result is unchanged) */
 	uint32_t* d_window_list;          /* optional [max_samples]: sample rows of the current window (neus2b_forward_compute_loss) */
 	uint32_t* d_window_lens;          /* optional [8]: the length of each window's list */
+	const uint32_t* d_prev_samples;   /* optional: the sample count of the previous training step, read on the device.  When it
+	                                     is not zero, rays whose samples end beyond that count rounded up to 128 are dropped
+	                                     like rays beyond max_samples: the training loop's max_inference
+	                                     (src/testbed_nerf.cu:3764-3769, passed to the generator as its max_samples :3801) */
 } neus2b_ray_workspace;
 
 /* generate_training_samples_nerf_with_global_movement (src/testbed_nerf.cu:1253-1446), static scene; sample order is

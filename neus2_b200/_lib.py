@@ -43,7 +43,7 @@ class RayWorkspace(C.Structure):
     _fields_ = [("max_rays", C.c_uint32), ("max_samples", C.c_uint32), ("d_ray_indices", C.c_void_p), ("d_rays", C.c_void_p),
                 ("d_numsteps", C.c_void_p), ("d_coords", C.c_void_p), ("d_counters", C.c_void_p), ("d_scan_tmp", C.c_void_p),
                 ("d_ray_tmp", C.c_void_p), ("d_n_rays_total", C.c_void_p), ("d_march_masks", C.c_void_p), ("d_occupied_bounds", C.c_void_p),
-                ("d_window_list", C.c_void_p), ("d_window_lens", C.c_void_p)]
+                ("d_window_list", C.c_void_p), ("d_window_lens", C.c_void_p), ("d_prev_samples", C.c_void_p)]
 
 
 class RenderCfg(C.Structure):

@@ -196,14 +196,21 @@ int launch_scan(uint32_t n_max, const uint32_t* d_n, uint64_t* data, cudaStream_
 
 // Second half of the sample generator (:1410-1445): canonical ranges, then march again and write the coordinates.
 __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg, uint32_t n_rays_max, const uint32_t* __restrict__ d_n_rays,
-                                                           uint32_t max_samples, const uint8_t* __restrict__ bitfield,
-                                                           const RayTmp* __restrict__ tmp,
+                                                           uint32_t max_samples, const uint32_t* __restrict__ d_prev_samples,
+                                                           const uint8_t* __restrict__ bitfield, const RayTmp* __restrict__ tmp,
                                                            const uint64_t* __restrict__ scan, uint32_t* __restrict__ ray_indices,
                                                            float* __restrict__ rays, uint32_t* __restrict__ numsteps,
                                                            float* __restrict__ coords, uint32_t* __restrict__ counters,
                                                            const uint32_t* __restrict__ masks) {
 	const int lane = threadIdx.x & 31;
 	if (blockIdx.x == 0 && threadIdx.x == 0) counters[1] = (uint32_t)(scan[n_rays_max] & 0xFFFFFFFFull);  // all steps, dropped rays included
+	// max_inference of the training loop (:3764-3769): after a step that took samples, the room is the previous step's count
+	// rounded up to the batch granularity, and rays beyond it are dropped like rays beyond the buffer
+	const uint32_t buffer_samples = max_samples;
+	if (d_prev_samples) {
+		const uint32_t prev = *d_prev_samples;
+		if (prev) max_samples = min(max_samples, (min(prev, max_samples) + 127u) / 128u * 128u);
+	}
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
 	for (uint32_t i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_rays; i += warps) {
@@ -213,8 +220,8 @@ __global__ void __launch_bounds__(128) emit_samples_kernel(neus2b_train_cfg cfg,
 		if (r.numsteps == 0) continue;
 		const uint64_t key = scan[i];
 		const uint32_t base = (uint32_t)(key & 0xFFFFFFFFull), kidx = (uint32_t)(key >> 32);
-		if (base + r.numsteps > max_samples) {  // sample buffer exhausted: drop the ray (:1412-1414)
-			if (lane == 0) atomicOr(&counters[3], 1u);
+		if (base + r.numsteps > max_samples) {  // no room left: drop the ray (:1412-1414); the flag reports an exhausted buffer only
+			if (lane == 0 && base + r.numsteps > buffer_samples) atomicOr(&counters[3], 1u);
 			continue;
 		}
 		if (lane == 0) {
@@ -636,7 +643,7 @@ using namespace n2b;
 extern "C" void neus2b_pcg32_seed(neus2b_pcg32* rng, uint64_t seed) {
 	Pcg32 r;
 	r.state = 0u;
-	r.inc = (0xda3e39cb94b95bdbULL << 1u) | 1u;
+	r.inc = (1ull << 1u) | 1u;  // default_rng_t{seed}: the constructor's default stream selector is 1 (src/testbed.cu:2077)
 	r.next_uint();
 	r.state += seed;
 	r.next_uint();
@@ -675,7 +682,7 @@ extern "C" int neus2b_generate_samples(const neus2b_dataset* ds, const neus2b_tr
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
+	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, ws->max_samples, ws->d_prev_samples, d_bitfield, (const RayTmp*)ws->d_ray_tmp,
 	                                                             ws->d_scan_tmp, ws->d_ray_indices, ws->d_rays, ws->d_numsteps,
 	                                                             ws->d_coords, ws->d_counters, ws->d_march_masks);
 	N2B_CHECK_LAUNCH();
@@ -842,7 +849,7 @@ extern "C" int neus2b_generate_samples_static(const neus2b_dataset* ds, const ne
 	N2B_CHECK_LAUNCH();
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, d_n_rays, scan);
 	N2B_CHECK_LAUNCH();
-	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, d_bitfield, (const RayTmp*)ray_tmp, scan,
+	emit_samples_kernel<<<min(div_up(n_rays, 4), (uint32_t)kSMs * 16u), 128, 0, stream>>>(*cfg, n_rays, d_n_rays, max_samples, nullptr, d_bitfield, (const RayTmp*)ray_tmp, scan,
 	                                                             d_ray_indices, d_rays, d_numsteps, d_coords, d_counters, nullptr);
 	N2B_CHECK_LAUNCH();
 	return NEUS2B_OK;

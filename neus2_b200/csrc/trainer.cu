@@ -29,12 +29,15 @@ __global__ void tune_kernel(TrainState* st, const uint32_t* __restrict__ counter
 	st->device_error = *device_error;
 	const uint32_t rays = st->rays_per_batch;
 	st->n_rays_total += rays;
-	st->measured_pre = counters[1];
 	st->evaluated = counters[5] ? counters[5] : counters[1];
-	st->measured = counters[2];
 	st->n_kept = counters[0];
 	st->overflow |= counters[3];
-	if (counters[1] == 0 || counters[2] == 0) return;  // the reference stops training here; keep the batch as it is
+	if (counters[1] == 0 || counters[2] == 0) {  // both read as zero (:3411-3416): the batch stays as it is, the next step has the whole buffer
+		st->measured_pre = st->measured = 0;
+		return;
+	}
+	st->measured_pre = counters[1];
+	st->measured = counters[2];
 	uint32_t next = (uint32_t)((float)rays * (float)target / (float)counters[2]);
 	next = (next + 127u) / 128u * 128u;
 	st->rays_per_batch = max(128u, min(next, max_rays));
@@ -211,7 +214,7 @@ extern "C" void neus2b_testbed_default_config(neus2b_testbed_config* c) {
 	c->anneal_end = 0;
 	c->density_grid_decay = 0.95f;
 	c->random_bg_color = 1;
-	c->snap_to_pixel_centers = 0;
+	c->snap_to_pixel_centers = 1;  // Nerf::Training::snap_to_pixel_centers (testbed.h:614)
 	c->world_size = 1;
 	c->rank = 0;
 	c->loss_scale = 128.f;
@@ -354,6 +357,7 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	tb->delta_ema_master = tb->delta_master + 36;
 	tb->delta_sums = tb->delta_master + 48;
 	tb->ws.d_n_rays_total = &tb->state->n_rays_total;
+	tb->ws.d_prev_samples = &tb->state->measured_pre;  // max_inference (src/testbed_nerf.cu:3764-3769)
 	{
 		const int erc = tc_error_device_ptr(&tb->d_device_error);
 		if (erc) {

@@ -16,9 +16,20 @@ import numpy as np
 NERF_SCALE = 0.33  # nerf_loader.h:31
 
 
+_F32 = np.float32
+_PI_F32 = np.float32(3.14159265358979323846)  # PI() is a float (random_val.cuh:30)
+
+
 def fov_to_focal_length(resolution, degrees):
-    """common_device.cuh:452-454"""
-    return 0.5 * float(resolution) / math.tan(0.5 * degrees * math.pi / 180.0)
+    """common_device.cuh:452-454, in single precision like the reference (the tangent is the correctly rounded one, which is what
+    the C library's tanf returns)."""
+    x = _F32(_F32(_F32(0.5) * _F32(degrees)) * _PI_F32) / _F32(180.0)
+    return float(_F32(_F32(0.5) * _F32(resolution)) / _F32(math.tan(float(x))))
+
+
+def radians_to_degrees(angle):
+    """(float)json["camera_angle_x"] * 180 / PI() (nerf_loader.cu:657)"""
+    return float(_F32(_F32(angle) * _F32(180.0)) / _PI_F32)
 
 
 def nerf_matrix_to_ngp(m, scale, offset, from_na=False, from_mitsuba=False):
@@ -116,7 +127,7 @@ def load_nerf_dataset(json_paths):
     if not json_paths:
         raise ValueError("Cannot load NeRF data from an empty set of paths.")
     res = dict(scale=NERF_SCALE, offset=[0.5, 0.5, 0.5], aabb_scale=1, from_na=False, from_mitsuba=False, render_aabb=None,
-               up=[0.0, 0.0, 1.0])
+               up=[0.0, 1.0, 0.0])  # NerfDataset::up (nerf_loader.h:81)
     pixels, xforms, focal, principal = [], [], [], []
     white = black = False
     for jp in json_paths:
@@ -193,11 +204,11 @@ def load_nerf_dataset(json_paths):
                 if "fl_" + axis in js:
                     return float(js["fl_" + axis])
                 if "camera_angle_" + axis in js:
-                    return fov_to_focal_length(resolution, float(js["camera_angle_" + axis]) * 180.0 / math.pi)
+                    return fov_to_focal_length(resolution, radians_to_degrees(js["camera_angle_" + axis]))
                 if "fl_" + axis in fr:
                     return float(fr["fl_" + axis])
                 if "camera_angle_" + axis in fr:
-                    return fov_to_focal_length(resolution, float(fr["camera_angle_" + axis]) * 180.0 / math.pi)
+                    return fov_to_focal_length(resolution, radians_to_degrees(fr["camera_angle_" + axis]))
                 return 0.0
             x_fl, y_fl = read_focal_length(w, "x"), read_focal_length(h, "y")
             p = list(pp)

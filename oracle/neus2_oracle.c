@@ -752,7 +752,9 @@ void n2o_accumulate_global_movement(const uint16_t* delta, float* acc_R, float* 
 /* ------------------------------------------------------------------ PCG32 (published generator; float = 23 mantissa bits) */
 #define PCG_MULT 0x5851f42d4c957f2dULL
 void n2o_pcg32_seed(n2o_pcg32* r, uint64_t seed) {
-	const uint64_t initseq = 0xda3e39cb94b95bdbULL;
+	/* default_rng_t{seed} in the reference (src/testbed.cu:2077, :2090): pcg32's constructor takes the stream selector
+	 * initseq = 1 by default; the generator's default stream constant belongs to the argument-less constructor only */
+	const uint64_t initseq = 1u;
 	r->state = 0u;
 	r->inc = (initseq << 1u) | 1u;
 	n2o_pcg32_next_uint(r);

@@ -11,10 +11,13 @@
  * json document, then frame() per training step -- the reference's host loop with its stream synchronisations, its own ray
  * marching / loss / occupancy kernels, its NerfNetwork, Trainer and optimizer objects; underneath those objects run this
  * repository's layered kernels.  It is the reference's code path on a B200, not the reference's tiny-cuda-nn kernels. */
+#include <neural-graphics-primitives/nerf_loader.h>
 #include <neural-graphics-primitives/testbed.h>
+#include <tiny-cuda-nn/trainer.h>
 
 #include <unistd.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 
@@ -24,32 +27,56 @@ extern "C" {
 
 /* workdir: directory to run in; must hold utils/mlp_weights.txt (the SDF network's initial weights, which
  * NerfNetwork::initialize_params reads relative to the working directory, nerf_network.h:773-803).
- * losses[n_warmup + n_steps]: Testbed::m_loss_scalar after every step.  wall_ms: host time of the n_steps timed steps
- * (synchronised before and after).  stats[4]: rays_per_batch, measured_batch_size, measured_batch_size_before_compaction,
- * training step, after the last step. */
+ * h_params (optional, n_params floats): full-precision parameters that replace the drawn ones before the first step
+ * (Trainer::set_params_full_precision), so that a run can start from the same weights as another implementation's.
+ * losses[n_warmup + n_steps]: Testbed::m_loss_scalar.val() after every step (the reference reads the loss back every 16th
+ * step).  step_stats (optional) [n_warmup + n_steps][3]: rays_per_batch, measured_batch_size,
+ * measured_batch_size_before_compaction after every step.  h_density_grid (optional, n_density_grid floats): the occupancy
+ * grid's running densities (Testbed::m_nerf.density_grid) as they stand after grid_after_steps steps; h_bitfield (optional,
+ * n_bitfield bytes): the occupancy bits of all cascades (density_grid_bitfield) at the same moment.  wall_ms: host time of the n_steps timed steps (synchronised before
+ * and after).  stats[4]: rays_per_batch, measured_batch_size, measured_batch_size_before_compaction, training step at the end. */
 int ref_testbed_train(const char* workdir, const char* transforms_json, const char* network_config_json, uint32_t batch_size, uint32_t n_warmup,
-                      uint32_t n_steps, float* losses, float* wall_ms, uint32_t* stats) {
+                      uint32_t n_steps, const float* h_params, uint64_t n_params, float* losses, uint32_t* step_stats, float* wall_ms, uint32_t* stats,
+                      uint32_t grid_after_steps, float* h_density_grid, uint64_t n_density_grid, uint8_t* h_bitfield, uint64_t n_bitfield) {
 	try {
 		if (chdir(workdir) != 0) return -3;
 		Testbed testbed{ETestbedMode::Nerf};
 		testbed.load_training_data(transforms_json);
 		testbed.reload_network_from_json(nlohmann::json::parse(network_config_json, nullptr, true, true), "");
+		if (h_params) {
+			if (n_params != testbed.m_trainer->n_params()) return -4;
+			testbed.m_trainer->set_params_full_precision(h_params, n_params);
+		}
 		testbed.m_train = true;
 		testbed.m_training_batch_size = batch_size;
+		const auto& c = testbed.m_nerf.training.counters_rgb;
+		auto record = [&](uint32_t i) {
+			if (h_density_grid && i + 1 == grid_after_steps)
+				CUDA_CHECK_THROW(cudaMemcpy(h_density_grid, testbed.m_nerf.density_grid.data(),
+				                            sizeof(float) * std::min<uint64_t>(n_density_grid, testbed.m_nerf.density_grid.size()), cudaMemcpyDeviceToHost));
+			if (h_bitfield && i + 1 == grid_after_steps)
+				CUDA_CHECK_THROW(cudaMemcpy(h_bitfield, testbed.m_nerf.density_grid_bitfield.data(),
+				                            std::min<uint64_t>(n_bitfield, testbed.m_nerf.density_grid_bitfield.size()), cudaMemcpyDeviceToHost));
+			if (losses) losses[i] = testbed.m_loss_scalar.val();
+			if (step_stats) {
+				step_stats[3 * i + 0] = c.rays_per_batch;
+				step_stats[3 * i + 1] = c.measured_batch_size;
+				step_stats[3 * i + 2] = c.measured_batch_size_before_compaction;
+			}
+		};
 		for (uint32_t i = 0; i < n_warmup; ++i) {
 			testbed.frame();
-			if (losses) losses[i] = testbed.m_loss_scalar.val();
+			record(i);
 		}
 		CUDA_CHECK_THROW(cudaDeviceSynchronize());
 		const auto t0 = std::chrono::steady_clock::now();
 		for (uint32_t i = 0; i < n_steps; ++i) {
 			testbed.frame();
-			if (losses) losses[n_warmup + i] = testbed.m_loss_scalar.val();
+			record(n_warmup + i);
 		}
 		CUDA_CHECK_THROW(cudaDeviceSynchronize());
 		if (wall_ms) *wall_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
 		if (stats) {
-			const auto& c = testbed.m_nerf.training.counters_rgb;
 			stats[0] = c.rays_per_batch;
 			stats[1] = c.measured_batch_size;
 			stats[2] = c.measured_batch_size_before_compaction;
@@ -58,6 +85,48 @@ int ref_testbed_train(const char* workdir, const char* transforms_json, const ch
 		return 0;
 	} catch (const std::exception& e) {
 		std::fprintf(stderr, "ref_testbed_train: %s\n", e.what());
+		return -1;
+	}
+}
+
+/* The reference's dataset loader (ngp::load_nerf, src/nerf_loader.cu:197) on one transforms file: what it hands to training.
+ * header[8]: n_images, width and height of image 0, bytes per pixel channel (EImageDataType as image_type_size), aabb_scale,
+ * is_hdr, from_na, from_mitsuba.  floats[8]: scale, offset xyz, up xyz, 0.  Per image (at most max_images): xforms [12] (the 3x4
+ * start matrix, row-major), focal [2], principal [2], and the pixel bytes of image i at pixels + i * width * height * 4 *
+ * bytes-per-channel (copied while they fit into pixel_capacity). */
+int ref_load_dataset(const char* transforms_json, uint32_t max_images, uint32_t* header, float* floats, float* xforms, float* focal, float* principal,
+                     uint8_t* pixels, uint64_t pixel_capacity) {
+	try {
+		NerfDataset ds = ngp::load_nerf({filesystem::path{transforms_json}}, 0.f);
+		const auto& m0 = ds.metadata.at(0);
+		header[0] = (uint32_t)ds.n_images;
+		header[1] = (uint32_t)m0.resolution.x();
+		header[2] = (uint32_t)m0.resolution.y();
+		header[3] = (uint32_t)image_type_size(m0.image_data_type);
+		header[4] = (uint32_t)ds.aabb_scale;
+		header[5] = ds.is_hdr;
+		header[6] = ds.from_na;
+		header[7] = ds.from_mitsuba;
+		floats[0] = ds.scale;
+		for (int k = 0; k < 3; ++k) {
+			floats[1 + k] = ds.offset[k];
+			floats[4 + k] = ds.up[k];
+		}
+		floats[7] = 0.f;
+		const uint64_t image_bytes = (uint64_t)header[1] * header[2] * 4 * header[3];
+		for (uint32_t i = 0; i < ds.n_images && i < max_images; ++i) {
+			for (int r = 0; r < 3; ++r)
+				for (int c = 0; c < 4; ++c) xforms[i * 12 + r * 4 + c] = ds.xforms[i].start(r, c);
+			focal[2 * i] = ds.metadata[i].focal_length.x();
+			focal[2 * i + 1] = ds.metadata[i].focal_length.y();
+			principal[2 * i] = ds.metadata[i].principal_point.x();
+			principal[2 * i + 1] = ds.metadata[i].principal_point.y();
+			if ((i + 1) * image_bytes <= pixel_capacity)
+				CUDA_CHECK_THROW(cudaMemcpy(pixels + i * image_bytes, ds.pixelmemory[i].data(), image_bytes, cudaMemcpyDeviceToHost));
+		}
+		return 0;
+	} catch (const std::exception& e) {
+		std::fprintf(stderr, "ref_load_dataset: %s\n", e.what());
 		return -1;
 	}
 }

