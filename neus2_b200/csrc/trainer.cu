@@ -167,6 +167,14 @@ struct neus2b_testbed {
 	uint32_t stats_step = 0;
 	bool tuned = false;         // the batch tuner already ran for the step whose optimizer pass is pending
 	bool pregenerated = false;  // the next step's samples are already in the ray workspace
+	// The next step's samples are drawn on a second stream, next to the optimizer pass: the generator reads the occupancy bits,
+	// the cameras and the tuner's ray count, none of which the optimizer touches, and writes the ray workspace, which nothing
+	// reads again once the tuner has run.  ev_tuned: behind the tuner on the training stream; ev_generated: behind the
+	// generator on the side stream (the training stream waits for it before the next step's network pass).
+	cudaStream_t gen_stream = nullptr;
+	cudaEvent_t ev_tuned = nullptr, ev_generated = nullptr;
+	bool gen_in_flight = false;  // the training stream has not yet waited for ev_generated
+	bool cam_on_gen_stream = false;  // the last camera upload went to the side stream
 	uint64_t render_samples = 0;  // of the last call
 	float render_ms = 0.f;
 	cudaEvent_t render_ev[2] = {nullptr, nullptr};
@@ -243,6 +251,7 @@ extern "C" void neus2b_testbed_default_config(neus2b_testbed_config* c) {
 
 extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 	if (!tb) return;
+	if (tb->gen_stream) cudaStreamSynchronize(tb->gen_stream);
 	if (tb->stream) cudaStreamSynchronize(tb->stream);
 	for (void* p : tb->allocs) cudaFree(p);
 	for (void* p : tb->render_allocs) cudaFree(p);
@@ -253,6 +262,9 @@ extern "C" void neus2b_testbed_destroy(neus2b_testbed* tb) {
 		if (e) cudaEventDestroy(e);
 	if (tb->cam_event) cudaEventDestroy(tb->cam_event);
 	if (tb->stats_event) cudaEventDestroy(tb->stats_event);
+	if (tb->ev_tuned) cudaEventDestroy(tb->ev_tuned);
+	if (tb->ev_generated) cudaEventDestroy(tb->ev_generated);
+	if (tb->gen_stream) cudaStreamDestroy(tb->gen_stream);
 	if (tb->stream) cudaStreamDestroy(tb->stream);
 	delete tb;
 }
@@ -294,8 +306,15 @@ extern "C" int neus2b_testbed_create(const neus2b_testbed_config* cfg, neus2b_te
 	tb->cfg = *cfg;
 	N2B_CHECK_CUDA(cudaGetDevice(&tb->device));
 	cudaError_t e = cudaStreamCreateWithFlags(&tb->stream, cudaStreamNonBlocking);
+	if (e == cudaSuccess) {  // the generator's small kernels go first where both streams have work ready
+		int lo = 0, hi = 0;
+		cudaDeviceGetStreamPriorityRange(&lo, &hi);
+		e = cudaStreamCreateWithPriority(&tb->gen_stream, cudaStreamNonBlocking, hi);
+	}
+	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&tb->ev_tuned, cudaEventDisableTiming);
+	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&tb->ev_generated, cudaEventDisableTiming);
 	if (e != cudaSuccess) {
-		delete tb;
+		neus2b_testbed_destroy(tb);
 		return (int)e;
 	}
 	tb->n_grid = (uint64_t)lv.offset[NEUS2B_MAX_LEVELS] * 2u;
@@ -394,20 +413,40 @@ extern "C" int neus2b_testbed_n_params(const neus2b_testbed* tb, uint64_t* n) {
 	return NEUS2B_OK;
 }
 
-extern "C" int neus2b_testbed_update_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal) {
-	if (!tb || !tb->ds.n_images || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
+// The training stream waits for samples that are still being drawn on the side stream.
+static int join_generation(neus2b_testbed* tb) {
+	if (tb->gen_in_flight) {
+		N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->stream, tb->ev_generated, 0));
+		tb->gen_in_flight = false;
+	}
+	if (tb->cam_on_gen_stream) {
+		N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->stream, tb->cam_event, 0));
+		tb->cam_on_gen_stream = false;
+	}
+	return NEUS2B_OK;
+}
+
+static int upload_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal, cudaStream_t stream) {
 	const uint32_t n = tb->ds.n_images;
 	tb->pregenerated = false;  // samples drawn ahead used the previous cameras
-	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
 	if (!tb->cam_event) N2B_CHECK_CUDA(cudaEventCreateWithFlags(&tb->cam_event, cudaEventDisableTiming));
 	else N2B_CHECK_CUDA(cudaEventSynchronize(tb->cam_event));  // the previous upload may still be reading the staging buffer
 	memcpy(tb->h_cam, h_xforms, sizeof(float) * 12 * n);
 	memcpy(tb->h_cam + 12 * n, h_focal, sizeof(float) * 2 * n);
 	memcpy(tb->h_cam + 14 * n, h_principal, sizeof(float) * 2 * n);
 	// the three arrays are one allocation, in this order
-	N2B_CHECK_CUDA(cudaMemcpyAsync((void*)tb->ds.d_xforms, tb->h_cam, sizeof(float) * 16 * n, cudaMemcpyHostToDevice, tb->stream));
-	N2B_CHECK_CUDA(cudaEventRecord(tb->cam_event, tb->stream));
+	N2B_CHECK_CUDA(cudaMemcpyAsync((void*)tb->ds.d_xforms, tb->h_cam, sizeof(float) * 16 * n, cudaMemcpyHostToDevice, stream));
+	N2B_CHECK_CUDA(cudaEventRecord(tb->cam_event, stream));
+	tb->cam_on_gen_stream = stream == tb->gen_stream;
 	return NEUS2B_OK;
+}
+
+extern "C" int neus2b_testbed_update_cameras(neus2b_testbed* tb, const float* h_xforms, const float* h_focal, const float* h_principal) {
+	if (!tb || !tb->ds.n_images || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
+	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	int rc = join_generation(tb);  // samples being drawn ahead still read the old cameras
+	if (rc) return rc;
+	return upload_cameras(tb, h_xforms, h_focal, h_principal, tb->stream);
 }
 
 extern "C" int neus2b_testbed_load_training_data(neus2b_testbed* tb, uint32_t n_images, uint32_t width, uint32_t height,
@@ -459,6 +498,7 @@ extern "C" int neus2b_testbed_device_ptrs(neus2b_testbed* tb, uint16_t** d_param
                                           float** d_grad_mlp, uint16_t** d_grad_grid, float** d_grad_variance, uint8_t** d_bitfield,
                                           float** d_density_grid, neus2b_stream_t* stream) {
 	if (!tb) return NEUS2B_E_INVALID;
+	if (int jr = join_generation(tb)) return jr;  // samples may still be drawn on the side stream
 	if (d_params) *d_params = (uint16_t*)tb->params;
 	if (d_params_ema) *d_params_ema = (uint16_t*)tb->params_ema;
 	if (d_master) *d_master = tb->master;
@@ -594,25 +634,26 @@ static uint32_t occupancy_skip(uint32_t step) { return step / 16u < 1u ? 1u : (s
 
 // The step's rays and samples (first half of train_nerf_step, src/testbed_nerf.cu:3782-3830).  Depends on the occupancy
 // bits, the batch tuner's ray count and the step's random stream, not on the parameters.
-static int generate_step_samples(neus2b_testbed* tb, const neus2b_train_cfg& tc, const neus2b_pcg32& rng) {
+static int generate_step_samples(neus2b_testbed* tb, const neus2b_train_cfg& tc, const neus2b_pcg32& rng, cudaStream_t stream) {
 	// one cascade: positions map straight to the finest level's cells, so rays that miss the box of occupied cells are
 	// not marched; the box is recomputed after every occupancy update (and after the bitfield's pointer was handed out)
 	tb->ws.d_occupied_bounds = nullptr;
 	if (tb->cfg.n_cascades == 1) {
 		if (tb->occ_bounds_stale) {
-			int rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, tb->stream);
+			int rc = neus2b_occupancy_bounds(tb->bitfield, tb->occ_bounds, stream);
 			if (rc) return rc;
 			tb->occ_bounds_stale = false;
 		}
 		tb->ws.d_occupied_bounds = tb->occ_bounds;
 	}
-	return neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, &tb->state->rays_per_batch, 0, rng, tb->bitfield, &tb->ws, tb->stream);
+	return neus2b_generate_samples(&tb->ds, &tc, tb->max_rays, &tb->state->rays_per_batch, 0, rng, tb->bitfield, &tb->ws, stream);
 }
 
 extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	if (!tb || !tb->ds.n_images) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
-	int rc;
+	int rc = join_generation(tb);
+	if (rc) return rc;
 	// a later frame of a dynamic sequence: the canonical model joins once the motion-only phase is over (src/testbed.cu:2649-2657)
 	if (tb->frame >= 1 && tb->training_step == predict_steps(tb)) {
 		tb->train_canonical = true;
@@ -635,7 +676,7 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	if (tb->pregenerated) {
 		tb->pregenerated = false;  // neus2b_testbed_train_pregenerate already drew this step's samples
 	} else {
-		rc = generate_step_samples(tb, tc, rng);
+		rc = generate_step_samples(tb, tc, rng, tb->stream);
 		if (rc) return rc;
 	}
 	neus2b_motion mo{};
@@ -679,12 +720,20 @@ extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
 	if (tb->step_pending && !tb->tuned) {
 		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
 		N2B_CHECK_LAUNCH();
+		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
 		tb->tuned = true;
+	} else if (!tb->step_pending) {  // no optimizer pass to run next to: behind everything the training stream holds
+		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
 	}
+	// on the side stream, behind the tuner (and behind a camera upload that went to the training stream)
+	N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->gen_stream, tb->ev_tuned, 0));
+	if (tb->cam_event && !tb->cam_on_gen_stream) N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->gen_stream, tb->cam_event, 0));
 	const neus2b_train_cfg tc = make_train_cfg(tb);  // (nothing the generator reads depends on the step number)
 	const neus2b_pcg32 rng{tb->rng.state, tb->rng.inc};  // already advanced to the next step's stream
-	int rc = generate_step_samples(tb, tc, rng);
+	int rc = generate_step_samples(tb, tc, rng, tb->gen_stream);
 	if (rc) return rc;
+	N2B_CHECK_CUDA(cudaEventRecord(tb->ev_generated, tb->gen_stream));
+	tb->gen_in_flight = true;
 	tb->pregenerated = true;
 	return NEUS2B_OK;
 }
@@ -814,14 +863,21 @@ extern "C" int neus2b_testbed_train_step(neus2b_testbed* tb, const float* h_next
 	if (!tb) return NEUS2B_E_INVALID;
 	int rc = neus2b_testbed_train_backward(tb);
 	if (rc) return rc;
-	rc = optimizer_enqueue(tb, h_stats != nullptr);
-	if (rc) return rc;
+	// the next step's cameras and samples go to the side stream, behind this step's tuner and next to its optimizer pass
 	if (h_next_xforms && h_next_focal && h_next_principal) {
-		rc = neus2b_testbed_update_cameras(tb, h_next_xforms, h_next_focal, h_next_principal);
+		if (!tb->ds.n_images) return NEUS2B_E_INVALID;
+		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
+		N2B_CHECK_LAUNCH();
+		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
+		tb->tuned = true;
+		N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->gen_stream, tb->ev_tuned, 0));  // this step's loss pass has read the old cameras
+		rc = upload_cameras(tb, h_next_xforms, h_next_focal, h_next_principal, tb->gen_stream);
 		if (rc) return rc;
 	}
 	rc = neus2b_testbed_train_pregenerate(tb);
 	if (rc != NEUS2B_OK && rc != 1) return rc;
+	rc = optimizer_enqueue(tb, h_stats != nullptr);
+	if (rc) return rc;
 	return h_stats ? neus2b_testbed_train_wait_stats(tb, h_stats) : NEUS2B_OK;
 }
 
@@ -830,6 +886,8 @@ extern "C" int neus2b_testbed_train(neus2b_testbed* tb, uint32_t n_steps, neus2b
 	for (uint32_t s = 0; s < n_steps; ++s) {
 		int rc = neus2b_testbed_train_backward(tb);
 		if (rc) return rc;
+		rc = neus2b_testbed_train_pregenerate(tb);  // (1: the next step starts with an occupancy update and draws its samples itself)
+		if (rc != NEUS2B_OK && rc != 1) return rc;
 		rc = neus2b_testbed_train_optimizer_step(tb, s + 1 == n_steps ? h_stats : nullptr);
 		if (rc) return rc;
 	}
@@ -994,6 +1052,7 @@ extern "C" int neus2b_testbed_next_frame(neus2b_testbed* tb, const uint32_t* h_p
 	if (!tb || !tb->ds.n_images || !h_pixels || !h_xforms || !h_focal || !h_principal) return NEUS2B_E_INVALID;
 	if (tb->step_pending) return NEUS2B_E_INVALID;  // between the halves of a step
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (int jr = join_generation(tb)) return jr;  // samples may still be drawn on the side stream
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	// NerfNetwork::accumulate_global_movement (src/testbed.cu:2044) with the motion as trained (its fp16 parameters)
 	if (tb->frame >= 1 && tb->cfg.predict_global_movement) {
@@ -1058,6 +1117,7 @@ extern "C" int neus2b_testbed_set_movement(neus2b_testbed* tb, uint32_t frame, c
                                            const float delta[12]) {
 	if (!tb || !rotation || !transition) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (int jr = join_generation(tb)) return jr;  // samples may still be drawn on the side stream
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	tb->frame = frame;
 	memcpy(tb->acc_rotation, rotation, sizeof(tb->acc_rotation));
@@ -1092,6 +1152,7 @@ extern "C" int neus2b_testbed_get_training_state(neus2b_testbed* tb, neus2b_trai
 extern "C" int neus2b_testbed_set_training_state(neus2b_testbed* tb, const neus2b_training_state* in) {
 	if (!tb || !in || in->rays_per_batch == 0 || in->rays_per_batch > tb->max_rays) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (int jr = join_generation(tb)) return jr;  // samples may still be drawn on the side stream
 	N2B_CHECK_CUDA(cudaStreamSynchronize(tb->stream));
 	tb->training_step = in->training_step;
 	tb->canonical_step = next_canonical_step(tb, tb->training_step);
@@ -1151,6 +1212,7 @@ extern "C" int neus2b_testbed_set_array(neus2b_testbed* tb, int which, const voi
 	if (rc) return rc;
 	if (bytes != n) return NEUS2B_E_INVALID;
 	N2B_CHECK_CUDA(cudaSetDevice(tb->device));
+	if (int jr = join_generation(tb)) return jr;  // samples may still be drawn on the side stream
 	N2B_CHECK_CUDA(cudaMemcpyAsync(p, h_in, n, cudaMemcpyHostToDevice, tb->stream));
 	if (which == NEUS2B_ARRAY_DENSITY_GRID) {  // update_density_grid_mean_and_bitfield, as load_snapshot does (src/testbed.cu:3228-3230)
 		rc = neus2b_occupancy_mean_and_bitfield(tb->cfg.n_cascades, tb->density_grid, tb->bitfield, tb->density_mean, tb->occ_partial, tb->stream);

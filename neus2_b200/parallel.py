@@ -158,8 +158,8 @@ class DataParallelTrainer:
             if next_cameras is not None:
                 self.tb.update_cameras(*next_cameras)
             return self.tb.optimizer_step(read_stats=read_stats)
-        # the collectives start behind the backward kernels on NCCL's own stream; the training stream meanwhile draws the
-        # next step's samples and only then waits for the summed gradients
+        # the collectives start behind the backward kernels on NCCL's own stream; the library draws the next step's samples on
+        # its second stream meanwhile (and on through the optimizer pass); the training stream waits for the summed gradients
         with torch.cuda.stream(self.stream):
             works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
             if next_cameras is not None:
@@ -171,35 +171,29 @@ class DataParallelTrainer:
 
     def probe_exchange(self, steps=20):
         """Where the gradient exchange sits in a step, by CUDA events on the training stream over `steps` real training steps:
-        the all-reduce alone (a step without overlap), the sample generation that is placed in front of the wait, and the wait
-        that is left (how long the training stream still stands at the collectives after the generation).  Milliseconds per
-        step, maxima over the ranks are the caller's business."""
+        the all-reduce alone (a step that draws no samples ahead), and the same wait while the library draws the next step's
+        samples on its second stream beside it (the optimizer pass follows the wait on the training stream; the generation
+        goes on next to both).  Milliseconds per step, maxima over the ranks are the caller's business."""
         assert self.world > 1
         ev = lambda: torch.cuda.Event(enable_timing=True)
-        alone, gen, exposed = [], [], []
+        alone, beside = [], []
         for k in range(steps):
             self.tb.train_backward()
-            e0, e1, e2 = ev(), ev(), ev()
+            e0, e1 = ev(), ev()
             with torch.cuda.stream(self.stream):
                 e0.record()
-                if k % 2 == 0:  # exchange with nothing in front of the wait
+                if k % 2 == 0:  # exchange with nothing beside it
                     for t in self.grads:
                         dist.all_reduce(t, op=dist.ReduceOp.SUM)
-                    e1.record()
                 else:
                     works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
                     self.tb.train_pregenerate()
-                    e1.record()
                     for w in works:
                         w.wait()
-                    e2.record()
+                e1.record()
             self.tb.optimizer_step(read_stats=False)
             torch.cuda.synchronize()
-            if k % 2 == 0:
-                alone.append(e0.elapsed_time(e1))
-            else:
-                gen.append(e0.elapsed_time(e1))
-                exposed.append(e1.elapsed_time(e2))
+            (alone if k % 2 == 0 else beside).append(e0.elapsed_time(e1))
         med = lambda v: float(sorted(v)[len(v) // 2]) if v else 0.0
-        return {"allreduce_ms": med(alone), "generation_in_front_ms": med(gen), "exposed_wait_ms": med(exposed)}
+        return {"allreduce_ms": med(alone), "allreduce_with_generation_beside_ms": med(beside)}
 

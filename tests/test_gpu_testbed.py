@@ -68,7 +68,7 @@ def test_first_step_matches_oracle_composition(scene, oracle):
     assert grid_close > 0.999 and bit_mismatch < 1e-4
     ods = O.make_dataset(scene["pixels"].numpy().view(np.uint32), scene["xforms"].numpy(), scene["focal"].numpy(),
                          scene["principal"].numpy())
-    cfg = O.train_cfg(ek_loss_weight=0.1)
+    cfg = O.train_cfg(ek_loss_weight=0.1, snap_to_pixel_centers=True)  # the training loop's default (testbed.h:614)
     gen = O.generate_samples(ods, cfg, 4096, 0, target * 16, m_rng, bits_gpu)
     used = int(gen["numsteps"][gen["n_kept"] - 1].sum())
     out = O.neus_forward(d, params, gen["coords"][:used])
