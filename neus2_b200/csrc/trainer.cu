@@ -676,6 +676,11 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	if (tb->pregenerated) {
 		tb->pregenerated = false;  // neus2b_testbed_train_pregenerate already drew this step's samples
 	} else {
+		// the running ray count that spreads the rays over the images restarts with every frame, and with every step while
+		// the canonical step stands at zero (the motion-only phase of a later frame) (src/testbed_nerf.cu:3779-3781);
+		// samples are never drawn ahead for such a step (it begins with an occupancy update)
+		if (tb->training_step == 0 || tb->canonical_step == 0)
+			N2B_CHECK_CUDA(cudaMemsetAsync(&tb->state->n_rays_total, 0, sizeof(uint32_t), tb->stream));
 		rc = generate_step_samples(tb, tc, rng, tb->stream);
 		if (rc) return rc;
 	}

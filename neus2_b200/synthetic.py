@@ -229,7 +229,15 @@ def init_params(grid_n_params, seed=1337, variance=0.3):
     return p
 
 
-def write_transforms_dataset(scene, directory):
+def write_sequence_dataset(scenes, directory):
+    """A dynamic sequence in the reference's layout: one transforms file per frame in one directory (frame_0000.json, ...; the
+    loader sorts them by name, src/testbed_nerf.cu:2958-2996), each with its own image folder.  Returns the directory."""
+    for f, scene in enumerate(scenes):
+        write_transforms_dataset(scene, directory, json_name="frame_%04d.json" % f, image_dir="images_%04d" % f)
+    return directory
+
+
+def write_transforms_dataset(scene, directory, json_name="transforms.json", image_dir="images"):
     """Writes a synthetic scene (the dict of render_sphere_views / render_csg_views) as a dataset in the reference's file format:
     <directory>/transforms.json plus one RGBA PNG per view, with `scale` 1 and `offset` 0 so that the loader's
     nerf_matrix_to_ngp gives back exactly the scene's camera matrices.  Returns the path of the json file."""
@@ -240,18 +248,18 @@ def write_transforms_dataset(scene, directory):
     t = lambda k: scene[k].cpu().numpy() if hasattr(scene[k], "cpu") else np.asarray(scene[k])
     px, xf, fl, pp = t("pixels"), t("xforms"), t("focal"), t("principal")
     n, h, w = px.shape
-    os.makedirs(os.path.join(directory, "images"), exist_ok=True)
+    os.makedirs(os.path.join(directory, image_dir), exist_ok=True)
     frames = []
     for i in range(n):
         rgba = np.ascontiguousarray(px[i]).view(np.uint8).reshape(h, w, 4)
-        Image.fromarray(rgba, "RGBA").save(os.path.join(directory, "images", "%04d.png" % i))
+        Image.fromarray(rgba, "RGBA").save(os.path.join(directory, image_dir, "%04d.png" % i))
         m = np.asarray(xf[i], np.float32).reshape(4, 3).T  # [12] column major -> 3x4
         nerf = ngp_matrix_to_nerf(m, 1.0, [0.0, 0.0, 0.0])
-        frames.append({"file_path": "images/%04d.png" % i, "transform_matrix": np.vstack([nerf, [0, 0, 0, 1]]).astype(float).tolist(),
+        frames.append({"file_path": "%s/%04d.png" % (image_dir, i), "transform_matrix": np.vstack([nerf, [0, 0, 0, 1]]).astype(float).tolist(),
                        "fl_x": float(fl[i][0]), "fl_y": float(fl[i][1]), "cx": float(pp[i][0] * w), "cy": float(pp[i][1] * h), "w": w, "h": h})
     js = {"scale": 1.0, "offset": [0.0, 0.0, 0.0], "aabb_scale": 1, "w": w, "h": h, "fl_x": float(fl[0][0]), "fl_y": float(fl[0][1]),
           "cx": float(pp[0][0] * w), "cy": float(pp[0][1] * h), "frames": frames}
-    path = os.path.join(directory, "transforms.json")
+    path = os.path.join(directory, json_name)
     with open(path, "w") as f:
         json.dump(js, f)
     return path

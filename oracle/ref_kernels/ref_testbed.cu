@@ -33,11 +33,16 @@ extern "C" {
  * step).  step_stats (optional) [n_warmup + n_steps][3]: rays_per_batch, measured_batch_size,
  * measured_batch_size_before_compaction after every step.  h_density_grid (optional, n_density_grid floats): the occupancy
  * grid's running densities (Testbed::m_nerf.density_grid) as they stand after grid_after_steps steps; h_bitfield (optional,
- * n_bitfield bytes): the occupancy bits of all cascades (density_grid_bitfield) at the same moment.  wall_ms: host time of the n_steps timed steps (synchronised before
+ * n_bitfield bytes): the occupancy bits of all cascades (density_grid_bitfield) at the same moment.  step_frames (optional)
+ * [n_warmup + n_steps][2]: the frame of a dynamic sequence and the frame's training step after every call of frame() (the data
+ * path may be a directory of per-frame transforms files; frame() moves on by itself, src/testbed.cu:1739-1746).  h_motion
+ * (optional, 28 fp16 values): the accumulated rotation (12 slots) and transition (4), and the current frame's own 6-D rotation
+ * (8) and transition (4), at the end.  wall_ms: host time of the n_steps timed steps (synchronised before
  * and after).  stats[4]: rays_per_batch, measured_batch_size, measured_batch_size_before_compaction, training step at the end. */
 int ref_testbed_train(const char* workdir, const char* transforms_json, const char* network_config_json, uint32_t batch_size, uint32_t n_warmup,
                       uint32_t n_steps, const float* h_params, uint64_t n_params, float* losses, uint32_t* step_stats, float* wall_ms, uint32_t* stats,
-                      uint32_t grid_after_steps, float* h_density_grid, uint64_t n_density_grid, uint8_t* h_bitfield, uint64_t n_bitfield) {
+                      uint32_t grid_after_steps, float* h_density_grid, uint64_t n_density_grid, uint8_t* h_bitfield, uint64_t n_bitfield,
+                      uint32_t* step_frames, uint16_t* h_motion) {
 	try {
 		if (chdir(workdir) != 0) return -3;
 		Testbed testbed{ETestbedMode::Nerf};
@@ -58,6 +63,10 @@ int ref_testbed_train(const char* workdir, const char* transforms_json, const ch
 				CUDA_CHECK_THROW(cudaMemcpy(h_bitfield, testbed.m_nerf.density_grid_bitfield.data(),
 				                            std::min<uint64_t>(n_bitfield, testbed.m_nerf.density_grid_bitfield.size()), cudaMemcpyDeviceToHost));
 			if (losses) losses[i] = testbed.m_loss_scalar.val();
+			if (step_frames) {
+				step_frames[2 * i + 0] = (uint32_t)testbed.current_training_time_frame;
+				step_frames[2 * i + 1] = testbed.m_training_step;
+			}
 			if (step_stats) {
 				step_stats[3 * i + 0] = c.rays_per_batch;
 				step_stats[3 * i + 1] = c.measured_batch_size;
@@ -76,6 +85,14 @@ int ref_testbed_train(const char* workdir, const char* transforms_json, const ch
 		}
 		CUDA_CHECK_THROW(cudaDeviceSynchronize());
 		if (wall_ms) *wall_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+		if (h_motion) {  // fp16 bits: accumulated rotation [12 slots], accumulated transition [4], the frame's own rotation [8] and transition [4]
+			const auto& net = testbed.m_nerf_network;
+			CUDA_CHECK_THROW(cudaMemcpy(h_motion, net->rotation()->params(), sizeof(uint16_t) * std::min<size_t>(12, net->rotation()->n_params()), cudaMemcpyDeviceToHost));
+			CUDA_CHECK_THROW(cudaMemcpy(h_motion + 12, net->transition()->params(), sizeof(uint16_t) * std::min<size_t>(4, net->transition()->n_params()), cudaMemcpyDeviceToHost));
+			const auto& dn = net->delta_network();
+			CUDA_CHECK_THROW(cudaMemcpy(h_motion + 16, dn->rotation()->params(), sizeof(uint16_t) * std::min<size_t>(8, dn->rotation()->n_params()), cudaMemcpyDeviceToHost));
+			CUDA_CHECK_THROW(cudaMemcpy(h_motion + 24, dn->transition()->params(), sizeof(uint16_t) * std::min<size_t>(4, dn->transition()->n_params()), cudaMemcpyDeviceToHost));
+		}
 		if (stats) {
 			stats[0] = c.rays_per_batch;
 			stats[1] = c.measured_batch_size;

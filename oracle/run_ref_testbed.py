@@ -35,6 +35,18 @@ def network_config(n_levels=16, per_level_scale=1.447, learning_rate=1e-2, ek_lo
                         "predict_global_movement": False, "mask_loss_weight": 0.0, "ek_loss_weight": ek_loss_weight, "anneal_end": 0}}
 
 
+def merged_config(extra=None):
+    """network_config() with `extra` merged into its hyperparams; the entry "optimizer_leaf" goes into the innermost optimizer."""
+    config = network_config()
+    extra = dict(extra or {})
+    leaf = config["optimizer"]
+    while "nested" in leaf:
+        leaf = leaf["nested"]
+    leaf.update(extra.pop("optimizer_leaf", {}))
+    config["hyperparams"].update(extra)
+    return config
+
+
 def load_only(transforms, out_path, max_images=256, pixel_capacity=1 << 28):
     """ngp::load_nerf on one transforms file; cameras and pixel bytes as the reference hands them to training."""
     import numpy as np
@@ -62,6 +74,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--data", default=None, help="directory of an existing dataset (transforms.json); default: a synthetic scene is written")
     ap.add_argument("--params", default=None, help=".npy file of full-precision initial parameters that replace the drawn ones")
+    ap.add_argument("--hyper", default=None, help="json object merged into the network configuration's hyperparams (and, under the key "
+                    "\"optimizer_leaf\", into the innermost optimizer)")
     ap.add_argument("--load-only", default=None, help="only run the reference's dataset loader on --data and write what it returns to this .npz file")
     ap.add_argument("--trace", default=None, help="write per-step rays_per_batch / measured batch sizes / loss to this .npz file")
     ap.add_argument("--grid-after", type=int, default=0, help="with --trace: also store the occupancy grid's densities after this many steps")
@@ -77,8 +91,10 @@ def main():
         return load_only(os.path.join(os.path.abspath(args.data), "transforms.json"), args.load_only)
     work = tempfile.mkdtemp(prefix="n2b_ref_")
     try:
-        if args.data:
+        if args.data:  # a directory with transforms.json, or a directory of per-frame transforms files (a dynamic sequence)
             transforms = os.path.join(os.path.abspath(args.data), "transforms.json")
+            if not os.path.exists(transforms):
+                transforms = os.path.abspath(args.data)
         else:
             scene = S.render_sphere_views(args.views, args.res, args.res, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
             transforms = S.write_transforms_dataset(scene, os.path.join(work, "data"))
@@ -93,15 +109,19 @@ def main():
         params = np.ascontiguousarray(np.load(args.params), np.float32) if args.params else None
         grid = np.zeros(128 ** 3, np.float32) if args.grid_after else None  # cascade 0
         bits = np.zeros(8 * 128 ** 3 // 8, np.uint8) if args.grid_after else None  # all cascades
+        step_frames, motion = np.zeros((n, 2), np.uint32), np.zeros(28, np.uint16)
         sys.stdout.flush()
-        rc = lib.ref_testbed_train(work.encode(), transforms.encode(), json.dumps(network_config()).encode(), C.c_uint32(args.batch),
+        config = merged_config(json.loads(args.hyper) if args.hyper else None)
+        rc = lib.ref_testbed_train(work.encode(), transforms.encode(), json.dumps(config).encode(), C.c_uint32(args.batch),
                                    C.c_uint32(args.warmup), C.c_uint32(args.steps), params.ctypes.data_as(C.c_void_p) if params is not None else None,
                                    C.c_uint64(params.size if params is not None else 0), losses, step_stats, C.byref(ms), stats,
                                    C.c_uint32(args.grid_after), grid.ctypes.data_as(C.c_void_p) if grid is not None else None, C.c_uint64(grid.size if grid is not None else 0),
-                                   bits.ctypes.data_as(C.c_void_p) if bits is not None else None, C.c_uint64(bits.size if bits is not None else 0))
+                                   bits.ctypes.data_as(C.c_void_p) if bits is not None else None, C.c_uint64(bits.size if bits is not None else 0),
+                                   step_frames.ctypes.data_as(C.c_void_p), motion.ctypes.data_as(C.c_void_p))
         ls = list(losses)
         if args.trace:
-            np.savez(args.trace, loss=np.array(ls, np.float32), stats=np.array(list(step_stats), np.uint32).reshape(n, 3),
+            np.savez(args.trace, loss=np.array(ls, np.float32), stats=np.array(list(step_stats), np.uint32).reshape(n, 3), frames=step_frames,
+                     motion=motion.view(np.float16).astype(np.float32),
                      **({"density_grid": grid, "bitfield": bits} if grid is not None else {}))
         print("\n" + json.dumps({"rc": rc, "ms_per_step": ms.value / max(args.steps, 1), "steps": args.steps, "warmup": args.warmup, "batch": args.batch,
                                  "views": args.views, "resolution": args.res, "loss_first": ls[0], "loss_after_warmup": ls[max(args.warmup - 1, 0)],

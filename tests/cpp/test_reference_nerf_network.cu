@@ -154,6 +154,129 @@ int main() {
 		EXPECT(std::fabs(v_layered - v_fused) <= 2e-2 * std::fmax(1.0, std::fabs(v_fused)));
 	}
 
+	// ---- a later frame of a dynamic sequence: the DeltaNetwork (transform_network.h) moves every sample ahead of the encoding
+	// (m_use_delta) and its twelve parameters get gradients (m_train_delta): reference objects against the fused kernels with a
+	// motion, and against the sums -> parameter gradients step of the motion's optimizer
+	{
+		const float t_[3] = {0.02f, -0.015f, 0.01f}, a1_[3] = {0.98f, 0.05f, -0.03f}, a2_[3] = {-0.04f, 1.02f, 0.06f};
+		std::vector<T> h_delta(12, __float2half(0.0f));  // transition [0..3], 6-D rotation [4..11]
+		for (int e = 0; e < 3; ++e) h_delta[e] = __float2half(t_[e]), h_delta[4 + e] = __float2half(a1_[e]), h_delta[7 + e] = __float2half(a2_[e]);
+		GPUMemory<T> delta, delta_grad(12);
+		delta.resize_and_copy_from_host(h_delta);
+		delta_grad.memset(0);
+		network->delta_network()->set_params(delta.data(), delta.data(), delta.data(), delta_grad.data());
+		network->m_use_delta = true;
+		network->m_train_delta = true;
+		GPUMatrix<T> moved_out{16, n, stream};
+		auto moved_ctx = network->forward(stream, input, &moved_out, false, false);
+		GPUMemory<float> sums(12), grad_out(12);
+		sums.memset(0);
+		neus2b_motion mo{};
+		mo.d_delta = (const uint16_t*)delta.data();
+		mo.d_sums = sums.data();
+		GPUMemory<T> fused_moved((size_t)n * 16);
+		EXPECT(neus2b_neus_forward_moved(&desc, (const uint16_t*)params.data(), -0.1f, n, nullptr, coords.data(), &mo, (uint16_t*)fused_moved.data(), stream) == 0);
+		CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+		{
+			auto a = to_host(moved_out.data(), (size_t)n * 16), b = to_host(fused_moved.data(), (size_t)n * 16), c = to_host(fused_out.data(), (size_t)n * 16);
+			size_t close = 0, total = 0, changed = 0, bad_row[11] = {};
+			for (uint32_t i = 0; i < n; ++i)
+				for (uint32_t r = 0; r < 11; ++r) {
+					const double p = __half2float(a[(size_t)i * 16 + r]), q = __half2float(b[(size_t)i * 16 + r]);
+					const bool ok = std::fabs(p - q) <= 4e-3 * std::fmax(1.0, std::fabs(q));
+					if (!ok) ++bad_row[r];
+					close += ok;
+					changed += std::fabs(q - __half2float(c[(size_t)i * 16 + r])) > 4e-3;
+					++total;
+				}
+			std::printf("moved forward: %zu of %zu outputs within 4e-3; the motion changes %zu of them\n", close, total, changed);
+			std::printf("  outside the tolerance per output row:");
+			for (int r = 0; r < 11; ++r) std::printf(" %zu", bad_row[r]);
+			std::printf("\n");
+			// The two motions give positions that differ by one ulp (checked below), and with this test's white-noise table
+			// (features of +-0.05 at a resolution of 4096) a normal moves by 1e-2 per ulp: the direct comparison is loose, the
+			// exact one is made below on coordinates that both sides share.
+			EXPECT((double)close >= 0.98 * (double)total);
+			EXPECT(changed > total / 20);
+		}
+		{  // the reference network without its DeltaNetwork on coordinates moved by neus2b_delta_forward: same positions on both sides
+			GPUMemory<float> pre((size_t)n * 7);
+			const float off[3] = {0.f, 0.f, 0.f};
+			EXPECT(neus2b_delta_forward((const uint16_t*)delta.data(), off, n, coords.data(), pre.data(), stream) == 0);
+			network->m_use_delta = false;
+			GPUMatrix<float> pre_in(pre.data(), 7, n);
+			GPUMatrix<T> pre_out{16, n, stream};
+			auto pre_ctx = network->forward(stream, pre_in, &pre_out, false, false);
+			network->m_use_delta = true;
+			CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+			auto a = to_host(moved_out.data(), (size_t)n * 16), b = to_host(fused_moved.data(), (size_t)n * 16), c = to_host(pre_out.data(), (size_t)n * 16);
+			size_t ref_vs_pre = 0, fused_vs_pre = 0;
+			for (uint32_t i = 0; i < n; ++i)
+				for (uint32_t r = 0; r < 11; ++r) {
+					const double p = __half2float(a[(size_t)i * 16 + r]), q = __half2float(b[(size_t)i * 16 + r]), w = __half2float(c[(size_t)i * 16 + r]);
+					ref_vs_pre += std::fabs(p - w) > 4e-3 * std::fmax(1.0, std::fabs(w));
+					fused_vs_pre += std::fabs(q - w) > 4e-3 * std::fmax(1.0, std::fabs(w));
+				}
+			{  // the DeltaNetwork alone against neus2b_delta_forward
+				std::vector<float> h6((size_t)n * 6);
+				for (uint32_t i = 0; i < n; ++i)
+					for (int e = 0; e < 3; ++e) h6[(size_t)i * 6 + e] = h_coords[(size_t)i * 7 + e], h6[(size_t)i * 6 + 3 + e] = h_coords[(size_t)i * 7 + 4 + e];
+				GPUMemory<float> in6;
+				in6.resize_and_copy_from_host(h6);
+				GPUMatrix<float> m6(in6.data(), 6, n);
+				GPUMatrix<float> o6{network->delta_network()->padded_output_width(), n, stream};
+				auto c6 = network->delta_network()->forward(stream, m6, &o6, false, false);
+				CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+				auto ho = to_host(o6.data(), (size_t)n * o6.m());
+				auto hp = to_host(pre.data(), (size_t)n * 7);
+				double worst_p = 0, worst_d = 0;
+				for (uint32_t i = 0; i < n; ++i)
+					for (int e = 0; e < 3; ++e) {
+						worst_p = std::fmax(worst_p, std::fabs(ho[(size_t)i * o6.m() + e] - hp[(size_t)i * 7 + e]));
+						worst_d = std::fmax(worst_d, std::fabs(ho[(size_t)i * o6.m() + 3 + e] - hp[(size_t)i * 7 + 4 + e]));
+					}
+				std::printf("moved forward: DeltaNetwork against neus2b_delta_forward: worst position difference %.3g, worst direction difference %.3g\n", worst_p, worst_d);
+				EXPECT(o6.m() == 6 && worst_p <= 2.5e-7 && worst_d <= 2.5e-7);
+			}
+			std::printf("moved forward: on shared moved coordinates %zu of %zu fused outputs are outside 4e-3 of the reference network's (%zu for the reference "
+			            "network with its own motion)\n", fused_vs_pre, (size_t)n * 11, ref_vs_pre);
+			EXPECT(fused_vs_pre <= (size_t)(0.001 * n * 11));
+		}
+		network->backward(stream, *moved_ctx, input, moved_out, dL_doutput, nullptr, false, EGradientMode::Overwrite);
+		fused_mlp.memset(0), fused_var.memset(0), fused_grid.memset(0);
+		EXPECT(neus2b_neus_train_moved(&desc, (const uint16_t*)params.data(), n, coords.data(), &mo, (const uint16_t*)dL.data(), n, fused_mlp.data(),
+		                               (uint16_t*)fused_grid.data(), fused_var.data(), stream) == 0);
+		EXPECT(neus2b_delta_optimizer_step(nullptr, sums.data(), nullptr, nullptr, nullptr, (uint16_t*)delta.data(), nullptr, nullptr, grad_out.data(), stream) == 0);
+		CUDA_CHECK_THROW(cudaStreamSynchronize(stream));
+		{
+			auto layered = to_host(gradients.data(), np);
+			auto fg = to_host(fused_grid.data(), n_grid);
+			std::vector<double> a, b;
+			for (size_t i = 0; i < n_grid; ++i) a.push_back(__half2float(layered[NEUS2B_MLP_N + i])), b.push_back(__half2float(fg[i]));
+			const double cg = cosine(a, b);
+			std::printf("moved backward: hash grid cosine %.6f\n", cg);
+			EXPECT(cg > 0.999);
+			auto ref_g = to_host(delta_grad.data(), 12);
+			auto mine_g = to_host(grad_out.data(), 12);
+			std::vector<double> rt, mt, rr, mr;
+			for (int e = 0; e < 3; ++e) rt.push_back(__half2float(ref_g[e])), mt.push_back(mine_g[e]);
+			for (int e = 0; e < 6; ++e) rr.push_back(__half2float(ref_g[4 + e])), mr.push_back(mine_g[4 + e]);
+			std::printf("moved backward: transition gradient reference (%.4g %.4g %.4g) fused (%.4g %.4g %.4g), cosine %.5f\n", rt[0], rt[1], rt[2], mt[0], mt[1], mt[2],
+			            cosine(rt, mt));
+			std::printf("moved backward: rotation gradient   reference (%.4g %.4g %.4g | %.4g %.4g %.4g)\n", rr[0], rr[1], rr[2], rr[3], rr[4], rr[5]);
+			std::printf("                                    fused     (%.4g %.4g %.4g | %.4g %.4g %.4g), cosine %.5f\n", mr[0], mr[1], mr[2], mr[3], mr[4], mr[5],
+			            cosine(rr, mr));
+			// (the reference keeps every sample's contribution and the sums in fp16)
+			EXPECT(cosine(rt, mt) > 0.995 && cosine(rr, mr) > 0.995);
+			double nr = 0, nm = 0;
+			for (int e = 0; e < 3; ++e) nr += rt[e] * rt[e], nm += mt[e] * mt[e];
+			for (int e = 0; e < 6; ++e) nr += rr[e] * rr[e], nm += mr[e] * mr[e];
+			EXPECT(std::fabs(std::sqrt(nr) - std::sqrt(nm)) <= 0.05 * std::sqrt(nm));
+		}
+		network->m_use_delta = false;
+		network->m_train_delta = false;
+	}
+
 	// ---- the SDF alone (marching cubes and the occupancy update call this)
 	{
 		GPUMatrix<T> sdf_out{16, n, stream};
