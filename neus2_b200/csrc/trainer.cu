@@ -711,6 +711,17 @@ extern "C" int neus2b_testbed_train_backward(neus2b_testbed* tb) {
 	return NEUS2B_OK;
 }
 
+// Counters::update_after_training for the step whose optimizer pass is pending, once; the event behind it is what the side
+// stream waits for before it touches the ray workspace or the cameras.
+static int run_tuner(neus2b_testbed* tb) {
+	if (tb->tuned) return NEUS2B_OK;
+	tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
+	N2B_CHECK_LAUNCH();
+	N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
+	tb->tuned = true;
+	return NEUS2B_OK;
+}
+
 // Between neus2b_testbed_train_backward and neus2b_testbed_train_optimizer_step: draws the NEXT step's rays and samples
 // now, so that this work overlaps a gradient exchange running on another stream (data-parallel training).  The batch
 // tuner of the pending step runs first (it reads the counters the generator is about to reuse).  Returns 1 and does
@@ -722,12 +733,9 @@ extern "C" int neus2b_testbed_train_pregenerate(neus2b_testbed* tb) {
 	const uint32_t next = next_canonical_step(tb, tb->training_step + (tb->step_pending ? 1u : 0u));
 	if (next % occupancy_skip(next) == 0) return 1;
 	if (tb->frame >= 1 && tb->training_step + (tb->step_pending ? 1u : 0u) == predict_steps(tb)) return 1;  // the phase change may clear the grid
-	if (tb->step_pending && !tb->tuned) {
-		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
-		N2B_CHECK_LAUNCH();
-		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
-		tb->tuned = true;
-	} else if (!tb->step_pending) {  // no optimizer pass to run next to: behind everything the training stream holds
+	if (tb->step_pending) {
+		if (int rc = run_tuner(tb)) return rc;
+	} else {  // no optimizer pass to run next to: behind everything the training stream holds
 		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
 	}
 	// on the side stream, behind the tuner (and behind a camera upload that went to the training stream)
@@ -813,10 +821,7 @@ static int optimizer_enqueue(neus2b_testbed* tb, bool want_stats) {
 		if (rc) return rc;
 		++tb->delta_adam_step;
 	}
-	if (!tb->tuned) {
-		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
-		N2B_CHECK_LAUNCH();
-	}
+	if (int rc2 = run_tuner(tb)) return rc2;
 	tb->tuned = false;
 	tb->step_pending = false;
 	++tb->training_step;
@@ -871,10 +876,8 @@ extern "C" int neus2b_testbed_train_step(neus2b_testbed* tb, const float* h_next
 	// the next step's cameras and samples go to the side stream, behind this step's tuner and next to its optimizer pass
 	if (h_next_xforms && h_next_focal && h_next_principal) {
 		if (!tb->ds.n_images) return NEUS2B_E_INVALID;
-		tune_kernel<<<1, 32, 0, tb->stream>>>(tb->state, tb->ws.d_counters, tb->target, tb->max_rays, tb->d_device_error);
-		N2B_CHECK_LAUNCH();
-		N2B_CHECK_CUDA(cudaEventRecord(tb->ev_tuned, tb->stream));
-		tb->tuned = true;
+		rc = run_tuner(tb);
+		if (rc) return rc;
 		N2B_CHECK_CUDA(cudaStreamWaitEvent(tb->gen_stream, tb->ev_tuned, 0));  // this step's loss pass has read the old cameras
 		rc = upload_cameras(tb, h_next_xforms, h_next_focal, h_next_principal, tb->gen_stream);
 		if (rc) return rc;
