@@ -136,6 +136,9 @@ class DataParallelTrainer:
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.grads = gradient_views(testbed, grid_n_params) if self.world > 1 else None
         self.stream = torch.cuda.ExternalStream(testbed.device_ptrs()["stream"])
+        # a second communicator for the small fp32 buffer(s): its collective then runs beside the 25 MB one instead of behind it
+        # (every rank creates the group here, in the same order)
+        self.small_group = dist.new_group() if self.world > 1 and dist.get_backend() == "nccl" else None
 
     def step(self, read_stats=False, next_cameras=None):
         """`next_cameras` = (xforms, focal, principal) host arrays for the step AFTER this one: uploaded behind this step's
@@ -161,13 +164,19 @@ class DataParallelTrainer:
         # the collectives start behind the backward kernels on NCCL's own stream; the library draws the next step's samples on
         # its second stream meanwhile (and on through the optimizer pass); the training stream waits for the summed gradients
         with torch.cuda.stream(self.stream):
-            works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
+            works = self._start_exchange()
             if next_cameras is not None:
                 self.tb.update_cameras(*next_cameras)
             self.tb.train_pregenerate()
             for w in works:
                 w.wait()
         return self.tb.optimizer_step(read_stats=read_stats)
+
+    def _start_exchange(self):
+        """Enqueues the step's collectives behind the current stream; returns their work handles."""
+        works = [dist.all_reduce(self.grads[0], op=dist.ReduceOp.SUM, async_op=True)]
+        works += [dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.small_group, async_op=True) for t in self.grads[1:]]
+        return works
 
     def probe_exchange(self, steps=20):
         """Where the gradient exchange sits in a step, by CUDA events on the training stream over `steps` real training steps:
@@ -183,10 +192,10 @@ class DataParallelTrainer:
             with torch.cuda.stream(self.stream):
                 e0.record()
                 if k % 2 == 0:  # exchange with nothing beside it
-                    for t in self.grads:
-                        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+                    for w in self._start_exchange():
+                        w.wait()
                 else:
-                    works = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in self.grads]
+                    works = self._start_exchange()
                     self.tb.train_pregenerate()
                     for w in works:
                         w.wait()
