@@ -169,7 +169,9 @@ extern "C" int neus2b_save_mesh(const char* path, uint32_t n_verts, const float*
 	};
 	auto unit_normal = [&](size_t i, float* n) {
 		const float* v = h_normals + i * 3;
-		const float z = v[0] * v[0] + v[1] * v[1] + v[2] * v[2];  // Eigen's normalized(): unchanged when the length is zero
+		// Eigen's normalized(): the three squares are summed as a0 + (a1 + a2), every component is divided by the root; unchanged
+		// when the length is zero
+		const float z = v[0] * v[0] + (v[1] * v[1] + v[2] * v[2]);
 		const float inv = z > 0.f ? sqrtf(z) : 1.f;
 		for (int e = 0; e < 3; ++e) n[e] = v[e] / inv;
 	};

@@ -1783,7 +1783,7 @@ int n2o_save_mesh(const char* path, uint32_t n_verts, const float* verts, const 
 	for (uint32_t i = 0; i < n_verts; ++i) {
 		float p[3], n[3];
 		const float* v = normals + (size_t)i * 3;
-		const float z = v[0] * v[0] + v[1] * v[1] + v[2] * v[2];
+		const float z = v[0] * v[0] + (v[1] * v[1] + v[2] * v[2]); /* Eigen sums three terms as a0 + (a1 + a2) */
 		for (int e = 0; e < 3; ++e) {
 			p[e] = (verts[(size_t)i * 3 + e] - nerf_offset[e]) / nerf_scale;
 			n[e] = z > 0.f ? v[e] / sqrtf(z) : v[e];
@@ -1801,7 +1801,7 @@ int n2o_save_mesh(const char* path, uint32_t n_verts, const float* verts, const 
 	if (!ply)
 		for (uint32_t i = 0; i < n_verts; ++i) {
 			const float* v = normals + (size_t)i * 3;
-			const float z = v[0] * v[0] + v[1] * v[1] + v[2] * v[2];
+			const float z = v[0] * v[0] + (v[1] * v[1] + v[2] * v[2]); /* Eigen sums three terms as a0 + (a1 + a2) */
 			const float s = z > 0.f ? sqrtf(z) : 1.f;
 			fprintf(f, "vn %0.5f %0.5f %0.5f\n", v[0] / s, v[1] / s, v[2] / s);
 		}

@@ -14,6 +14,7 @@
 #include <neural-graphics-primitives/nerf_loader.h>
 #include <neural-graphics-primitives/testbed.h>
 #include <tiny-cuda-nn/trainer.h>
+#include <neural-graphics-primitives/marching_cubes.h>
 
 #include <unistd.h>
 
@@ -144,6 +145,60 @@ int ref_load_dataset(const char* transforms_json, uint32_t max_images, uint32_t*
 		return 0;
 	} catch (const std::exception& e) {
 		std::fprintf(stderr, "ref_load_dataset: %s\n", e.what());
+		return -1;
+	}
+}
+
+/* The reference's marching cubes (marching_cubes_gpu, src/marching_cubes.cu:794-822) on a host lattice of rx * ry * rz values
+ * (x fastest) in the unit cube.  counts[2]: vertex slots (the reference rounds the count up to 128) and indices; vertices and
+ * indices are copied out while they fit.  Vertex numbering follows the arrival order of the reference's atomics. */
+int ref_marching_cubes(uint32_t rx, uint32_t ry, uint32_t rz, float thresh, const float* h_density, uint32_t* counts, float* h_verts, uint64_t verts_capacity,
+                       uint32_t* h_indices, uint64_t indices_capacity) {
+	try {
+		tcnn::GPUMemory<float> density;
+		density.resize_and_copy_from_host(h_density, (size_t)rx * ry * rz);
+		tcnn::GPUMemory<Eigen::Vector3f> verts;
+		tcnn::GPUMemory<uint32_t> indices;
+		marching_cubes_gpu(nullptr, BoundingBox{Eigen::Vector3f::Zero(), Eigen::Vector3f::Ones()}, Eigen::Vector3i((int)rx, (int)ry, (int)rz), thresh, density, verts,
+		                   indices);
+		CUDA_CHECK_THROW(cudaDeviceSynchronize());
+		counts[0] = (uint32_t)verts.size();
+		counts[1] = (uint32_t)indices.size();
+		if (verts.size() && verts.size() <= verts_capacity) CUDA_CHECK_THROW(cudaMemcpy(h_verts, verts.data(), sizeof(float) * 3 * verts.size(), cudaMemcpyDeviceToHost));
+		if (indices.size() && indices.size() <= indices_capacity)
+			CUDA_CHECK_THROW(cudaMemcpy(h_indices, indices.data(), sizeof(uint32_t) * indices.size(), cudaMemcpyDeviceToHost));
+		return 0;
+	} catch (const std::exception& e) {
+		std::fprintf(stderr, "ref_marching_cubes: %s\n", e.what());
+		return -1;
+	}
+}
+
+/* The reference's mesh post-processing on a given mesh: compute_mesh_1ring (src/marching_cubes.cu:720-738) -> h_ring [n][4],
+ * h_normals [n][3]; then save_mesh (:824-976, no texture unwrap) with the given normals and colours to every file name that is
+ * not NULL (the extension selects OBJ or PLY). */
+int ref_mesh_postprocess(uint32_t n_verts, const float* h_verts, uint32_t n_indices, const uint32_t* h_indices, float* h_ring, float* h_normals,
+                         const float* h_save_normals, const float* h_save_colors, const char* file_a, const char* file_b, float nerf_scale,
+                         const float* nerf_offset, int invert_normals) {
+	try {
+		tcnn::GPUMemory<Eigen::Vector3f> verts(n_verts), normals, save_normals(n_verts), colors(n_verts);
+		tcnn::GPUMemory<Eigen::Vector4f> ring;
+		tcnn::GPUMemory<uint32_t> indices(n_indices);
+		CUDA_CHECK_THROW(cudaMemcpy(verts.data(), h_verts, sizeof(float) * 3 * n_verts, cudaMemcpyHostToDevice));
+		CUDA_CHECK_THROW(cudaMemcpy(indices.data(), h_indices, sizeof(uint32_t) * n_indices, cudaMemcpyHostToDevice));
+		compute_mesh_1ring(verts, indices, ring, normals);
+		CUDA_CHECK_THROW(cudaDeviceSynchronize());
+		if (ring.size() < n_verts || normals.size() < n_verts) return -2;
+		CUDA_CHECK_THROW(cudaMemcpy(h_ring, ring.data(), sizeof(float) * 4 * n_verts, cudaMemcpyDeviceToHost));
+		CUDA_CHECK_THROW(cudaMemcpy(h_normals, normals.data(), sizeof(float) * 3 * n_verts, cudaMemcpyDeviceToHost));
+		CUDA_CHECK_THROW(cudaMemcpy(save_normals.data(), h_save_normals, sizeof(float) * 3 * n_verts, cudaMemcpyHostToDevice));
+		CUDA_CHECK_THROW(cudaMemcpy(colors.data(), h_save_colors, sizeof(float) * 3 * n_verts, cudaMemcpyHostToDevice));
+		const Eigen::Vector3f offset(nerf_offset[0], nerf_offset[1], nerf_offset[2]);
+		if (file_a) save_mesh(verts, save_normals, colors, indices, file_a, false, nerf_scale, offset, invert_normals != 0);
+		if (file_b) save_mesh(verts, save_normals, colors, indices, file_b, false, nerf_scale, offset, invert_normals != 0);
+		return 0;
+	} catch (const std::exception& e) {
+		std::fprintf(stderr, "ref_mesh_postprocess: %s\n", e.what());
 		return -1;
 	}
 }

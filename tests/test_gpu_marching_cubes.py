@@ -6,6 +6,8 @@ import numpy as np
 import pytest
 import torch
 
+from util import record
+
 pytestmark = pytest.mark.gpu
 
 
@@ -153,3 +155,44 @@ def test_testbed_sharded_mesh_matches_single_pass(oracle):
     assert np.array_equal(v.view(np.uint32), v_ref.cpu().numpy().view(np.uint32))
     assert np.array_equal(i, i_ref.cpu().numpy().view(np.uint32))
     tb.close()
+
+
+@pytest.mark.parametrize("kind,res", [("sphere", (40, 36, 44)), ("torus_box", (64, 64, 64)), ("noise", (17, 13, 9))])
+def test_marching_cubes_equals_the_reference_kernels(kind, res):
+    """marching_cubes_gpu of the reference (src/marching_cubes.cu:794-822, its gen_vertices / gen_faces kernels, linked unmodified
+    into oracle/_ref/libref_testbed.so) against neus2b_marching_cubes with the reference's case table on the same lattice.  The
+    reference numbers vertices in the arrival order of its atomics: vertices are matched by position (nearest neighbour, which
+    must be a bijection within 1e-6), then the two triangle lists must be the same set, vertex order inside a triangle included."""
+    import ctypes as C
+    import os
+    from scipy.spatial import cKDTree
+    from neus2_b200 import ops
+    lib_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libref_testbed.so")
+    if not os.path.exists(lib_path):
+        pytest.skip("oracle/_ref/libref_testbed.so was not built: no reference checkout at build time")
+    tab = table("reference")
+    sdf = sdf_field(res, kind)  # [rz][ry][rx]
+    rz, ry, rx = sdf.shape
+    lib = C.CDLL(lib_path)
+    counts = np.zeros(2, np.uint32)
+    cap_v, cap_i = 1 << 20, 1 << 22
+    rv, ri = np.zeros((cap_v, 3), np.float32), np.zeros(cap_i, np.uint32)
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    rc = lib.ref_marching_cubes(C.c_uint32(rx), C.c_uint32(ry), C.c_uint32(rz), C.c_float(0.0), ptr(np.ascontiguousarray(sdf)), ptr(counts), ptr(rv),
+                                C.c_uint64(cap_v), ptr(ri), C.c_uint64(cap_i))
+    assert rc == 0 and counts[0] <= cap_v and counts[1] <= cap_i
+    ri = ri[:counts[1]]
+    n_ref = int(ri.max()) + 1 if ri.size else 0
+    rv = rv[:n_ref]
+    v, i = ops.marching_cubes(torch.from_numpy(sdf).cuda(), tri_table=torch.from_numpy(tab))
+    torch.cuda.synchronize()
+    v, i = v.cpu().numpy(), i.cpu().numpy().view(np.uint32)
+    assert v.shape[0] == n_ref and (n_ref + 127) // 128 * 128 == counts[0], "vertex count (the reference rounds its buffer up to 128)"
+    assert i.shape[0] == ri.shape[0], "index count"
+    dist, nearest = cKDTree(v).query(rv)
+    assert dist.max() <= 1e-6 and np.unique(nearest).size == n_ref, "every reference vertex has its own counterpart"
+    ref_tris = nearest[ri.astype(np.int64)].reshape(-1, 3)
+    mine_tris = i.astype(np.int64).reshape(-1, 3)
+    order = lambda t: t[np.lexsort((t[:, 2], t[:, 1], t[:, 0]))]
+    assert np.array_equal(order(ref_tris), order(mine_tris)), "the same triangles, corner order included"
+    record("ref_kernel_marching_cubes_%s" % kind, vertices=n_ref, triangles=int(mine_tris.shape[0]), worst_vertex_distance=float(dist.max()))

@@ -63,3 +63,42 @@ def test_compute_and_save_mesh(gpu, oracle, trained, tmp_path):
     ref_n, _ = oracle.mesh_1ring(mesh["verts"], mesh["indices"])
     np.testing.assert_allclose(mesh["normals"], ref_n, rtol=1e-3, atol=1e-9)
     assert 0.05 < mesh["colors"].mean() < 0.95
+
+
+def test_mesh_postprocessing_equals_the_reference(gpu, tmp_path):
+    """compute_mesh_1ring and save_mesh of the reference (src/marching_cubes.cu:720-738, :824-976, linked unmodified into
+    oracle/_ref/libref_testbed.so) on the same mesh: 1-ring sums and normals within the rounding of float atomics in another order,
+    and -- given the same normals and colours -- the OBJ and PLY files byte for byte."""
+    import ctypes as C
+    import os
+    L, ops = gpu
+    lib_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libref_testbed.so")
+    if not os.path.exists(lib_path):
+        pytest.skip("oracle/_ref/libref_testbed.so was not built: no reference checkout at build time")
+    lib = C.CDLL(lib_path)
+    verts, idx = icosphere(4)
+    verts = np.ascontiguousarray(verts * 0.3 + 0.5, np.float32)
+    idx = np.ascontiguousarray(idx).view(np.uint32)
+    n = verts.shape[0]
+    rng = np.random.default_rng(5)
+    colors = rng.uniform(0, 1, (n, 3)).astype(np.float32)
+    ring, normals = np.zeros((n, 4), np.float32), np.zeros((n, 3), np.float32)
+    mine_n, mine_r = ops.mesh_1ring(torch.from_numpy(verts).cuda(), torch.from_numpy(idx.view(np.int32)).cuda(), want_ring=True)
+    mine_n, mine_r = mine_n.cpu().numpy(), mine_r.cpu().numpy()
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    offset = np.array([0.5, 0.5, 0.5], np.float32)
+    for invert in (0, 1):
+        obj, ply = tmp_path / f"ref{invert}.obj", tmp_path / f"ref{invert}.ply"
+        rc = lib.ref_mesh_postprocess(C.c_uint32(n), ptr(verts), C.c_uint32(idx.size), ptr(idx), ptr(ring), ptr(normals), ptr(mine_n), ptr(colors),
+                                      str(obj).encode(), str(ply).encode(), C.c_float(0.33), ptr(offset), C.c_int(invert))
+        assert rc == 0
+        np.testing.assert_allclose(mine_n, normals, rtol=1e-4, atol=1e-8)
+        np.testing.assert_allclose(mine_r, ring, rtol=1e-5, atol=1e-6)
+        for ref_file in (obj, ply):
+            mine_file = tmp_path / ("mine%d%s" % (invert, ref_file.suffix))
+            ops.save_mesh(mine_file, verts, mine_n, colors, idx, nerf_scale=0.33, nerf_offset=(0.5, 0.5, 0.5), invert_normals=bool(invert))
+            a, b = mine_file.read_bytes(), ref_file.read_bytes()
+            if a != b:
+                la, lb = a.split(b"\n"), b.split(b"\n")
+                bad = [(k, x, y) for k, (x, y) in enumerate(zip(la, lb)) if x != y]
+                raise AssertionError("%s: %d of %d lines differ, first: line %d %r (this repository) %r (reference)" % (ref_file.name, len(bad), len(lb), *bad[0]))
