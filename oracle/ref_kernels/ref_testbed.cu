@@ -203,4 +203,25 @@ int ref_mesh_postprocess(uint32_t n_verts, const float* h_verts, uint32_t n_indi
 	}
 }
 
+/* Testbed::get_density_on_grid (src/testbed_nerf.cu:4082-4135; the lattice marching cubes runs on) of a testbed built like in
+ * ref_testbed_train, with the given parameters and no training step: h_out [rz][ry][rx] floats over the unit cube. */
+int ref_testbed_sdf_grid(const char* workdir, const char* transforms_json, const char* network_config_json, const float* h_params, uint64_t n_params,
+                         uint32_t rx, uint32_t ry, uint32_t rz, float* h_out) {
+	try {
+		if (chdir(workdir) != 0) return -3;
+		Testbed testbed{ETestbedMode::Nerf};
+		testbed.load_training_data(transforms_json);
+		testbed.reload_network_from_json(nlohmann::json::parse(network_config_json, nullptr, true, true), "");
+		if (n_params != testbed.m_trainer->n_params()) return -4;
+		testbed.m_trainer->set_params_full_precision(h_params, n_params);
+		tcnn::GPUMemory<float> grid = testbed.get_density_on_grid(Eigen::Vector3i((int)rx, (int)ry, (int)rz), BoundingBox{Eigen::Vector3f::Zero(), Eigen::Vector3f::Ones()});
+		CUDA_CHECK_THROW(cudaDeviceSynchronize());
+		CUDA_CHECK_THROW(cudaMemcpy(h_out, grid.data(), sizeof(float) * (size_t)rx * ry * rz, cudaMemcpyDeviceToHost));
+		return 0;
+	} catch (const std::exception& e) {
+		std::fprintf(stderr, "ref_testbed_sdf_grid: %s\n", e.what());
+		return -1;
+	}
+}
+
 }  // extern "C"

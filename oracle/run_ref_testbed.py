@@ -76,6 +76,8 @@ def main():
     ap.add_argument("--params", default=None, help=".npy file of full-precision initial parameters that replace the drawn ones")
     ap.add_argument("--hyper", default=None, help="json object merged into the network configuration's hyperparams (and, under the key "
                     "\"optimizer_leaf\", into the innermost optimizer)")
+    ap.add_argument("--sdf-grid", default=None, help="with --params and --sdf-res: evaluate Testbed::get_density_on_grid without training and write it to this .npy file")
+    ap.add_argument("--sdf-res", type=int, default=64)
     ap.add_argument("--load-only", default=None, help="only run the reference's dataset loader on --data and write what it returns to this .npz file")
     ap.add_argument("--trace", default=None, help="write per-step rays_per_batch / measured batch sizes / loss to this .npz file")
     ap.add_argument("--grid-after", type=int, default=0, help="with --trace: also store the occupancy grid's densities after this many steps")
@@ -104,6 +106,16 @@ def main():
         init = S.init_params(L.grid_n_params(L.grid_desc()), seed=1337)
         np.savetxt(os.path.join(work, "utils", "mlp_weights.txt"), init[:4096].astype(np.float32), fmt="%.9g")
         lib = C.CDLL(LIB)
+        if args.sdf_grid:
+            params = np.ascontiguousarray(np.load(args.params), np.float32)
+            r = args.sdf_res
+            out = np.zeros((r, r, r), np.float32)
+            rc = lib.ref_testbed_sdf_grid(work.encode(), transforms.encode(), json.dumps(merged_config(json.loads(args.hyper) if args.hyper else None)).encode(),
+                                          params.ctypes.data_as(C.c_void_p), C.c_uint64(params.size), C.c_uint32(r), C.c_uint32(r), C.c_uint32(r),
+                                          out.ctypes.data_as(C.c_void_p))
+            np.save(args.sdf_grid, out)
+            print("\n" + json.dumps({"rc": rc, "sdf_res": r}), flush=True)
+            return 0 if rc == 0 else 1
         n = args.warmup + args.steps
         losses, ms, stats, step_stats = (C.c_float * n)(), C.c_float(0), (C.c_uint32 * 4)(), (C.c_uint32 * (3 * n))()
         params = np.ascontiguousarray(np.load(args.params), np.float32) if args.params else None

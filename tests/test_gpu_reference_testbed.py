@@ -216,3 +216,39 @@ def test_dynamic_sequence_follows_the_reference_loop(tmp_path):
     in_step = _lockstep(mine_i, t["stats"].astype(np.int64), [m[3] for m in mine], t["loss"], restart_steps=(first,))
     assert in_step >= first + motion_only + 8, "the loops left each other after %d steps" % in_step
     record("loop_parity_sequence", steps_in_lockstep=in_step, steps=n)
+
+
+def test_sdf_lattice_equals_the_reference_testbed(tmp_path):
+    """Testbed::get_density_on_grid of the reference (the lattice its marching cubes runs on: lattice positions, order, and the SDF
+    through its NerfNetwork over the layered kernels) against neus2b_testbed_sdf_grid with the same parameters."""
+    _need_ref()
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import run_ref_testbed as R
+    from neus2_b200 import _lib as L
+    from neus2_b200 import synthetic as S
+    from neus2_b200 import testbed as T
+    from util import record
+    scene = S.render_sphere_views(4, 64, 64, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
+    tr = S.write_transforms_dataset(scene, str(tmp_path / "data"))
+    tb = T.Testbed.from_network_config(R.network_config())
+    tb.load_training_data_from_json(tr)
+    ng = L.grid_n_params(tb.config.grid)
+    p0 = S.init_params(ng, seed=1337)
+    rng = np.random.default_rng(9)
+    p0[12288:12288 + ng] = rng.uniform(-2e-2, 2e-2, ng)  # a table that matters
+    p0[:3072].reshape(64, 48)[:, 3:35] = rng.normal(0, 0.05, (64, 32))
+    tb.set_params(p0)
+    np.save(str(tmp_path / "p0.npy"), tb.get_params())
+    res = 48
+    mine = tb.sdf_grid(res, use_ema=False).cpu().numpy()
+    tb.close()
+    out = _run_ref(["--data", str(tmp_path / "data"), "--params", str(tmp_path / "p0.npy"), "--sdf-grid", str(tmp_path / "sdf.npy"), "--sdf-res", str(res)])
+    assert out["rc"] == 0
+    ref = np.load(str(tmp_path / "sdf.npy"))
+    assert mine.shape == ref.shape == (res, res, res)
+    err = np.abs(mine - ref)
+    record("ref_testbed_sdf_lattice", max_abs_err=float(err.max()), mean_abs_err=float(err.mean()), std=float(ref.std()))
+    assert ref.std() > 0.05 and (ref < 0).any() and (ref > 0).any()
+    assert err.max() <= 4e-3 * max(1.0, float(np.abs(ref).max())), err.max()
+    assert (np.sign(mine) == np.sign(ref)).mean() > 0.999
