@@ -87,10 +87,11 @@ def save_snapshot(tb, path, include_optimizer_state=False):
                    "density_rng": [int(st.density_rng.state), int(st.density_rng.inc)]},
     }
     # dynamic sequences (NerfNetwork::save_global_movement / save_local_movement, nerf_network.h:1169-1196, 1231-1235): the
-    # accumulated movement (9 + 3 fp16 values) and the current frame's motion parameters (8 + 4 fp16 values)
+    # accumulated movement as the reference's buffers hold it (rotation: 12 fp16 slots, the matrix row-major in the first nine;
+    # transition: 4 slots) and the current frame's motion parameters (8 + 4 fp16 values)
     frame, R_acc, t_acc, delta = tb.movement()
-    snap["rotation"] = R_acc.astype(np.float16).tobytes()
-    snap["transition"] = t_acc.astype(np.float16).tobytes()
+    snap["rotation"] = np.concatenate([R_acc.reshape(9), np.zeros(3)]).astype(np.float16).tobytes()
+    snap["transition"] = np.concatenate([t_acc.reshape(3), np.zeros(1)]).astype(np.float16).tobytes()
     snap["local_rotation"] = delta[4:12].astype(np.float16).tobytes()
     snap["local_transition"] = delta[0:4].astype(np.float16).tobytes()
     snap["neus2b"]["frame"] = int(frame)
@@ -143,8 +144,8 @@ def load_snapshot(tb, path):
     elif grid.size != 0:  # size 0: a model that was never trained
         raise ValueError("Incompatible number of grid cascades.")
     if "rotation" in snap:  # load_global_movement / load_local_movement (nerf_network.h:1198-1261)
-        R_acc = np.frombuffer(snap["rotation"], np.float16).astype(np.float32)
-        t_acc = np.frombuffer(snap["transition"], np.float16).astype(np.float32)
+        R_acc = np.frombuffer(snap["rotation"], np.float16).astype(np.float32)[:9]
+        t_acc = np.frombuffer(snap["transition"], np.float16).astype(np.float32)[:3]
         if "local_movement_fp32" in extra:
             delta = np.frombuffer(extra["local_movement_fp32"], np.float32)
         else:

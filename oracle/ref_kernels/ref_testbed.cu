@@ -21,6 +21,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
+#include <vector>
 
 using namespace ngp;
 
@@ -220,6 +221,48 @@ int ref_testbed_sdf_grid(const char* workdir, const char* transforms_json, const
 		return 0;
 	} catch (const std::exception& e) {
 		std::fprintf(stderr, "ref_testbed_sdf_grid: %s\n", e.what());
+		return -1;
+	}
+}
+
+/* Testbed::save_snapshot / load_snapshot (src/testbed.cu:3134-3244).  With load_path the testbed takes network, parameters,
+ * occupancy grid and counters from that file (network_config_json and h_params are not used); otherwise it is built from the
+ * configuration and h_params and trained for n_steps.  With save_path the state is then written there (no optimizer state).
+ * h_sdf [res]^3: get_density_on_grid afterwards; info[4]: training step, rays per batch, measured batch size, occupied cells of the
+ * finest level. */
+int ref_testbed_snapshot(const char* workdir, const char* transforms_json, const char* network_config_json, const float* h_params, uint64_t n_params,
+                         uint32_t n_steps, const char* load_path, const char* save_path, uint32_t res, float* h_sdf, uint32_t* info) {
+	try {
+		if (chdir(workdir) != 0) return -3;
+		Testbed testbed{ETestbedMode::Nerf};
+		testbed.load_training_data(transforms_json);
+		if (load_path) {
+			testbed.load_snapshot(load_path);
+		} else {
+			testbed.reload_network_from_json(nlohmann::json::parse(network_config_json, nullptr, true, true), "");
+			if (n_params != testbed.m_trainer->n_params()) return -4;
+			testbed.m_trainer->set_params_full_precision(h_params, n_params);
+			testbed.m_train = true;
+			for (uint32_t i = 0; i < n_steps; ++i) testbed.frame();
+			testbed.m_train = false;
+		}
+		CUDA_CHECK_THROW(cudaDeviceSynchronize());
+		if (save_path) testbed.save_snapshot(save_path, false);
+		tcnn::GPUMemory<float> grid = testbed.get_density_on_grid(Eigen::Vector3i::Constant((int)res), BoundingBox{Eigen::Vector3f::Zero(), Eigen::Vector3f::Ones()});
+		CUDA_CHECK_THROW(cudaDeviceSynchronize());
+		CUDA_CHECK_THROW(cudaMemcpy(h_sdf, grid.data(), sizeof(float) * (size_t)res * res * res, cudaMemcpyDeviceToHost));
+		info[0] = testbed.m_training_step;
+		info[1] = testbed.m_nerf.training.counters_rgb.rays_per_batch;
+		info[2] = testbed.m_nerf.training.counters_rgb.measured_batch_size;
+		std::vector<uint8_t> bits(NERF_GRIDSIZE() * NERF_GRIDSIZE() * NERF_GRIDSIZE() / 8);
+		info[3] = 0;
+		if (testbed.m_nerf.density_grid_bitfield.size() >= bits.size()) {
+			CUDA_CHECK_THROW(cudaMemcpy(bits.data(), testbed.m_nerf.density_grid_bitfield.data(), bits.size(), cudaMemcpyDeviceToHost));
+			for (uint8_t b : bits) info[3] += (uint32_t)__builtin_popcount(b);
+		}
+		return 0;
+	} catch (const std::exception& e) {
+		std::fprintf(stderr, "ref_testbed_snapshot: %s\n", e.what());
 		return -1;
 	}
 }

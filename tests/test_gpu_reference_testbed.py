@@ -252,3 +252,55 @@ def test_sdf_lattice_equals_the_reference_testbed(tmp_path):
     assert ref.std() > 0.05 and (ref < 0).any() and (ref > 0).any()
     assert err.max() <= 4e-3 * max(1.0, float(np.abs(ref).max())), err.max()
     assert (np.sign(mine) == np.sign(ref)).mean() > 0.999
+
+
+def test_snapshots_load_across_the_two_testbeds(tmp_path):
+    """Testbed::save_snapshot / load_snapshot of the reference (src/testbed.cu:3134-3244) against neus2_b200.snapshot, both ways:
+    the reference trains 40 steps and saves, this repository loads the file (same SDF lattice, step and tuner state) and trains
+    on; then this repository saves and the reference's load_snapshot takes the file (same lattice, step and tuner state)."""
+    _need_ref()
+    import ctypes as C
+    import numpy as np
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import run_ref_testbed as R
+    from neus2_b200 import _lib as L
+    from neus2_b200 import synthetic as S
+    from neus2_b200 import testbed as T
+    from util import record
+    res, batch = 40, 1 << 16
+    scene = S.render_sphere_views(8, 96, 96, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
+    S.write_transforms_dataset(scene, str(tmp_path / "data"))
+    common = ["--data", str(tmp_path / "data"), "--batch", str(batch), "--sdf-res", str(res)]
+    tb = T.Testbed.from_network_config(R.network_config(), batch_size=batch)
+    tb.load_training_data_from_json(str(tmp_path / "data" / "transforms.json"))
+    tb.set_params(S.init_params(L.grid_n_params(tb.config.grid), seed=1337))
+    np.save(str(tmp_path / "p0.npy"), tb.get_params())
+
+    def occupied(t):
+        bits = torch.empty(128 ** 3 // 8, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        C.CDLL("libcudart.so.12").cudaMemcpy(C.c_void_p(bits.data_ptr()), C.c_void_p(t.device_ptrs()["bitfield"]), C.c_size_t(bits.numel()), 3)
+        return int(np.unpackbits(bits.cpu().numpy()).sum())
+
+    saved = _run_ref(common + ["--params", str(tmp_path / "p0.npy"), "--steps", "40", "--snapshot-save", str(tmp_path / "ref.msgpack"), "--sdf-grid",
+                               str(tmp_path / "ref_sdf.npy")])
+    assert saved["rc"] == 0 and saved["training_step"] == 40
+    tb.load_snapshot(str(tmp_path / "ref.msgpack"))
+    ref_sdf = np.load(str(tmp_path / "ref_sdf.npy"))
+    err_in = float(np.abs(tb.sdf_grid(res, use_ema=True).cpu().numpy() - ref_sdf).max())
+    assert err_in <= 1e-3 and ref_sdf.std() > 0.02 and (ref_sdf < 0).any() and (ref_sdf > 0).any()
+    assert tb.training_step == 40 and tb.stats.rays_per_batch == saved["rays_per_batch"]
+    assert abs(occupied(tb) - saved["occupied_cells"]) <= 0.002 * saved["occupied_cells"]  # (the file holds the grid in fp16)
+    st = tb.train(5)
+    assert st.training_step == 45 and np.isfinite(st.loss)
+    tb.save_snapshot(str(tmp_path / "mine.msgpack"))
+    mine_sdf = tb.sdf_grid(res, use_ema=True).cpu().numpy()
+    loaded = _run_ref(common + ["--snapshot-load", str(tmp_path / "mine.msgpack"), "--sdf-grid", str(tmp_path / "ref2_sdf.npy")])
+    assert loaded["rc"] == 0 and loaded["training_step"] == 45 and loaded["rays_per_batch"] == st.rays_per_batch
+    assert loaded["measured_batch_size"] == st.measured_batch_size
+    err_out = float(np.abs(mine_sdf - np.load(str(tmp_path / "ref2_sdf.npy"))).max())
+    assert err_out <= 1e-3
+    assert abs(occupied(tb) - loaded["occupied_cells"]) <= 0.002 * loaded["occupied_cells"]
+    record("snapshot_cross_load", sdf_err_reference_to_this=err_in, sdf_err_this_to_reference=err_out)
+    tb.close()
