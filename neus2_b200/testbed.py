@@ -297,19 +297,45 @@ class Testbed:
         L.check(L.lib().neus2b_testbed_profile(self._h, C.c_uint32(max_steps), C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
-    def compute_marching_cubes_mesh(self, resolution=256, thresh=0.0, tri_table=None, use_ema=True):
-        """Testbed::compute_and_save_marching_cubes_mesh without the file writer (src/testbed.cu:298): SDF on the lattice with the
-        EMA parameters, then marching cubes at `thresh`.  Returns (verts, indices) as CUDA tensors."""
-        from . import ops
-        return ops.marching_cubes(self.sdf_grid(resolution, use_ema=use_ema), tri_table=tri_table, thresh=thresh)
+    @staticmethod
+    def marching_cubes_resolution(resolution):
+        """Testbed::marching_cubes rounds every axis up to a multiple of 16 (src/testbed_nerf.cu:4161-4163)."""
+        res = [int(r) for r in (resolution if hasattr(resolution, "__len__") else (resolution,) * 3)]
+        return [(r + 15) // 16 * 16 for r in res]
 
-    def compute_and_save_marching_cubes_mesh(self, filename, resolution=256, thresh=0.0, tri_table=None, use_ema=True,
-                                             nerf_scale=1.0, nerf_offset=(0.0, 0.0, 0.0), invert_normals=False):
-        """Testbed::compute_and_save_marching_cubes_mesh (src/testbed.cu:298-306; python_api.cu:352): marching cubes on the
-        SDF lattice, 1-ring normals, vertex colours from the network, OBJ or PLY file.  Returns the mesh as host arrays."""
+    def compute_marching_cubes_mesh(self, resolution=256, thresh=0.0, tri_table=None, use_ema=True):
+        """Testbed::marching_cubes (src/testbed_nerf.cu:4160-4181): SDF on the lattice (every axis rounded up to a multiple of 16)
+        with the EMA parameters, marching cubes at `thresh`, and -- on a later frame of a dynamic sequence -- the vertices taken
+        from the canonical frame to the current one by the accumulated movement, v <- R_acc^-1 (v - t_acc)
+        (transform_mesh_with_6d, src/testbed_nerf.cu:98-128).  Returns (verts, indices) as CUDA tensors."""
         import torch
         from . import ops
+        verts, indices = ops.marching_cubes(self.sdf_grid(self.marching_cubes_resolution(resolution), use_ema=use_ema), tri_table=tri_table, thresh=thresh)
+        frame, R_acc, t_acc, _ = self.movement()
+        if frame >= 1 and (np.any(R_acc != np.eye(3, dtype=np.float32).reshape(R_acc.shape)) or np.any(t_acc != 0)):
+            R = torch.from_numpy(np.ascontiguousarray(R_acc, np.float32).reshape(3, 3)).to(verts.device)
+            t = torch.from_numpy(np.ascontiguousarray(t_acc, np.float32).reshape(3)).to(verts.device)
+            verts = ((verts - t) @ torch.linalg.inv(R).T).contiguous()
+        return verts, indices
+
+    def compute_and_save_marching_cubes_mesh(self, filename, resolution=256, thresh=0.0, tri_table=None, use_ema=True,
+                                             nerf_scale=None, nerf_offset=None, invert_normals=None):
+        """Testbed::compute_and_save_marching_cubes_mesh (src/testbed.cu:298-306; python_api.cu:352): marching cubes on the
+        SDF lattice, 1-ring normals, vertex colours from the network, OBJ or PLY file.  Scale, offset and the normals' side default
+        to the loaded dataset's `scale`, `offset` and `from_na`, which is what the reference passes to its writer (1, 0 and False
+        without a dataset description).  Returns the mesh as host arrays."""
+        import torch
+        from . import ops
+        ds = getattr(self, "dataset", None) or {}
+        nerf_scale = float(ds.get("scale", 1.0)) if nerf_scale is None else nerf_scale
+        nerf_offset = tuple(ds.get("offset", (0.0, 0.0, 0.0))) if nerf_offset is None else nerf_offset
+        invert_normals = bool(ds.get("from_na", False)) if invert_normals is None else invert_normals
         verts, indices = self.compute_marching_cubes_mesh(resolution, thresh, tri_table, use_ema)
+        # the reference sizes its vertex buffer up to a multiple of 128 (src/marching_cubes.cu:813) and writes the unused entries
+        # too: vertices at the origin that no face refers to.  The file gets them here as well; compute_marching_cubes_mesh does not.
+        pad = (-verts.shape[0]) % 128
+        if pad:
+            verts = torch.cat([verts, torch.zeros((pad, 3), dtype=verts.dtype, device=verts.device)])
         ptrs = self.device_ptrs()
         normals = ops.mesh_1ring(verts, indices)
         colors = ops.mesh_vertex_colors(self.config.grid, ptrs["params_ema" if use_ema else "params"], self.config.sdf_bias, verts)

@@ -229,9 +229,9 @@ int ref_testbed_sdf_grid(const char* workdir, const char* transforms_json, const
  * occupancy grid and counters from that file (network_config_json and h_params are not used); otherwise it is built from the
  * configuration and h_params and trained for n_steps.  With save_path the state is then written there (no optimizer state).
  * h_sdf [res]^3: get_density_on_grid afterwards; info[4]: training step, rays per batch, measured batch size, occupied cells of the
- * finest level. */
+ * finest level.  mesh_path (optional): the reference's mesh export of that state (OBJ or PLY by extension). */
 int ref_testbed_snapshot(const char* workdir, const char* transforms_json, const char* network_config_json, const float* h_params, uint64_t n_params,
-                         uint32_t n_steps, const char* load_path, const char* save_path, uint32_t res, float* h_sdf, uint32_t* info) {
+                         uint32_t n_steps, const char* load_path, const char* save_path, uint32_t res, float* h_sdf, uint32_t* info, const char* mesh_path) {
 	try {
 		if (chdir(workdir) != 0) return -3;
 		Testbed testbed{ETestbedMode::Nerf};
@@ -251,6 +251,8 @@ int ref_testbed_snapshot(const char* workdir, const char* transforms_json, const
 		tcnn::GPUMemory<float> grid = testbed.get_density_on_grid(Eigen::Vector3i::Constant((int)res), BoundingBox{Eigen::Vector3f::Zero(), Eigen::Vector3f::Ones()});
 		CUDA_CHECK_THROW(cudaDeviceSynchronize());
 		CUDA_CHECK_THROW(cudaMemcpy(h_sdf, grid.data(), sizeof(float) * (size_t)res * res * res, cudaMemcpyDeviceToHost));
+		// Testbed::compute_and_save_marching_cubes_mesh (src/testbed.cu:298-306) at the same resolution, threshold 0
+		if (mesh_path) testbed.compute_and_save_marching_cubes_mesh(mesh_path, Eigen::Vector3i::Constant((int)res), BoundingBox{}, 0.0f, false);
 		info[0] = testbed.m_training_step;
 		info[1] = testbed.m_nerf.training.counters_rgb.rays_per_batch;
 		info[2] = testbed.m_nerf.training.counters_rgb.measured_batch_size;

@@ -78,6 +78,7 @@ def main():
                     "\"optimizer_leaf\", into the innermost optimizer)")
     ap.add_argument("--snapshot-save", default=None, help="snapshot mode: build from --params, train --steps, save a snapshot here")
     ap.add_argument("--snapshot-load", default=None, help="snapshot mode: take everything from this snapshot instead")
+    ap.add_argument("--mesh", default=None, help="snapshot mode: also run Testbed::compute_and_save_marching_cubes_mesh at --sdf-res into this file")
     ap.add_argument("--sdf-grid", default=None, help="with --params and --sdf-res: evaluate Testbed::get_density_on_grid without training and write it to this .npy file")
     ap.add_argument("--sdf-res", type=int, default=64)
     ap.add_argument("--load-only", default=None, help="only run the reference's dataset loader on --data and write what it returns to this .npz file")
@@ -108,14 +109,14 @@ def main():
         init = S.init_params(L.grid_n_params(L.grid_desc()), seed=1337)
         np.savetxt(os.path.join(work, "utils", "mlp_weights.txt"), init[:4096].astype(np.float32), fmt="%.9g")
         lib = C.CDLL(LIB)
-        if args.snapshot_save or args.snapshot_load:
+        if args.snapshot_save or args.snapshot_load or args.mesh:
             params = np.ascontiguousarray(np.load(args.params), np.float32) if args.params else np.zeros(1, np.float32)
             r = args.sdf_res
             out, info = np.zeros((r, r, r), np.float32), np.zeros(4, np.uint32)
             enc = lambda v: v.encode() if v else None
             rc = lib.ref_testbed_snapshot(work.encode(), transforms.encode(), json.dumps(merged_config(json.loads(args.hyper) if args.hyper else None)).encode(),
                                           params.ctypes.data_as(C.c_void_p), C.c_uint64(params.size), C.c_uint32(args.steps), enc(args.snapshot_load),
-                                          enc(args.snapshot_save), C.c_uint32(r), out.ctypes.data_as(C.c_void_p), info.ctypes.data_as(C.c_void_p))
+                                          enc(args.snapshot_save), C.c_uint32(r), out.ctypes.data_as(C.c_void_p), info.ctypes.data_as(C.c_void_p), enc(args.mesh))
             if args.sdf_grid:
                 np.save(args.sdf_grid, out)
             print("\n" + json.dumps({"rc": rc, "training_step": int(info[0]), "rays_per_batch": int(info[1]), "measured_batch_size": int(info[2]),

@@ -130,8 +130,7 @@ def test_training_loop_follows_the_reference_loop(tmp_path):
     weights, occupancy cells near the threshold fall differently, and the runs are compared by their averages and their loss."""
     _need_ref()
     import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import run_ref_testbed as R
+    from oracle import run_ref_testbed as R
     from neus2_b200 import _lib as L
     from neus2_b200 import synthetic as S
     from neus2_b200 import testbed as T
@@ -184,8 +183,7 @@ def test_dynamic_sequence_follows_the_reference_loop(tmp_path):
     part one above."""
     _need_ref()
     import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import run_ref_testbed as R
+    from oracle import run_ref_testbed as R
     from neus2_b200 import synthetic as S
     from neus2_b200 import testbed as T
     from util import record
@@ -223,8 +221,7 @@ def test_sdf_lattice_equals_the_reference_testbed(tmp_path):
     through its NerfNetwork over the layered kernels) against neus2b_testbed_sdf_grid with the same parameters."""
     _need_ref()
     import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import run_ref_testbed as R
+    from oracle import run_ref_testbed as R
     from neus2_b200 import _lib as L
     from neus2_b200 import synthetic as S
     from neus2_b200 import testbed as T
@@ -262,8 +259,7 @@ def test_snapshots_load_across_the_two_testbeds(tmp_path):
     import ctypes as C
     import numpy as np
     import torch
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import run_ref_testbed as R
+    from oracle import run_ref_testbed as R
     from neus2_b200 import _lib as L
     from neus2_b200 import synthetic as S
     from neus2_b200 import testbed as T
@@ -304,3 +300,76 @@ def test_snapshots_load_across_the_two_testbeds(tmp_path):
     assert abs(occupied(tb) - loaded["occupied_cells"]) <= 0.002 * loaded["occupied_cells"]
     record("snapshot_cross_load", sdf_err_reference_to_this=err_in, sdf_err_this_to_reference=err_out)
     tb.close()
+
+
+def test_mesh_export_equals_the_reference_testbed(tmp_path):
+    """Testbed::compute_and_save_marching_cubes_mesh of the reference (lattice, marching cubes, 1-ring normals, vertex colours from
+    the network, writer) against Testbed.compute_and_save_marching_cubes_mesh here, from the same parameters after a short training
+    of the reference's loop handed over as a snapshot.  The reference numbers vertices in the arrival order of its atomics:
+    the OBJ files are compared as sets -- vertices matched by position, then positions, colours and normals as printed, and the
+    faces through the matching."""
+    _need_ref()
+    import numpy as np
+    from scipy.spatial import cKDTree
+    from oracle import run_ref_testbed as R
+    from neus2_b200 import _lib as L
+    from neus2_b200 import synthetic as S
+    from neus2_b200 import testbed as T
+    from oracle import extract_mc_table as X
+    from util import record
+    table = X.load()
+    if table is None:
+        pytest.skip("the reference's case table was not extracted on this machine (oracle/_ref/mc_tri_table.npy is missing)")
+    res, batch = 64, 1 << 16
+    scene = S.render_sphere_views(8, 96, 96, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
+    S.write_transforms_dataset(scene, str(tmp_path / "data"))
+    tb = T.Testbed.from_network_config(R.network_config(), batch_size=batch)
+    tb.load_training_data_from_json(str(tmp_path / "data" / "transforms.json"))
+    tb.set_params(S.init_params(L.grid_n_params(tb.config.grid), seed=1337))
+    np.save(str(tmp_path / "p0.npy"), tb.get_params())
+    out = _run_ref(["--data", str(tmp_path / "data"), "--batch", str(batch), "--sdf-res", str(res), "--params", str(tmp_path / "p0.npy"), "--steps", "60",
+                    "--snapshot-save", str(tmp_path / "ref.msgpack"), "--mesh", str(tmp_path / "ref.obj")])
+    assert out["rc"] == 0
+    tb.load_snapshot(str(tmp_path / "ref.msgpack"))
+    import torch
+    tb.compute_and_save_marching_cubes_mesh(str(tmp_path / "mine.obj"), resolution=res, tri_table=torch.from_numpy(table))
+    tb.close()
+
+    def read(path):
+        v, vn, f = [], [], []
+        for line in open(path):
+            p = line.split()
+            if not p:
+                continue
+            if p[0] == "v":
+                v.append([float(x) for x in p[1:7]])
+            elif p[0] == "vn":
+                vn.append([float(x) for x in p[1:4]])
+            elif p[0] == "f":
+                f.append([int(x.split("/")[0]) - 1 for x in p[1:4]])
+        return np.array(v), np.array(vn), np.array(f, np.int64)
+    rv, rn, rf = read(tmp_path / "ref.obj")
+    mv, mn, mf = read(tmp_path / "mine.obj")
+    assert len(rv) == len(mv) > 1000 and len(rv) % 128 == 0 and len(rf) == len(mf) and len(rn) == len(mn) == len(rv)
+    used = int(rf.max()) + 1  # the files end with the unused entries of the reference's vertex buffer (all at the origin)
+    assert int(mf.max()) + 1 == used and np.array_equal(rv[used:], mv[used:]) and np.array_equal(rn[used:], mn[used:])
+    rv, rn, mv, mn = rv[:used], rn[:used], mv[:used], mn[:used]
+    # positions are printed with five decimals (vertices next to a lattice point can print alike): every reference vertex is held
+    # against the vertices here that print at the nearest position, and takes the one closest in colour and normal
+    tree = cKDTree(mv[:, :3])
+    dist, _ = tree.query(rv[:, :3])
+    assert np.quantile(dist, 0.99) <= 2e-5 and dist.max() <= 2e-3, (dist.max(), np.quantile(dist, 0.99))
+    color_err, normal_err = np.zeros(len(rv)), np.zeros(len(rv))
+    for k, cand in enumerate(tree.query_ball_point(rv[:, :3], dist + 1e-9)):
+        d = np.abs(mv[cand, 3:6] - rv[k, 3:6]).max(1) + np.abs(mn[cand] - rn[k]).max(1)
+        j = cand[int(np.argmin(d))]
+        color_err[k], normal_err[k] = np.abs(mv[j, 3:6] - rv[k, 3:6]).max(), np.abs(mn[j] - rn[k]).max()
+    record("ref_testbed_mesh_export", vertices=len(rv), faces=len(rf), worst_position=float(dist.max()), worst_colour=float(color_err.max()),
+           mean_colour=float(color_err.mean()), worst_normal=float(normal_err.max()))
+    assert color_err.max() <= 0.02 and color_err.mean() <= 2e-3, "vertex colours (printed with three decimals)"
+    assert np.quantile(normal_err, 0.99) <= 0.02
+    # the faces by their printed corner positions, so that the comparison does not depend on either numbering
+    corners = lambda v, f: np.round(v[f.reshape(-1), :3].reshape(-1, 9), 5)
+    order = lambda t: t[np.lexsort(t.T[::-1])]
+    a, b = order(corners(rv, rf)), order(corners(mv, mf))
+    assert np.abs(a - b).max() <= 2e-3 and (np.abs(a - b).max(1) <= 2e-5).mean() >= 0.99, "the same faces"

@@ -85,3 +85,4 @@ def model(O, seed=0, n=4096, L=16, log2T=19, base=16, scale=1.447, grid_amp=0.1,
 
 def to_lib_desc(L, d):
     return L.GridDesc(d.n_levels, d.log2_hashmap_size, d.base_resolution, d.per_level_scale, d.n_active_levels)
+
