@@ -136,3 +136,27 @@ def test_directory_of_per_frame_files_is_a_sequence(tmp_path):
     empty.mkdir()
     with pytest.raises(ValueError):
         loader.list_frame_jsons(empty)
+
+
+def test_focal_length_bits_are_the_reference_loaders():
+    """Known answers taken from ngp::load_nerf itself (the reference's loader run on files with these fields): the conversion from
+    camera_angle_x / camera_angle_y to a focal length is single-precision arithmetic, and it is compared bit for bit."""
+    from neus2_b200 import loader
+    got = [np.float32(loader.fov_to_focal_length(96, loader.radians_to_degrees(0.61))), np.float32(loader.fov_to_focal_length(64, loader.radians_to_degrees(0.47)))]
+    assert [int(v.view(np.uint32)) for v in got] == [1125676910, 1124444030]  # 152.46652, 133.65427
+
+
+def test_up_vector_default_and_sequence_writer(tmp_path):
+    from neus2_b200 import loader
+    from neus2_b200 import synthetic as S
+    path, _, _ = write_scene(tmp_path)
+    assert loader.load_nerf_dataset(path)["up"] == [0.0, 1.0, 0.0]  # NerfDataset::up (nerf_loader.h:81)
+    scenes = [S.render_sphere_views(2, 16, 12, device="cpu", seed=s) for s in (1, 2)]
+    d = S.write_sequence_dataset(scenes, str(tmp_path / "seq"))
+    files = loader.list_frame_jsons(d)
+    assert [f.split("/")[-1] for f in files] == ["frame_0000.json", "frame_0001.json"]
+    for f, sc in zip(files, scenes):
+        ds = loader.load_nerf_dataset(f)
+        np.testing.assert_array_equal(ds["pixels"], sc["pixels"].numpy().view(np.uint32))
+        np.testing.assert_array_equal(ds["xforms"], sc["xforms"].numpy())  # scale 1, offset 0: the matrices come back exactly
+        np.testing.assert_allclose(ds["focal"], sc["focal"].numpy(), rtol=1e-7)
