@@ -1,4 +1,4 @@
-/* TEST AND MEASUREMENT INFRASTRUCTURE, not product code: the reference's own headless training loop, made callable.
+/* TEST AND MEASUREMENT INFRASTRUCTURE, not product code: the reference's own headless training loop and host code, made callable.
  *
  * oracle/build_ref_kernels.py compiles the reference's sources on the NeuS path where they lie in a reference checkout
  * (src/testbed.cu, testbed_nerf.cu, marching_cubes.cu, nerf_loader.cu, common_device.cu, camera_path.cu, triangle_bvh.cu,
@@ -10,7 +10,11 @@
  * ref_testbed_train does what scripts/run.py does without a window: Testbed(Nerf), load_training_data, network from a
  * json document, then frame() per training step -- the reference's host loop with its stream synchronisations, its own ray
  * marching / loss / occupancy kernels, its NerfNetwork, Trainer and optimizer objects; underneath those objects run this
- * repository's layered kernels.  It is the reference's code path on a B200, not the reference's tiny-cuda-nn kernels. */
+ * repository's layered kernels.  It is the reference's code path on a B200, not the reference's tiny-cuda-nn kernels.
+ *
+ * The other entry points hand single pieces of the same library to the tests: ref_load_dataset (ngp::load_nerf),
+ * ref_marching_cubes (marching_cubes_gpu), ref_mesh_postprocess (compute_mesh_1ring, save_mesh), ref_testbed_sdf_grid
+ * (Testbed::get_density_on_grid) and ref_testbed_snapshot (save_snapshot / load_snapshot / compute_and_save_marching_cubes_mesh). */
 #include <neural-graphics-primitives/nerf_loader.h>
 #include <neural-graphics-primitives/testbed.h>
 #include <tiny-cuda-nn/trainer.h>
