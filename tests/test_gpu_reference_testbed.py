@@ -420,3 +420,43 @@ def test_reconstruction_accuracy_next_to_the_reference_loop(tmp_path):
            loss=float(st.loss))
     assert ref_n > 5000 and mine_n > 5000 and ref_err < 0.02 and mine_err < 0.02
     assert mine_err <= 1.25 * ref_err + 1e-3, (mine_err, ref_err)
+
+
+def test_config1_long_run_shares_the_fate_of_the_reference_loop(tmp_path):
+    """BASELINE config 1 as it is written (learning rate 1e-2, eikonal weight 0.1, all 16 levels open from the first step) for 2000
+    steps in both loops, same initialisation, same files.  On the synthetic sphere this combination trains well for 1200-1500
+    steps and then falls apart within a few dozen steps -- to a fog (loss 3e-3, the tuner back at its smallest ray counts) or to
+    an empty occupancy grid (the tuner at its largest), depending on the run -- in this repository's loop and in the reference's
+    own loop alike, which is the point of the test: both are in good shape at step 1000, and at step 2000 they are either both
+    still in good shape or both not."""
+    _need_ref()
+    import numpy as np
+    from oracle import run_ref_testbed as R
+    from neus2_b200 import _lib as L
+    from neus2_b200 import synthetic as S
+    from neus2_b200 import testbed as T
+    from util import record
+    steps = 2000
+    scene = S.render_sphere_views(64, 512, 512, fov_deg=40.0, radius=0.3, seed=0, device="cuda")
+    S.write_transforms_dataset(scene, str(tmp_path / "data"))
+    tb = T.Testbed.from_network_config(R.network_config())
+    tb.load_training_data_from_json(str(tmp_path / "data" / "transforms.json"))
+    tb.set_params(S.init_params(L.grid_n_params(tb.config.grid), seed=1337))
+    np.save(str(tmp_path / "p0.npy"), tb.get_params())
+    mine = {}
+    for k in range(steps // 100):
+        st = tb.train(100)
+        mine[int(st.training_step)] = (float(st.loss), int(st.rays_per_batch))
+    tb.close()
+    out = _run_ref(["--data", str(tmp_path / "data"), "--warmup", "0", "--steps", str(steps), "--params", str(tmp_path / "p0.npy"), "--trace",
+                    str(tmp_path / "trace.npz")], timeout=900)
+    assert out["rc"] == 0
+    t = np.load(str(tmp_path / "trace.npz"))
+    ref = {s: (float(t["loss"][(s - 1) // 16 * 16]), int(t["stats"][s - 1][0])) for s in mine}
+    best_mine, best_ref = min(v[0] for v in mine.values()), min(v[0] for v in ref.values())
+    record("config1_long_run", this_repository={str(k): v for k, v in mine.items()}, reference_loop={str(k): v for k, v in ref.items()})
+    assert best_mine < 1e-4 and best_ref < 1e-4, "both reach a sharp surface on the way"
+    assert 0.4 * best_ref <= best_mine <= 2.5 * best_ref
+    good = lambda v: v[0] < 1.5e-4 and 4096 <= v[1] <= 200000  # a sharp surface: small loss, tens of thousands of rays per batch
+    assert good(mine[1000]) and good(ref[1000]), (mine[1000], ref[1000])
+    assert good(mine[steps]) == good(ref[steps]), (mine[steps], ref[steps])
