@@ -66,6 +66,10 @@ const char* neus2b_version(void);
  * want to state how many of the library's kernels ran inside a timed region). */
 uint64_t neus2b_launch_count(void);
 const char* neus2b_error_string(int code);
+/* sizeof of the structures of this header as the loaded library was compiled, in header order: grid_desc, motion, pcg32, dataset,
+ * train_cfg, ray_workspace, adam_cfg, testbed_config, train_stats, render_cfg, render_workspace, render_request, training_state.
+ * Writes at most `capacity` entries and returns how many there are; a binding compares them with its own before it passes a pointer. */
+uint32_t neus2b_abi_struct_sizes(uint32_t* sizes, uint32_t capacity);
 
 /* GridEncoding::level_n_params / level_params_offset (src/testbed.cu:1861-1877).  offsets[17] in grid ENTRIES (2 fp16). */
 int neus2b_grid_level_table(const neus2b_grid_desc* desc, uint32_t* offsets, uint32_t* resolutions, float* scales,

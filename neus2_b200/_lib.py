@@ -124,7 +124,7 @@ EXPORTS = [
     "neus2b_set_mma_path", "neus2b_get_mma_path", "neus2b_device_error_flags", "neus2b_set_device_error_flags",
     "neus2b_per_level_scale_from_top_resolution", "neus2b_testbed_config_active_levels", "neus2b_neus_forward", "neus2b_neus_train", "neus2b_neus_sdf",
     "neus2b_neus_forward_moved", "neus2b_neus_forward_indexed", "neus2b_forward_compute_loss", "neus2b_neus_train_moved", "neus2b_neus_sdf_moved", "neus2b_delta_forward", "neus2b_delta_backward",
-    "neus2b_delta_optimizer_step", "neus2b_movement_accumulate", "neus2b_occupancy_update_moved", "neus2b_pcg32_seed", "neus2b_pcg32_advance",
+    "neus2b_delta_optimizer_step", "neus2b_movement_accumulate", "neus2b_occupancy_update_moved", "neus2b_pcg32_seed", "neus2b_pcg32_advance", "neus2b_abi_struct_sizes",
     "neus2b_generate_samples", "neus2b_generate_samples_static", "neus2b_compute_loss", "neus2b_occupancy_update", "neus2b_occupancy_bounds", "neus2b_adam_step", "neus2b_adam_step_packed",
     "neus2b_testbed_default_config", "neus2b_testbed_create", "neus2b_testbed_destroy", "neus2b_testbed_load_training_data",
     "neus2b_testbed_update_cameras", "neus2b_testbed_set_params", "neus2b_testbed_get_params", "neus2b_testbed_n_params",
@@ -154,7 +154,27 @@ def lib():
         _lib.neus2b_per_level_scale_from_top_resolution.argtypes = [C.c_uint32, C.c_uint32, C.c_float, C.c_uint32]
         _lib.neus2b_testbed_config_active_levels.restype = C.c_uint32
         _lib.neus2b_launch_count.restype = C.c_uint64
+        _check_layout(_lib)
     return _lib
+
+
+def abi_structs():
+    """The ctypes mirrors of the header's structures, in the order of neus2b_abi_struct_sizes."""
+    return [GridDesc, Motion, Pcg32, Dataset, TrainCfg, RayWorkspace, AdamCfg, TestbedConfig, TrainStats, RenderCfg, RenderWorkspace, RenderRequest,
+            TrainingState]
+
+
+def _check_layout(library):
+    """A structure that is laid out differently here than in the loaded library would be read past its end or with shifted
+    fields: refuse the library instead."""
+    mirrors = abi_structs()
+    sizes = (C.c_uint32 * len(mirrors))()
+    library.neus2b_abi_struct_sizes.restype = C.c_uint32
+    n = library.neus2b_abi_struct_sizes(sizes, C.c_uint32(len(mirrors)))
+    bad = [(m.__name__, C.sizeof(m), int(sz)) for m, sz in zip(mirrors, sizes) if C.sizeof(m) != int(sz)]
+    if n != len(mirrors) or bad:
+        raise Neus2bError(f"{LIB_PATH} and neus2_b200/_lib.py disagree on the C ABI's structures: {n} in the library, {len(mirrors)} here; "
+                          f"(name, size here, size there): {bad}; rebuild with `python -m neus2_b200.build`")
 
 
 MMA_SYNC, MMA_TCGEN05 = 0, 1

@@ -101,3 +101,16 @@ def test_progressive_level_schedules():
     cfg.grid.n_levels = cfg.grid.n_active_levels = 16
     cfg.progressive_start_levels, cfg.progressive_levels_per_increment, cfg.progressive_steps_per_increment = 8, 2, 500
     assert [act(s) for s in (0, 499, 500, 1999, 2000, 9999)] == [8, 8, 10, 14, 16, 16]
+
+
+def test_structure_sizes_match_the_loaded_library():
+    """The ctypes mirrors against sizeof in the library (the binding refuses a library that disagrees; this states the sizes)."""
+    import ctypes as C
+    from neus2_b200 import _lib as L
+    lib = L.lib()
+    mirrors = L.abi_structs()
+    sizes = (C.c_uint32 * 32)()
+    n = lib.neus2b_abi_struct_sizes(sizes, C.c_uint32(32))
+    assert n == len(mirrors)
+    assert [int(v) for v in sizes[:n]] == [C.sizeof(m) for m in mirrors]
+    assert lib.neus2b_abi_struct_sizes(None, C.c_uint32(0)) == n  # asking for the count alone
