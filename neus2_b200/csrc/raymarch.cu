@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(128) window_first_kernel(const uint32_t* __res
 __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_train_cfg cfg, uint32_t n_rays_max,
                                                    const uint32_t* __restrict__ d_n_rays, uint32_t n_rays_total,
                                                    const uint32_t* __restrict__ d_n_rays_total, Pcg32 rng0,
-                                                   uint32_t max_compacted, uint32_t* __restrict__ counters,
+                                                   uint32_t max_compacted, int rollover, uint32_t* __restrict__ counters,
                                                    const __half* __restrict__ mlp_out, const uint32_t* __restrict__ ray_indices,
                                                    uint32_t* __restrict__ numsteps, const float* __restrict__ coords,
                                                    const CompTmp* __restrict__ tmp, const uint64_t* __restrict__ scan,
@@ -437,7 +437,14 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
                                                    float* __restrict__ loss_out, float* __restrict__ ek_loss_out) {
 	const int lane = threadIdx.x & 31;
 	if (d_n_rays_total) n_rays_total = *d_n_rays_total;
-	if (blockIdx.x == 0 && threadIdx.x == 0) counters[2] = (uint32_t)scan[n_rays_max];
+	const uint32_t n_compacted = (uint32_t)scan[n_rays_max];
+	if (blockIdx.x == 0 && threadIdx.x == 0) counters[2] = n_compacted;
+	// fill_rollover_and_rescale (call site :3913-3916): when the batch is padded with copies, every gradient row is scaled by
+	// n_valid / n_target.  Done here on the value as it was rounded to fp16, which is what a separate pass over the buffer
+	// would read: the same bits, one pass over 8 MB less.
+	const uint32_t n_valid = min(n_compacted, max_compacted);
+	const bool rescale = rollover && n_valid != 0 && n_valid < max_compacted;
+	const float rollover_scale = rescale ? (float)n_valid / (float)max_compacted : 1.0f;
 	const uint32_t n_kept = counters[0];
 	const uint32_t n_rays = d_n_rays ? min(*d_n_rays, n_rays_max) : n_rays_max;
 	const uint32_t warps = gridDim.x * (blockDim.x >> 5);
@@ -599,6 +606,10 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 				__align__(16) __half gh[16];
 #pragma unroll
 				for (int k = 0; k < 16; ++k) gh[k] = __float2half_rn(g[k]);
+				if (rescale) {
+#pragma unroll
+					for (int k = 0; k < 16; ++k) gh[k] = __float2half_rn(__half2float(gh[k]) * rollover_scale);
+				}
 				uint4* dst = reinterpret_cast<uint4*>(dloss_dout + (size_t)(compacted_base + j) * 16);
 				dst[0] = reinterpret_cast<const uint4*>(gh)[0];
 				dst[1] = reinterpret_cast<const uint4*>(gh)[1];
@@ -614,26 +625,19 @@ __global__ void __launch_bounds__(128) loss_kernel(neus2b_dataset ds, neus2b_tra
 }
 
 // fill_rollover / fill_rollover_and_rescale (call sites :3908-3916): pad [n_valid, n_target) with wrap-around copies
-// of [0, n_valid); the gradient is also rescaled by n_valid / n_target so the copies do not over-weight the batch.
+// of [0, n_valid).  The gradient is also rescaled by n_valid / n_target so the copies do not over-weight the batch: the loss
+// pass has written the rows [0, n_valid) already rescaled, so the copies are plain copies.
 __global__ void rollover_tail_kernel(uint32_t n_target, const uint32_t* __restrict__ counters, float* __restrict__ coords,
                                      __half* __restrict__ dloss) {
 	const uint32_t nv = min(counters[2], n_target);
 	if (nv == 0 || nv >= n_target) return;
-	const float scale = (float)nv / (float)n_target;
 	const size_t n_tail = (size_t)(n_target - nv);
 	for (size_t r = blockIdx.x * (size_t)blockDim.x + threadIdx.x; r < n_tail * 16; r += (size_t)gridDim.x * blockDim.x) {
 		const size_t row = nv + r / 16, k = r % 16;
 		const size_t src = row % nv;
-		dloss[row * 16 + k] = __float2half_rn(__half2float(dloss[src * 16 + k]) * scale);
+		dloss[row * 16 + k] = dloss[src * 16 + k];
 		if (k < 7) coords[row * 7 + k] = coords[src * 7 + k];
 	}
-}
-__global__ void rollover_head_kernel(uint32_t n_target, const uint32_t* __restrict__ counters, __half* __restrict__ dloss) {
-	const uint32_t nv = min(counters[2], n_target);
-	if (nv == 0 || nv >= n_target) return;
-	const float scale = (float)nv / (float)n_target;
-	for (size_t r = blockIdx.x * (size_t)blockDim.x + threadIdx.x; r < (size_t)nv * 16; r += (size_t)gridDim.x * blockDim.x)
-		dloss[r] = __float2half_rn(__half2float(dloss[r]) * scale);
 }
 
 }  // namespace n2b
@@ -717,15 +721,13 @@ static int loss_after_composite(const neus2b_dataset* ds, const neus2b_train_cfg
 	const uint32_t ray_ctas = min(div_up(n_rays, 4), (uint32_t)kSMs * 16u);
 	scan_kernel<<<64, 1024, 0, stream>>>(n_rays, ws->d_counters, ws->d_scan_tmp);
 	N2B_CHECK_LAUNCH();
-	loss_kernel<<<ray_ctas, 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted,
+	loss_kernel<<<ray_ctas, 128, 0, stream>>>(*ds, *cfg, n_rays, d_n_rays, n_rays_total, ws->d_n_rays_total, r, max_compacted, rollover,
 	                                          ws->d_counters, (const __half*)d_mlp_out, ws->d_ray_indices, ws->d_numsteps, ws->d_coords,
 	                                          (const CompTmp*)ws->d_ray_tmp, ws->d_scan_tmp, d_coords_out, (__half*)d_dloss_dout, d_loss,
 	                                          d_ek_loss);
 	N2B_CHECK_LAUNCH();
 	if (rollover) {
 		rollover_tail_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, d_coords_out, (__half*)d_dloss_dout);
-		N2B_CHECK_LAUNCH();
-		rollover_head_kernel<<<2 * kSMs, 256, 0, stream>>>(max_compacted, ws->d_counters, (__half*)d_dloss_dout);
 		N2B_CHECK_LAUNCH();
 	}
 	return NEUS2B_OK;
