@@ -114,3 +114,10 @@ def test_structure_sizes_match_the_loaded_library():
     assert n == len(mirrors)
     assert [int(v) for v in sizes[:n]] == [C.sizeof(m) for m in mirrors]
     assert lib.neus2b_abi_struct_sizes(None, C.c_uint32(0)) == n  # asking for the count alone
+
+
+def test_marching_cubes_resolution_rounds_up_to_sixteen():
+    """Testbed::marching_cubes rounds every axis of the lattice up to a multiple of 16 (src/testbed_nerf.cu:4161-4163)."""
+    from neus2_b200.testbed import Testbed
+    assert Testbed.marching_cubes_resolution(100) == [112, 112, 112]
+    assert Testbed.marching_cubes_resolution((16, 17, 512)) == [16, 32, 512]
