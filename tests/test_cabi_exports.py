@@ -121,3 +121,28 @@ def test_marching_cubes_resolution_rounds_up_to_sixteen():
     from neus2_b200.testbed import Testbed
     assert Testbed.marching_cubes_resolution(100) == [112, 112, 112]
     assert Testbed.marching_cubes_resolution((16, 17, 512)) == [16, 32, 512]
+
+
+def test_pcg32_known_answers(oracle):
+    """The generator against the published known answer of PCG32 (seed 42, stream 54: 0xa15c02b7 0x7b47f409 0xba1d3330 0x83d2f293
+    0xbfa4784b 0xcbed606e), and the seeding of default_rng_t{seed} -- stream selector 1, the default of the generator's constructor
+    -- against a plain restatement; the library and the oracle seed alike."""
+    from neus2_b200 import _lib as L
+    mask = (1 << 64) - 1
+    r = type(oracle.pcg32(0))()  # state 0, then the published seeding steps with the oracle's own generator step
+    r.state, r.inc = 0, ((54 << 1) | 1) & mask
+    oracle.pcg32_next_uint(r)
+    r.state = (r.state + 42) & mask
+    oracle.pcg32_next_uint(r)
+    assert [oracle.pcg32_next_uint(r) for _ in range(6)] == [0xa15c02b7, 0x7b47f409, 0xba1d3330, 0x83d2f293, 0xbfa4784b, 0xcbed606e]
+
+    def seeded(seed, initseq=1):
+        state, inc = 0, ((initseq << 1) | 1) & mask
+        state = (state * 6364136223846793005 + inc) & mask
+        state = (state + seed) & mask
+        state = (state * 6364136223846793005 + inc) & mask
+        return state, inc
+    for seed in (0, 1, 1337, 2 ** 40 + 7):
+        want = seeded(seed)
+        a, b = L.pcg32(seed), oracle.pcg32(seed)
+        assert (a.state, a.inc) == want and (b.state, b.inc) == want
