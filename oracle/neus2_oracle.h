@@ -2,13 +2,15 @@
  * CPU oracle for the NeuS2 training step.  TEST INFRASTRUCTURE ONLY: it is the checker that the
  * CUDA path is compared against and the timed CPU baseline; nothing in the product links it.
  *
- * Parity status: "parity unpinned" for the hash-grid encoding, the fused MLPs, the SH encoding,
- * Adam/EMA and pcg32, because the reference keeps that arithmetic in an un-vendored submodule
- * (dependencies/neus2_tcnn, empty; pin unknown).  Those parts restate the published algorithms
- * (multiresolution hash encoding, dense ReLU MLP, real spherical harmonics, Adam, PCG32) and are
- * anchored on the reference's call sites.  The ray-march, NeuS compositing, loss, occupancy-grid and
- * marching-cubes parts follow reference source that is present (src/testbed_nerf.cu,
- * src/marching_cubes.cu, include/neural-graphics-primitives/nerf_network.h) and cite it per function.
+ * Parity status: "parity unpinned" for the arithmetic inside the hash-grid encoding, the fused MLPs, the SH
+ * encoding and Adam/EMA, because the reference keeps it in an un-vendored submodule (dependencies/neus2_tcnn,
+ * empty; pin unknown).  Those parts restate the published algorithms (multiresolution hash encoding, dense ReLU
+ * MLP, real spherical harmonics, Adam) and are anchored on the reference's call sites.  Pinned: the ray-march,
+ * NeuS compositing, loss, occupancy-grid, tracer, marching-cubes and mesh parts follow reference source that is
+ * present (src/testbed_nerf.cu, src/marching_cubes.cu, include/neural-graphics-primitives/nerf_network.h), cite it
+ * per function, and the CUDA path that is checked against this oracle is also run against the reference's own
+ * kernels and host code on the GPU (oracle/ref_kernels, tests/test_gpu_reference_*.py); PCG32 is checked against
+ * its published known answer, its seeding against the reference's training loop.
  *
  * All matrices are "AoS": one sample's values are contiguous ([n][width]).  fp16 values travel as
  * uint16_t bit patterns.  Every rounding to fp16 that the reference's data flow implies is explicit.
