@@ -368,11 +368,13 @@ def test_mesh_export_equals_the_reference_testbed(tmp_path):
            mean_colour=float(color_err.mean()), worst_normal=float(normal_err.max()))
     assert color_err.max() <= 0.02 and color_err.mean() <= 2e-3, "vertex colours (printed with three decimals)"
     assert np.quantile(normal_err, 0.99) <= 0.02
-    # the faces by their printed corner positions, so that the comparison does not depend on either numbering
-    corners = lambda v, f: np.round(v[f.reshape(-1), :3].reshape(-1, 9), 5)
-    order = lambda t: t[np.lexsort(t.T[::-1])]
-    a, b = order(corners(rv, rf)), order(corners(mv, mf))
-    assert np.abs(a - b).max() <= 2e-3 and (np.abs(a - b).max(1) <= 2e-5).mean() >= 0.99, "the same faces"
+    # the faces by their printed corner positions (nine numbers each), matched by nearest neighbour so that the comparison depends
+    # neither on the numbering of the vertices nor on the order of the faces
+    corners = lambda v, f: v[f.reshape(-1), :3].reshape(-1, 9)
+    face_dist, _ = cKDTree(corners(mv, mf)).query(corners(rv, rf))
+    back_dist, _ = cKDTree(corners(rv, rf)).query(corners(mv, mf))
+    for d in (face_dist, back_dist):
+        assert d.max() <= 4e-3 and np.quantile(d, 0.99) <= 6e-5, "the same faces, corner order included"
 
 
 def test_reconstruction_accuracy_next_to_the_reference_loop(tmp_path):
