@@ -60,7 +60,8 @@ def load_only(transforms, out_path, max_images=256, pixel_capacity=1 << 28):
     n = int(min(header[0], max_images))
     image_bytes = int(header[1]) * int(header[2]) * 4 * int(header[3])
     n_pix = min(n, pixel_capacity // max(image_bytes, 1))
-    np.savez(out_path, header=header, floats=floats, xforms=xforms[:n], focal=focal[:n], principal=principal[:n], pixels=pixels[:n_pix * image_bytes])
+    if rc == 0:
+        np.savez(out_path, header=header, floats=floats, xforms=xforms[:n], focal=focal[:n], principal=principal[:n], pixels=pixels[:n_pix * image_bytes])
     print("\n" + json.dumps({"rc": rc, "n_images": n}), flush=True)
     return 0 if rc == 0 else 1
 

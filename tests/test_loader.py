@@ -160,3 +160,22 @@ def test_up_vector_default_and_sequence_writer(tmp_path):
         np.testing.assert_array_equal(ds["pixels"], sc["pixels"].numpy().view(np.uint32))
         np.testing.assert_array_equal(ds["xforms"], sc["xforms"].numpy())  # scale 1, offset 0: the matrices come back exactly
         np.testing.assert_allclose(ds["focal"], sc["focal"].numpy(), rtol=1e-7)
+
+
+def test_loader_equals_the_reference_loader_on_the_golden_case():
+    """tests/golden/loader_case: a tiny dataset and what ngp::load_nerf returned for it (written by tests/golden/make_loader_golden.py
+    where the reference's loader could run).  Cameras, intrinsics and pixel bytes bit for bit."""
+    import os
+    from neus2_b200 import loader
+    case = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "loader_case")
+    t = np.load(os.path.join(case, "expected.npz"))
+    ds = loader.load_nerf_dataset(os.path.join(case, "transforms.json"))
+    assert int(t["header"][0]) == ds["n_images"] == 2 and (int(t["header"][1]), int(t["header"][2]), int(t["header"][3])) == (16, 12, 1)
+    assert int(t["header"][4]) == ds["aabb_scale"] and bool(t["header"][6]) == ds["from_na"] and bool(t["header"][7]) == ds["from_mitsuba"]
+    assert np.float32(t["floats"][0]) == np.float32(ds["scale"])
+    assert np.array_equal(t["floats"][1:4], np.asarray(ds["offset"], np.float32)) and np.array_equal(t["floats"][4:7], np.asarray(ds["up"], np.float32))
+    mine = np.asarray(ds["xforms"], np.float32).reshape(-1, 4, 3).transpose(0, 2, 1).reshape(-1, 12)  # column major -> row major
+    assert np.array_equal(mine.view(np.uint32), t["xforms"].view(np.uint32))
+    assert np.array_equal(np.asarray(ds["focal"], np.float32).view(np.uint32), t["focal"].view(np.uint32))
+    assert np.array_equal(np.asarray(ds["principal"], np.float32).view(np.uint32), t["principal"].view(np.uint32))
+    assert np.array_equal(np.ascontiguousarray(ds["pixels"]).view(np.uint8).reshape(-1), t["pixels"])
